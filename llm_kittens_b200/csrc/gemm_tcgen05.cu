@@ -1,0 +1,497 @@
+// bf16 GEMM family on the 5th-generation tensor cores (tcgen05.mma, accumulators in TMEM),
+// operands staged by TMA into 128-byte-swizzled shared memory, persistent warp-specialised CTAs.
+//
+//   mode NT : C[M,N] = A[M,K] * B[N,K]^T      forward linear layers (weight stored (out,in))
+//   mode NN : C[M,N] = A[M,K] * B[K,N]        input gradients       (B is the same weight, read MN-major)
+//   mode TN : C[M,N] = A[K,M]^T * B[K,N]      weight gradients      (both operands read MN-major, K = tokens)
+//
+// Epilogue flags (compile-time): +bias[N]; tanh-GELU with the pre-activation stored to a second
+// output; multiply by GELU'(aux); add a bf16 [M,N] addend (residual add / gradient accumulation);
+// or raw fp32 partials for split-K. Same job as matmul_forward / matmul_forward_gelu /
+// matmul_backward in the reference (llmc/matmul.cuh:678-785, 1138-1201, 1238-1338), which has no
+// sm_100 path; this is a new design:
+//
+//   warp 0      : TMA producer  (4-stage ring of 128x64 A and 256x64 B tiles, mbarrier tx-count)
+//   warp 1      : MMA issuer    (one elected lane; 128x256x16 tcgen05.mma; commit -> stage release)
+//   warps 2..5  : epilogue      (tcgen05.ld 32 lanes x 32 columns -> math -> swizzled smem -> TMA store)
+//   TMEM        : 2 x 256 fp32 columns, so the epilogue of tile i overlaps the main loop of tile i+1.
+//
+// No cluster launch and no multicast: each CTA loads its own tiles; reuse comes from the L2 through
+// the grouped tile order. Every wait is bounded (ptx::mbar_wait) and reports through `status`.
+#include "ptx_sm100.cuh"
+
+namespace llmk {
+namespace gemm {
+
+constexpr int BM = 128, BN = 256, BK = 64;
+constexpr int STAGES = 4;
+constexpr int A_STAGE_BYTES = BM * BK * 2;  // 16 KiB
+constexpr int B_STAGE_BYTES = BN * BK * 2;  // 32 KiB
+constexpr int STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
+constexpr int CHUNK_BYTES = 64 * BK * 2;          // one 64(MN) x 64(K) MN-major box = 8 KiB
+constexpr int STAGING_BYTES = 32 * 128;           // 32 rows x 64 bf16 per epilogue warp buffer
+constexpr int NUM_EPI_WARPS = 4;
+constexpr int THREADS = 32 * (2 + NUM_EPI_WARPS);
+constexpr int SMEM_MAIN = STAGES * STAGE_BYTES + NUM_EPI_WARPS * 2 * STAGING_BYTES;
+constexpr int SMEM_BYTES = SMEM_MAIN + 1024 /*alignment slack*/ + 256 /*barriers*/;
+constexpr int GROUP_M = 8;
+constexpr int TMEM_COLS = 512;
+
+enum { MODE_NT = 0, MODE_NN = 1, MODE_TN = 2 };
+enum { EPI_BIAS = 1, EPI_GELU = 2, EPI_DGELU = 4, EPI_ADD = 8, EPI_PARTIAL = 16 };
+
+struct Params {
+    int M, N, K;
+    int tiles_m, tiles_n, splits, kb_total, kb_per_split;
+    const bf16* bias;  // [N]
+    const bf16* aux;   // [M,N] pre-GELU input (DGELU) or addend (ADD; may alias C)
+    float* partial;    // [splits, M, N] fp32 (PARTIAL)
+    int* status;
+};
+
+struct Work {
+    int m0, n0, kb_begin, kb_end, split;
+};
+
+__device__ __forceinline__ Work decode_unit(const Params& p, int u) {
+    Work w;
+    const int tile = u / p.splits;
+    w.split = u - tile * p.splits;
+    const int group_size = GROUP_M * p.tiles_n;
+    const int group = tile / group_size;
+    const int first_m = group * GROUP_M;
+    const int gm = min(p.tiles_m - first_m, GROUP_M);
+    const int r = tile - group * group_size;
+    w.m0 = (first_m + r % gm) * BM;
+    w.n0 = (r / gm) * BN;
+    w.kb_begin = w.split * p.kb_per_split;
+    w.kb_end = min(p.kb_total, w.kb_begin + p.kb_per_split);
+    return w;
+}
+
+template <int MODE, int EPI>
+__global__ void __launch_bounds__(THREADS, 1)
+gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+            const __grid_constant__ CUtensorMap tmC, const __grid_constant__ CUtensorMap tmC2, const Params p) {
+    constexpr bool A_MN = (MODE == MODE_TN);
+    constexpr bool B_MN = (MODE != MODE_NT);
+
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint8_t* staging = smem + STAGES * STAGE_BYTES;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + SMEM_MAIN);
+    uint64_t* full_bar = bars;                 // [STAGES]
+    uint64_t* empty_bar = bars + STAGES;       // [STAGES]
+    uint64_t* acc_full = bars + 2 * STAGES;    // [2]
+    uint64_t* acc_empty = bars + 2 * STAGES + 2;  // [2]
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int total_units = p.tiles_m * p.tiles_n * p.splits;
+
+    if (threadIdx.x == 0) {
+        for (int i = 0; i < STAGES; i++) {
+            ptx::mbar_init(&full_bar[i], 1);
+            ptx::mbar_init(&empty_bar[i], 1);
+        }
+        for (int i = 0; i < 2; i++) {
+            ptx::mbar_init(&acc_full[i], 1);
+            ptx::mbar_init(&acc_empty[i], NUM_EPI_WARPS);
+        }
+        *abort_flag = 0;
+        ptx::fence_barrier_init();
+        ptx::prefetch_tmap(&tmA);
+        ptx::prefetch_tmap(&tmB);
+        ptx::prefetch_tmap(&tmC);
+    }
+    if (warp == 1) {
+        ptx::tmem_alloc(tmem_slot, TMEM_COLS);
+        ptx::tmem_relinquish();
+    }
+    ptx::tc_fence_before();
+    __syncthreads();
+    ptx::tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        // ------------------------------------------------------------ TMA producer
+        int s = 0;
+        uint32_t ph = 0;
+        bool ok = true;
+        for (int u = blockIdx.x; u < total_units && ok; u += gridDim.x) {
+            const Work w = decode_unit(p, u);
+            for (int kb = w.kb_begin; kb < w.kb_end; kb++) {
+                ok = ptx::mbar_wait(&empty_bar[s], ph ^ 1, abort_flag, p.status, LLMK_ST_TIMEOUT_TMA_EMPTY, u);
+                if (!ok) break;
+                if (lane == 0) {
+                    uint8_t* sA = smem + s * STAGE_BYTES;
+                    uint8_t* sB = sA + A_STAGE_BYTES;
+                    ptx::mbar_arrive_expect_tx(&full_bar[s], STAGE_BYTES);
+                    const int k0 = kb * BK;
+                    if (A_MN) {
+#pragma unroll
+                        for (int j = 0; j < BM / 64; j++)
+                            ptx::tma_load_2d(sA + j * CHUNK_BYTES, &tmA, &full_bar[s], w.m0 + 64 * j, k0);
+                    } else {
+                        ptx::tma_load_2d(sA, &tmA, &full_bar[s], k0, w.m0);
+                    }
+                    if (B_MN) {
+#pragma unroll
+                        for (int j = 0; j < BN / 64; j++)
+                            ptx::tma_load_2d(sB + j * CHUNK_BYTES, &tmB, &full_bar[s], w.n0 + 64 * j, k0);
+                    } else {
+                        ptx::tma_load_2d(sB, &tmB, &full_bar[s], k0, w.n0);
+                    }
+                }
+                __syncwarp();
+                if (++s == STAGES) { s = 0; ph ^= 1; }
+            }
+        }
+        if (ok) {
+            // drain: wait until the MMA warp has released every stage, i.e. all loads landed and were used
+            for (int i = 0; i < STAGES; i++) {
+                if (!ptx::mbar_wait(&empty_bar[s], ph ^ 1, abort_flag, p.status, LLMK_ST_TIMEOUT_TMA_EMPTY, -1)) break;
+                if (++s == STAGES) { s = 0; ph ^= 1; }
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------ MMA issuer
+        constexpr uint32_t idesc = ptx::make_idesc_bf16(BM, BN, A_MN ? 1 : 0, B_MN ? 1 : 0);
+        int s = 0;
+        uint32_t ph = 0;
+        int it = 0;
+        bool ok = true;
+        for (int u = blockIdx.x; u < total_units && ok; u += gridDim.x, it++) {
+            const Work w = decode_unit(p, u);
+            const int a = it & 1;
+            const uint32_t acc_ph = (it >> 1) & 1;
+            ok = ptx::mbar_wait(&acc_empty[a], acc_ph ^ 1, abort_flag, p.status, LLMK_ST_TIMEOUT_ACC_EMPTY, u);
+            if (!ok) break;
+            ptx::tc_fence_after();
+            const uint32_t d_tmem = tmem_base + a * BN;
+            for (int kb = w.kb_begin; kb < w.kb_end; kb++) {
+                ok = ptx::mbar_wait(&full_bar[s], ph, abort_flag, p.status, LLMK_ST_TIMEOUT_TMA_FULL, u);
+                if (!ok) break;
+                ptx::tc_fence_after();
+                if (lane == 0) {
+                    const uint32_t a_addr = ptx::smem_u32(smem + s * STAGE_BYTES);
+                    const uint32_t b_addr = a_addr + A_STAGE_BYTES;
+#pragma unroll
+                    for (int kk = 0; kk < BK / 16; kk++) {
+                        const uint64_t adesc = A_MN ? ptx::make_smem_desc(a_addr + kk * 2048, CHUNK_BYTES, 1024)
+                                                    : ptx::make_smem_desc(a_addr + kk * 32, 16, 1024);
+                        const uint64_t bdesc = B_MN ? ptx::make_smem_desc(b_addr + kk * 2048, CHUNK_BYTES, 1024)
+                                                    : ptx::make_smem_desc(b_addr + kk * 32, 16, 1024);
+                        ptx::mma_f16_ss(d_tmem, adesc, bdesc, idesc, (kb > w.kb_begin || kk > 0) ? 1u : 0u);
+                    }
+                    ptx::mma_commit(&empty_bar[s]);
+                }
+                __syncwarp();
+                if (++s == STAGES) { s = 0; ph ^= 1; }
+            }
+            if (!ok) break;
+            if (lane == 0) ptx::mma_commit(&acc_full[a]);
+            __syncwarp();
+        }
+    } else {
+        // ------------------------------------------------------------ epilogue warps
+        const int e = warp - 2;              // staging slot
+        const int lane_group = warp & 3;     // TMEM lanes [32*lane_group, +32) are visible to this warp
+        uint8_t* stg0 = staging + (e * 2) * STAGING_BYTES;
+        uint8_t* stg1 = stg0 + STAGING_BYTES;
+        int it = 0;
+        int nbuf = 0;
+        bool ok = true;
+        for (int u = blockIdx.x; u < total_units && ok; u += gridDim.x, it++) {
+            const Work w = decode_unit(p, u);
+            const int a = it & 1;
+            const uint32_t acc_ph = (it >> 1) & 1;
+            ok = ptx::mbar_wait(&acc_full[a], acc_ph, abort_flag, p.status, LLMK_ST_TIMEOUT_ACC_FULL, u);
+            if (!ok) break;
+            ptx::tc_fence_after();
+            const int row = w.m0 + lane_group * 32 + lane;
+            const uint32_t t_row = tmem_base + a * BN + ((uint32_t)(lane_group * 32) << 16);
+#pragma unroll 1
+            for (int chunk = 0; chunk < BN / 64; chunk++) {
+                const int n_base = w.n0 + chunk * 64;
+                if (n_base >= p.N) break;
+                uint8_t* buf = nullptr;
+                uint8_t* buf2 = nullptr;
+                if (!(EPI & EPI_PARTIAL)) {
+                    if (EPI & EPI_GELU) {
+                        if (lane == 0) ptx::tma_store_wait_read<0>();
+                        buf = stg0;
+                        buf2 = stg1;
+                    } else {
+                        if (lane == 0) ptx::tma_store_wait_read<1>();
+                        buf = (nbuf & 1) ? stg1 : stg0;
+                        nbuf++;
+                    }
+                    __syncwarp();
+                }
+#pragma unroll
+                for (int half = 0; half < 2; half++) {
+                    uint32_t v[32];
+                    ptx::tmem_ld_32x32b_x32(t_row + chunk * 64 + half * 32, v);
+                    ptx::tmem_ld_wait();
+                    const int col0 = n_base + half * 32;
+                    if (EPI & EPI_PARTIAL) {
+                        if (row < p.M) {
+                            float* dst = p.partial + ((size_t)w.split * p.M + row) * p.N + col0;
+#pragma unroll
+                            for (int q = 0; q < 8; q++) {
+                                if (col0 + q * 4 < p.N) {
+                                    float4 f = make_float4(__uint_as_float(v[4 * q]), __uint_as_float(v[4 * q + 1]),
+                                                           __uint_as_float(v[4 * q + 2]), __uint_as_float(v[4 * q + 3]));
+                                    *reinterpret_cast<float4*>(dst + q * 4) = f;
+                                }
+                            }
+                        }
+                        continue;
+                    }
+#pragma unroll
+                    for (int q = 0; q < 4; q++) {
+                        float x[8];
+#pragma unroll
+                        for (int j = 0; j < 8; j++) x[j] = __uint_as_float(v[q * 8 + j]);
+                        const int col = col0 + q * 8;
+                        const bool col_ok = col < p.N;
+                        if ((EPI & EPI_BIAS) && col_ok) {
+                            float b[8];
+                            unpack8(*reinterpret_cast<const bf16x8*>(p.bias + col), b);
+#pragma unroll
+                            for (int j = 0; j < 8; j++) x[j] += b[j];
+                        }
+                        if ((EPI & (EPI_DGELU | EPI_ADD)) && col_ok && row < p.M) {
+                            float g[8];
+                            unpack8(ld128(p.aux + (size_t)row * p.N + col), g);
+#pragma unroll
+                            for (int j = 0; j < 8; j++) x[j] = (EPI & EPI_DGELU) ? x[j] * gelu_grad(g[j]) : x[j] + g[j];
+                        }
+                        const int cc = half * 4 + q;
+                        const uint32_t off = lane * 128 + ((cc ^ (lane & 7)) << 4);
+                        if (EPI & EPI_GELU) {
+                            *reinterpret_cast<bf16x8*>(buf2 + off) = pack8(x);  // pre-activation
+#pragma unroll
+                            for (int j = 0; j < 8; j++) x[j] = gelu_fwd(x[j]);
+                        }
+                        *reinterpret_cast<bf16x8*>(buf + off) = pack8(x);
+                    }
+                }
+                if (!(EPI & EPI_PARTIAL)) {
+                    ptx::fence_proxy_async_smem();
+                    __syncwarp();
+                    if (lane == 0) {
+                        ptx::tma_store_2d(&tmC, buf, n_base, w.m0 + lane_group * 32);
+                        if (EPI & EPI_GELU) ptx::tma_store_2d(&tmC2, buf2, n_base, w.m0 + lane_group * 32);
+                        ptx::tma_store_commit();
+                    }
+                }
+            }
+            // accumulator fully read by this warp: hand it back to the MMA warp
+            ptx::tc_fence_before();
+            __syncwarp();
+            if (lane == 0) ptx::mbar_arrive(&acc_empty[a]);
+        }
+        if (lane == 0) ptx::tma_store_wait_all<0>();
+        __syncwarp();
+    }
+
+    // ---------------------------------------------------------------- teardown (all paths meet here)
+    ptx::tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        ptx::tc_fence_after();
+        ptx::tmem_dealloc(tmem_base, TMEM_COLS);
+    }
+}
+
+// fp32 split-K partials -> bf16 output (optionally += existing contents).
+__global__ void splitk_reduce_kernel(bf16* __restrict__ out, const float* __restrict__ partial, size_t n, int splits,
+                                     int accumulate) {
+    size_t i = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) * 8;
+    if (i >= n) return;
+    float acc[8];
+    if (accumulate) {
+        unpack8(ld128(out + i), acc);
+    } else {
+#pragma unroll
+        for (int j = 0; j < 8; j++) acc[j] = 0.f;
+    }
+    for (int s = 0; s < splits; s++) {
+        const float4* src = reinterpret_cast<const float4*>(partial + (size_t)s * n + i);
+        float4 a = __ldcs(src), b = __ldcs(src + 1);
+        acc[0] += a.x; acc[1] += a.y; acc[2] += a.z; acc[3] += a.w;
+        acc[4] += b.x; acc[5] += b.y; acc[6] += b.z; acc[7] += b.w;
+    }
+    st128(out + i, pack8(acc));
+}
+
+// ------------------------------------------------------------------------------------ host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn get_encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    static bool tried = false;
+    if (!tried) {
+        tried = true;
+        void* sym = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &qres) == cudaSuccess &&
+            qres == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(sym);
+    }
+    return fn;
+}
+
+// 2-D bf16 row-major tensor [outer, inner] with 128-byte swizzle; box = [box_outer, box_inner].
+int make_tmap_2d(CUtensorMap* m, const void* ptr, uint64_t inner, uint64_t outer, uint64_t row_stride_elems,
+                 uint32_t box_inner, uint32_t box_outer) {
+    EncodeTiledFn fn = get_encode_fn();
+    if (!fn) return LLMK_ERR_DRIVER;
+    cuuint64_t gdim[2] = {inner, outer};
+    cuuint64_t gstride[1] = {row_stride_elems * 2};
+    cuuint32_t box[2] = {box_inner, box_outer};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = fn(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), gdim, gstride, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? LLMK_OK : LLMK_ERR_TMAP;
+}
+
+static int g_num_sms = 0;
+
+template <int MODE, int EPI>
+static int launch(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmC, const CUtensorMap& tmC2,
+                  const Params& p, int max_ctas, cudaStream_t stream) {
+    static bool configured = false;
+    if (!configured) {
+        LLMK_CUDA_TRY(cudaFuncSetAttribute(gemm_kernel<MODE, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+        configured = true;
+    }
+    if (g_num_sms == 0) {
+        int dev = 0;
+        LLMK_CUDA_TRY(cudaGetDevice(&dev));
+        LLMK_CUDA_TRY(cudaDeviceGetAttribute(&g_num_sms, cudaDevAttrMultiProcessorCount, dev));
+    }
+    const int units = p.tiles_m * p.tiles_n * p.splits;
+    int grid = units < g_num_sms ? units : g_num_sms;
+    if (max_ctas > 0 && grid > max_ctas) grid = max_ctas;
+    gemm_kernel<MODE, EPI><<<grid, THREADS, SMEM_BYTES, stream>>>(tmA, tmB, tmC, tmC2, p);
+    LLMK_LAUNCH_CHECK();
+    return LLMK_OK;
+}
+
+}  // namespace gemm
+}  // namespace llmk
+
+using namespace llmk;
+using namespace llmk::gemm;
+
+// Bytes of fp32 workspace that llmk_gemm needs for (mode, M, N, K) with the split count it will pick.
+LLMK_API long llmk_gemm_workspace_bytes(int mode, int M, int N, int K, int num_sms);
+
+static int pick_splits(int mode, int M, int N, int K, int num_sms) {
+    if (mode != MODE_TN) return 1;
+    const int tiles = ceil_div(M, BM) * ceil_div(N, BN);
+    const int kb = ceil_div(K, BK);
+    if (tiles * 2 > num_sms) return 1;
+    int s = num_sms / tiles;
+    if (s > 16) s = 16;
+    if (s > kb) s = kb;
+    return s < 1 ? 1 : s;
+}
+
+long llmk_gemm_workspace_bytes(int mode, int M, int N, int K, int num_sms) {
+    const int s = pick_splits(mode, M, N, K, num_sms > 0 ? num_sms : 148);
+    return s > 1 ? (long)s * M * N * 4 : 0;
+}
+
+// C = op(A) op(B) with the epilogue selected by `epi` (bit-or of: 1 bias, 2 GELU with pre-activation
+// to C2, 4 multiply by GELU'(aux), 8 add aux). For mode TN, `epi` 8 means C += result and the
+// launcher may split K through `workspace`. All matrices are dense row-major bf16; K, N (and M for
+// TN) must be multiples of 8 so that every row starts on a 16-byte boundary.
+LLMK_API int llmk_gemm(int mode, int epi, const void* A, const void* B, void* C, void* C2, const void* bias,
+                       const void* aux, int M, int N, int K, void* workspace, long workspace_bytes, int* status,
+                       int max_ctas, void* stream_) {
+    cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+    if (M <= 0 || N <= 0 || K <= 0) return LLMK_ERR_SHAPE;
+    if ((N % 8) || (K % 8 && mode != MODE_TN) || (mode == MODE_TN && (M % 8))) return LLMK_ERR_SHAPE;
+    if ((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(B) | reinterpret_cast<uintptr_t>(C)) & 15)
+        return LLMK_ERR_SHAPE;
+    if (g_num_sms == 0) {
+        int dev = 0;
+        LLMK_CUDA_TRY(cudaGetDevice(&dev));
+        LLMK_CUDA_TRY(cudaDeviceGetAttribute(&g_num_sms, cudaDevAttrMultiProcessorCount, dev));
+    }
+    Params p;
+    p.M = M; p.N = N; p.K = K;
+    p.tiles_m = ceil_div(M, BM);
+    p.tiles_n = ceil_div(N, BN);
+    p.kb_total = ceil_div(K, BK);
+    p.splits = 1;
+    p.bias = static_cast<const bf16*>(bias);
+    p.aux = static_cast<const bf16*>(aux);
+    p.partial = nullptr;
+    p.status = status;
+    bool split_accumulate = false;
+    if (mode == MODE_TN && (epi == 0 || epi == EPI_ADD)) {
+        int s = pick_splits(mode, M, N, K, max_ctas > 0 && max_ctas < g_num_sms ? max_ctas : g_num_sms);
+        if (s > 1) {
+            if (workspace == nullptr || workspace_bytes < (long)s * M * N * 4) return LLMK_ERR_WORKSPACE;
+            p.splits = s;
+            p.partial = static_cast<float*>(workspace);
+            split_accumulate = (epi == EPI_ADD);
+            epi = EPI_PARTIAL;
+        }
+    }
+    p.kb_per_split = ceil_div(p.kb_total, p.splits);
+    if ((long)p.kb_per_split * (p.splits - 1) >= p.kb_total) {  // avoid empty trailing splits
+        p.splits = ceil_div(p.kb_total, p.kb_per_split);
+    }
+
+    CUtensorMap tmA, tmB, tmC, tmC2;
+    int rc;
+    if (mode == MODE_TN) rc = make_tmap_2d(&tmA, A, M, K, M, 64, BK);   // A[K,M], box 64(m) x 64(k)
+    else rc = make_tmap_2d(&tmA, A, K, M, K, BK, BM);                    // A[M,K], box 64(k) x 128(m)
+    if (rc) return rc;
+    if (mode == MODE_NT) rc = make_tmap_2d(&tmB, B, K, N, K, BK, BN);   // B[N,K], box 64(k) x 256(n)
+    else rc = make_tmap_2d(&tmB, B, N, K, N, 64, BK);                    // B[K,N], box 64(n) x 64(k)
+    if (rc) return rc;
+    rc = make_tmap_2d(&tmC, C, N, M, N, 64, 32);
+    if (rc) return rc;
+    tmC2 = tmC;
+    if (epi & EPI_GELU) {
+        if (C2 == nullptr) return LLMK_ERR_SHAPE;
+        rc = make_tmap_2d(&tmC2, C2, N, M, N, 64, 32);
+        if (rc) return rc;
+    }
+
+#define LLMK_GEMM_CASE(MODE_, EPI_) \
+    if (mode == MODE_ && epi == (EPI_)) rc = launch<MODE_, EPI_>(tmA, tmB, tmC, tmC2, p, max_ctas, stream); else
+    rc = LLMK_ERR_SHAPE;
+    LLMK_GEMM_CASE(MODE_NT, 0)
+    LLMK_GEMM_CASE(MODE_NT, EPI_BIAS)
+    LLMK_GEMM_CASE(MODE_NT, EPI_BIAS | EPI_GELU)
+    LLMK_GEMM_CASE(MODE_NT, EPI_ADD)
+    LLMK_GEMM_CASE(MODE_NT, EPI_BIAS | EPI_ADD)
+    LLMK_GEMM_CASE(MODE_NN, 0)
+    LLMK_GEMM_CASE(MODE_NN, EPI_DGELU)
+    LLMK_GEMM_CASE(MODE_NN, EPI_ADD)
+    LLMK_GEMM_CASE(MODE_TN, 0)
+    LLMK_GEMM_CASE(MODE_TN, EPI_ADD)
+    LLMK_GEMM_CASE(MODE_TN, EPI_PARTIAL)
+    { rc = LLMK_ERR_SHAPE; }
+#undef LLMK_GEMM_CASE
+    if (rc) return rc;
+    if (epi == EPI_PARTIAL) {
+        const size_t n = (size_t)M * N;
+        splitk_reduce_kernel<<<ceil_div((long)(n / 8), 256), 256, 0, stream>>>(static_cast<bf16*>(C), p.partial, n, p.splits,
+                                                                            split_accumulate ? 1 : 0);
+        LLMK_LAUNCH_CHECK();
+    }
+    return LLMK_OK;
+}

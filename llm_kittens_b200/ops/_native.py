@@ -1,0 +1,125 @@
+"""ctypes bridge to the in-tree CUDA library (``_lib/libllmk_cuda.so``).
+
+Every op wrapper in this package goes through :func:`call`, which passes raw device pointers and the
+current CUDA stream, and turns a non-zero return code into a Python exception. There is no eager
+PyTorch fallback behind these wrappers: if the library is missing or fails to load, the ops raise.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+import threading
+from typing import Any
+
+import torch
+
+from .. import build as _build
+
+_LOCK = threading.Lock()
+_LIB: ctypes.CDLL | None = None
+
+ERRORS = {
+    -1: "CUDA runtime error",
+    -2: "unsupported or misaligned shape",
+    -3: "tensor-map encoding failed",
+    -4: "workspace too small",
+    -5: "driver entry point missing",
+    -6: "size beyond a compiled-in maximum",
+}
+
+STATUS_CODES = {
+    1: "timeout waiting for a filled TMA stage",
+    2: "timeout waiting for a released TMA stage",
+    3: "timeout waiting for a finished accumulator",
+    4: "timeout waiting for a drained accumulator",
+    5: "timeout waiting for a peer flag",
+    6: "device-side bounds check failed",
+}
+
+
+class NativeError(RuntimeError):
+    pass
+
+
+def lib() -> ctypes.CDLL:
+    """Load (building first when the shared object is absent) the CUDA library."""
+    global _LIB
+    if _LIB is None:
+        with _LOCK:
+            if _LIB is None:
+                path = _build.cuda_lib_path()
+                if not path.exists():
+                    if os.environ.get("LLMK_NO_AUTOBUILD"):
+                        raise NativeError(f"{path} is missing; run `python -m llm_kittens_b200.build`")
+                    _build.build()
+                handle = ctypes.CDLL(str(path))
+                handle.llmk_last_error.restype = ctypes.c_char_p
+                handle.llmk_gemm_workspace_bytes.restype = ctypes.c_long
+                _LIB = handle
+    return _LIB
+
+
+def ptr(t: torch.Tensor | None) -> ctypes.c_void_p:
+    if t is None:
+        return ctypes.c_void_p(0)
+    return ctypes.c_void_p(t.data_ptr())
+
+
+def stream_handle() -> ctypes.c_void_p:
+    return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _conv(a: Any):
+    if isinstance(a, torch.Tensor):
+        return ctypes.c_void_p(a.data_ptr())
+    if a is None:
+        return ctypes.c_void_p(0)
+    if isinstance(a, bool):
+        return ctypes.c_long(int(a))
+    if isinstance(a, int):
+        # 64-bit slot: correct for both `int` and `long` C parameters on x86-64 / aarch64
+        return ctypes.c_long(a)
+    if isinstance(a, float):
+        return ctypes.c_float(a)
+    return a
+
+
+def call(name: str, *args: Any) -> None:
+    """Call ``int name(args..., void* stream)``; tensors become device pointers; raises on failure."""
+    fn = getattr(lib(), name)
+    rc = fn(*[_conv(a) for a in args], stream_handle())
+    if rc != 0:
+        detail = lib().llmk_last_error().decode() if rc == -1 else ""
+        raise NativeError(f"{name} failed: {ERRORS.get(rc, rc)} {detail}")
+
+
+_STATUS: dict[int, torch.Tensor] = {}
+
+
+def status_word() -> torch.Tensor:
+    """Per-device int32[4] that kernels with bounded waits write their failure code into."""
+    dev = torch.cuda.current_device()
+    if dev not in _STATUS:
+        _STATUS[dev] = torch.zeros(4, dtype=torch.int32, device=f"cuda:{dev}")
+    return _STATUS[dev]
+
+
+def check_status(reset: bool = True) -> None:
+    """Synchronise and raise if any kernel recorded a bounded-wait failure since the last check."""
+    st = status_word()
+    vals = st.tolist()
+    if vals[0] != 0:
+        if reset:
+            st.zero_()
+        raise NativeError(
+            f"kernel reported status {vals[0]} ({STATUS_CODES.get(vals[0], '?')}), tag={vals[1]} block={vals[2]} thread={vals[3]}"
+        )
+
+
+def require_cuda_tensor(t: torch.Tensor, dtype: torch.dtype | None = None, name: str = "tensor") -> None:
+    if not t.is_cuda:
+        raise NativeError(f"{name} must be a CUDA tensor")
+    if not t.is_contiguous():
+        raise NativeError(f"{name} must be contiguous")
+    if dtype is not None and t.dtype != dtype:
+        raise NativeError(f"{name} must be {dtype}, got {t.dtype}")

@@ -1,0 +1,91 @@
+"""tcgen05 GEMM vs an fp32 PyTorch reference (tolerance of the reference's dev/cuda/test_matmul.cu:216
+is max-abs 0.5; ours is far tighter because accumulation is fp32 in TMEM)."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _rand(*shape, scale=1.0):
+    return (torch.randn(*shape, device="cuda", dtype=torch.float32) * scale).to(torch.bfloat16)
+
+
+def _close(got, ref, tol):
+    err = (got.float() - ref).abs().max().item()
+    assert err <= tol, f"max abs err {err} > {tol}"
+
+
+def _gelu(x):
+    return torch.nn.functional.gelu(x, approximate="tanh")
+
+
+SHAPES_NT = [(128, 256, 64), (256, 512, 128), (384, 768, 768), (200, 264, 72), (1024, 2304, 768), (512, 50304, 768)]
+
+
+@pytest.mark.parametrize("M,N,K", SHAPES_NT)
+def test_gemm_nt_plain_and_bias(M, N, K):
+    from llm_kittens_b200.ops import gemm, _native
+
+    a, b, bias = _rand(M, K), _rand(N, K, scale=0.05), _rand(N)
+    ref = a.float() @ b.float().T
+    _close(gemm.gemm_nt(a, b), ref, 0.05)
+    _close(gemm.gemm_nt(a, b, bias=bias), ref + bias.float(), 0.06)
+    _native.check_status()
+
+
+@pytest.mark.parametrize("M,N,K", [(256, 512, 128), (1024, 3072, 768), (200, 264, 72)])
+def test_gemm_nt_gelu_and_add(M, N, K):
+    from llm_kittens_b200.ops import gemm, _native
+
+    a, b, bias = _rand(M, K), _rand(N, K, scale=0.05), _rand(N)
+    ref = a.float() @ b.float().T + bias.float()
+    pre = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+    out = gemm.gemm_nt(a, b, bias=bias, gelu_pre_out=pre)
+    _close(pre, ref, 0.06)
+    _close(out, _gelu(ref), 0.06)
+    res = _rand(M, N)
+    out2 = gemm.gemm_nt(a, b, bias=bias, add=res)
+    _close(out2, ref + res.float(), 0.08)
+    res2 = res.clone()
+    gemm.gemm_nt(a, b, bias=bias, add=res2, out=res2)  # in-place residual add
+    _close(res2, ref + res.float(), 0.08)
+    _native.check_status()
+
+
+@pytest.mark.parametrize("M,N,K", [(128, 256, 64), (256, 768, 2304), (1024, 768, 3072), (200, 264, 72), (512, 768, 50304)])
+def test_gemm_nn(M, N, K):
+    from llm_kittens_b200.ops import gemm, _native
+
+    a, b = _rand(M, K), _rand(K, N, scale=0.05)
+    ref = a.float() @ b.float()
+    tol = 0.05 if K < 10000 else 0.3
+    _close(gemm.gemm_nn(a, b), ref, tol)
+    pre = _rand(M, N)
+    xg = pre.float().requires_grad_(True)
+    _gelu(xg).sum().backward()
+    _close(gemm.gemm_nn(a, b, dgelu_of=pre), ref * xg.grad, tol)
+    _native.check_status()
+
+
+@pytest.mark.parametrize("M,N,K", [(128, 256, 64), (768, 768, 4096), (2304, 768, 8192), (200, 264, 136), (50304, 768, 1024)])
+def test_gemm_tn(M, N, K):
+    from llm_kittens_b200.ops import gemm, _native
+
+    a, b = _rand(K, M, scale=0.1), _rand(K, N, scale=0.1)
+    ref = a.float().T @ b.float()
+    out = gemm.gemm_tn(a, b)
+    _close(out, ref, 0.1)
+    acc = _rand(M, N)
+    acc0 = acc.clone()
+    gemm.gemm_tn(a, b, out=acc, accumulate=True)
+    _close(acc, ref + acc0.float(), 0.15)
+    _native.check_status()
+
+
+def test_gemm_deterministic():
+    from llm_kittens_b200.ops import gemm
+
+    a, b = _rand(4096, 768), _rand(4096, 768)
+    o1 = gemm.gemm_tn(a, b).clone()
+    o2 = gemm.gemm_tn(a, b)
+    assert torch.equal(o1, o2)
