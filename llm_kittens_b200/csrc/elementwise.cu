@@ -1,0 +1,356 @@
+// Bandwidth-bound element-wise kernels: GELU, SwiGLU, RoPE, residual adds, bias-gradient column
+// reduction, encoder (token + position embedding) forward / backward, casts.
+//
+// Counterparts in the reference: llmc/gelu.cuh:57-81, llmc/swiglu.cuh:66-86, llmc/rope.cuh:47-81,
+// llmc/encoder.cuh:157-234, matmul_backward_bias (llmc/matmul.cuh:1203-1236) and the Llama-local
+// add/gather kernels (train_llama3.cu:189-251). All use 128-bit accesses; everything that sums over
+// tokens does so in a fixed order (no atomics), so gradients are bit-reproducible.
+#include "common.cuh"
+
+namespace llmk {
+namespace ew {
+
+constexpr int TPB = 256;
+
+__global__ void gelu_fwd_kernel(bf16* __restrict__ out, const bf16* __restrict__ inp, size_t n) {
+    size_t i = ((size_t)blockIdx.x * TPB + threadIdx.x) * 8;
+    if (i >= n) return;
+    float f[8];
+    unpack8(ld128_stream(inp + i), f);
+#pragma unroll
+    for (int j = 0; j < 8; j++) f[j] = gelu_fwd(f[j]);
+    st128(out + i, pack8(f));
+}
+// dinout *= gelu'(inp)
+__global__ void gelu_bwd_kernel(bf16* __restrict__ dinout, const bf16* __restrict__ inp, size_t n) {
+    size_t i = ((size_t)blockIdx.x * TPB + threadIdx.x) * 8;
+    if (i >= n) return;
+    float f[8], d[8];
+    unpack8(ld128_stream(inp + i), f);
+    unpack8(ld128(dinout + i), d);
+#pragma unroll
+    for (int j = 0; j < 8; j++) d[j] *= gelu_grad(f[j]);
+    st128(dinout + i, pack8(d));
+}
+
+__device__ __forceinline__ float sigmoidf_(float x) { return 1.0f / (1.0f + __expf(-x)); }
+
+// out = silu(gate) * up
+__global__ void swiglu_fwd_kernel(bf16* __restrict__ out, const bf16* __restrict__ gate, const bf16* __restrict__ up, size_t n) {
+    size_t i = ((size_t)blockIdx.x * TPB + threadIdx.x) * 8;
+    if (i >= n) return;
+    float g[8], u[8];
+    unpack8(ld128_stream(gate + i), g);
+    unpack8(ld128_stream(up + i), u);
+#pragma unroll
+    for (int j = 0; j < 8; j++) g[j] = g[j] * sigmoidf_(g[j]) * u[j];
+    st128(out + i, pack8(g));
+}
+// dgate = dout * up * silu'(gate) ; dup = dout * silu(gate)
+__global__ void swiglu_bwd_kernel(bf16* __restrict__ dgate, bf16* __restrict__ dup, const bf16* __restrict__ dout,
+                                  const bf16* __restrict__ gate, const bf16* __restrict__ up, size_t n) {
+    size_t i = ((size_t)blockIdx.x * TPB + threadIdx.x) * 8;
+    if (i >= n) return;
+    float g[8], u[8], d[8], dg[8], du[8];
+    unpack8(ld128_stream(gate + i), g);
+    unpack8(ld128_stream(up + i), u);
+    unpack8(ld128_stream(dout + i), d);
+#pragma unroll
+    for (int j = 0; j < 8; j++) {
+        float s = sigmoidf_(g[j]);
+        float silu = g[j] * s;
+        dg[j] = d[j] * u[j] * (s + silu * (1.0f - s));
+        du[j] = d[j] * silu;
+    }
+    st128(dgate + i, pack8(dg));
+    st128(dup + i, pack8(du));
+}
+
+// SwiGLU over a fused [rows, 2H] tensor whose first H columns are `up` and last H are `gate`.
+__global__ void swiglu_fused_fwd_kernel(bf16* __restrict__ out, const bf16* __restrict__ upgate, int rows, int H) {
+    size_t idx = ((size_t)blockIdx.x * TPB + threadIdx.x) * 8;
+    if (idx >= (size_t)rows * H) return;
+    const size_t r = idx / H, c = idx % H;
+    float g[8], u[8];
+    unpack8(ld128_stream(upgate + r * 2 * H + c), u);
+    unpack8(ld128_stream(upgate + r * 2 * H + H + c), g);
+#pragma unroll
+    for (int j = 0; j < 8; j++) g[j] = g[j] * sigmoidf_(g[j]) * u[j];
+    st128(out + idx, pack8(g));
+}
+__global__ void swiglu_fused_bwd_kernel(bf16* __restrict__ dupgate, const bf16* __restrict__ dout,
+                                        const bf16* __restrict__ upgate, int rows, int H) {
+    size_t idx = ((size_t)blockIdx.x * TPB + threadIdx.x) * 8;
+    if (idx >= (size_t)rows * H) return;
+    const size_t r = idx / H, c = idx % H;
+    float g[8], u[8], d[8], dg[8], du[8];
+    unpack8(ld128_stream(upgate + r * 2 * H + c), u);
+    unpack8(ld128_stream(upgate + r * 2 * H + H + c), g);
+    unpack8(ld128_stream(dout + idx), d);
+#pragma unroll
+    for (int j = 0; j < 8; j++) {
+        float s = sigmoidf_(g[j]);
+        float silu = g[j] * s;
+        dg[j] = d[j] * u[j] * (s + silu * (1.0f - s));
+        du[j] = d[j] * silu;
+    }
+    st128(dupgate + r * 2 * H + c, pack8(du));
+    st128(dupgate + r * 2 * H + H + c, pack8(dg));
+}
+
+// out = a + b
+__global__ void add_kernel(bf16* __restrict__ out, const bf16* __restrict__ a, const bf16* __restrict__ b, size_t n) {
+    size_t i = ((size_t)blockIdx.x * TPB + threadIdx.x) * 8;
+    if (i >= n) return;
+    float x[8], y[8];
+    unpack8(ld128(a + i), x);
+    unpack8(ld128(b + i), y);
+#pragma unroll
+    for (int j = 0; j < 8; j++) x[j] += y[j];
+    st128(out + i, pack8(x));
+}
+
+// RoPE on the q and k heads of a packed [B, T, (NH + 2*NKVH) * HS] tensor, in place.
+// Pairs are (i, i + HS/2) ("half-split", as the reference's CUDA kernels: llmc/rope.cuh:36-43) or
+// (2i, 2i+1) ("interleaved", as train_llama3.py:105-115) depending on `interleaved`.
+// freqs: [T, HS/2] float2 (cos, sin). `inverse` applies the transpose rotation (backward).
+__global__ void rope_qk_kernel(bf16* __restrict__ qkv, const float2* __restrict__ freqs, int B, int T, int NH, int NKVH, int HS,
+                               int interleaved, int inverse) {
+    const int half = HS / 2;
+    const int heads = NH + NKVH;  // q heads then k heads are rotated; v untouched
+    const size_t total = (size_t)B * T * heads * half;
+    size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= total) return;
+    const int i = idx % half;
+    const int h = (idx / half) % heads;
+    const int t = (idx / ((size_t)half * heads)) % T;
+    const size_t bt = idx / ((size_t)half * heads);
+    const int width = (NH + 2 * NKVH) * HS;
+    bf16* base = qkv + bt * width + (size_t)h * HS;
+    const int i0 = interleaved ? 2 * i : i;
+    const int i1 = interleaved ? 2 * i + 1 : i + half;
+    float2 cs = freqs[(size_t)t * half + i];
+    if (inverse) cs.y = -cs.y;
+    const float x0 = __bfloat162float(base[i0]), x1 = __bfloat162float(base[i1]);
+    base[i0] = __float2bfloat16_rn(x0 * cs.x - x1 * cs.y);
+    base[i1] = __float2bfloat16_rn(x0 * cs.y + x1 * cs.x);
+}
+
+// ------------------------------------------------------------------ bias gradient (column sums)
+// stage 1: partial[chunk][c] = sum over the chunk's rows of dout[row][c]; stage 2 sums chunks in order.
+constexpr int DB_ROWS = 256;  // rows per chunk
+__global__ void dbias_partial_kernel(float* __restrict__ partial, const bf16* __restrict__ dout, int rows, int OC) {
+    // block = 32 (column vectors of 8) x 8 (row lanes); grid = (OC/256, chunks)
+    __shared__ float sh[8][32][8];
+    const int cv = blockIdx.x * 32 + threadIdx.x;  // column vector index
+    const int c = cv * 8;
+    float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    const int r0 = blockIdx.y * DB_ROWS;
+    const int r1 = min(rows, r0 + DB_ROWS);
+    if (c < OC) {
+        for (int r = r0 + threadIdx.y; r < r1; r += 8) {
+            float f[8];
+            unpack8(ld128_stream(dout + (size_t)r * OC + c), f);
+#pragma unroll
+            for (int j = 0; j < 8; j++) acc[j] += f[j];
+        }
+    }
+#pragma unroll
+    for (int j = 0; j < 8; j++) sh[threadIdx.y][threadIdx.x][j] = acc[j];
+    __syncthreads();
+    if (threadIdx.y == 0 && c < OC) {
+#pragma unroll
+        for (int j = 0; j < 8; j++) {
+            float s = 0.f;
+#pragma unroll
+            for (int y = 0; y < 8; y++) s += sh[y][threadIdx.x][j];
+            partial[(size_t)blockIdx.y * OC + c + j] = s;
+        }
+    }
+}
+__global__ void dbias_finish_kernel(bf16* __restrict__ dbias, const float* __restrict__ partial, int chunks, int OC,
+                                    int accumulate) {
+    const int c = blockIdx.x * blockDim.x + threadIdx.x;
+    if (c >= OC) return;
+    float s = accumulate ? __bfloat162float(dbias[c]) : 0.f;
+    for (int k = 0; k < chunks; k++) s += partial[(size_t)k * OC + c];
+    dbias[c] = __float2bfloat16_rn(s);
+}
+
+// ------------------------------------------------------------------ encoder
+// out[b,t,:] = wte[tok[b,t],:] (+ wpe[t,:])
+__global__ void encoder_fwd_kernel(bf16* __restrict__ out, const int* __restrict__ tokens, const bf16* __restrict__ wte,
+                                   const bf16* __restrict__ wpe, int B, int T, int C) {
+    const int cvecs = C / 8;
+    size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= (size_t)B * T * cvecs) return;
+    const int cv = idx % cvecs;
+    const size_t bt = idx / cvecs;
+    const int t = bt % T;
+    const int tok = tokens[bt];
+    float a[8];
+    unpack8(ld128(wte + (size_t)tok * C + cv * 8), a);
+    if (wpe != nullptr) {
+        float p[8];
+        unpack8(ld128(wpe + (size_t)t * C + cv * 8), p);
+#pragma unroll
+        for (int j = 0; j < 8; j++) a[j] += p[j];
+    }
+    st128(out + idx * 8, pack8(a));
+}
+// dwpe[t,:] += sum_b dout[b,t,:]
+__global__ void wpe_bwd_kernel(bf16* __restrict__ dwpe, const bf16* __restrict__ dout, int B, int T, int C) {
+    const int cvecs = C / 8;
+    size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= (size_t)T * cvecs) return;
+    const int cv = idx % cvecs;
+    const int t = idx / cvecs;
+    float acc[8];
+    unpack8(ld128(dwpe + (size_t)t * C + cv * 8), acc);
+    for (int b = 0; b < B; b++) {
+        float f[8];
+        unpack8(ld128_stream(dout + ((size_t)b * T + t) * C + cv * 8), f);
+#pragma unroll
+        for (int j = 0; j < 8; j++) acc[j] += f[j];
+    }
+    st128(dwpe + (size_t)t * C + cv * 8, pack8(acc));
+}
+// dwte[tok,:] += sum over the positions holding `tok`. `sorted_tok`/`sorted_pos` list the B*T positions
+// ordered by token id (stable, so positions ascend inside a run); block i handles the run that starts
+// at sorted index i and exits when i is not a run start. Fixed summation order => deterministic.
+__global__ void wte_bwd_kernel(bf16* __restrict__ dwte, const bf16* __restrict__ dout, const int* __restrict__ sorted_tok,
+                               const int* __restrict__ sorted_pos, int BT, int C) {
+    const int i = blockIdx.x;
+    const int tok = sorted_tok[i];
+    if (i > 0 && sorted_tok[i - 1] == tok) return;
+    const int cvecs = C / 8;
+    for (int cv = threadIdx.x; cv < cvecs; cv += blockDim.x) {
+        float acc[8];
+        unpack8(ld128(dwte + (size_t)tok * C + cv * 8), acc);
+        for (int k = i; k < BT && sorted_tok[k] == tok; k++) {
+            float f[8];
+            unpack8(ld128(dout + (size_t)sorted_pos[k] * C + cv * 8), f);
+#pragma unroll
+            for (int j = 0; j < 8; j++) acc[j] += f[j];
+        }
+        st128(dwte + (size_t)tok * C + cv * 8, pack8(acc));
+    }
+}
+
+__global__ void cast_f32_to_bf16_kernel(bf16* __restrict__ out, const float* __restrict__ in, size_t n) {
+    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) out[i] = __float2bfloat16_rn(in[i]);
+}
+__global__ void cast_bf16_to_f32_kernel(float* __restrict__ out, const bf16* __restrict__ in, size_t n) {
+    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) out[i] = __bfloat162float(in[i]);
+}
+
+}  // namespace ew
+}  // namespace llmk
+
+using namespace llmk;
+using namespace llmk::ew;
+
+#define VEC_GRID(n) ceil_div((long)((n) / 8), TPB)
+
+LLMK_API int llmk_gelu_fwd(void* out, const void* inp, long n, void* stream) {
+    if (n % 8) return LLMK_ERR_SHAPE;
+    gelu_fwd_kernel<<<VEC_GRID(n), TPB, 0, (cudaStream_t)stream>>>((bf16*)out, (const bf16*)inp, (size_t)n);
+    LLMK_LAUNCH_CHECK();
+    return LLMK_OK;
+}
+LLMK_API int llmk_gelu_bwd_inplace(void* dinout, const void* inp, long n, void* stream) {
+    if (n % 8) return LLMK_ERR_SHAPE;
+    gelu_bwd_kernel<<<VEC_GRID(n), TPB, 0, (cudaStream_t)stream>>>((bf16*)dinout, (const bf16*)inp, (size_t)n);
+    LLMK_LAUNCH_CHECK();
+    return LLMK_OK;
+}
+LLMK_API int llmk_swiglu_fwd(void* out, const void* gate, const void* up, long n, void* stream) {
+    if (n % 8) return LLMK_ERR_SHAPE;
+    swiglu_fwd_kernel<<<VEC_GRID(n), TPB, 0, (cudaStream_t)stream>>>((bf16*)out, (const bf16*)gate, (const bf16*)up, (size_t)n);
+    LLMK_LAUNCH_CHECK();
+    return LLMK_OK;
+}
+LLMK_API int llmk_swiglu_bwd(void* dgate, void* dup, const void* dout, const void* gate, const void* up, long n, void* stream) {
+    if (n % 8) return LLMK_ERR_SHAPE;
+    swiglu_bwd_kernel<<<VEC_GRID(n), TPB, 0, (cudaStream_t)stream>>>((bf16*)dgate, (bf16*)dup, (const bf16*)dout,
+                                                                     (const bf16*)gate, (const bf16*)up, (size_t)n);
+    LLMK_LAUNCH_CHECK();
+    return LLMK_OK;
+}
+LLMK_API int llmk_swiglu_fused_fwd(void* out, const void* upgate, int rows, int H, void* stream) {
+    if (H % 8) return LLMK_ERR_SHAPE;
+    swiglu_fused_fwd_kernel<<<VEC_GRID((long)rows * H), TPB, 0, (cudaStream_t)stream>>>((bf16*)out, (const bf16*)upgate, rows, H);
+    LLMK_LAUNCH_CHECK();
+    return LLMK_OK;
+}
+LLMK_API int llmk_swiglu_fused_bwd(void* dupgate, const void* dout, const void* upgate, int rows, int H, void* stream) {
+    if (H % 8) return LLMK_ERR_SHAPE;
+    swiglu_fused_bwd_kernel<<<VEC_GRID((long)rows * H), TPB, 0, (cudaStream_t)stream>>>((bf16*)dupgate, (const bf16*)dout,
+                                                                                        (const bf16*)upgate, rows, H);
+    LLMK_LAUNCH_CHECK();
+    return LLMK_OK;
+}
+LLMK_API int llmk_add(void* out, const void* a, const void* b, long n, void* stream) {
+    if (n % 8) return LLMK_ERR_SHAPE;
+    add_kernel<<<VEC_GRID(n), TPB, 0, (cudaStream_t)stream>>>((bf16*)out, (const bf16*)a, (const bf16*)b, (size_t)n);
+    LLMK_LAUNCH_CHECK();
+    return LLMK_OK;
+}
+LLMK_API int llmk_rope_qk(void* qkv, const void* freqs, int B, int T, int NH, int NKVH, int HS, int interleaved, int inverse,
+                          void* stream) {
+    if (HS % 2) return LLMK_ERR_SHAPE;
+    const size_t total = (size_t)B * T * (NH + NKVH) * (HS / 2);
+    rope_qk_kernel<<<ceil_div((long)total, TPB), TPB, 0, (cudaStream_t)stream>>>((bf16*)qkv, (const float2*)freqs, B, T, NH,
+                                                                                NKVH, HS, interleaved, inverse);
+    LLMK_LAUNCH_CHECK();
+    return LLMK_OK;
+}
+LLMK_API long llmk_dbias_scratch_bytes(int rows, int OC) { return (long)ceil_div(rows, DB_ROWS) * OC * 4; }
+// dbias (+)= column sums of dout[rows, OC]
+LLMK_API int llmk_dbias(void* dbias, void* scratch, const void* dout, int rows, int OC, int accumulate, void* stream) {
+    if (OC % 8) return LLMK_ERR_SHAPE;
+    const int chunks = ceil_div(rows, DB_ROWS);
+    dim3 grid(ceil_div(OC, 256), chunks), block(32, 8);
+    dbias_partial_kernel<<<grid, block, 0, (cudaStream_t)stream>>>((float*)scratch, (const bf16*)dout, rows, OC);
+    LLMK_LAUNCH_CHECK();
+    dbias_finish_kernel<<<ceil_div(OC, 256), 256, 0, (cudaStream_t)stream>>>((bf16*)dbias, (const float*)scratch, chunks, OC,
+                                                                          accumulate);
+    LLMK_LAUNCH_CHECK();
+    return LLMK_OK;
+}
+LLMK_API int llmk_encoder_fwd(void* out, const void* tokens, const void* wte, const void* wpe, int B, int T, int C, void* stream) {
+    if (C % 8) return LLMK_ERR_SHAPE;
+    const size_t total = (size_t)B * T * (C / 8);
+    encoder_fwd_kernel<<<ceil_div((long)total, TPB), TPB, 0, (cudaStream_t)stream>>>((bf16*)out, (const int*)tokens,
+                                                                                    (const bf16*)wte, (const bf16*)wpe, B, T, C);
+    LLMK_LAUNCH_CHECK();
+    return LLMK_OK;
+}
+// dwte += scatter of dout rows by token, dwpe += sum over batch (dwpe may be null for models without wpe).
+LLMK_API int llmk_encoder_bwd(void* dwte, void* dwpe, const void* dout, const void* sorted_tok, const void* sorted_pos, int B,
+                              int T, int C, void* stream) {
+    if (C % 8) return LLMK_ERR_SHAPE;
+    if (dwpe != nullptr) {
+        wpe_bwd_kernel<<<ceil_div((long)T * (C / 8), TPB), TPB, 0, (cudaStream_t)stream>>>((bf16*)dwpe, (const bf16*)dout, B, T, C);
+        LLMK_LAUNCH_CHECK();
+    }
+    int threads = C / 8;
+    if (threads > 256) threads = 256;
+    threads = ((threads + 31) / 32) * 32;
+    wte_bwd_kernel<<<B * T, threads, 0, (cudaStream_t)stream>>>((bf16*)dwte, (const bf16*)dout, (const int*)sorted_tok,
+                                                              (const int*)sorted_pos, B * T, C);
+    LLMK_LAUNCH_CHECK();
+    return LLMK_OK;
+}
+LLMK_API int llmk_cast_f32_to_bf16(void* out, const void* in, long n, void* stream) {
+    cast_f32_to_bf16_kernel<<<ceil_div(n, TPB), TPB, 0, (cudaStream_t)stream>>>((bf16*)out, (const float*)in, (size_t)n);
+    LLMK_LAUNCH_CHECK();
+    return LLMK_OK;
+}
+LLMK_API int llmk_cast_bf16_to_f32(void* out, const void* in, long n, void* stream) {
+    cast_bf16_to_f32_kernel<<<ceil_div(n, TPB), TPB, 0, (cudaStream_t)stream>>>((float*)out, (const bf16*)in, (size_t)n);
+    LLMK_LAUNCH_CHECK();
+    return LLMK_OK;
+}

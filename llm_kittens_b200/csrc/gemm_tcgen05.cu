@@ -13,7 +13,7 @@
 //
 //   warp 0      : TMA producer  (4-stage ring of 128x64 A and 256x64 B tiles, mbarrier tx-count)
 //   warp 1      : MMA issuer    (one elected lane; 128x256x16 tcgen05.mma; commit -> stage release)
-//   warps 2..5  : epilogue      (tcgen05.ld 32 lanes x 32 columns -> math -> swizzled smem -> TMA store)
+//   warps 2..9  : epilogue      (tcgen05.ld 32 lanes x 32 columns -> math -> swizzled smem -> TMA store)
 //   TMEM        : 2 x 256 fp32 columns, so the epilogue of tile i overlaps the main loop of tile i+1.
 //
 // No cluster launch and no multicast: each CTA loads its own tiles; reuse comes from the L2 through
@@ -24,21 +24,30 @@ namespace llmk {
 namespace gemm {
 
 constexpr int BM = 128, BN = 256, BK = 64;
-constexpr int STAGES = 4;
+// 4 pipeline stages when the epilogue needs one staging buffer per warp, 3 when it needs two (a second
+// output or a TMA-loaded auxiliary input tile).
+template <int EPI> struct Cfg;
 constexpr int A_STAGE_BYTES = BM * BK * 2;  // 16 KiB
 constexpr int B_STAGE_BYTES = BN * BK * 2;  // 32 KiB
 constexpr int STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
 constexpr int CHUNK_BYTES = 64 * BK * 2;          // one 64(MN) x 64(K) MN-major box = 8 KiB
 constexpr int STAGING_BYTES = 32 * 128;           // 32 rows x 64 bf16 per epilogue warp buffer
-constexpr int NUM_EPI_WARPS = 4;
+constexpr int NUM_EPI_WARPS = 8;  // two per TMEM lane group; each takes alternate 64-column chunks
 constexpr int THREADS = 32 * (2 + NUM_EPI_WARPS);
-constexpr int SMEM_MAIN = STAGES * STAGE_BYTES + NUM_EPI_WARPS * 2 * STAGING_BYTES;
-constexpr int SMEM_BYTES = SMEM_MAIN + 1024 /*alignment slack*/ + 256 /*barriers*/;
+constexpr int MAX_STAGES = 4;
 constexpr int GROUP_M = 8;
 constexpr int TMEM_COLS = 512;
 
 enum { MODE_NT = 0, MODE_NN = 1, MODE_TN = 2 };
 enum { EPI_BIAS = 1, EPI_GELU = 2, EPI_DGELU = 4, EPI_ADD = 8, EPI_PARTIAL = 16 };
+
+template <int EPI>
+struct Cfg {
+    static constexpr bool DUAL = (EPI & (EPI_GELU | EPI_DGELU | EPI_ADD)) != 0;
+    static constexpr int STAGES = DUAL ? 3 : 4;
+    static constexpr int SMEM_MAIN = STAGES * STAGE_BYTES + NUM_EPI_WARPS * (DUAL ? 2 : 1) * STAGING_BYTES;
+    static constexpr int SMEM_BYTES = SMEM_MAIN + 1024 /*alignment slack*/ + 256 /*barriers*/;
+};
 
 struct Params {
     int M, N, K;
@@ -72,7 +81,11 @@ __device__ __forceinline__ Work decode_unit(const Params& p, int u) {
 template <int MODE, int EPI>
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-            const __grid_constant__ CUtensorMap tmC, const __grid_constant__ CUtensorMap tmC2, const Params p) {
+            const __grid_constant__ CUtensorMap tmC, const __grid_constant__ CUtensorMap tmX, const Params p) {
+    // tmX: second output (GELU pre-activation) or auxiliary [M,N] input (DGELU / ADD); same geometry as tmC
+    constexpr int STAGES = Cfg<EPI>::STAGES;
+    constexpr int SMEM_MAIN = Cfg<EPI>::SMEM_MAIN;
+    constexpr bool DUAL = Cfg<EPI>::DUAL;
     constexpr bool A_MN = (MODE == MODE_TN);
     constexpr bool B_MN = (MODE != MODE_NT);
 
@@ -80,11 +93,12 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint8_t* staging = smem + STAGES * STAGE_BYTES;
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + SMEM_MAIN);
-    uint64_t* full_bar = bars;                 // [STAGES]
-    uint64_t* empty_bar = bars + STAGES;       // [STAGES]
-    uint64_t* acc_full = bars + 2 * STAGES;    // [2]
-    uint64_t* acc_empty = bars + 2 * STAGES + 2;  // [2]
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
+    uint64_t* full_bar = bars;                         // [MAX_STAGES]
+    uint64_t* empty_bar = bars + MAX_STAGES;           // [MAX_STAGES]
+    uint64_t* acc_full = bars + 2 * MAX_STAGES;        // [2]
+    uint64_t* acc_empty = bars + 2 * MAX_STAGES + 2;   // [2]
+    uint64_t* aux_bar = bars + 2 * MAX_STAGES + 4;     // [NUM_EPI_WARPS]
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * MAX_STAGES + 4 + NUM_EPI_WARPS);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -99,11 +113,13 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
             ptx::mbar_init(&acc_full[i], 1);
             ptx::mbar_init(&acc_empty[i], NUM_EPI_WARPS);
         }
+        for (int i = 0; i < NUM_EPI_WARPS; i++) ptx::mbar_init(&aux_bar[i], 1);
         *abort_flag = 0;
         ptx::fence_barrier_init();
         ptx::prefetch_tmap(&tmA);
         ptx::prefetch_tmap(&tmB);
         ptx::prefetch_tmap(&tmC);
+        if (DUAL) ptx::prefetch_tmap(&tmX);
     }
     if (warp == 1) {
         ptx::tmem_alloc(tmem_slot, TMEM_COLS);
@@ -196,48 +212,46 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
         }
     } else {
         // ------------------------------------------------------------ epilogue warps
-        const int e = warp - 2;              // staging slot
+        const int e = warp - 2;              // 0..7
         const int lane_group = warp & 3;     // TMEM lanes [32*lane_group, +32) are visible to this warp
-        uint8_t* stg0 = staging + (e * 2) * STAGING_BYTES;
-        uint8_t* stg1 = stg0 + STAGING_BYTES;
+        const int chunk_sel = e >> 2;        // this warp takes chunks with (chunk & 1) == chunk_sel
+        uint8_t* buf = staging + e * (DUAL ? 2 : 1) * STAGING_BYTES;  // output tile
+        uint8_t* buf2 = buf + STAGING_BYTES;                          // second output / aux input (DUAL only)
+        constexpr bool AUX_IN = (EPI & (EPI_DGELU | EPI_ADD)) != 0;
+        uint32_t aux_ph = 0;
         int it = 0;
-        int nbuf = 0;
         bool ok = true;
         for (int u = blockIdx.x; u < total_units && ok; u += gridDim.x, it++) {
             const Work w = decode_unit(p, u);
             const int a = it & 1;
             const uint32_t acc_ph = (it >> 1) & 1;
+            const int row0 = w.m0 + lane_group * 32;
+            if (AUX_IN && w.n0 + chunk_sel * 64 < p.N) {
+                // fetch the first aux tile while the main loop of this tile is still running
+                if (lane == 0) {
+                    ptx::mbar_arrive_expect_tx(&aux_bar[e], STAGING_BYTES);
+                    ptx::tma_load_2d(buf2, &tmX, &aux_bar[e], w.n0 + chunk_sel * 64, row0);
+                }
+                __syncwarp();
+            }
             ok = ptx::mbar_wait(&acc_full[a], acc_ph, abort_flag, p.status, LLMK_ST_TIMEOUT_ACC_FULL, u);
             if (!ok) break;
             ptx::tc_fence_after();
-            const int row = w.m0 + lane_group * 32 + lane;
+            const int row = row0 + lane;
+            const bool row_ok = row < p.M;
             const uint32_t t_row = tmem_base + a * BN + ((uint32_t)(lane_group * 32) << 16);
 #pragma unroll 1
-            for (int chunk = 0; chunk < BN / 64; chunk++) {
+            for (int chunk = chunk_sel; chunk < BN / 64; chunk += 2) {
                 const int n_base = w.n0 + chunk * 64;
                 if (n_base >= p.N) break;
-                uint8_t* buf = nullptr;
-                uint8_t* buf2 = nullptr;
-                if (!(EPI & EPI_PARTIAL)) {
-                    if (EPI & EPI_GELU) {
-                        if (lane == 0) ptx::tma_store_wait_read<0>();
-                        buf = stg0;
-                        buf2 = stg1;
-                    } else {
-                        if (lane == 0) ptx::tma_store_wait_read<1>();
-                        buf = (nbuf & 1) ? stg1 : stg0;
-                        nbuf++;
-                    }
-                    __syncwarp();
-                }
+                if (EPI & EPI_PARTIAL) {
 #pragma unroll
-                for (int half = 0; half < 2; half++) {
-                    uint32_t v[32];
-                    ptx::tmem_ld_32x32b_x32(t_row + chunk * 64 + half * 32, v);
-                    ptx::tmem_ld_wait();
-                    const int col0 = n_base + half * 32;
-                    if (EPI & EPI_PARTIAL) {
-                        if (row < p.M) {
+                    for (int half = 0; half < 2; half++) {
+                        uint32_t v[32];
+                        ptx::tmem_ld_32x32b_x32(t_row + chunk * 64 + half * 32, v);
+                        ptx::tmem_ld_wait();
+                        const int col0 = n_base + half * 32;
+                        if (row_ok) {
                             float* dst = p.partial + ((size_t)w.split * p.M + row) * p.N + col0;
 #pragma unroll
                             for (int q = 0; q < 8; q++) {
@@ -248,47 +262,74 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
                                 }
                             }
                         }
-                        continue;
                     }
+                    continue;
+                }
+                bf16x8 res[8];
+                bf16x8 res2[(EPI & EPI_GELU) ? 8 : 1];
+                if (AUX_IN) {
+                    ok = ptx::mbar_wait(&aux_bar[e], aux_ph, abort_flag, p.status, LLMK_ST_TIMEOUT_ACC_FULL, -2);
+                    aux_ph ^= 1;
+                    if (!ok) break;
+                }
+#pragma unroll
+                for (int half = 0; half < 2; half++) {
+                    uint32_t v[32];
+                    ptx::tmem_ld_32x32b_x32(t_row + chunk * 64 + half * 32, v);
+                    ptx::tmem_ld_wait();
+                    const int col0 = n_base + half * 32;
 #pragma unroll
                     for (int q = 0; q < 4; q++) {
                         float x[8];
 #pragma unroll
                         for (int j = 0; j < 8; j++) x[j] = __uint_as_float(v[q * 8 + j]);
                         const int col = col0 + q * 8;
-                        const bool col_ok = col < p.N;
-                        if ((EPI & EPI_BIAS) && col_ok) {
+                        const int cc = half * 4 + q;
+                        const uint32_t off = lane * 128 + ((cc ^ (lane & 7)) << 4);
+                        if ((EPI & EPI_BIAS) && col < p.N) {
                             float b[8];
                             unpack8(*reinterpret_cast<const bf16x8*>(p.bias + col), b);
 #pragma unroll
                             for (int j = 0; j < 8; j++) x[j] += b[j];
                         }
-                        if ((EPI & (EPI_DGELU | EPI_ADD)) && col_ok && row < p.M) {
+                        if (AUX_IN) {
                             float g[8];
-                            unpack8(ld128(p.aux + (size_t)row * p.N + col), g);
+                            unpack8(*reinterpret_cast<const bf16x8*>(buf2 + off), g);
 #pragma unroll
                             for (int j = 0; j < 8; j++) x[j] = (EPI & EPI_DGELU) ? x[j] * gelu_grad(g[j]) : x[j] + g[j];
                         }
-                        const int cc = half * 4 + q;
-                        const uint32_t off = lane * 128 + ((cc ^ (lane & 7)) << 4);
                         if (EPI & EPI_GELU) {
-                            *reinterpret_cast<bf16x8*>(buf2 + off) = pack8(x);  // pre-activation
+                            res2[(EPI & EPI_GELU) ? cc : 0] = pack8(x);  // pre-activation
 #pragma unroll
                             for (int j = 0; j < 8; j++) x[j] = gelu_fwd(x[j]);
                         }
-                        *reinterpret_cast<bf16x8*>(buf + off) = pack8(x);
+                        res[cc] = pack8(x);
                     }
                 }
-                if (!(EPI & EPI_PARTIAL)) {
-                    ptx::fence_proxy_async_smem();
-                    __syncwarp();
+                if (lane == 0) ptx::tma_store_wait_read<0>();  // earlier stores have finished reading the buffers
+                __syncwarp();
+                if (AUX_IN && chunk + 2 < BN / 64 && n_base + 128 < p.N) {
+                    // every lane has consumed the aux tile (res[] is complete): fetch the next one
                     if (lane == 0) {
-                        ptx::tma_store_2d(&tmC, buf, n_base, w.m0 + lane_group * 32);
-                        if (EPI & EPI_GELU) ptx::tma_store_2d(&tmC2, buf2, n_base, w.m0 + lane_group * 32);
-                        ptx::tma_store_commit();
+                        ptx::mbar_arrive_expect_tx(&aux_bar[e], STAGING_BYTES);
+                        ptx::tma_load_2d(buf2, &tmX, &aux_bar[e], n_base + 128, row0);
                     }
+                }
+#pragma unroll
+                for (int cc = 0; cc < 8; cc++) {
+                    const uint32_t off = lane * 128 + ((cc ^ (lane & 7)) << 4);
+                    *reinterpret_cast<bf16x8*>(buf + off) = res[cc];
+                    if (EPI & EPI_GELU) *reinterpret_cast<bf16x8*>(buf2 + off) = res2[(EPI & EPI_GELU) ? cc : 0];
+                }
+                ptx::fence_proxy_async_smem();
+                __syncwarp();
+                if (lane == 0) {
+                    ptx::tma_store_2d(&tmC, buf, n_base, row0);
+                    if (EPI & EPI_GELU) ptx::tma_store_2d(&tmX, buf2, n_base, row0);
+                    ptx::tma_store_commit();
                 }
             }
+            if (!ok) break;
             // accumulator fully read by this warp: hand it back to the MMA warp
             ptx::tc_fence_before();
             __syncwarp();
@@ -365,8 +406,9 @@ int make_tmap_2d(CUtensorMap* m, const void* ptr, uint64_t inner, uint64_t outer
 static int g_num_sms = 0;
 
 template <int MODE, int EPI>
-static int launch(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmC, const CUtensorMap& tmC2,
+static int launch(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmC, const CUtensorMap& tmX,
                   const Params& p, int max_ctas, cudaStream_t stream) {
+    constexpr int SMEM_BYTES = Cfg<EPI>::SMEM_BYTES;
     static bool configured = false;
     if (!configured) {
         LLMK_CUDA_TRY(cudaFuncSetAttribute(gemm_kernel<MODE, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
@@ -380,7 +422,7 @@ static int launch(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensor
     const int units = p.tiles_m * p.tiles_n * p.splits;
     int grid = units < g_num_sms ? units : g_num_sms;
     if (max_ctas > 0 && grid > max_ctas) grid = max_ctas;
-    gemm_kernel<MODE, EPI><<<grid, THREADS, SMEM_BYTES, stream>>>(tmA, tmB, tmC, tmC2, p);
+    gemm_kernel<MODE, EPI><<<grid, THREADS, SMEM_BYTES, stream>>>(tmA, tmB, tmC, tmX, p);
     LLMK_LAUNCH_CHECK();
     return LLMK_OK;
 }
@@ -398,11 +440,17 @@ static int pick_splits(int mode, int M, int N, int K, int num_sms) {
     if (mode != MODE_TN) return 1;
     const int tiles = ceil_div(M, BM) * ceil_div(N, BN);
     const int kb = ceil_div(K, BK);
-    if (tiles * 2 > num_sms) return 1;
-    int s = num_sms / tiles;
-    if (s > 16) s = 16;
-    if (s > kb) s = kb;
-    return s < 1 ? 1 : s;
+    if (tiles >= 2 * num_sms) return 1;
+    // pick the split count whose work units fill whole waves best; ties go to fewer splits
+    int best = 1;
+    double best_cost = 1e30;
+    for (int s = 1; s <= 16 && s <= kb; s++) {
+        const int units = tiles * s;
+        const int waves = ceil_div(units, num_sms);
+        const double cost = (double)waves * ceil_div(kb, s) + 0.35 * s;  // k-blocks on the critical path + reduce cost
+        if (cost < best_cost - 1e-9) { best_cost = cost; best = s; }
+    }
+    return best;
 }
 
 long llmk_gemm_workspace_bytes(int mode, int M, int N, int K, int num_sms) {
@@ -453,7 +501,7 @@ LLMK_API int llmk_gemm(int mode, int epi, const void* A, const void* B, void* C,
         p.splits = ceil_div(p.kb_total, p.kb_per_split);
     }
 
-    CUtensorMap tmA, tmB, tmC, tmC2;
+    CUtensorMap tmA, tmB, tmC, tmX;
     int rc;
     if (mode == MODE_TN) rc = make_tmap_2d(&tmA, A, M, K, M, 64, BK);   // A[K,M], box 64(m) x 64(k)
     else rc = make_tmap_2d(&tmA, A, K, M, K, BK, BM);                    // A[M,K], box 64(k) x 128(m)
@@ -463,15 +511,16 @@ LLMK_API int llmk_gemm(int mode, int epi, const void* A, const void* B, void* C,
     if (rc) return rc;
     rc = make_tmap_2d(&tmC, C, N, M, N, 64, 32);
     if (rc) return rc;
-    tmC2 = tmC;
-    if (epi & EPI_GELU) {
-        if (C2 == nullptr) return LLMK_ERR_SHAPE;
-        rc = make_tmap_2d(&tmC2, C2, N, M, N, 64, 32);
+    tmX = tmC;
+    if (epi & (EPI_GELU | EPI_DGELU | EPI_ADD)) {
+        const void* x = (epi & EPI_GELU) ? C2 : aux;
+        if (x == nullptr || (reinterpret_cast<uintptr_t>(x) & 15)) return LLMK_ERR_SHAPE;
+        rc = make_tmap_2d(&tmX, x, N, M, N, 64, 32);
         if (rc) return rc;
     }
 
 #define LLMK_GEMM_CASE(MODE_, EPI_) \
-    if (mode == MODE_ && epi == (EPI_)) rc = launch<MODE_, EPI_>(tmA, tmB, tmC, tmC2, p, max_ctas, stream); else
+    if (mode == MODE_ && epi == (EPI_)) rc = launch<MODE_, EPI_>(tmA, tmB, tmC, tmX, p, max_ctas, stream); else
     rc = LLMK_ERR_SHAPE;
     LLMK_GEMM_CASE(MODE_NT, 0)
     LLMK_GEMM_CASE(MODE_NT, EPI_BIAS)

@@ -1,0 +1,185 @@
+// Optimizer-side kernels: squared gradient norm, clip coefficient, AdamW with stochastic rounding and
+// optional fp32 master weights, master -> bf16 re-materialisation, all driven by a SEGMENT TABLE.
+//
+// A segment is one contiguous run of elements that this rank updates: with ZeRO >= 1 the rank owns,
+// for every tensor and every layer slice, the r-th of P equal parts, so its share of the model is a
+// list of (parameter offset, gradient offset, state offset, length, flags) tuples rather than one
+// range. The table lives on the device as int64[nseg][5]; blockIdx.y walks segments, blockIdx.x
+// strides inside one. Counterparts in the reference: adamw_update / init_from_master
+// (llmc/adamw.cuh:113-171), global_norm_squared (llmc/global_norm.cuh:77-101); the reference
+// launches one kernel per tensor from a host loop (train_gpt2.cu:1283-1348), here one launch covers
+// the whole shard.
+#include "common.cuh"
+
+namespace llmk {
+namespace optim {
+
+constexpr int TPB = 256;
+constexpr int SEG_FIELDS = 5;  // p_off, g_off, s_off, len, flags(bit0 = weight decay)
+
+template <typename G>
+__device__ __forceinline__ float load_grad(const G* g, size_t i);
+template <>
+__device__ __forceinline__ float load_grad<bf16>(const bf16* g, size_t i) { return __bfloat162float(g[i]); }
+template <>
+__device__ __forceinline__ float load_grad<float>(const float* g, size_t i) { return g[i]; }
+
+// partials[blockIdx.y * gridDim.x + blockIdx.x] = sum of squares of this block's elements
+template <typename G>
+__global__ void __launch_bounds__(TPB)
+norm2_kernel(float* __restrict__ partials, const G* __restrict__ grads, const long long* __restrict__ segs) {
+    __shared__ float sh[32];
+    const long long* seg = segs + (size_t)blockIdx.y * SEG_FIELDS;
+    const size_t g_off = (size_t)seg[1], len = (size_t)seg[3];
+    float acc = 0.f;
+    for (size_t i = (size_t)blockIdx.x * TPB + threadIdx.x; i < len; i += (size_t)gridDim.x * TPB) {
+        const float g = load_grad<G>(grads, g_off + i);
+        acc += g * g;
+    }
+    acc = block_sum(acc, sh);
+    if (threadIdx.x == 0) partials[(size_t)blockIdx.y * gridDim.x + blockIdx.x] = acc;
+}
+
+// out[0] = sum(partials) in fixed order
+__global__ void sum_partials_kernel(float* __restrict__ out, const float* __restrict__ partials, int n) {
+    __shared__ float sh[32];
+    float s = 0.f;
+    for (int i = threadIdx.x; i < n; i += blockDim.x) s += partials[i];
+    s = block_sum(s, sh);
+    if (threadIdx.x == 0) out[0] = s;
+}
+
+// scale_out[0] = min(1, clip / sqrt(norm2)) ; norm_out[0] = sqrt(norm2). A non-finite norm gives scale 0
+// and raises flag_out[0] so the host can skip the step.
+__global__ void clip_scale_kernel(float* scale_out, float* norm_out, int* flag_out, const float* norm2, float clip) {
+    const float n2 = norm2[0];
+    const float n = sqrtf(n2);
+    norm_out[0] = n;
+    if (!isfinite(n)) {
+        scale_out[0] = 0.f;
+        if (flag_out) flag_out[0] = 1;
+    } else {
+        scale_out[0] = (clip > 0.f && n > clip) ? clip / n : 1.0f;
+        if (flag_out) flag_out[0] = 0;
+    }
+}
+
+struct AdamArgs {
+    float lr, beta1, beta2, beta1_corr, beta2_corr, eps, wd;
+    unsigned int seed;
+};
+
+template <typename G>
+__global__ void __launch_bounds__(TPB)
+adamw_kernel(bf16* __restrict__ params, float* __restrict__ master, const G* __restrict__ grads, float* __restrict__ m,
+             float* __restrict__ v, const long long* __restrict__ segs, const float* __restrict__ grad_scale_ptr,
+             float grad_scale_host, AdamArgs a) {
+    const long long* seg = segs + (size_t)blockIdx.y * SEG_FIELDS;
+    const size_t p_off = (size_t)seg[0], g_off = (size_t)seg[1], s_off = (size_t)seg[2], len = (size_t)seg[3];
+    const float wd = (seg[4] & 1) ? a.wd : 0.f;
+    const float gs = grad_scale_ptr ? grad_scale_ptr[0] * grad_scale_host : grad_scale_host;
+    for (size_t i = (size_t)blockIdx.x * TPB + threadIdx.x; i < len; i += (size_t)gridDim.x * TPB) {
+        const float g = gs * load_grad<G>(grads, g_off + i);
+        float mi = m[s_off + i], vi = v[s_off + i];
+        mi = a.beta1 * mi + (1.0f - a.beta1) * g;
+        vi = a.beta2 * vi + (1.0f - a.beta2) * g * g;
+        m[s_off + i] = mi;
+        v[s_off + i] = vi;
+        const float mh = mi / a.beta1_corr, vh = vi / a.beta2_corr;
+        const float old = master ? master[s_off + i] : __bfloat162float(params[p_off + i]);
+        const float p = old - a.lr * (mh / (sqrtf(vh) + a.eps) + wd * old);
+        // the rounding noise is keyed on the element's index in the full parameter arena, so every rank
+        // (and every sharding) rounds a given parameter the same way
+        params[p_off + i] = sr_round(p, squirrel5((unsigned int)(p_off + i), a.seed));
+        if (master) master[s_off + i] = p;
+    }
+}
+
+// master[s] = float(params[p])   (first step with master weights)
+__global__ void __launch_bounds__(TPB)
+master_from_params_kernel(float* __restrict__ master, const bf16* __restrict__ params, const long long* __restrict__ segs) {
+    const long long* seg = segs + (size_t)blockIdx.y * SEG_FIELDS;
+    const size_t p_off = (size_t)seg[0], s_off = (size_t)seg[2], len = (size_t)seg[3];
+    for (size_t i = (size_t)blockIdx.x * TPB + threadIdx.x; i < len; i += (size_t)gridDim.x * TPB)
+        master[s_off + i] = __bfloat162float(params[p_off + i]);
+}
+// params[p] = SR(master[s]) with the same noise the update used (bit-exact resume from master weights)
+__global__ void __launch_bounds__(TPB)
+params_from_master_kernel(bf16* __restrict__ params, const float* __restrict__ master, const long long* __restrict__ segs,
+                          unsigned int seed) {
+    const long long* seg = segs + (size_t)blockIdx.y * SEG_FIELDS;
+    const size_t p_off = (size_t)seg[0], s_off = (size_t)seg[2], len = (size_t)seg[3];
+    for (size_t i = (size_t)blockIdx.x * TPB + threadIdx.x; i < len; i += (size_t)gridDim.x * TPB)
+        params[p_off + i] = sr_round(master[s_off + i], squirrel5((unsigned int)(p_off + i), seed));
+}
+
+static inline int grid_x_for(long max_len) {
+    long g = (max_len + TPB * 4 - 1) / (TPB * 4);
+    if (g > 1024) g = 1024;
+    if (g < 1) g = 1;
+    return (int)g;
+}
+
+}  // namespace optim
+}  // namespace llmk
+
+using namespace llmk;
+using namespace llmk::optim;
+
+// Grid x-extent used for a table whose longest segment has `max_len` elements.
+LLMK_API int llmk_optim_grid_x(long max_len) { return grid_x_for(max_len); }
+
+// norm2_out[0] = sum over the table's segments of grad^2; partials needs nseg * llmk_optim_grid_x(max_len) floats.
+LLMK_API int llmk_global_norm2(void* norm2_out, void* partials, const void* grads, int grads_fp32, const void* segs, int nseg,
+                               long max_len, void* stream_) {
+    cudaStream_t stream = (cudaStream_t)stream_;
+    if (nseg <= 0) return LLMK_ERR_SHAPE;
+    const int gx = grid_x_for(max_len);
+    dim3 grid(gx, nseg);
+    if (grads_fp32) norm2_kernel<float><<<grid, TPB, 0, stream>>>((float*)partials, (const float*)grads, (const long long*)segs);
+    else norm2_kernel<bf16><<<grid, TPB, 0, stream>>>((float*)partials, (const bf16*)grads, (const long long*)segs);
+    LLMK_LAUNCH_CHECK();
+    sum_partials_kernel<<<1, 1024, 0, stream>>>((float*)norm2_out, (const float*)partials, gx * nseg);
+    LLMK_LAUNCH_CHECK();
+    return LLMK_OK;
+}
+
+LLMK_API int llmk_clip_scale(void* scale_out, void* norm_out, void* flag_out, const void* norm2, float clip, void* stream) {
+    clip_scale_kernel<<<1, 1, 0, (cudaStream_t)stream>>>((float*)scale_out, (float*)norm_out, (int*)flag_out, (const float*)norm2,
+                                                         clip);
+    LLMK_LAUNCH_CHECK();
+    return LLMK_OK;
+}
+
+LLMK_API int llmk_adamw(void* params, void* master, const void* grads, int grads_fp32, void* m, void* v, const void* segs,
+                        int nseg, long max_len, float lr, float beta1, float beta2, float beta1_corr, float beta2_corr,
+                        float eps, float wd, const void* grad_scale_ptr, float grad_scale_host, unsigned int seed,
+                        void* stream_) {
+    cudaStream_t stream = (cudaStream_t)stream_;
+    if (nseg <= 0) return LLMK_ERR_SHAPE;
+    AdamArgs a{lr, beta1, beta2, beta1_corr, beta2_corr, eps, wd, seed};
+    dim3 grid(grid_x_for(max_len), nseg);
+    if (grads_fp32)
+        adamw_kernel<float><<<grid, TPB, 0, stream>>>((bf16*)params, (float*)master, (const float*)grads, (float*)m, (float*)v,
+                                                      (const long long*)segs, (const float*)grad_scale_ptr, grad_scale_host, a);
+    else
+        adamw_kernel<bf16><<<grid, TPB, 0, stream>>>((bf16*)params, (float*)master, (const bf16*)grads, (float*)m, (float*)v,
+                                                     (const long long*)segs, (const float*)grad_scale_ptr, grad_scale_host, a);
+    LLMK_LAUNCH_CHECK();
+    return LLMK_OK;
+}
+
+LLMK_API int llmk_master_from_params(void* master, const void* params, const void* segs, int nseg, long max_len, void* stream) {
+    dim3 grid(grid_x_for(max_len), nseg);
+    master_from_params_kernel<<<grid, TPB, 0, (cudaStream_t)stream>>>((float*)master, (const bf16*)params, (const long long*)segs);
+    LLMK_LAUNCH_CHECK();
+    return LLMK_OK;
+}
+LLMK_API int llmk_params_from_master(void* params, const void* master, const void* segs, int nseg, long max_len,
+                                     unsigned int seed, void* stream) {
+    dim3 grid(grid_x_for(max_len), nseg);
+    params_from_master_kernel<<<grid, TPB, 0, (cudaStream_t)stream>>>((bf16*)params, (const float*)master,
+                                                                     (const long long*)segs, seed);
+    LLMK_LAUNCH_CHECK();
+    return LLMK_OK;
+}

@@ -54,7 +54,9 @@ def lib() -> ctypes.CDLL:
                     _build.build()
                 handle = ctypes.CDLL(str(path))
                 handle.llmk_last_error.restype = ctypes.c_char_p
-                handle.llmk_gemm_workspace_bytes.restype = ctypes.c_long
+                for fn in ("llmk_gemm_workspace_bytes", "llmk_norm_bwd_scratch_bytes", "llmk_dbias_scratch_bytes"):
+                    getattr(handle, fn).restype = ctypes.c_long
+                handle.llmk_optim_grid_x.argtypes = [ctypes.c_long]
                 _LIB = handle
     return _LIB
 

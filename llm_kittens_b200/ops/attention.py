@@ -1,0 +1,22 @@
+"""Causal flash attention on packed QKV (``csrc/attention.cu``). Reference jobs:
+llmc/attention.cuh:261-338, 481-604 and llmc/attention_gqa.cuh:415-572."""
+from __future__ import annotations
+
+import torch
+
+from . import _native as N
+
+
+def attention_fwd(qkv, B, T, NH, NKVH, HS, out=None, lse=None):
+    """``qkv``: [B, T, (NH+2*NKVH)*HS] -> ``out`` [B, T, NH*HS], ``lse`` [B, NH, T] fp32."""
+    out = torch.empty(B, T, NH * HS, dtype=qkv.dtype, device=qkv.device) if out is None else out
+    lse = torch.empty(B, NH, T, dtype=torch.float32, device=qkv.device) if lse is None else lse
+    N.call("llmk_attention_fwd", out, lse, qkv, B, T, NH, NKVH, HS)
+    return out, lse
+
+
+def attention_bwd(dout, qkv, out, lse, B, T, NH, NKVH, HS, dqkv=None, dvec=None):
+    dqkv = torch.empty_like(qkv) if dqkv is None else dqkv
+    dvec = torch.empty(B, NH, T, dtype=torch.float32, device=qkv.device) if dvec is None else dvec
+    N.call("llmk_attention_bwd", dqkv, dvec, dout, qkv, out, lse, B, T, NH, NKVH, HS)
+    return dqkv

@@ -1,0 +1,116 @@
+"""Per-kernel micro-benchmarks: ``python -m llm_kittens_b200.ops.bench [gemm|attention|norm|classifier|optim|all]``.
+
+Timing follows the same rules as the end-to-end bench: warm-up iterations, CUDA events on the
+launching stream, an L2 flush (a 256 MiB write) between timed iterations, median of the samples.
+Each row prints the achieved TFLOP/s or GB/s and its fraction of the measured peaks found in
+``MEASURED_PEAKS.json`` at the repository root when present (else 1590 TFLOP/s / 6650 GB/s).
+The cuBLAS / SDPA columns are the library baselines the hand-written kernels are compared to.
+"""
+from __future__ import annotations
+
+import json
+import os
+import statistics
+import sys
+
+import torch
+
+from . import _native as N
+
+
+def peaks():
+    root = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    p = os.path.join(root, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        d = json.load(open(p))
+        return d.get("bf16_tflops", 1590.0), d.get("hbm_gbs", 6650.0), "measured"
+    return 1590.0, 6650.0, "fallback"
+
+
+_FLUSH = None
+
+
+def flush_l2():
+    global _FLUSH
+    if _FLUSH is None:
+        _FLUSH = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+    N.call("llmk_flush_l2", _FLUSH, _FLUSH.numel())
+
+
+def time_fn(fn, warmup=3, iters=10):
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    samples = []
+    for _ in range(iters):
+        flush_l2()
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s.record()
+        fn()
+        e.record()
+        torch.cuda.synchronize()
+        samples.append(s.elapsed_time(e))
+    return statistics.median(samples)
+
+
+def bench_gemm(BT=65536):
+    from . import gemm
+
+    tf_peak, _, how = peaks()
+    C, V = 768, 50304
+    rows = []
+
+    def rnd(*s):
+        return (torch.randn(*s, device="cuda") * 0.05).to(torch.bfloat16)
+
+    shapes_nt = [("qkv", BT, 3 * C, C), ("attproj", BT, C, C), ("fc+gelu", BT, 4 * C, C), ("fcproj", BT, C, 4 * C),
+                 ("lmhead", BT, V, C), ("llama8b qkv", 8192, 6144, 4096), ("llama8b up", 8192, 14336, 4096),
+                 ("llama8b down", 8192, 4096, 14336)]
+    for name, M, Nn, K in shapes_nt:
+        a, b, bias = rnd(M, K), rnd(Nn, K), rnd(Nn)
+        out = torch.empty(M, Nn, dtype=torch.bfloat16, device="cuda")
+        pre = torch.empty_like(out) if "gelu" in name else None
+        t = time_fn(lambda: gemm.gemm_nt(a, b, bias=bias, out=out, gelu_pre_out=pre))
+        t_ref = time_fn(lambda: torch.addmm(bias, a, b.T, out=out))
+        rows.append(("NT " + name, M, Nn, K, t, t_ref))
+        del a, b, out, pre
+    shapes_nn = [("d qkv", BT, C, 3 * C), ("d fc (dgelu src)", BT, C, 4 * C), ("d fcproj+dgelu", BT, 4 * C, C), ("d lmhead", BT, C, V)]
+    for name, M, Nn, K in shapes_nn:
+        a, b = rnd(M, K), rnd(K, Nn)
+        out = torch.empty(M, Nn, dtype=torch.bfloat16, device="cuda")
+        aux = rnd(M, Nn) if "dgelu" in name and "src" not in name else None
+        t = time_fn(lambda: gemm.gemm_nn(a, b, out=out, dgelu_of=aux))
+        t_ref = time_fn(lambda: torch.matmul(a, b, out=out))
+        rows.append(("NN " + name, M, Nn, K, t, t_ref))
+        del a, b, out
+    shapes_tn = [("dW qkv", 3 * C, C, BT), ("dW attproj", C, C, BT), ("dW fc", 4 * C, C, BT), ("dW fcproj", C, 4 * C, BT),
+                 ("dW lmhead", V, C, BT)]
+    for name, M, Nn, K in shapes_tn:
+        a, b = rnd(K, M), rnd(K, Nn)
+        out = torch.zeros(M, Nn, dtype=torch.bfloat16, device="cuda")
+        t = time_fn(lambda: gemm.gemm_tn(a, b, out=out, accumulate=True))
+        t_ref = time_fn(lambda: torch.matmul(a.T, b, out=out))
+        rows.append(("TN " + name, M, Nn, K, t, t_ref))
+        del a, b, out
+    N.check_status()
+    print(f"# GEMM (tcgen05) vs cuBLAS; peak {tf_peak} TFLOP/s bf16 ({how})")
+    print(f"{'shape':28s} {'M':>6s} {'N':>6s} {'K':>6s} {'ms':>8s} {'TFLOP/s':>8s} {'frac':>6s} {'cublas ms':>9s} {'ratio':>6s}")
+    for name, M, Nn, K, t, t_ref in rows:
+        tf = 2.0 * M * Nn * K / (t * 1e-3) / 1e12
+        print(f"{name:28s} {M:6d} {Nn:6d} {K:6d} {t:8.3f} {tf:8.1f} {tf / tf_peak:6.2f} {t_ref:9.3f} {t_ref / t:6.2f}")
+
+
+def main(argv):
+    what = argv[1] if len(argv) > 1 else "all"
+    if what in ("gemm", "all"):
+        bench_gemm()
+    if what in ("attention", "all"):
+        from .bench_more import bench_attention
+        bench_attention()
+    if what in ("elementwise", "norm", "classifier", "optim", "all"):
+        from .bench_more import bench_bandwidth_ops
+        bench_bandwidth_ops()
+
+
+if __name__ == "__main__":
+    main(sys.argv)
