@@ -1,0 +1,264 @@
+#!/usr/bin/env python
+"""Headline benchmark: GPT-2 124M pre-training throughput (tokens/s) on N B200 GPUs of one node.
+
+Config (the reference's published run: `-e d12 -b 64 -t 1024 -d 524288`, bf16, AdamW, ZeRO-1):
+micro-batch 64 x 1024 tokens per GPU, 524,288 tokens per optimizer step (gradient accumulation
+524288 / (65536 * N) micro-steps), random-init weights, synthetic uniform tokens.
+
+    python bench.py --gpus 1 --steps 5 --warmup 3
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 --master-port P \
+        bench.py --gpus N --steps K --warmup W
+
+Two timed regions of K steps each, both bracketed by barrier + synchronize and timed with CUDA events
+(max over ranks):
+  * `value`  - device-resident token batches, no read-back: the kernel-side step rate;
+  * `e2e`    - through the public API (`Trainer.train_step`): every micro-step copies its tokens and
+               targets from pinned host memory, every step reads loss and grad-norm back.
+Rank 0 prints one JSON line. `--impl reference` reports why the reference cannot run here.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+REPO = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, REPO)
+
+PUBLISHED_TOKENS_PER_S = 212316.0  # reference's best published run (1x RTX 5090, GPT-2 124M, same config)
+MICRO_B, SEQ_T, TOTAL_BATCH = 64, 1024, 524288
+
+
+def reference_arm(args) -> int:
+    why = ("reference is a Makefile/nvcc project without setup.py or pyproject.toml (pip: 'not installable') and its "
+           "sources need ../ThunderKittens headers that are not on this machine; it also has no sm_100 kernel path")
+    if int(os.environ.get("RANK", "0")) == 0:
+        print(json.dumps({"impl": "reference", "unavailable": why}))
+    return 0
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons with nvidia-smi while the timed region runs."""
+
+    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+             "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+             "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.gpu_index = gpu_index
+        self.proc = None
+        self.lines = []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
+                                          "-lms", "200", "-i", str(self.gpu_index)], stdout=subprocess.PIPE,
+                                         stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._pump, daemon=True).start()
+        except Exception:
+            self.proc = None
+
+    def _pump(self):
+        for line in self.proc.stdout:
+            self.lines.append((time.time(), line.strip()))
+
+    def stop(self):
+        if self.proc is not None:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except Exception:
+                self.proc.kill()
+
+    def summary(self, t0: float, t1: float) -> dict:
+        sm, mx, reasons, power = [], [], set(), []
+        for ts, line in self.lines:
+            if ts < t0 or ts > t1:
+                continue
+            f = [x.strip() for x in line.split(",")]
+            if len(f) < 8:
+                continue
+            try:
+                sm.append(float(f[1]))
+                mx.append(float(f[2]))
+                power.append(float(f[3]))
+            except ValueError:
+                continue
+            for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[4:8]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        if not sm:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        return {"sm_mhz": statistics.median(sm), "sm_max_mhz": max(mx), "reasons": sorted(reasons), "samples": len(sm),
+                "power_w_max": max(power)}
+
+
+def main() -> int:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=5)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference", "library"])
+    ap.add_argument("--zero", type=int, default=1)
+    ap.add_argument("--comm", default="auto", choices=["auto", "fused", "library"])
+    ap.add_argument("--recompute", type=int, default=0)
+    ap.add_argument("--model", default="d12")
+    ap.add_argument("--micro-batch", type=int, default=MICRO_B)
+    ap.add_argument("--seq-len", type=int, default=SEQ_T)
+    ap.add_argument("--total-batch", type=int, default=TOTAL_BATCH)
+    args = ap.parse_args()
+    if args.impl == "reference":
+        return reference_arm(args)
+    if args.warmup < 3:
+        args.warmup = 3
+
+    import torch
+    import torch.distributed as dist
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus:
+        if rank == 0:
+            print(f"bench.py: --gpus {args.gpus} but WORLD_SIZE={world}; launch with torch.distributed.run", file=sys.stderr)
+        if world == 1 and args.gpus > 1:
+            return 2
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=device)
+
+    from llm_kittens_b200.models.config import config_from_descriptor
+    from llm_kittens_b200.ops import _native
+    from llm_kittens_b200.runtime.trainer import Trainer
+    from llm_kittens_b200.parallel.bootstrap import make_comm
+    from llm_kittens_b200.parallel.zero import ZeroPlan
+
+    config = config_from_descriptor(args.model)
+    B, T = args.micro_batch, args.seq_len
+    accum = args.total_batch // (B * T * world)
+    assert accum >= 1 and accum * B * T * world == args.total_batch, "total batch must be divisible by B*T*gpus"
+
+    if args.impl == "library":
+        from llm_kittens_b200.oracle.torch_model import TorchTransformer
+
+        model = TorchTransformer(config, device=device, dtype=torch.bfloat16)
+    else:
+        from llm_kittens_b200.models.transformer import Transformer
+
+        model = Transformer(config, device=device, recompute=args.recompute)
+    model.init_weights(seed=42)
+    zero = args.zero if world > 1 else 0
+    plan = ZeroPlan(config, world, rank, zero)
+    comm = make_comm(plan, model, world, rank, device, prefer=args.comm if args.impl == "ours" else "library")
+    trainer = Trainer(model, zero_stage=zero, use_master_weights=True, learning_rate=6e-4, weight_decay=0.1, comm=comm,
+                      num_processes=world, rank=rank)
+
+    # synthetic uniform tokens: a pool of pinned host batches (e2e) and device copies (device-timed)
+    gen = torch.Generator().manual_seed(1337 + rank)
+    pool = 8
+    host = [(torch.randint(0, config.vocab_size, (B, T), generator=gen, dtype=torch.int32).pin_memory(),
+             torch.randint(0, config.vocab_size, (B, T), generator=gen, dtype=torch.int32).pin_memory()) for _ in range(pool)]
+    dev = [(x.to(device), y.to(device)) for x, y in host]
+
+    def batches(src, step):
+        return [src[(step * accum + i) % pool] for i in range(accum)]
+
+    from llm_kittens_b200.utils.schedulers import LearningRateScheduler
+
+    sched = LearningRateScheduler("cosine", 6e-4, 700, 20000, 0.0)
+
+    def sync_all():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(fn, steps):
+        sync_all()
+        t0 = time.time()
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s.record()
+        for i in range(steps):
+            fn(i)
+        e.record()
+        sync_all()
+        t1 = time.time()
+        ms = torch.tensor([s.elapsed_time(e)], device=device)
+        if world > 1:
+            dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        return float(ms.item()), t0, t1
+
+    step_no = [0]
+
+    def device_step(i):
+        trainer.accumulate(batches(dev, step_no[0]))
+        trainer.update(sched.get(step_no[0]))
+        step_no[0] += 1
+
+    last = {}
+
+    def e2e_step(i):
+        r = trainer.train_step(batches(host, step_no[0]), lr=sched.get(step_no[0]))
+        last["loss"], last["norm"] = r.loss, r.grad_norm
+        step_no[0] += 1
+
+    for i in range(args.warmup):
+        e2e_step(i)
+    _native.check_status() if args.impl == "ours" else None
+    first_loss = last.get("loss")
+
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+        time.sleep(0.3)
+    launches0 = _native.launch_count()
+    ms_dev, t0, t1 = timed(device_step, args.steps)
+    launches = _native.launch_count() - launches0
+    ms_e2e, t2, t3 = timed(e2e_step, args.steps)
+    if rank == 0:
+        time.sleep(0.25)
+        sampler.stop()
+    if args.impl == "ours":
+        _native.check_status()
+
+    if rank == 0:
+        tokens = args.total_batch * args.steps
+        value = tokens / (ms_dev / 1e3)
+        e2e_value = tokens / (ms_e2e / 1e3)
+        clocks = sampler.summary(t0, t3)
+        h2d = accum * 2 * B * T * 4 * world
+        d2h = 12 * world
+        out = {
+            "metric": "train tokens/sec (GPT-2 124M, device-timed, max over ranks)",
+            "value": round(value, 1), "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": round(ms_dev / args.steps, 3), "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": round(value / PUBLISHED_TOKENS_PER_S, 3), "dtype": "bf16", "data": "synthetic",
+            "impl": args.impl,
+            "config": {"model": "gpt2-124M (d12: L12 H12 C768 V50257/50304 T1024)", "global_batch": args.total_batch,
+                       "micro_batch": B, "seq_len": T, "grad_accum_steps": accum,
+                       "parallelism": f"dp{world}" + (f"-zero{zero}" if world > 1 else ""),
+                       "optimizer": "AdamW fp32 m/v + fp32 master, bf16 params/grads, clip 1.0, cosine lr 6e-4 warmup 700",
+                       "comm": type(comm).__name__, "recompute": args.recompute,
+                       "l2": "working set per step (~20 GB activations, 250 MB weights) far exceeds the 126 MB L2; no flush needed",
+                       "weights": "random init N(0,0.02), seed 42"},
+            "clocks": clocks,
+            "e2e": {"value": round(e2e_value, 1), "unit": "tokens/s", "ms_per_step": round(ms_e2e / args.steps, 3),
+                    "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "api": "Trainer.train_step(pinned host batches)"},
+            "gpu_launches": int(launches),
+            "loss_first_warmup": first_loss, "loss_last": last.get("loss"), "grad_norm_last": last.get("norm"),
+        }
+        print(json.dumps(out))
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

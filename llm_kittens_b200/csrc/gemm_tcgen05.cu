@@ -299,7 +299,11 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
                             for (int j = 0; j < 8; j++) x[j] = (EPI & EPI_DGELU) ? x[j] * gelu_grad(g[j]) : x[j] + g[j];
                         }
                         if (EPI & EPI_GELU) {
-                            res2[(EPI & EPI_GELU) ? cc : 0] = pack8(x);  // pre-activation
+                            // the activation is computed from the ROUNDED pre-activation, so that recomputing
+                            // it later from the stored bf16 tensor gives the same bits
+                            const bf16x8 pre = pack8(x);
+                            res2[(EPI & EPI_GELU) ? cc : 0] = pre;
+                            unpack8(pre, x);
 #pragma unroll
                             for (int j = 0; j < 8; j++) x[j] = gelu_fwd(x[j]);
                         }

@@ -158,15 +158,195 @@ norm_bwd_kernel(bf16* __restrict__ dinp, float* __restrict__ scratch, const bf16
 // dweight[c] += sum_b scratch[b][0][c] ; dbias[c] += sum_b scratch[b][1][c]   (fixed order over b)
 __global__ void norm_bwd_finish_kernel(bf16* __restrict__ dweight, bf16* __restrict__ dbias, const float* __restrict__ scratch,
                                        int nblocks, int C) {
-    const int c = blockIdx.x * blockDim.x + threadIdx.x;
-    if (c >= C) return;
+    // block = (32 columns, 8 partial-row lanes); lane y sums partials y, y+8, ...; then the 8 lanes are
+    // added in fixed order, so the result does not depend on scheduling
+    __shared__ float shw[8][33], shb[8][33];
+    const int c = blockIdx.x * 32 + threadIdx.x;
     float sw = 0.f, sb = 0.f;
-    for (int b = 0; b < nblocks; b++) {
-        sw += scratch[(size_t)b * 2 * C + c];
-        if (dbias != nullptr) sb += scratch[(size_t)b * 2 * C + C + c];
+    if (c < C) {
+        for (int b = threadIdx.y; b < nblocks; b += 8) {
+            sw += scratch[(size_t)b * 2 * C + c];
+            if (dbias != nullptr) sb += scratch[(size_t)b * 2 * C + C + c];
+        }
     }
-    dweight[c] = __float2bfloat16_rn(__bfloat162float(dweight[c]) + sw);
-    if (dbias != nullptr) dbias[c] = __float2bfloat16_rn(__bfloat162float(dbias[c]) + sb);
+    shw[threadIdx.y][threadIdx.x] = sw;
+    shb[threadIdx.y][threadIdx.x] = sb;
+    __syncthreads();
+    if (threadIdx.y == 0 && c < C) {
+        float tw = 0.f, tb = 0.f;
+#pragma unroll
+        for (int y = 0; y < 8; y++) {
+            tw += shw[y][threadIdx.x];
+            tb += shb[y][threadIdx.x];
+        }
+        dweight[c] = __float2bfloat16_rn(__bfloat162float(dweight[c]) + tw);
+        if (dbias != nullptr) dbias[c] = __float2bfloat16_rn(__bfloat162float(dbias[c]) + tb);
+    }
+}
+
+// ------------------------------------------------------------------------------------------------
+// Fast paths for C = 256 * NVEC: the whole row lives in registers (lane l owns the 16-byte vectors
+// l, l+32, ...), so global memory is read exactly once, and the backward keeps its dweight / dbias
+// sums in registers across all rows of the warp. 8 warps per block, one row per warp at a time.
+constexpr int REG_WARPS = 8;
+
+template <bool RMS, bool FUSED_RESIDUAL, int NVEC>
+__global__ void __launch_bounds__(REG_WARPS * 32)
+norm_fwd_reg_kernel(bf16* __restrict__ normed, float* __restrict__ mean_out, float* __restrict__ rstd_out,
+                    bf16* __restrict__ residual_out, const bf16* __restrict__ inp1, const bf16* __restrict__ inp2,
+                    const bf16* __restrict__ weight, const bf16* __restrict__ bias, int N, float eps) {
+    constexpr int C = NVEC * 256;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const float inv_c = 1.0f / (float)C;
+    for (int row = blockIdx.x * REG_WARPS + warp; row < N; row += gridDim.x * REG_WARPS) {
+        bf16x8 xv[NVEC];
+#pragma unroll
+        for (int k = 0; k < NVEC; k++) xv[k] = ld128_stream(inp1 + (size_t)row * C + (lane + 32 * k) * 8);
+        if (FUSED_RESIDUAL) {
+            bf16x8 yv[NVEC];
+#pragma unroll
+            for (int k = 0; k < NVEC; k++) yv[k] = ld128_stream(inp2 + (size_t)row * C + (lane + 32 * k) * 8);
+#pragma unroll
+            for (int k = 0; k < NVEC; k++) {
+                float a[8], b[8];
+                unpack8(xv[k], a);
+                unpack8(yv[k], b);
+#pragma unroll
+                for (int j = 0; j < 8; j++) a[j] += b[j];
+                xv[k] = pack8(a);
+                st128(residual_out + (size_t)row * C + (lane + 32 * k) * 8, xv[k]);
+            }
+        }
+        float sum = 0.f;
+#pragma unroll
+        for (int k = 0; k < NVEC; k++) {
+            float f[8];
+            unpack8(xv[k], f);
+#pragma unroll
+            for (int j = 0; j < 8; j++) sum += RMS ? f[j] * f[j] : f[j];
+        }
+        sum = warp_sum(sum);
+        float mean = 0.f, rstd;
+        if (RMS) {
+            rstd = rsqrtf(sum * inv_c + eps);
+        } else {
+            mean = sum * inv_c;
+            float var = 0.f;
+#pragma unroll
+            for (int k = 0; k < NVEC; k++) {
+                float f[8];
+                unpack8(xv[k], f);
+#pragma unroll
+                for (int j = 0; j < 8; j++) {
+                    const float d = f[j] - mean;
+                    var += d * d;
+                }
+            }
+            var = warp_sum(var);
+            rstd = rsqrtf(var * inv_c + eps);
+        }
+        if (lane == 0) {
+            if (!RMS && mean_out != nullptr) mean_out[row] = mean;
+            if (rstd_out != nullptr) rstd_out[row] = rstd;
+        }
+#pragma unroll
+        for (int k = 0; k < NVEC; k++) {
+            float f[8], w[8], b[8];
+            unpack8(xv[k], f);
+            unpack8(ld128(weight + (lane + 32 * k) * 8), w);
+            if (!RMS) unpack8(ld128(bias + (lane + 32 * k) * 8), b);
+#pragma unroll
+            for (int j = 0; j < 8; j++) {
+                const float n = (f[j] - mean) * rstd;
+                f[j] = RMS ? n * w[j] : n * w[j] + b[j];
+            }
+            st128(normed + (size_t)row * C + (lane + 32 * k) * 8, pack8(f));
+        }
+    }
+}
+
+// scratch layout as for norm_bwd_kernel: [gridDim.x][2][C] fp32
+template <bool RMS, int NVEC>
+__global__ void __launch_bounds__(REG_WARPS * 32)
+norm_bwd_reg_kernel(bf16* __restrict__ dinp, float* __restrict__ scratch, const bf16* __restrict__ dout,
+                    const bf16* __restrict__ inp, const bf16* __restrict__ weight, const float* __restrict__ mean,
+                    const float* __restrict__ rstd, int N, int accumulate_dinp) {
+    constexpr int C = NVEC * 256;
+    constexpr int PLANES = RMS ? 1 : 2;
+    extern __shared__ __align__(16) uint8_t smem_raw[];
+    float* sh = reinterpret_cast<float*>(smem_raw);  // [REG_WARPS][PLANES][C], used only for the final reduction
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const float inv_c = 1.0f / (float)C;
+    float dw[NVEC][8], db[RMS ? 1 : NVEC][8];
+#pragma unroll
+    for (int k = 0; k < NVEC; k++)
+#pragma unroll
+        for (int j = 0; j < 8; j++) {
+            dw[k][j] = 0.f;
+            if (!RMS) db[k][j] = 0.f;
+        }
+    for (int row = blockIdx.x * REG_WARPS + warp; row < N; row += gridDim.x * REG_WARPS) {
+        bf16x8 dv[NVEC], xv[NVEC];
+#pragma unroll
+        for (int k = 0; k < NVEC; k++) {
+            dv[k] = ld128_stream(dout + (size_t)row * C + (lane + 32 * k) * 8);
+            xv[k] = ld128_stream(inp + (size_t)row * C + (lane + 32 * k) * 8);
+        }
+        const float m = RMS ? 0.f : mean[row];
+        const float rs = rstd[row];
+        float s1 = 0.f, s2 = 0.f;
+#pragma unroll
+        for (int k = 0; k < NVEC; k++) {
+            float fd[8], fx[8], fw[8];
+            unpack8(dv[k], fd);
+            unpack8(xv[k], fx);
+            unpack8(ld128(weight + (lane + 32 * k) * 8), fw);
+#pragma unroll
+            for (int j = 0; j < 8; j++) {
+                const float n = (fx[j] - m) * rs;
+                const float dn = fd[j] * fw[j];
+                s1 += dn;
+                s2 += dn * n;
+                dw[k][j] += fd[j] * n;
+                if (!RMS) db[k][j] += fd[j];
+            }
+        }
+        s1 = warp_sum(s1) * inv_c;
+        s2 = warp_sum(s2) * inv_c;
+#pragma unroll
+        for (int k = 0; k < NVEC; k++) {
+            float fd[8], fx[8], fw[8], fo[8];
+            unpack8(dv[k], fd);
+            unpack8(xv[k], fx);
+            unpack8(ld128(weight + (lane + 32 * k) * 8), fw);
+            bf16* dx = dinp + (size_t)row * C + (lane + 32 * k) * 8;
+            if (accumulate_dinp) unpack8(ld128(dx), fo);
+#pragma unroll
+            for (int j = 0; j < 8; j++) {
+                const float n = (fx[j] - m) * rs;
+                const float dn = fd[j] * fw[j];
+                const float d = RMS ? (dn - n * s2) * rs : (dn - s1 - n * s2) * rs;
+                fo[j] = accumulate_dinp ? fo[j] + d : d;
+            }
+            st128(dx, pack8(fo));
+        }
+    }
+    // per-warp sums -> shared memory -> fixed-order sum over warps -> one partial per block
+#pragma unroll
+    for (int k = 0; k < NVEC; k++)
+#pragma unroll
+        for (int j = 0; j < 8; j++) {
+            sh[(size_t)warp * PLANES * C + (lane + 32 * k) * 8 + j] = dw[k][j];
+            if (!RMS) sh[(size_t)warp * PLANES * C + C + (lane + 32 * k) * 8 + j] = db[k][j];
+        }
+    __syncthreads();
+    float* dst = scratch + (size_t)blockIdx.x * 2 * C;
+    for (int i = threadIdx.x; i < PLANES * C; i += blockDim.x) {
+        float s = 0.f;
+#pragma unroll
+        for (int w = 0; w < REG_WARPS; w++) s += sh[(size_t)w * PLANES * C + i];
+        dst[i] = s;
+    }
 }
 
 static int g_sms = 0;
@@ -184,6 +364,29 @@ template <bool RMS, bool FUSED>
 static int launch_fwd(bf16* normed, float* mean, float* rstd, bf16* residual, const bf16* inp1, const bf16* inp2,
                       const bf16* weight, const bf16* bias, int N, int C, float eps, cudaStream_t stream) {
     if (C % 8 != 0 || C > 16384) return LLMK_ERR_SHAPE;
+    if (C % 256 == 0) {
+        int grid = ceil_div(N, REG_WARPS);
+        const int cap = num_sms() * 16;
+        if (grid > cap) grid = cap;
+#define LLMK_NORM_FWD_CASE(NV)                                                                                              \
+    case NV:                                                                                                                \
+        norm_fwd_reg_kernel<RMS, FUSED, NV><<<grid, REG_WARPS * 32, 0, stream>>>(normed, mean, rstd, residual, inp1, inp2,   \
+                                                                                 weight, bias, N, eps);                     \
+        LLMK_LAUNCH_CHECK();                                                                                                \
+        return LLMK_OK;
+        switch (C / 256) {
+            LLMK_NORM_FWD_CASE(1)
+            LLMK_NORM_FWD_CASE(2)
+            LLMK_NORM_FWD_CASE(3)
+            LLMK_NORM_FWD_CASE(4)
+            LLMK_NORM_FWD_CASE(5)
+            LLMK_NORM_FWD_CASE(6)
+            LLMK_NORM_FWD_CASE(8)
+            LLMK_NORM_FWD_CASE(16)
+            default: break;
+        }
+#undef LLMK_NORM_FWD_CASE
+    }
     const int smem = FWD_WARPS * C * 2;
     static bool configured = false;
     if (!configured) {
@@ -239,7 +442,35 @@ LLMK_API int llmk_norm_bwd_blocks(int N, int C) {
     const int need = ceil_div(N, BWD_WARPS);
     return grid < need ? grid : need;
 }
-LLMK_API long llmk_norm_bwd_scratch_bytes(int N, int C) { return (long)llmk_norm_bwd_blocks(N, C) * 2 * C * 4; }
+// Upper bound over both backward implementations (at most 4 blocks per SM).
+LLMK_API long llmk_norm_bwd_scratch_bytes(int N, int C) { return (long)num_sms() * 4 * 2 * C * 4; }
+
+namespace llmk {
+namespace norm {
+// Register-resident backward when C = 256 * NVEC and the accumulators fit; returns false if not applicable.
+template <bool RMS, int NVEC>
+static int launch_bwd_reg(bf16* dinp, bf16* dweight, bf16* dbias, float* scratch, const bf16* dout, const bf16* inp,
+                          const bf16* weight, const float* mean, const float* rstd, int N, int accumulate_dinp,
+                          cudaStream_t stream) {
+    constexpr int C = NVEC * 256;
+    constexpr int SMEM = REG_WARPS * (RMS ? 1 : 2) * C * 4;
+    static bool configured = false;
+    if (!configured) {
+        LLMK_CUDA_TRY(cudaFuncSetAttribute(norm_bwd_reg_kernel<RMS, NVEC>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM));
+        configured = true;
+    }
+    int grid = num_sms() * 2;
+    const int need = ceil_div(N, REG_WARPS);
+    if (grid > need) grid = need;
+    norm_bwd_reg_kernel<RMS, NVEC><<<grid, REG_WARPS * 32, SMEM, stream>>>(dinp, scratch, dout, inp, weight, mean, rstd, N,
+                                                                          accumulate_dinp);
+    LLMK_LAUNCH_CHECK();
+    norm_bwd_finish_kernel<<<ceil_div(C, 32), dim3(32, 8), 0, stream>>>(dweight, dbias, scratch, grid, C);
+    LLMK_LAUNCH_CHECK();
+    return LLMK_OK;
+}
+}  // namespace norm
+}  // namespace llmk
 
 namespace llmk {
 namespace norm {
@@ -248,6 +479,14 @@ int layernorm_bwd_impl(bf16* dinp, bf16* dweight, bf16* dbias, float* scratch, c
                        const bf16* weight, const float* mean, const float* rstd, int N, int C, int accumulate_dinp,
                        cudaStream_t stream) {
     if (C % 8 != 0 || C > 12288) return LLMK_ERR_SHAPE;
+    switch (C % 256 == 0 ? C / 256 : 0) {
+        case 1: return launch_bwd_reg<false, 1>(dinp, dweight, dbias, scratch, dout, inp, weight, mean, rstd, N, accumulate_dinp, stream);
+        case 2: return launch_bwd_reg<false, 2>(dinp, dweight, dbias, scratch, dout, inp, weight, mean, rstd, N, accumulate_dinp, stream);
+        case 3: return launch_bwd_reg<false, 3>(dinp, dweight, dbias, scratch, dout, inp, weight, mean, rstd, N, accumulate_dinp, stream);
+        case 4: return launch_bwd_reg<false, 4>(dinp, dweight, dbias, scratch, dout, inp, weight, mean, rstd, N, accumulate_dinp, stream);
+        case 5: return launch_bwd_reg<false, 5>(dinp, dweight, dbias, scratch, dout, inp, weight, mean, rstd, N, accumulate_dinp, stream);
+        default: break;
+    }
     static bool configured = false;
     if (!configured) {
         LLMK_CUDA_TRY(cudaFuncSetAttribute(norm_bwd_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -260,7 +499,7 @@ int layernorm_bwd_impl(bf16* dinp, bf16* dweight, bf16* dbias, float* scratch, c
     norm_bwd_kernel<false><<<grid, BWD_WARPS * 32, smem, stream>>>(dinp, scratch, dout, inp, weight, mean, rstd, N, C,
                                                                   accumulate_dinp);
     LLMK_LAUNCH_CHECK();
-    norm_bwd_finish_kernel<<<ceil_div(C, 256), 256, 0, stream>>>(dweight, dbias, scratch, grid, C);
+    norm_bwd_finish_kernel<<<ceil_div(C, 32), dim3(32, 8), 0, stream>>>(dweight, dbias, scratch, grid, C);
     LLMK_LAUNCH_CHECK();
     return LLMK_OK;
 }
@@ -280,6 +519,21 @@ LLMK_API int llmk_rmsnorm_bwd(void* dinp, void* dweight, void* scratch, const vo
                               const void* rstd, int N, int C, int accumulate_dinp, void* stream_) {
     cudaStream_t stream = (cudaStream_t)stream_;
     if (C % 8 != 0 || C > 12288) return LLMK_ERR_SHAPE;
+#define LLMK_RMS_BWD_CASE(NV)                                                                                             \
+    case NV:                                                                                                              \
+        return launch_bwd_reg<true, NV>((bf16*)dinp, (bf16*)dweight, nullptr, (float*)scratch, (const bf16*)dout,         \
+                                        (const bf16*)inp, (const bf16*)weight, nullptr, (const float*)rstd, N,            \
+                                        accumulate_dinp, stream);
+    switch (C % 256 == 0 ? C / 256 : 0) {
+        LLMK_RMS_BWD_CASE(1)
+        LLMK_RMS_BWD_CASE(2)
+        LLMK_RMS_BWD_CASE(3)
+        LLMK_RMS_BWD_CASE(4)
+        LLMK_RMS_BWD_CASE(8)
+        LLMK_RMS_BWD_CASE(16)
+        default: break;
+    }
+#undef LLMK_RMS_BWD_CASE
     static bool configured = false;
     if (!configured) {
         LLMK_CUDA_TRY(cudaFuncSetAttribute(norm_bwd_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -292,7 +546,7 @@ LLMK_API int llmk_rmsnorm_bwd(void* dinp, void* dweight, void* scratch, const vo
                                                                  (const bf16*)inp, (const bf16*)weight, nullptr,
                                                                  (const float*)rstd, N, C, accumulate_dinp);
     LLMK_LAUNCH_CHECK();
-    norm_bwd_finish_kernel<<<ceil_div(C, 256), 256, 0, stream>>>((bf16*)dweight, nullptr, (const float*)scratch, grid, C);
+    norm_bwd_finish_kernel<<<ceil_div(C, 32), dim3(32, 8), 0, stream>>>((bf16*)dweight, nullptr, (const float*)scratch, grid, C);
     LLMK_LAUNCH_CHECK();
     return LLMK_OK;
 }

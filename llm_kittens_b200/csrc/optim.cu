@@ -24,6 +24,22 @@ __device__ __forceinline__ float load_grad<bf16>(const bf16* g, size_t i) { retu
 template <>
 __device__ __forceinline__ float load_grad<float>(const float* g, size_t i) { return g[i]; }
 
+// four consecutive gradients (8- or 16-byte aligned loads)
+template <typename G>
+__device__ __forceinline__ void load_grad4(const G* g, size_t i, float* out);
+template <>
+__device__ __forceinline__ void load_grad4<bf16>(const bf16* g, size_t i, float* out) {
+    const uint2 raw = *reinterpret_cast<const uint2*>(g + i);
+    const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.x));
+    const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.y));
+    out[0] = a.x; out[1] = a.y; out[2] = b.x; out[3] = b.y;
+}
+template <>
+__device__ __forceinline__ void load_grad4<float>(const float* g, size_t i, float* out) {
+    const float4 r = *reinterpret_cast<const float4*>(g + i);
+    out[0] = r.x; out[1] = r.y; out[2] = r.z; out[3] = r.w;
+}
+
 // partials[blockIdx.y * gridDim.x + blockIdx.x] = sum of squares of this block's elements
 template <typename G>
 __global__ void __launch_bounds__(TPB)
@@ -32,9 +48,11 @@ norm2_kernel(float* __restrict__ partials, const G* __restrict__ grads, const lo
     const long long* seg = segs + (size_t)blockIdx.y * SEG_FIELDS;
     const size_t g_off = (size_t)seg[1], len = (size_t)seg[3];
     float acc = 0.f;
-    for (size_t i = (size_t)blockIdx.x * TPB + threadIdx.x; i < len; i += (size_t)gridDim.x * TPB) {
-        const float g = load_grad<G>(grads, g_off + i);
-        acc += g * g;
+    // four elements per thread and iteration (offsets and lengths are multiples of 4 by construction)
+    for (size_t i = ((size_t)blockIdx.x * TPB + threadIdx.x) * 4; i < len; i += (size_t)gridDim.x * TPB * 4) {
+        float g4[4];
+        load_grad4<G>(grads, g_off + i, g4);
+        acc += g4[0] * g4[0] + g4[1] * g4[1] + g4[2] * g4[2] + g4[3] * g4[3];
     }
     acc = block_sum(acc, sh);
     if (threadIdx.x == 0) partials[(size_t)blockIdx.y * gridDim.x + blockIdx.x] = acc;
@@ -78,20 +96,36 @@ adamw_kernel(bf16* __restrict__ params, float* __restrict__ master, const G* __r
     const size_t p_off = (size_t)seg[0], g_off = (size_t)seg[1], s_off = (size_t)seg[2], len = (size_t)seg[3];
     const float wd = (seg[4] & 1) ? a.wd : 0.f;
     const float gs = grad_scale_ptr ? grad_scale_ptr[0] * grad_scale_host : grad_scale_host;
-    for (size_t i = (size_t)blockIdx.x * TPB + threadIdx.x; i < len; i += (size_t)gridDim.x * TPB) {
-        const float g = gs * load_grad<G>(grads, g_off + i);
-        float mi = m[s_off + i], vi = v[s_off + i];
-        mi = a.beta1 * mi + (1.0f - a.beta1) * g;
-        vi = a.beta2 * vi + (1.0f - a.beta2) * g * g;
-        m[s_off + i] = mi;
-        v[s_off + i] = vi;
-        const float mh = mi / a.beta1_corr, vh = vi / a.beta2_corr;
-        const float old = master ? master[s_off + i] : __bfloat162float(params[p_off + i]);
-        const float p = old - a.lr * (mh / (sqrtf(vh) + a.eps) + wd * old);
-        // the rounding noise is keyed on the element's index in the full parameter arena, so every rank
-        // (and every sharding) rounds a given parameter the same way
-        params[p_off + i] = sr_round(p, squirrel5((unsigned int)(p_off + i), a.seed));
-        if (master) master[s_off + i] = p;
+    const float inv_b1c = 1.0f / a.beta1_corr, inv_b2c = 1.0f / a.beta2_corr;
+    // four elements per thread and iteration: 8-byte bf16 and 16-byte fp32 accesses
+    for (size_t i = ((size_t)blockIdx.x * TPB + threadIdx.x) * 4; i < len; i += (size_t)gridDim.x * TPB * 4) {
+        float g4[4], old4[4], p4[4];
+        load_grad4<G>(grads, g_off + i, g4);
+        float4 m4 = *reinterpret_cast<const float4*>(m + s_off + i);
+        float4 v4 = *reinterpret_cast<const float4*>(v + s_off + i);
+        float mm[4] = {m4.x, m4.y, m4.z, m4.w}, vv[4] = {v4.x, v4.y, v4.z, v4.w};
+        if (master) {
+            const float4 o = *reinterpret_cast<const float4*>(master + s_off + i);
+            old4[0] = o.x; old4[1] = o.y; old4[2] = o.z; old4[3] = o.w;
+        } else {
+            load_grad4<bf16>(params, p_off + i, old4);
+        }
+        __align__(8) __nv_bfloat16 out[4];
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            const float g = gs * g4[j];
+            mm[j] = a.beta1 * mm[j] + (1.0f - a.beta1) * g;
+            vv[j] = a.beta2 * vv[j] + (1.0f - a.beta2) * g * g;
+            const float mh = mm[j] * inv_b1c, vh = vv[j] * inv_b2c;
+            p4[j] = old4[j] - a.lr * (mh / (sqrtf(vh) + a.eps) + wd * old4[j]);
+            // the rounding noise is keyed on the element's index in the full parameter arena, so every
+            // rank (and every sharding) rounds a given parameter the same way
+            out[j] = sr_round(p4[j], squirrel5((unsigned int)(p_off + i + j), a.seed));
+        }
+        *reinterpret_cast<float4*>(m + s_off + i) = make_float4(mm[0], mm[1], mm[2], mm[3]);
+        *reinterpret_cast<float4*>(v + s_off + i) = make_float4(vv[0], vv[1], vv[2], vv[3]);
+        *reinterpret_cast<uint2*>(params + p_off + i) = *reinterpret_cast<const uint2*>(out);
+        if (master) *reinterpret_cast<float4*>(master + s_off + i) = make_float4(p4[0], p4[1], p4[2], p4[3]);
     }
 }
 

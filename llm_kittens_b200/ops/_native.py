@@ -86,10 +86,24 @@ def _conv(a: Any):
     return a
 
 
+# kernels launched by one call of a library entry point (default 1); used for the launch counter
+_KERNELS_PER_CALL = {"llmk_layernorm_bwd": 2, "llmk_rmsnorm_bwd": 2, "llmk_dbias": 2, "llmk_attention_bwd": 3,
+                     "llmk_encoder_bwd": 2, "llmk_global_norm2": 2}
+_LAUNCHES = 0
+
+
+def launch_count() -> int:
+    """Number of kernels of this library launched so far by this process (split-K GEMMs count their
+    reduction kernel as well)."""
+    return _LAUNCHES
+
+
 def call(name: str, *args: Any) -> None:
     """Call ``int name(args..., void* stream)``; tensors become device pointers; raises on failure."""
+    global _LAUNCHES
     fn = getattr(lib(), name)
     rc = fn(*[_conv(a) for a in args], stream_handle())
+    _LAUNCHES += _KERNELS_PER_CALL.get(name, 1)
     if rc != 0:
         detail = lib().llmk_last_error().decode() if rc == -1 else ""
         raise NativeError(f"{name} failed: {ERRORS.get(rc, rc)} {detail}")

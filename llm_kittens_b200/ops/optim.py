@@ -12,6 +12,8 @@ SEG_FIELDS = 5
 def make_segments(rows, device="cuda") -> tuple[torch.Tensor, int]:
     """``rows``: iterable of (param_off, grad_off, state_off, length, weight_decay?) -> (int64 table, max length)."""
     rows = [(int(p), int(g), int(s), int(n), int(bool(wd))) for p, g, s, n, wd in rows if n > 0]
+    if any(x % 4 for r in rows for x in r[:4]):
+        raise ValueError("segment offsets and lengths must be multiples of 4 elements")
     t = torch.tensor(rows, dtype=torch.int64).reshape(-1, SEG_FIELDS)
     return t.to(device), max(r[3] for r in rows)
 

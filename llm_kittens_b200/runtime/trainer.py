@@ -1,0 +1,207 @@
+"""Training step orchestration: gradient accumulation, data-parallel reduction, global-norm
+clipping, AdamW on this rank's ZeRO shard, parameter all-gather, loss / norm read-back.
+
+Plays the role of the inner loop of the reference trainers (train_gpt2.cu:2227-2316: micro-steps,
+gpt2_calculate_grad_norm, gpt2_update) with these differences: the clip coefficient is computed on
+the device and consumed by the AdamW kernel through a pointer (no host sync between norm and
+update), one AdamW launch covers the whole shard via a segment table, and the only device-to-host
+traffic per step is one small read-back of (loss, grad-norm, overflow flag) after everything has been
+queued.
+
+The optimizer has two back-ends with the same semantics: the CUDA kernels of ``ops/optim.py`` (with
+stochastic rounding and optional fp32 master weights) and a PyTorch one used when the model lives on
+the CPU (oracle / gloo tests).
+"""
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass
+
+import torch
+
+from ..parallel.comm import SingleProcessComm
+from ..parallel.zero import ZeroPlan
+from ..utils.rand import Xorshift
+
+
+@dataclass
+class StepResult:
+    loss: float
+    grad_norm: float
+    lr: float
+    skipped: bool = False
+
+
+class Trainer:
+    def __init__(self, model, *, zero_stage: int = 0, use_master_weights: bool = True, learning_rate: float = 3e-4,
+                 weight_decay: float = 0.0, beta1: float = 0.9, beta2: float = 0.95, eps: float = 1e-8, grad_clip: float = 1.0,
+                 comm=None, num_processes: int = 1, rank: int = 0, rng_state: int = 13371337):
+        self.model = model
+        self.device = model.device
+        self.native = self.device.type == "cuda" and hasattr(model, "recompute")
+        self.cuda = self.device.type == "cuda"
+        self.plan = ZeroPlan(model.config, num_processes, rank, zero_stage)
+        self.comm = comm if comm is not None else SingleProcessComm(self.plan)
+        self.use_master = use_master_weights and model.params.dtype != torch.float32
+        self.lr, self.wd, self.beta1, self.beta2, self.eps, self.grad_clip = learning_rate, weight_decay, beta1, beta2, eps, grad_clip
+        self.step_count = 0
+        self.rng = Xorshift(rng_state)
+        self.rng_state_last_update = rng_state
+        n = self.plan.state_elements
+        dev = self.device
+        self.m = torch.zeros(n, dtype=torch.float32, device=dev)
+        self.v = torch.zeros(n, dtype=torch.float32, device=dev)
+        self.master = torch.zeros(n, dtype=torch.float32, device=dev) if self.use_master else None
+        self._master_ready = False
+        self.rows = self.plan.segment_rows()
+        # device scalars: [norm2], [scale], [norm], flag
+        self.norm2 = torch.zeros(1, dtype=torch.float32, device=dev)
+        self.scale = torch.ones(1, dtype=torch.float32, device=dev)
+        self.norm = torch.zeros(1, dtype=torch.float32, device=dev)
+        self.flag = torch.zeros(1, dtype=torch.int32, device=dev)
+        self.readback = torch.zeros(3, dtype=torch.float32, device=dev)
+        self.readback_host = torch.zeros(3, dtype=torch.float32)
+        if self.cuda:
+            self.readback_host = self.readback_host.pin_memory()
+        if self.native:
+            from ..ops import optim
+
+            self.segs, self.max_len = optim.make_segments(self.rows, device=dev)
+            self.partials = torch.empty(int(self.segs.shape[0]) * 1024, dtype=torch.float32, device=dev)
+
+    # ------------------------------------------------------------------ optimizer pieces
+    def _local_norm2(self) -> None:
+        g = self.model.grads
+        if self.native:
+            from ..ops import optim
+
+            optim.global_norm2(g, self.segs, self.max_len, out=self.norm2, partials=self.partials)
+        else:
+            acc = torch.zeros((), dtype=torch.float32, device=self.device)
+            for p_off, g_off, s_off, n, wd in self.rows:
+                acc += g[g_off:g_off + n].float().pow(2).sum()
+            self.norm2[0] = acc
+
+    def _clip(self) -> None:
+        if self.native:
+            from ..ops import optim
+
+            optim.clip_scale(self.norm2, self.grad_clip, self.scale, self.norm, self.flag)
+        else:
+            n = torch.sqrt(self.norm2[0])
+            self.norm[0] = n
+            finite = torch.isfinite(n)
+            self.flag[0] = 0 if finite else 1
+            self.scale[0] = (self.grad_clip / n if (self.grad_clip > 0 and n > self.grad_clip) else 1.0) if finite else 0.0
+
+    def _ensure_master(self) -> None:
+        if self.use_master and not self._master_ready:
+            if self.native:
+                from ..ops import optim
+
+                optim.master_from_params(self.master, self.model.params, self.segs, self.max_len)
+            else:
+                for p_off, g_off, s_off, n, wd in self.rows:
+                    self.master[s_off:s_off + n] = self.model.params[p_off:p_off + n].float()
+            self._master_ready = True
+
+    def _adamw(self, lr: float, seed: int) -> None:
+        t = self.step_count + 1
+        if self.native:
+            from ..ops import optim
+
+            optim.adamw(self.model.params, self.master, self.model.grads, self.m, self.v, self.segs, self.max_len, lr,
+                        self.beta1, self.beta2, t, self.eps, self.wd, grad_scale_ptr=self.scale, seed=seed)
+            return
+        b1c, b2c = 1.0 - self.beta1 ** t, 1.0 - self.beta2 ** t
+        gs = self.scale[0]
+        P, G = self.model.params, self.model.grads
+        for p_off, g_off, s_off, n, wd in self.rows:
+            g = G[g_off:g_off + n].float() * gs
+            m, v = self.m[s_off:s_off + n], self.v[s_off:s_off + n]
+            m.mul_(self.beta1).add_(g, alpha=1 - self.beta1)
+            v.mul_(self.beta2).addcmul_(g, g, value=1 - self.beta2)
+            old = self.master[s_off:s_off + n] if self.use_master else P[p_off:p_off + n].float()
+            new = old - lr * ((m / b1c) / ((v / b2c).sqrt() + self.eps) + (self.wd if wd else 0.0) * old)
+            if self.use_master:
+                self.master[s_off:s_off + n] = new
+            P[p_off:p_off + n] = new.to(P.dtype)
+
+    # ------------------------------------------------------------------ the step
+    def accumulate(self, micro_batches) -> int:
+        """zero grads, run forward/backward over the micro-batches, start bucket reductions."""
+        model = self.model
+        model.zero_grad()
+        batches = list(micro_batches)
+        accum = len(batches)
+        for i, (x, y) in enumerate(batches):
+            model.forward(x, y, grad_accum_steps=accum, micro_step=i)
+            model.backward(last_micro_step=(i == accum - 1), bucket_ready=self._bucket_ready)
+        return accum
+
+    def _bucket_ready(self, layer) -> None:
+        self.comm.reduce_bucket(self.model.grads, layer)
+
+    def update(self, lr: float | None = None, skip: bool = False) -> None:
+        """Queue reduction -> norm -> clip -> AdamW -> parameter gather on the current stream (no host
+        sync). With ``skip`` the optimizer part is left out; :meth:`apply_update` can run it later."""
+        self.comm.finish_reduce()
+        self.comm.all_reduce_scalar(self.model.acts["loss_acc"], "avg")
+        self._local_norm2()
+        if self.plan.sharded:
+            self.comm.all_reduce_scalar(self.norm2, "sum")
+        self._clip()
+        if not skip:
+            self.apply_update(lr)
+
+    def apply_update(self, lr: float | None = None) -> None:
+        lr = self.lr if lr is None else lr
+        self._ensure_master()
+        self.rng_state_last_update = self.rng.state
+        seed = self.rng.u32()
+        self._adamw(lr, seed)
+        self.comm.gather_params(self.model.params)
+        self.step_count += 1
+
+    def read_scalars(self) -> tuple[float, float, bool]:
+        """(mean loss, grad norm, non-finite flag): one device-to-host copy of 12 bytes, then a sync."""
+        self.readback[0:1].copy_(self.model.acts["loss_acc"])
+        self.readback[1:2].copy_(self.norm)
+        self.readback[2:3].copy_(self.flag.float())
+        self.readback_host.copy_(self.readback, non_blocking=True)
+        if self.cuda:
+            torch.cuda.current_stream().synchronize()
+        loss, norm, flag = self.readback_host.tolist()
+        return loss, norm, flag != 0.0
+
+    def train_step(self, micro_batches, lr: float | None = None) -> StepResult:
+        """One optimizer step over an iterable of (tokens, targets) micro-batches (pinned-host or device
+        int32 tensors of shape (B, T)). Returns loss / grad-norm read back from the device."""
+        lr = self.lr if lr is None else lr
+        self.accumulate(micro_batches)
+        self.update(lr)
+        loss, norm, bad = self.read_scalars()
+        return StepResult(loss=loss, grad_norm=norm, lr=lr, skipped=False)
+
+    # ------------------------------------------------------------------ evaluation
+    @torch.no_grad()
+    def validate(self, tokens, targets) -> float:
+        self.model.forward(tokens, targets, grad_accum_steps=1, micro_step=0, compute_dlogits=False)
+        return self.model.mean_loss()
+
+    def restore_params_from_master(self) -> None:
+        """Re-derive the bf16 parameters of this rank's shard from the fp32 master copy with the
+        rounding noise of the last update (bit-exact resume), then gather the other shards."""
+        if not self.use_master:
+            return
+        rng = Xorshift(self.rng_state_last_update)
+        seed = rng.u32()
+        if self.native:
+            from ..ops import optim
+
+            optim.params_from_master(self.model.params, self.master, self.segs, self.max_len, seed)
+        else:
+            for p_off, g_off, s_off, n, wd in self.rows:
+                self.model.params[p_off:p_off + n] = self.master[s_off:s_off + n].to(self.model.params.dtype)
+        self._master_ready = True
+        self.comm.gather_params(self.model.params)

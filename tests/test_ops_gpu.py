@@ -137,7 +137,8 @@ def test_dbias_and_encoder():
     db0 = rnd(2304)
     db = db0.clone()
     ew.dbias(db, dout, accumulate=True)
-    assert maxerr(db, db0.float() + dout.float().sum(0)) < 0.3
+    ref_db = db0.float() + dout.float().sum(0)
+    assert ((db.float() - ref_db).abs() <= 0.01 * ref_db.abs() + 0.05).all()
     B, T, C, V = 4, 64, 768, 1000
     wte, wpe = rnd(V, C), rnd(T, C)
     tok = torch.randint(0, V, (B, T), device="cuda", dtype=torch.int32)
