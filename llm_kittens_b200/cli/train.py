@@ -250,7 +250,7 @@ def train(args: TrainArgs, trainer_name: str) -> int:
             batches = [(train_loader.inputs, train_loader.targets)] * grad_accum
             trainer.accumulate(batches)
         else:
-            model.zero_grad()
+            trainer.begin_step()
             for micro in range(grad_accum):
                 x, y = train_loader.next_batch()
                 model.forward(x, y, grad_accum_steps=grad_accum, micro_step=micro)

@@ -1,0 +1,311 @@
+// Data-parallel communication fused into the optimizer path, over NVLink peer memory.
+//
+// The reference reduces gradients with ncclReduceScatter / ncclAllReduce per tensor on a side stream,
+// computes the gradient norm and AdamW in separate kernels and then all-gathers the updated shards
+// with ncclAllGather (llmc/zero.cuh:623-668, train_gpt2.cu:1193-1248, 1283-1375). Here the same work
+// is three kinds of kernels of our own that read and write the peers' buffers directly (every rank
+// maps every other rank's gradient / parameter / control buffer; the pointers arrive as a table):
+//
+//   rs_bucket_kernel      per layer bucket, as soon as the bucket's gradients are final on all ranks:
+//                         waits (bounded) for the peers' "bucket ready" flags, then for this rank's
+//                         shard of every tensor slice reads the P copies with 128-bit peer loads, sums
+//                         them in rank order in fp32, scales by 1/P, stores the averaged shard as fp32
+//                         and leaves a per-block partial of its squared norm
+//                         = reduce-scatter + scale + norm partial in one pass, overlapped with backward.
+//   norm_exchange_kernel  sums the partials in fixed order, writes the local sum into every peer's
+//                         control buffer, waits for the peers' sums, adds them in rank order (so every
+//                         rank gets the same bits) and produces the clip coefficient on the device
+//                         = the scalar all-reduce, without a library call.
+//   adamw_push_kernel     AdamW (+ stochastic rounding, fp32 master) on the rank's fp32 averaged shard,
+//                         each updated bf16 value stored straight into the parameter buffer of EVERY
+//                         rank (P2P stores) = optimizer + all-gather in one pass.
+//   signal / wait kernels release-store and acquire-poll epoch flags in the peers' control buffers.
+//
+// Only plain peer loads/stores and system-scope release/acquire are used: no multicast objects, no
+// TMA from remote memory. Every wait is bounded by a caller-given time limit; on expiry the kernel
+// records LLMK_ST_TIMEOUT_PEER in the status word and returns without touching peer data.
+#include "common.cuh"
+
+namespace llmk {
+namespace comm {
+
+constexpr int MAXP = 8;            // ranks in one NVLink domain served by the fused path
+constexpr int TPB = 256;
+constexpr int NORM_VAL_OFFSET = 2048;  // float slots for the exchanged norm sums inside the control buffer
+constexpr int CTRL_INTS = 4096;
+
+struct Peers {
+    void* p[MAXP];
+};
+
+__device__ __forceinline__ void st_release_sys(int* ptr, int v) {
+    asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(ptr), "r"(v) : "memory");
+}
+__device__ __forceinline__ int ld_acquire_sys(const int* ptr) {
+    int v;
+    asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(ptr) : "memory");
+    return v;
+}
+__device__ __forceinline__ uint4 ld_volatile_v4(const void* ptr) {
+    uint4 v;
+    asm volatile("ld.volatile.global.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(ptr) : "memory");
+    return v;
+}
+__device__ __forceinline__ float ld_volatile_f32(const float* ptr) {
+    float v;
+    asm volatile("ld.volatile.global.f32 %0, [%1];" : "=f"(v) : "l"(ptr) : "memory");
+    return v;
+}
+__device__ __forceinline__ unsigned long long now_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+
+// Threads 0..P-1 of the block each poll one flag until it reaches `epoch` or the limit runs out.
+// Returns (to every thread of the block) whether all flags arrived. Contains __syncthreads.
+__device__ __forceinline__ bool wait_flags_block(const int* my_ctrl, int slot, int epoch, int P, long long limit_ns,
+                                                 int* status, int tag) {
+    __shared__ int sh_ok;
+    if (threadIdx.x == 0) sh_ok = 1;
+    __syncthreads();
+    if ((int)threadIdx.x < P) {
+        const int* f = my_ctrl + slot * MAXP + threadIdx.x;
+        const unsigned long long t0 = now_ns();
+        unsigned int spins = 0;
+        while (ld_acquire_sys(f) < epoch) {
+            if ((++spins & 63u) == 0 && (long long)(now_ns() - t0) > limit_ns) {
+                sh_ok = 0;
+                if (status != nullptr && atomicCAS(status, 0, LLMK_ST_TIMEOUT_PEER) == 0) {
+                    status[1] = tag;
+                    status[2] = slot;
+                    status[3] = (int)threadIdx.x;  // the peer that never signalled
+                }
+                break;
+            }
+            __nanosleep(64);
+        }
+    }
+    __syncthreads();
+    return sh_ok != 0;
+}
+
+// ctrl[dst][slot][my_rank] = epoch for every dst (release at system scope: everything this rank wrote
+// before this kernel is visible to a peer that acquires the flag)
+__global__ void signal_kernel(Peers ctrl, int slot, int my_rank, int P, int epoch) {
+    if ((int)threadIdx.x < P) {
+        __threadfence_system();
+        st_release_sys(static_cast<int*>(ctrl.p[threadIdx.x]) + slot * MAXP + my_rank, epoch);
+    }
+}
+
+__global__ void wait_kernel(const int* my_ctrl, int slot, int epoch, int P, long long limit_ns, int* status) {
+    wait_flags_block(my_ctrl, slot, epoch, P, limit_ns, status, 100 + slot);
+}
+
+// Segment table: int64[nseg][3] = (offset of this rank's slice in the flat gradient buffer,
+// offset in the fp32 shard buffer, length); lengths are multiples of 8.
+__global__ void __launch_bounds__(TPB)
+rs_bucket_kernel(Peers grads, const int* my_ctrl, int slot, int epoch, const long long* __restrict__ segs,
+                 float* __restrict__ gshard, float* __restrict__ norm_partials, int P, float inv_p, long long limit_ns,
+                 int* status) {
+    __shared__ float sh[32];
+    const bool ok = wait_flags_block(my_ctrl, slot, epoch, P, limit_ns, status, slot);
+    const long long* seg = segs + (size_t)blockIdx.y * 3;
+    const size_t g_off = (size_t)seg[0], s_off = (size_t)seg[1], len = (size_t)seg[2];
+    float nrm = 0.f;
+    if (ok) {
+        for (size_t i = ((size_t)blockIdx.x * TPB + threadIdx.x) * 8; i < len; i += (size_t)gridDim.x * TPB * 8) {
+            float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+            uint4 raw[MAXP];
+#pragma unroll
+            for (int r = 0; r < MAXP; r++)
+                if (r < P) raw[r] = ld_volatile_v4(static_cast<const bf16*>(grads.p[r]) + g_off + i);
+#pragma unroll
+            for (int r = 0; r < MAXP; r++) {
+                if (r < P) {
+                    float f[8];
+                    unpack8(*reinterpret_cast<const bf16x8*>(&raw[r]), f);
+#pragma unroll
+                    for (int j = 0; j < 8; j++) acc[j] += f[j];
+                }
+            }
+#pragma unroll
+            for (int j = 0; j < 8; j++) {
+                acc[j] *= inv_p;
+                nrm += acc[j] * acc[j];
+            }
+            float4* dst = reinterpret_cast<float4*>(gshard + s_off + i);
+            dst[0] = make_float4(acc[0], acc[1], acc[2], acc[3]);
+            dst[1] = make_float4(acc[4], acc[5], acc[6], acc[7]);
+        }
+    }
+    nrm = block_sum(nrm, sh);
+    if (threadIdx.x == 0) norm_partials[(size_t)blockIdx.y * gridDim.x + blockIdx.x] = nrm;
+}
+
+// One block. Sums `n` partials, exchanges the sum with the peers, clip coefficient on the device.
+__global__ void __launch_bounds__(1024)
+norm_exchange_kernel(Peers ctrl, const float* __restrict__ partials, int n, int norm_slot, int my_rank, int P, int epoch,
+                     float clip, float* scale_out, float* norm_out, int* flag_out, long long limit_ns, int* status) {
+    __shared__ float sh[32];
+    float s = 0.f;
+    for (int i = threadIdx.x; i < n; i += blockDim.x) s += partials[i];
+    s = block_sum(s, sh);
+    if ((int)threadIdx.x < P) {
+        float* dst_val = reinterpret_cast<float*>(static_cast<int*>(ctrl.p[threadIdx.x]) + NORM_VAL_OFFSET) + my_rank;
+        *reinterpret_cast<volatile float*>(dst_val) = s;
+        __threadfence_system();
+        st_release_sys(static_cast<int*>(ctrl.p[threadIdx.x]) + norm_slot * MAXP + my_rank, epoch);
+    }
+    const int* my_ctrl = static_cast<const int*>(ctrl.p[my_rank]);
+    const bool ok = wait_flags_block(my_ctrl, norm_slot, epoch, P, limit_ns, status, 200);
+    if (threadIdx.x == 0) {
+        float total = 0.f;
+        if (ok) {
+            const float* vals = reinterpret_cast<const float*>(my_ctrl + NORM_VAL_OFFSET);
+            for (int r = 0; r < P; r++) total += ld_volatile_f32(vals + r);
+        } else {
+            total = NAN;
+        }
+        const float nv = sqrtf(total);
+        norm_out[0] = nv;
+        if (!isfinite(nv)) {
+            scale_out[0] = 0.f;
+            if (flag_out) flag_out[0] = 1;
+        } else {
+            scale_out[0] = (clip > 0.f && nv > clip) ? clip / nv : 1.0f;
+            if (flag_out) flag_out[0] = 0;
+        }
+    }
+}
+
+struct AdamArgs {
+    float lr, beta1, beta2, inv_b1c, inv_b2c, eps, wd;
+    unsigned int seed;
+};
+
+// Segment table int64[nseg][4] = (parameter offset in the flat buffer, state offset, length, flags).
+// The averaged fp32 gradient of element i of a segment is gshard[state offset + i].
+__global__ void __launch_bounds__(TPB)
+adamw_push_kernel(Peers params, float* __restrict__ master, const float* __restrict__ gshard, float* __restrict__ m,
+                  float* __restrict__ v, const long long* __restrict__ segs, const float* __restrict__ grad_scale_ptr, int P,
+                  int my_rank, AdamArgs a) {
+    const long long* seg = segs + (size_t)blockIdx.y * 4;
+    const size_t p_off = (size_t)seg[0], s_off = (size_t)seg[1], len = (size_t)seg[2];
+    const float wd = (seg[3] & 1) ? a.wd : 0.f;
+    const float gs = grad_scale_ptr ? grad_scale_ptr[0] : 1.0f;
+    const bf16* my_params = static_cast<const bf16*>(params.p[my_rank]);
+    for (size_t i = ((size_t)blockIdx.x * TPB + threadIdx.x) * 8; i < len; i += (size_t)gridDim.x * TPB * 8) {
+        float g[8], mm[8], vv[8], old[8], pn[8];
+        const float4* gp = reinterpret_cast<const float4*>(gshard + s_off + i);
+        const float4* mp = reinterpret_cast<const float4*>(m + s_off + i);
+        const float4* vp = reinterpret_cast<const float4*>(v + s_off + i);
+        float4 t0 = gp[0], t1 = gp[1];
+        g[0] = t0.x; g[1] = t0.y; g[2] = t0.z; g[3] = t0.w; g[4] = t1.x; g[5] = t1.y; g[6] = t1.z; g[7] = t1.w;
+        t0 = mp[0]; t1 = mp[1];
+        mm[0] = t0.x; mm[1] = t0.y; mm[2] = t0.z; mm[3] = t0.w; mm[4] = t1.x; mm[5] = t1.y; mm[6] = t1.z; mm[7] = t1.w;
+        t0 = vp[0]; t1 = vp[1];
+        vv[0] = t0.x; vv[1] = t0.y; vv[2] = t0.z; vv[3] = t0.w; vv[4] = t1.x; vv[5] = t1.y; vv[6] = t1.z; vv[7] = t1.w;
+        if (master) {
+            const float4* op = reinterpret_cast<const float4*>(master + s_off + i);
+            t0 = op[0]; t1 = op[1];
+            old[0] = t0.x; old[1] = t0.y; old[2] = t0.z; old[3] = t0.w; old[4] = t1.x; old[5] = t1.y; old[6] = t1.z; old[7] = t1.w;
+        } else {
+            unpack8(ld128(my_params + p_off + i), old);
+        }
+        bf16x8 outv;
+        bf16* out = reinterpret_cast<bf16*>(&outv);
+#pragma unroll
+        for (int j = 0; j < 8; j++) {
+            const float gj = gs * g[j];
+            mm[j] = a.beta1 * mm[j] + (1.0f - a.beta1) * gj;
+            vv[j] = a.beta2 * vv[j] + (1.0f - a.beta2) * gj * gj;
+            const float mh = mm[j] * a.inv_b1c, vh = vv[j] * a.inv_b2c;
+            pn[j] = old[j] - a.lr * (mh / (sqrtf(vh) + a.eps) + wd * old[j]);
+            out[j] = sr_round(pn[j], squirrel5((unsigned int)(p_off + i + j), a.seed));
+        }
+        float4* mo = reinterpret_cast<float4*>(m + s_off + i);
+        float4* vo = reinterpret_cast<float4*>(v + s_off + i);
+        mo[0] = make_float4(mm[0], mm[1], mm[2], mm[3]); mo[1] = make_float4(mm[4], mm[5], mm[6], mm[7]);
+        vo[0] = make_float4(vv[0], vv[1], vv[2], vv[3]); vo[1] = make_float4(vv[4], vv[5], vv[6], vv[7]);
+        if (master) {
+            float4* po = reinterpret_cast<float4*>(master + s_off + i);
+            po[0] = make_float4(pn[0], pn[1], pn[2], pn[3]); po[1] = make_float4(pn[4], pn[5], pn[6], pn[7]);
+        }
+        // the all-gather: the updated shard goes to every rank's full parameter buffer
+#pragma unroll
+        for (int r = 0; r < MAXP; r++)
+            if (r < P) st128(static_cast<bf16*>(params.p[r]) + p_off + i, outv);
+    }
+}
+
+static inline Peers make_peers(const long long* ptrs, int P) {
+    Peers q;
+    for (int i = 0; i < MAXP; i++) q.p[i] = i < P ? reinterpret_cast<void*>(ptrs[i]) : nullptr;
+    return q;
+}
+
+}  // namespace comm
+}  // namespace llmk
+
+using namespace llmk;
+using namespace llmk::comm;
+
+LLMK_API int llmk_comm_max_ranks() { return MAXP; }
+LLMK_API int llmk_comm_ctrl_ints() { return CTRL_INTS; }
+
+// `ptrs`: host array of P device pointers (one per rank, this rank's own included).
+LLMK_API int llmk_comm_signal(const long long* ctrl_ptrs, int slot, int my_rank, int P, int epoch, void* stream) {
+    if (P > MAXP || slot < 0 || (slot + 1) * MAXP > NORM_VAL_OFFSET) return LLMK_ERR_SHAPE;
+    signal_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(make_peers(ctrl_ptrs, P), slot, my_rank, P, epoch);
+    LLMK_LAUNCH_CHECK();
+    return LLMK_OK;
+}
+
+LLMK_API int llmk_comm_wait(const void* my_ctrl, int slot, int epoch, int P, long limit_ns, int* status, void* stream) {
+    if (P > MAXP || slot < 0 || (slot + 1) * MAXP > NORM_VAL_OFFSET) return LLMK_ERR_SHAPE;
+    wait_kernel<<<1, 32, 0, (cudaStream_t)stream>>>((const int*)my_ctrl, slot, epoch, P, (long long)limit_ns, status);
+    LLMK_LAUNCH_CHECK();
+    return LLMK_OK;
+}
+
+// Reduce-scatter + 1/P scale + norm partials for one bucket. norm_partials must hold nseg * grid_x floats.
+LLMK_API int llmk_comm_rs_bucket(const long long* grad_ptrs, const void* my_ctrl, int slot, int epoch, const void* segs, int nseg,
+                                 void* gshard, void* norm_partials, int grid_x, int P, long limit_ns, int* status, void* stream) {
+    if (P > MAXP || nseg <= 0 || grid_x <= 0) return LLMK_ERR_SHAPE;
+    dim3 grid(grid_x, nseg);
+    rs_bucket_kernel<<<grid, TPB, 0, (cudaStream_t)stream>>>(make_peers(grad_ptrs, P), (const int*)my_ctrl, slot, epoch,
+                                                            (const long long*)segs, (float*)gshard, (float*)norm_partials, P,
+                                                            1.0f / (float)P, (long long)limit_ns, status);
+    LLMK_LAUNCH_CHECK();
+    return LLMK_OK;
+}
+
+LLMK_API int llmk_comm_norm_exchange(const long long* ctrl_ptrs, const void* partials, int n, int norm_slot, int my_rank, int P,
+                                     int epoch, float clip, void* scale_out, void* norm_out, void* flag_out, long limit_ns,
+                                     int* status, void* stream) {
+    if (P > MAXP) return LLMK_ERR_SHAPE;
+    norm_exchange_kernel<<<1, 1024, 0, (cudaStream_t)stream>>>(make_peers(ctrl_ptrs, P), (const float*)partials, n, norm_slot,
+                                                              my_rank, P, epoch, clip, (float*)scale_out, (float*)norm_out,
+                                                              (int*)flag_out, (long long)limit_ns, status);
+    LLMK_LAUNCH_CHECK();
+    return LLMK_OK;
+}
+
+LLMK_API int llmk_comm_adamw_push(const long long* param_ptrs, void* master, const void* gshard, void* m, void* v, const void* segs,
+                                  int nseg, long max_len, float lr, float beta1, float beta2, float beta1_corr, float beta2_corr,
+                                  float eps, float wd, const void* grad_scale_ptr, unsigned int seed, int P, int my_rank,
+                                  void* stream) {
+    if (P > MAXP || nseg <= 0) return LLMK_ERR_SHAPE;
+    AdamArgs a{lr, beta1, beta2, 1.0f / beta1_corr, 1.0f / beta2_corr, eps, wd, seed};
+    long gx = (max_len + TPB * 8 - 1) / (TPB * 8);
+    if (gx > 512) gx = 512;
+    if (gx < 1) gx = 1;
+    dim3 grid((unsigned)gx, nseg);
+    adamw_push_kernel<<<grid, TPB, 0, (cudaStream_t)stream>>>(make_peers(param_ptrs, P), (float*)master, (const float*)gshard,
+                                                             (float*)m, (float*)v, (const long long*)segs,
+                                                             (const float*)grad_scale_ptr, P, my_rank, a);
+    LLMK_LAUNCH_CHECK();
+    return LLMK_OK;
+}

@@ -131,13 +131,19 @@ class Trainer:
     def accumulate(self, micro_batches) -> int:
         """zero grads, run forward/backward over the micro-batches, start bucket reductions."""
         model = self.model
-        model.zero_grad()
+        self.begin_step()
         batches = list(micro_batches)
         accum = len(batches)
         for i, (x, y) in enumerate(batches):
             model.forward(x, y, grad_accum_steps=accum, micro_step=i)
             model.backward(last_micro_step=(i == accum - 1), bucket_ready=self._bucket_ready)
         return accum
+
+    def begin_step(self) -> None:
+        """Start of an optimizer step: wait for the peers (fused communication) and zero the gradients."""
+        if getattr(self.comm, "fused", False):
+            self.comm.begin_step()
+        self.model.zero_grad()
 
     def _bucket_ready(self, layer) -> None:
         self.comm.reduce_bucket(self.model.grads, layer)
@@ -147,10 +153,14 @@ class Trainer:
         sync). With ``skip`` the optimizer part is left out; :meth:`apply_update` can run it later."""
         self.comm.finish_reduce()
         self.comm.all_reduce_scalar(self.model.acts["loss_acc"], "avg")
-        self._local_norm2()
-        if self.plan.sharded:
-            self.comm.all_reduce_scalar(self.norm2, "sum")
-        self._clip()
+        if getattr(self.comm, "fused", False):
+            # the bucket kernels already left the norm partials of the averaged shard
+            self.comm.norm_and_clip(self.grad_clip, self.scale, self.norm, self.flag)
+        else:
+            self._local_norm2()
+            if self.plan.sharded:
+                self.comm.all_reduce_scalar(self.norm2, "sum")
+            self._clip()
         if not skip:
             self.apply_update(lr)
 
@@ -159,8 +169,12 @@ class Trainer:
         self._ensure_master()
         self.rng_state_last_update = self.rng.state
         seed = self.rng.u32()
-        self._adamw(lr, seed)
-        self.comm.gather_params(self.model.params)
+        if getattr(self.comm, "fused", False):
+            self.comm.adamw_push(self.master, self.m, self.v, lr, self.beta1, self.beta2, self.step_count + 1, self.eps,
+                                 self.wd, self.scale, seed)
+        else:
+            self._adamw(lr, seed)
+            self.comm.gather_params(self.model.params)
         self.step_count += 1
 
     def read_scalars(self) -> tuple[float, float, bool]:

@@ -1,0 +1,101 @@
+"""Worker process for the multi-rank tests (spawned by test_dist_cpu.py / test_dist_gpu.py).
+
+argv: mode out_dir  (rank / world / rendezvous come from the environment set by the test).
+modes:
+  cpu_zero<k>      gloo, PyTorch oracle model in fp32, ZeRO stage k, library collectives
+  gpu_library<k>   NCCL, CUDA model, ZeRO stage k, library collectives
+  gpu_fused        NCCL bootstrap, CUDA model, ZeRO-1 through the fused peer-memory kernels
+  cpu_fail_rank1   gloo; rank 1 raises before its first collective (failure-detection test)
+Each rank writes ``rank<r>.pt`` with its per-step losses / norms and a parameter checksum sample.
+"""
+import datetime
+import os
+import sys
+
+import torch
+import torch.distributed as dist
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+
+from llm_kittens_b200.models.config import ModelConfig  # noqa: E402
+from llm_kittens_b200.parallel.comm import LibraryComm  # noqa: E402
+from llm_kittens_b200.parallel.zero import ZeroPlan  # noqa: E402
+from llm_kittens_b200.runtime.trainer import Trainer  # noqa: E402
+
+
+def tiny_config():
+    return ModelConfig(family="gpt2", max_seq_len=64, vocab_size=512, padded_vocab_size=512, num_layers=2, num_heads=2,
+                       num_kv_heads=2, channels=128, hidden_dim=512)
+
+
+def global_batches(cfg, steps, world, B, T):
+    g = torch.Generator().manual_seed(1234)
+    out = []
+    for _ in range(steps):
+        x = torch.randint(0, cfg.vocab_size, (world * B, T), generator=g, dtype=torch.int32)
+        y = torch.randint(0, cfg.vocab_size, (world * B, T), generator=g, dtype=torch.int32)
+        out.append((x, y))
+    return out
+
+
+def main():
+    mode, out_dir = sys.argv[1], sys.argv[2]
+    rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+    cpu = mode.startswith("cpu")
+    timeout = datetime.timedelta(seconds=int(os.environ.get("LLMK_TEST_PG_TIMEOUT", "120")))
+    if cpu:
+        dist.init_process_group("gloo", timeout=timeout)
+        device = torch.device("cpu")
+    else:
+        torch.cuda.set_device(rank)
+        device = torch.device("cuda", rank)
+        dist.init_process_group("nccl", device_id=device, timeout=timeout)
+    if mode == "cpu_fail_rank1":
+        if rank == 1:
+            raise RuntimeError("injected failure on rank 1 before its first collective")
+        t = torch.ones(1)
+        try:
+            dist.all_reduce(t)  # the peer never joins: the short process-group timeout ends this with an error
+            outcome = "completed"
+        except Exception as e:  # noqa: BLE001
+            outcome = "error:" + type(e).__name__
+        torch.save({"outcome": outcome}, os.path.join(out_dir, f"rank{rank}.pt"))
+        os._exit(0)
+    cfg = tiny_config()
+    B, T, steps = 2, 64, 4
+    stage = int(mode[-1]) if mode[-1].isdigit() else 1
+    if cpu:
+        from llm_kittens_b200.oracle.torch_model import TorchTransformer
+
+        model = TorchTransformer(cfg, device=device, dtype=torch.float32)
+    else:
+        from llm_kittens_b200.models.transformer import Transformer
+
+        model = Transformer(cfg, device=device, recompute=0)
+    model.init_weights(42)
+    plan = ZeroPlan(cfg, world, rank, stage)
+    if mode == "gpu_fused":
+        from llm_kittens_b200.parallel.fused import FusedComm
+
+        comm = FusedComm(plan, model, device, timeout_ms=20000)
+    else:
+        comm = LibraryComm(plan, None, device)
+    trainer = Trainer(model, zero_stage=stage, use_master_weights=True, learning_rate=1e-3, weight_decay=0.1, comm=comm,
+                      num_processes=world, rank=rank)
+    losses, norms = [], []
+    for x, y in global_batches(cfg, steps, world, B, T):
+        xs, ys = x[rank * B:(rank + 1) * B].contiguous(), y[rank * B:(rank + 1) * B].contiguous()
+        r = trainer.train_step([(xs, ys)])
+        losses.append(r.loss)
+        norms.append(r.grad_norm)
+    if not cpu:
+        from llm_kittens_b200.ops import _native
+
+        _native.check_status()
+    torch.save({"losses": losses, "norms": norms, "params": model.params.float().cpu()}, os.path.join(out_dir, f"rank{rank}.pt"))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,79 @@
+"""Multi-process tests of the ZeRO / trainer logic on CPU ranks (gloo, world size 2): every stage must
+train exactly like one process that sees the whole global batch; a rank that fails on the host is
+detected by the others through the process-group timeout (no GPU involved)."""
+import os
+import socket
+import subprocess
+import sys
+
+import pytest
+import torch
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+
+
+def free_port():
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    p = s.getsockname()[1]
+    s.close()
+    return p
+
+
+def launch(mode, out_dir, world=2, extra_env=None, timeout=300):
+    port = free_port()
+    procs = []
+    for r in range(world):
+        env = dict(os.environ, RANK=str(r), WORLD_SIZE=str(world), MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port),
+                   LOCAL_RANK=str(r), OMP_NUM_THREADS="2")
+        env.update(extra_env or {})
+        procs.append(subprocess.Popen([sys.executable, os.path.join(HERE, "dist_worker.py"), mode, str(out_dir)], env=env,
+                                      stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True))
+    outs = []
+    for p in procs:
+        try:
+            out, _ = p.communicate(timeout=timeout)
+        except subprocess.TimeoutExpired:
+            p.kill()
+            out, _ = p.communicate()
+        outs.append((p.returncode, out))
+    return outs
+
+
+def single_process_reference(steps=4):
+    sys.path.insert(0, HERE)
+    from dist_worker import global_batches, tiny_config
+    from llm_kittens_b200.oracle.torch_model import TorchTransformer
+    from llm_kittens_b200.runtime.trainer import Trainer
+
+    cfg = tiny_config()
+    model = TorchTransformer(cfg, device="cpu", dtype=torch.float32)
+    model.init_weights(42)
+    tr = Trainer(model, learning_rate=1e-3, weight_decay=0.1)
+    losses = []
+    for x, y in global_batches(cfg, steps, 2, 2, 64):
+        # two micro-batches of the rank-local size == the data-parallel average over two ranks
+        losses.append(tr.train_step([(x[:2], y[:2]), (x[2:], y[2:])]).loss)
+    return losses, model.params.clone()
+
+
+@pytest.mark.parametrize("stage", [0, 1, 2, 3])
+def test_zero_stages_match_single_process(tmp_path, stage):
+    outs = launch(f"cpu_zero{stage}", tmp_path)
+    for rc, out in outs:
+        assert rc == 0, out
+    ref_losses, ref_params = single_process_reference()
+    r0, r1 = torch.load(tmp_path / "rank0.pt"), torch.load(tmp_path / "rank1.pt")
+    assert torch.equal(r0["params"], r1["params"])  # replicas stay identical
+    for a, b in zip(r0["losses"], ref_losses):
+        assert abs(a - b) < 1e-4
+    assert r0["losses"] == r1["losses"] and r0["norms"] == r1["norms"]
+    assert (r0["params"] - ref_params).abs().max().item() < 1e-5
+    assert r0["losses"][-1] < r0["losses"][0]
+
+
+def test_failed_rank_is_detected_by_the_survivor(tmp_path):
+    outs = launch("cpu_fail_rank1", tmp_path, extra_env={"LLMK_TEST_PG_TIMEOUT": "5"}, timeout=120)
+    assert outs[1][0] != 0 and "injected failure" in outs[1][1]
+    survivor = torch.load(tmp_path / "rank0.pt")
+    assert survivor["outcome"].startswith("error:")

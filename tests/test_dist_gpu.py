@@ -1,0 +1,41 @@
+"""Two-GPU tests (skipped when fewer than two GPUs are visible): the fused peer-memory communication
+path must train like the library-collective path and like ZeRO-0, within bf16 tolerance."""
+import os
+import sys
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+HERE = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, HERE)
+
+
+def _need_two_gpus():
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+
+
+def _run(mode, tmp_path):
+    from test_dist_cpu import launch
+
+    d = tmp_path / mode
+    d.mkdir()
+    outs = launch(mode, d, extra_env={"NCCL_NVLS_ENABLE": "0", "TORCH_SYMM_MEM_DISABLE_MULTICAST": "1"})
+    for rc, out in outs:
+        assert rc == 0, out[-3000:]
+    return torch.load(d / "rank0.pt"), torch.load(d / "rank1.pt")
+
+
+def test_fused_comm_matches_library_and_zero0(tmp_path):
+    _need_two_gpus()
+    f0, f1 = _run("gpu_fused", tmp_path)
+    l0, l1 = _run("gpu_library1", tmp_path)
+    z0, _ = _run("gpu_library0", tmp_path)
+    assert torch.equal(f0["params"], f1["params"]) and torch.equal(l0["params"], l1["params"])
+    for a, b, c in zip(f0["losses"], l0["losses"], z0["losses"]):
+        assert abs(a - b) < 0.02 and abs(a - c) < 0.02
+    for a, b in zip(f0["norms"], l0["norms"]):
+        assert abs(a - b) < 0.03 * max(1.0, b)
+    assert (f0["params"] - l0["params"]).abs().max().item() < 0.02
+    assert f0["losses"][-1] < f0["losses"][0]
