@@ -1,0 +1,181 @@
+"""GPT-2 shaped transformer whose MLP is a top-k mixture of GELU experts, with expert parallelism.
+
+The reference has no MoE model, only un-wired primitives (llmc/moe.cuh, llmc/gemm_ext.cuh:132-158,
+llmc/distributed_ext.cuh:27-48, llmc/losses.cuh:522-559); the model is defined here from their
+semantics:
+
+* router ``logits = ln2 . Wr^T`` (fp32), softmax over E, top-k, weights renormalised to sum 1;
+* capacity ``cap = ceil(capacity_factor * k * tokens_per_rank / E)`` rows per (source rank, expert);
+  assignments beyond it are dropped in deterministic (token, k) order;
+* dispatch / combine are direct row stores / loads through a table of peer pointers: rank r owns
+  experts ``[r*E/P, (r+1)*E/P)`` and receives rows in ``recv[e_local][src][cap][C]``; padded slots are
+  zeroed by the sender. With one process the same kernels run on a single-entry table;
+* expert ``y = GELU(x W1^T + b1) W2^T + b2`` = two tcgen05 GEMMs per local expert on its row block;
+* output ``res3 = res2 + sum_k w_k y_k``; auxiliary loss ``coef * E * sum_e density_e^2`` (density =
+  mean router probability per expert on this rank) is added to the reported loss and to the router
+  gradient.
+
+Dense parameters (attention, norms, router, embeddings) are data-parallel (ZeRO like the dense
+models); expert parameters are owned by one rank each and are neither reduced nor gathered.
+"""
+from __future__ import annotations
+
+import torch
+
+from ..ops import elementwise as ew
+from ..ops import gemm
+from ..ops import moe as moe_ops
+from .config import ModelConfig
+from .transformer import BF16, Transformer
+
+
+class LocalExchange:
+    """Single-process stand-in for the expert-parallel exchange: buffers are ordinary tensors, the
+    pointer tables have one entry, and the signal / wait steps are no-ops."""
+
+    world_size, rank = 1, 0
+
+    def alloc(self, numel: int, device) -> tuple[torch.Tensor, object]:
+        t = torch.zeros(numel, dtype=BF16, device=device)
+        return t, moe_ops.ptr_table([t])
+
+    def sync(self, tag: int) -> None:
+        pass
+
+
+class MoETransformer(Transformer):
+    def __init__(self, config: ModelConfig, device="cuda", recompute: int = 0, exchange=None, **kw):
+        if config.family != "moe":
+            raise ValueError("MoETransformer needs a 'moe' configuration")
+        super().__init__(config, device=device, recompute=min(int(recompute), 2), **kw)
+        self.exchange = exchange if exchange is not None else LocalExchange()
+        self.E, self.K = config.num_experts, config.top_k
+        self.P, self.ep_rank = self.exchange.world_size, self.exchange.rank
+        if self.E % self.P != 0:
+            raise ValueError(f"{self.E} experts cannot be split over {self.P} expert-parallel ranks")
+        self.Eloc = self.E // self.P
+
+    # ------------------------------------------------------------------ activations
+    def allocate(self, B: int, T: int) -> None:
+        if (B, T) == (self.B, self.T) and self.acts is not None:
+            return
+        super().allocate(B, T)
+        cfg, a, dev = self.config, self.acts, self.device
+        N, C, H, L = B * T, cfg.channels, cfg.hidden_dim, cfg.num_layers
+        E, K, P, Eloc = self.E, self.K, self.P, self.Eloc
+        cap = int(-(-cfg.capacity_factor * K * N // E))
+        self.cap = cap = (cap + 7) // 8 * 8
+        rows = Eloc * P * cap                      # rows this rank's experts process per layer
+        self.rows = rows
+        f32, i32 = torch.float32, torch.int32
+        a["probs"] = torch.empty(L, N, E, dtype=f32, device=dev)
+        a["top_idx"] = torch.empty(L, N, K, dtype=i32, device=dev)
+        a["top_w"] = torch.empty(L, N, K, dtype=f32, device=dev)
+        a["slot"] = torch.empty(L, N, K, dtype=i32, device=dev)
+        a["counts"] = torch.empty(L, E, dtype=i32, device=dev)
+        a["density"] = torch.empty(L, E, dtype=f32, device=dev)
+        a["aux_acc"] = torch.zeros(1, dtype=f32, device=dev)
+        a["dw"] = torch.empty(N, K, dtype=f32, device=dev)
+        a["dlogits"] = torch.empty(N, (E + 7) // 8 * 8, dtype=BF16, device=dev)
+        Lg = 1 if self.recompute >= 1 else L
+        a["hid_pre"] = torch.empty(L, rows, H, dtype=BF16, device=dev)
+        a["hid_act"] = torch.empty(Lg, rows, H, dtype=BF16, device=dev)
+        a["y_loc"] = torch.empty(rows, C, dtype=BF16, device=dev)        # expert outputs / input grads before return
+        a["d_hid"] = torch.empty(rows, H, dtype=BF16, device=dev)
+        # exchange buffers (symmetric memory when expert-parallel)
+        self.recv_x, self.recv_x_ptrs = [], []
+        self.back_y, self.back_y_ptrs = [], []
+        for _ in range(L):
+            t, p = self.exchange.alloc(rows * C, dev)
+            self.recv_x.append(t.view(rows, C))
+            self.recv_x_ptrs.append(p)
+            t, p = self.exchange.alloc(E * cap * C, dev)
+            self.back_y.append(t.view(E * cap, C))
+            self.back_y_ptrs.append(p)
+        t, self.recv_dy_ptrs = self.exchange.alloc(rows * C, dev)
+        self.recv_dy = t.view(rows, C)
+        t, self.back_dx_ptrs = self.exchange.alloc(E * cap * C, dev)
+        self.back_dx = t.view(E * cap, C)
+
+    def _dense_mlp_buffers(self) -> bool:
+        return False
+
+    # ------------------------------------------------------------------ MLP = mixture of experts
+    def _expert_views(self, l: int, el: int):
+        e = self.ep_rank * self.Eloc + el
+        p, g = self.p, self.g
+        return (p["fcw"][l][e], p["fcb"][l][e], p["fcprojw"][l][e], p["fcprojb"][l][e],
+                g["fcw"][l][e], g["fcb"][l][e], g["fcprojw"][l][e], g["fcprojb"][l][e])
+
+    def _mlp_forward(self, l, k, gi, ln2, res2, out):
+        a, p, cfg = self.acts, self.p, self.config
+        E, K, P, cap = self.E, self.K, self.P, self.cap
+        moe_ops.router_fwd(ln2, p["routerw"][l], K, a["probs"][l], a["top_idx"][l], a["top_w"][l])
+        moe_ops.assign_slots(a["top_idx"][l], E, cap, a["slot"][l], a["counts"][l])
+        moe_ops.density(a["probs"][l], cfg.aux_loss_coef * self._loss_scale, a["density"][l], a["aux_acc"], accumulate=True)
+        moe_ops.dispatch(self.recv_x_ptrs[l], ln2, a["top_idx"][l], a["slot"][l], a["top_w"][l], a["counts"][l], E, cap,
+                         self.ep_rank, P, scale_by_weight=False)
+        self.exchange.sync(4 * l + 0)
+        per = P * cap
+        act_l = a["hid_act"][0 if self.recompute >= 1 else l]
+        for el in range(self.Eloc):
+            w1, b1, w2, b2 = self._expert_views(l, el)[:4]
+            rows = slice(el * per, (el + 1) * per)
+            gemm.gemm_nt(self.recv_x[l][rows], w1, bias=b1, out=act_l[rows], gelu_pre_out=a["hid_pre"][l][rows])
+            gemm.gemm_nt(act_l[rows], w2, bias=b2, out=a["y_loc"][rows])
+        moe_ops.return_rows(self.back_y_ptrs[l], a["y_loc"], cfg.channels, E, cap, self.ep_rank, P)
+        self.exchange.sync(4 * l + 1)
+        moe_ops.combine(out, res2, self.back_y[l], a["top_idx"][l], a["slot"][l], a["top_w"][l], cap)
+
+    def _mlp_backward(self, l, k, gi, dres, d_ln2, ln2):
+        a, p, g, cfg = self.acts, self.p, self.g, self.config
+        E, K, P, cap, C = self.E, self.K, self.P, self.cap, cfg.channels
+        N = self.B * self.T
+        idx, slot, w = a["top_idx"][l], a["slot"][l], a["top_w"][l]
+        moe_ops.combine_dweight(dres, self.back_y[l], idx, slot, cap, dw=a["dw"])
+        moe_ops.dispatch(self.recv_dy_ptrs, dres, idx, slot, w, a["counts"][l], E, cap, self.ep_rank, P, scale_by_weight=True)
+        self.exchange.sync(4 * l + 2)
+        per = P * cap
+        act_l = a["hid_act"][0 if self.recompute >= 1 else l]
+        for el in range(self.Eloc):
+            w1, b1, w2, b2, gw1, gb1, gw2, gb2 = self._expert_views(l, el)
+            rows = slice(el * per, (el + 1) * per)
+            dy, x = self.recv_dy[rows], self.recv_x[l][rows]
+            if self.recompute >= 1:
+                ew.gelu_fwd(a["hid_pre"][l][rows], out=act_l[rows])
+            gemm.gemm_tn(dy, act_l[rows], out=gw2, accumulate=True)
+            ew.dbias(gb2, dy, accumulate=True)
+            gemm.gemm_nn(dy, w2, out=a["d_hid"][rows], dgelu_of=a["hid_pre"][l][rows])
+            gemm.gemm_tn(a["d_hid"][rows], x, out=gw1, accumulate=True)
+            ew.dbias(gb1, a["d_hid"][rows], accumulate=True)
+            gemm.gemm_nn(a["d_hid"][rows], w1, out=a["y_loc"][rows])
+        moe_ops.return_rows(self.back_dx_ptrs, a["y_loc"], C, E, cap, self.ep_rank, P)
+        self.exchange.sync(4 * l + 3)
+        moe_ops.combine(d_ln2, None, self.back_dx, idx, slot, None, cap)
+        # router: gradient through the renormalised top-k weights plus the load-balance term
+        aux_scale = cfg.aux_loss_coef * E * 2.0 / N * self._loss_scale
+        dlog = moe_ops.router_bwd(a["probs"][l], idx, w, a["dw"], slot, a["density"][l], aux_scale, dlogits=a["dlogits"])
+        if E % 8 == 0:
+            gemm.gemm_tn(dlog, ln2, out=g["routerw"][l], accumulate=True)
+            gemm.gemm_nn(dlog, p["routerw"][l], out=d_ln2, add=d_ln2)
+        else:  # expert counts that are not a multiple of 8 take the (tiny) library path
+            dl = dlog[:, :E].float()
+            g["routerw"][l].add_((dl.T @ ln2.float()).to(BF16))
+            d_ln2.add_((dl @ p["routerw"][l].float()).to(BF16))
+
+    # ------------------------------------------------------------------ forward wrapper: aux-loss bookkeeping
+    def forward(self, tokens, targets=None, grad_accum_steps: int = 1, micro_step: int = 0, compute_dlogits: bool = True):
+        self.allocate(*tokens.shape)
+        self._loss_scale = 1.0 / grad_accum_steps
+        if micro_step == 0:
+            self.acts["aux_acc"].zero_()
+        super().forward(tokens, targets, grad_accum_steps, micro_step, compute_dlogits)
+        if targets is not None:
+            # reported loss = cross-entropy + auxiliary load-balance loss (both already scaled by 1/accum)
+            self.acts["loss_total"] = self.acts["loss_acc"] + self.acts["aux_acc"]
+
+    def mean_loss(self) -> float:
+        return float(self.acts["loss_acc"].item())
+
+    def aux_loss(self) -> float:
+        return float(self.acts["aux_acc"].item())

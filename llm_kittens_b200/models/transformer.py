@@ -40,7 +40,7 @@ BF16 = torch.bfloat16
 class Transformer:
     def __init__(self, config: ModelConfig, device: str | torch.device = "cuda", recompute: int = 1,
                  rope_interleaved: bool = True):
-        if config.family not in ("gpt2", "llama3"):
+        if config.family not in ("gpt2", "llama3") and type(self) is Transformer:
             raise ValueError("Transformer handles the dense families; use models.moe.MoETransformer for 'moe'")
         self.config = config
         self.device = torch.device(device)
@@ -128,7 +128,7 @@ class Transformer:
             a["up"] = e(Lk, BT, H)
             a["gate"] = e(Lk, BT, H)
             a["act"] = e(Lg, BT, H)
-        else:
+        elif self._dense_mlp_buffers():
             a["fch"] = e(Lk, BT, H)
             a["act"] = e(Lg, BT, H)
         a["lnf"] = e(BT, C)
@@ -147,6 +147,10 @@ class Transformer:
         self.acts = a
         self.tokens = torch.zeros(B, T, dtype=torch.int32, device=dev)
         self.targets = torch.zeros(B, T, dtype=torch.int32, device=dev)
+
+    def _dense_mlp_buffers(self) -> bool:
+        """Whether the dense-MLP activation buffers are needed (a subclass with another MLP says no)."""
+        return True
 
     def activation_bytes(self) -> int:
         return sum(t.numel() * t.element_size() for t in self.acts.values() if isinstance(t, torch.Tensor))
@@ -192,16 +196,50 @@ class Transformer:
         res2 = a["res2"][k]
         gemm.gemm_nt(a["atty"][k], p["attprojw"][l], bias=None if self.is_llama else p["attprojb"][l], out=res2, add=x)
         self._norm_fwd(res2, p["ln2w"][l], None if self.is_llama else p["ln2b"][l], ln2, mean2, a["ln2_rstd"][k])
+        self._mlp_forward(l, k, gi, ln2, res2, a["res3"][k])
+        return a["res3"][k]
+
+    def _mlp_forward(self, l: int, k: int, gi: int, ln2: torch.Tensor, res2: torch.Tensor, out: torch.Tensor) -> None:
+        """``out = res2 + MLP(ln2)`` for block ``l`` (dense GELU MLP or SwiGLU)."""
+        a, p = self.acts, self.p
         act = a["act"][gi]
         if self.is_llama:
             gemm.gemm_nt(ln2, p["fcw_up"][l], out=a["up"][k])
             gemm.gemm_nt(ln2, p["fcw_gate"][l], out=a["gate"][k])
             ew.swiglu_fwd(a["gate"][k], a["up"][k], out=act)
-            gemm.gemm_nt(act, p["fcprojw"][l], out=a["res3"][k], add=res2)
+            gemm.gemm_nt(act, p["fcprojw"][l], out=out, add=res2)
         else:
             gemm.gemm_nt(ln2, p["fcw"][l], bias=p["fcb"][l], out=act, gelu_pre_out=a["fch"][k])
-            gemm.gemm_nt(act, p["fcprojw"][l], bias=p["fcprojb"][l], out=a["res3"][k], add=res2)
-        return a["res3"][k]
+            gemm.gemm_nt(act, p["fcprojw"][l], bias=p["fcprojb"][l], out=out, add=res2)
+
+    def _mlp_backward(self, l: int, k: int, gi: int, dres: torch.Tensor, d_ln2: torch.Tensor, ln2: torch.Tensor) -> None:
+        """Backward of ``res3 = res2 + MLP(ln2)``: given ``dres`` = d(res3), accumulate the MLP weight
+        gradients and write d(ln2) into ``d_ln2`` (the residual path keeps ``dres`` as is)."""
+        a, p, g = self.acts, self.p, self.g
+        BT, H = self.B * self.T, self.config.hidden_dim
+        act = a["act"][gi]
+        if self.is_llama:
+            if 1 <= self.recompute < 3:
+                ew.swiglu_fwd(a["gate"][k], a["up"][k], out=act)
+            d_act = a["d_wide"].view(-1)[: BT * H].view(BT, H)
+            gemm.gemm_nn(dres, p["fcprojw"][l], out=d_act)
+            gemm.gemm_tn(dres, act, out=g["fcprojw"][l], accumulate=True)
+            d_gate, d_up = a["d_wide2"], d_act
+            ew.swiglu_bwd(d_act, a["gate"][k], a["up"][k], dgate=d_gate, dup=d_up)
+            gemm.gemm_nn(d_up, p["fcw_up"][l], out=d_ln2)
+            gemm.gemm_nn(d_gate, p["fcw_gate"][l], out=d_ln2, add=d_ln2)
+            gemm.gemm_tn(d_up, ln2, out=g["fcw_up"][l], accumulate=True)
+            gemm.gemm_tn(d_gate, ln2, out=g["fcw_gate"][l], accumulate=True)
+        else:
+            if 1 <= self.recompute < 3:
+                ew.gelu_fwd(a["fch"][k], out=act)
+            d_fch = a["d_wide"].view(-1)[: BT * H].view(BT, H)
+            gemm.gemm_tn(dres, act, out=g["fcprojw"][l], accumulate=True)
+            ew.dbias(g["fcprojb"][l], dres, accumulate=True)
+            gemm.gemm_nn(dres, p["fcprojw"][l], out=d_fch, dgelu_of=a["fch"][k])
+            gemm.gemm_nn(d_fch, p["fcw"][l], out=d_ln2)
+            gemm.gemm_tn(d_fch, ln2, out=g["fcw"][l], accumulate=True)
+            ew.dbias(g["fcb"][l], d_fch, accumulate=True)
 
     # ------------------------------------------------------------------ forward
     def forward(self, tokens: torch.Tensor, targets: torch.Tensor | None = None, grad_accum_steps: int = 1,
@@ -269,37 +307,14 @@ class Transformer:
                 if self.param_hook:
                     self.param_hook(l, "backward")
             k, n, gi = self._idx(l, "k"), self._idx(l, "n"), self._idx(l, "g")
-            ln1, ln2, act = a["ln1"][n], a["ln2"][n], a["act"][gi]
+            ln1, ln2 = a["ln1"][n], a["ln2"][n]
             mean1 = None if self.is_llama else a["ln1_mean"][k]
             mean2 = None if self.is_llama else a["ln2_mean"][k]
             res2 = a["res2"][k]
             # ---- MLP
-            if self.is_llama:
-                if 1 <= self.recompute < 3:
-                    ew.swiglu_fwd(a["gate"][k], a["up"][k], out=act)
-                if self.recompute == 2:
-                    self._norm_fwd(res2, p["ln2w"][l], None, ln2, None, a["ln2_rstd"][k])
-                d_act = a["d_wide"][:, :H] if a["d_wide"].shape[1] == H else a["d_wide"].view(-1)[: BT * H].view(BT, H)
-                gemm.gemm_nn(dres, p["fcprojw"][l], out=d_act)
-                gemm.gemm_tn(dres, act, out=g["fcprojw"][l], accumulate=True)
-                d_gate, d_up = a["d_wide2"], d_act
-                ew.swiglu_bwd(d_act, a["gate"][k], a["up"][k], dgate=d_gate, dup=d_up)
-                gemm.gemm_nn(d_up, p["fcw_up"][l], out=d_btc)
-                gemm.gemm_nn(d_gate, p["fcw_gate"][l], out=d_btc, add=d_btc)
-                gemm.gemm_tn(d_up, ln2, out=g["fcw_up"][l], accumulate=True)
-                gemm.gemm_tn(d_gate, ln2, out=g["fcw_gate"][l], accumulate=True)
-            else:
-                if 1 <= self.recompute < 3:
-                    ew.gelu_fwd(a["fch"][k], out=act)
-                if self.recompute == 2:
-                    self._norm_fwd(res2, p["ln2w"][l], p["ln2b"][l], ln2, mean2, a["ln2_rstd"][k])
-                d_fch = a["d_wide"].view(-1)[: BT * H].view(BT, H)
-                gemm.gemm_tn(dres, act, out=g["fcprojw"][l], accumulate=True)
-                ew.dbias(g["fcprojb"][l], dres, accumulate=True)
-                gemm.gemm_nn(dres, p["fcprojw"][l], out=d_fch, dgelu_of=a["fch"][k])
-                gemm.gemm_nn(d_fch, p["fcw"][l], out=d_btc)
-                gemm.gemm_tn(d_fch, ln2, out=g["fcw"][l], accumulate=True)
-                ew.dbias(g["fcb"][l], d_fch, accumulate=True)
+            if self.recompute == 2:
+                self._norm_fwd(res2, p["ln2w"][l], None if self.is_llama else p["ln2b"][l], ln2, mean2, a["ln2_rstd"][k])
+            self._mlp_backward(l, k, gi, dres, d_btc, ln2)
             self._norm_bwd(dres, g["ln2w"][l], None if self.is_llama else g["ln2b"][l], d_btc, res2, p["ln2w"][l], mean2,
                            a["ln2_rstd"][k], accumulate=True)
             # ---- attention

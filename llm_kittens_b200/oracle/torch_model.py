@@ -54,8 +54,40 @@ def causal_attention(q, k, v):
     return F.scaled_dot_product_attention(q, k, v, is_causal=True)
 
 
-def forward_logits(config: ModelConfig, p: dict, tokens: torch.Tensor, rope_interleaved: bool = True) -> torch.Tensor:
-    """``p``: name -> parameter view (any float dtype); ``tokens``: (B, T) integer; returns (B, T, Vp) logits."""
+def moe_mlp(cfg: ModelConfig, p: dict, l: int, h: torch.Tensor, aux: list) -> torch.Tensor:
+    """Top-k mixture of GELU experts with capacity dropping in (token, k) order; appends this layer's
+    load-balance loss ``coef * E * sum_e density_e^2`` to ``aux``. ``h``: (B, T, C)."""
+    B, T, C = h.shape
+    E, K = cfg.num_experts, cfg.top_k
+    x = h.reshape(-1, C)
+    N = x.shape[0]
+    probs = torch.softmax(F.linear(x.float(), p["routerw"][l].float()), dim=-1)
+    top_p, top_i = probs.topk(K, dim=-1)
+    w = top_p / top_p.sum(-1, keepdim=True)
+    cap = int(-(-cfg.capacity_factor * K * N // E))
+    cap = (cap + 7) // 8 * 8
+    onehot = F.one_hot(top_i.reshape(-1), E)                       # (N*K, E) in (token, k) order
+    slot = (onehot.cumsum(0) - 1)[torch.arange(N * K, device=x.device), top_i.reshape(-1)]
+    keep = (slot < cap).reshape(N, K)
+    out = torch.zeros_like(x)
+    for e in range(E):
+        sel = (top_i == e) & keep                                      # (N, K)
+        tok = sel.any(-1)
+        if tok.any():
+            xe = x[tok]
+            ye = F.linear(F.gelu(F.linear(xe, p["fcw"][l][e], p["fcb"][l][e]), approximate="tanh"), p["fcprojw"][l][e],
+                          p["fcprojb"][l][e])
+            we = (w * sel)[tok].sum(-1, keepdim=True).to(ye.dtype)
+            out[tok] += we * ye
+    density = probs.mean(0)
+    aux.append(cfg.aux_loss_coef * E * (density * density).sum())
+    return out.view(B, T, C)
+
+
+def forward_logits(config: ModelConfig, p: dict, tokens: torch.Tensor, rope_interleaved: bool = True,
+                   aux: list | None = None) -> torch.Tensor:
+    """``p``: name -> parameter view (any float dtype); ``tokens``: (B, T) integer; returns (B, T, Vp) logits.
+    For the MoE family the per-layer load-balance losses are appended to ``aux``."""
     cfg = config
     B, T = tokens.shape
     C, NH, NKVH, HS = cfg.channels, cfg.num_heads, cfg.num_kv_heads, cfg.head_size
@@ -85,6 +117,8 @@ def forward_logits(config: ModelConfig, p: dict, tokens: torch.Tensor, rope_inte
         if llama:
             m = F.silu(F.linear(h, p["fcw_gate"][l])) * F.linear(h, p["fcw_up"][l])
             x = x + F.linear(m, p["fcprojw"][l])
+        elif cfg.family == "moe":
+            x = x + moe_mlp(cfg, p, l, h, aux if aux is not None else [])
         else:
             m = F.gelu(F.linear(h, p["fcw"][l], p["fcb"][l]), approximate="tanh")
             x = x + F.linear(m, p["fcprojw"][l], p["fcprojb"][l])
@@ -150,7 +184,8 @@ class TorchTransformer:
         leaf = self.params.detach().clone().requires_grad_(need_grad)
         views = self.layout.views(leaf)
         with torch.set_grad_enabled(need_grad):
-            logits = forward_logits(cfg, views, tokens, self.rope_interleaved)
+            aux = []
+            logits = forward_logits(cfg, views, tokens, self.rope_interleaved, aux)
             self.logits = logits.detach()
             if targets is not None:
                 tgt = targets.to(self.device).long().view(-1)
@@ -160,7 +195,12 @@ class TorchTransformer:
                 loss = losses.mean() / grad_accum_steps
                 if micro_step == 0:
                     self.acts["loss_acc"].zero_()
+                    self.acts["aux_acc"] = torch.zeros(1, dtype=torch.float32, device=self.device)
                 self.acts["loss_acc"] += loss.detach()
+                if aux:   # mixture of experts: the load-balance loss joins the objective, not the reported CE
+                    aux_total = torch.stack(aux).sum() / grad_accum_steps
+                    self.acts["aux_acc"] += aux_total.detach().float()
+                    loss = loss + aux_total.to(loss.dtype)
                 self._loss, self._leaf = (loss, leaf) if need_grad else (None, None)
 
     def backward(self, last_micro_step=True, bucket_ready: Callable | None = None):
