@@ -7,11 +7,20 @@ import torch
 from . import _native as N
 
 
-def attention_fwd(qkv, B, T, NH, NKVH, HS, out=None, lse=None):
+import os
+
+# "tc" = tcgen05/TMEM kernels (csrc/attention_tc.cu) where the shape allows, "warp" = warp-level MMA kernels
+IMPL = os.environ.get("LLMK_ATTENTION", "tc")
+
+
+def attention_fwd(qkv, B, T, NH, NKVH, HS, out=None, lse=None, impl=None):
     """``qkv``: [B, T, (NH+2*NKVH)*HS] -> ``out`` [B, T, NH*HS], ``lse`` [B, NH, T] fp32."""
     out = torch.empty(B, T, NH * HS, dtype=qkv.dtype, device=qkv.device) if out is None else out
     lse = torch.empty(B, NH, T, dtype=torch.float32, device=qkv.device) if lse is None else lse
-    N.call("llmk_attention_fwd", out, lse, qkv, B, T, NH, NKVH, HS)
+    if (impl or IMPL) == "tc" and T % 128 == 0:
+        N.call("llmk_attention_fwd_tc", out, lse, qkv, B, T, NH, NKVH, HS, N.status_word())
+    else:
+        N.call("llmk_attention_fwd", out, lse, qkv, B, T, NH, NKVH, HS)
     return out, lse
 
 

@@ -87,6 +87,14 @@ class FusedComm:
             table = torch.tensor(rows, dtype=torch.int64, device=device)
             self.buckets[layer] = (table, len(rows), base)
             base += len(rows) * self.grid_x
+        # expert-parallel tensors are not reduced: their (already 1/P-scaled) local gradients are only
+        # converted into the fp32 shard buffer, through the same kernel with a one-entry peer table
+        lay = plan.layout
+        erows = [(s.param_off, s.state_off, s.length) for s in plan.segments if lay[s.tensor].spec.expert]
+        self.expert_table = torch.tensor(erows, dtype=torch.int64, device=device) if erows else None
+        self.expert_base = base
+        base += len(erows) * self.grid_x
+        self.own_grad_ptr = (ctypes.c_longlong * 1)(int(self.grads.data_ptr()))
         self.num_partials = base
         self.partials = torch.zeros(base, dtype=torch.float32, device=device)
         # optimizer table (parameter offset, state offset, length, decay flag)
@@ -114,6 +122,10 @@ class FusedComm:
                    self.partials[base:], self.grid_x, self.world_size, self.limit_ns, N.status_word())
 
     def finish_reduce(self) -> None:
+        if self.expert_table is not None:
+            # epoch 0 is always satisfied: no peer is involved in this copy
+            N.call("llmk_comm_rs_bucket", self.own_grad_ptr, self.ctrl, 0, 0, self.expert_table, int(self.expert_table.shape[0]),
+                   self.gshard, self.partials[self.expert_base:], self.grid_x, 1, self.limit_ns, N.status_word())
         torch.cuda.current_stream().wait_stream(self.stream)
 
     def norm_and_clip(self, clip: float, scale: torch.Tensor, norm: torch.Tensor, flag: torch.Tensor) -> None:

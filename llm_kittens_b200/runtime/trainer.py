@@ -54,6 +54,12 @@ class Trainer:
         self.master = torch.zeros(n, dtype=torch.float32, device=dev) if self.use_master else None
         self._master_ready = False
         self.rows = self.plan.segment_rows()
+        # expert-parallel tensors: the owner's gradient is a SUM over the tokens of all ranks, while dense
+        # gradients are averaged over ranks; dividing by P puts both on the same (global mean) scale
+        lay = self.plan.layout
+        self.expert_ranges = [(sg.param_off, sg.length) for sg in self.plan.segments if lay[sg.tensor].spec.expert] \
+            if num_processes > 1 else []
+        self.num_processes = num_processes
         # device scalars: [norm2], [scale], [norm], flag
         self.norm2 = torch.zeros(1, dtype=torch.float32, device=dev)
         self.scale = torch.ones(1, dtype=torch.float32, device=dev)
@@ -151,6 +157,8 @@ class Trainer:
     def update(self, lr: float | None = None, skip: bool = False) -> None:
         """Queue reduction -> norm -> clip -> AdamW -> parameter gather on the current stream (no host
         sync). With ``skip`` the optimizer part is left out; :meth:`apply_update` can run it later."""
+        for off, n in self.expert_ranges:
+            self.model.grads[off:off + n].mul_(1.0 / self.num_processes)
         self.comm.finish_reduce()
         self.comm.all_reduce_scalar(self.model.acts["loss_acc"], "avg")
         if getattr(self.comm, "fused", False):

@@ -5,6 +5,8 @@ modes:
   cpu_zero<k>      gloo, PyTorch oracle model in fp32, ZeRO stage k, library collectives
   gpu_library<k>   NCCL, CUDA model, ZeRO stage k, library collectives
   gpu_fused        NCCL bootstrap, CUDA model, ZeRO-1 through the fused peer-memory kernels
+  gpu_moe_library1 / gpu_moe_fused   mixture-of-experts model, experts split over the ranks (peer-memory
+                   dispatch / combine), dense parameters ZeRO-1 through library / fused communication
   cpu_fail_rank1   gloo; rank 1 raises before its first collective (failure-detection test)
 Each rank writes ``rank<r>.pt`` with its per-step losses / norms and a parameter checksum sample.
 """
@@ -26,6 +28,14 @@ from llm_kittens_b200.runtime.trainer import Trainer  # noqa: E402
 def tiny_config():
     return ModelConfig(family="gpt2", max_seq_len=64, vocab_size=512, padded_vocab_size=512, num_layers=2, num_heads=2,
                        num_kv_heads=2, channels=128, hidden_dim=512)
+
+
+def tiny_moe_config():
+    # generous capacity: nothing is dropped, so the expert-parallel run equals a single process that
+    # accumulates the ranks' micro-batches
+    return ModelConfig(family="moe", max_seq_len=128, vocab_size=512, padded_vocab_size=512, num_layers=2, num_heads=2,
+                       num_kv_heads=2, channels=128, hidden_dim=512, num_experts=8, top_k=2, capacity_factor=4.0,
+                       aux_loss_coef=0.01)
 
 
 def global_batches(cfg, steps, world, B, T):
@@ -61,10 +71,16 @@ def main():
             outcome = "error:" + type(e).__name__
         torch.save({"outcome": outcome}, os.path.join(out_dir, f"rank{rank}.pt"))
         os._exit(0)
-    cfg = tiny_config()
-    B, T, steps = 2, 64, 4
+    moe = "moe" in mode
+    cfg = tiny_moe_config() if moe else tiny_config()
+    B, T, steps = (2, 128, 3) if moe else (2, 64, 4)
     stage = int(mode[-1]) if mode[-1].isdigit() else 1
-    if cpu:
+    if moe:
+        from llm_kittens_b200.models.moe import MoETransformer
+        from llm_kittens_b200.parallel.expert import PeerExchange
+
+        model = MoETransformer(cfg, device=device, recompute=0, exchange=PeerExchange(device, timeout_ms=20000))
+    elif cpu:
         from llm_kittens_b200.oracle.torch_model import TorchTransformer
 
         model = TorchTransformer(cfg, device=device, dtype=torch.float32)
@@ -74,7 +90,7 @@ def main():
         model = Transformer(cfg, device=device, recompute=0)
     model.init_weights(42)
     plan = ZeroPlan(cfg, world, rank, stage)
-    if mode == "gpu_fused":
+    if mode in ("gpu_fused", "gpu_moe_fused"):
         from llm_kittens_b200.parallel.fused import FusedComm
 
         comm = FusedComm(plan, model, device, timeout_ms=20000)

@@ -39,3 +39,24 @@ def test_fused_comm_matches_library_and_zero0(tmp_path):
         assert abs(a - b) < 0.03 * max(1.0, b)
     assert (f0["params"] - l0["params"]).abs().max().item() < 0.02
     assert f0["losses"][-1] < f0["losses"][0]
+
+
+def test_expert_parallel_moe_matches_single_process(tmp_path):
+    _need_two_gpus()
+    from dist_worker import global_batches, tiny_moe_config
+    from llm_kittens_b200.models.moe import MoETransformer
+    from llm_kittens_b200.runtime.trainer import Trainer
+
+    cfg = tiny_moe_config()
+    model = MoETransformer(cfg, device="cuda:0", recompute=0)
+    model.init_weights(42)
+    tr = Trainer(model, learning_rate=1e-3, weight_decay=0.1)
+    ref = []
+    for x, y in global_batches(cfg, 3, 2, 2, 128):
+        ref.append(tr.train_step([(x[:2].contiguous(), y[:2].contiguous()), (x[2:].contiguous(), y[2:].contiguous())]).loss)
+    for mode in ("gpu_moe_library1", "gpu_moe_fused"):
+        r0, r1 = _run(mode, tmp_path)
+        assert r0["losses"] == r1["losses"]
+        for a, b in zip(r0["losses"], ref):
+            assert abs(a - b) < 0.03, (mode, r0["losses"], ref)
+        assert r0["losses"][-1] < r0["losses"][0]

@@ -195,10 +195,13 @@ def _ref_attention(qkv, B, T, NH, NKVH, HS):
 @pytest.mark.parametrize("B,T,NH,NKVH,HS", [(2, 128, 4, 4, 64), (1, 256, 12, 12, 64), (2, 192, 8, 2, 64), (1, 128, 4, 2, 128),
                                             (1, 1024, 2, 1, 128)])
 def test_attention_fwd_bwd(B, T, NH, NKVH, HS):
-    from llm_kittens_b200.ops import attention
+    from llm_kittens_b200.ops import _native, attention
 
     qkv = rnd(B, T, (NH + 2 * NKVH) * HS)
-    out, lse = attention.attention_fwd(qkv, B, T, NH, NKVH, HS)
+    out_w, lse_w = attention.attention_fwd(qkv, B, T, NH, NKVH, HS, impl="warp")
+    out, lse = attention.attention_fwd(qkv, B, T, NH, NKVH, HS, impl="tc")   # tcgen05 path when T % 128 == 0
+    _native.check_status()
+    assert maxerr(out, out_w) < 0.03 and maxerr(lse, lse_w) < 0.02
     qf = qkv.float().requires_grad_(True)
     ref, ref_lse = _ref_attention(qf, B, T, NH, NKVH, HS)
     assert maxerr(out, ref) < 0.03
