@@ -559,3 +559,13 @@ LLMK_API int llmk_attention_bwd(void* dqkv, void* dvec, const void* dout, const 
     LLMK_LAUNCH_CHECK();
     return LLMK_OK;
 }
+
+// D = rowsum(dO * O) as [B, NH, T] fp32: the pre-pass shared by both backward implementations.
+LLMK_API int llmk_attention_bwd_prep(void* dvec, const void* dout, const void* out, int B, int T, int NH, int HS, void* stream_) {
+    cudaStream_t stream = (cudaStream_t)stream_;
+    const long warps = (long)B * T * NH;
+    attn_bwd_prep_kernel<<<ceil_div(warps * 32, 256), 256, 0, stream>>>((float*)dvec, (const bf16*)out, (const bf16*)dout, B * T,
+                                                                       NH, HS, T);
+    LLMK_LAUNCH_CHECK();
+    return LLMK_OK;
+}

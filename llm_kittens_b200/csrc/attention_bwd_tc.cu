@@ -1,0 +1,530 @@
+// Causal flash-attention BACKWARD on tcgen05 / TMEM for MHA and GQA, deterministic (no atomics):
+//
+//   dkv kernel  one CTA per (128-row K/V tile, KV head, batch); loops over the query tiles at or after
+//               it and over the query heads that share the KV head. Works on TRANSPOSED scores so a
+//               thread owns one key row:
+//                   S^T  = K Q^T          dP^T = V dO^T                 (tcgen05, K-major operands)
+//                   P^T  = exp2(S^T c - LSE[q])      dS^T = P^T * (dP^T - D[q])     (softmax warps)
+//                   dV  += P^T dO         dK  += dS^T Q                 (tcgen05, accumulate in TMEM)
+//   dq kernel   one CTA per (128-row query tile, head, batch); loops over the K/V tiles at or before it:
+//                   S = Q K^T, dP = dO V^T, dS = P * (dP - D[row]), dQ += dS K.
+//
+// Both recompute P from the saved log-sum-exp; D = rowsum(dO * O) comes from the small pre-pass in
+// attention.cu. Inputs are the packed QKV activation and dO through TMA tensor maps; outputs go
+// straight into the packed dQKV tensor. Same job as attention_backward / attention_gqa_backward in
+// the reference (llmc/attention.cuh:481-604, llmc/attention_gqa.cuh:483-572). Warp roles as in the
+// forward kernel (attention_tc.cu): warp 0 TMA producer, warp 1 MMA issuer, warps 2-5 one row per
+// thread. All waits are bounded.
+#include "ptx_sm100.cuh"
+
+namespace llmk {
+namespace gemm {
+int make_tmap_2d(CUtensorMap* m, const void* ptr, uint64_t inner, uint64_t outer, uint64_t row_stride_elems, uint32_t box_inner,
+                 uint32_t box_outer);
+}
+namespace attn_bwd_tc {
+
+constexpr int BT_ = 128;  // tile rows (queries and keys)
+constexpr int THREADS = 192;
+constexpr int ATOM_BYTES = 128 * 128;
+constexpr int TMEM_COLS = 512;
+constexpr float LOG2E = 1.4426950408889634f;
+
+__device__ __forceinline__ float ex2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
+// [128 x HS] K-major A/B operand at `base` (atoms of 64 columns): descriptor of k-step kk (16 columns)
+__device__ __forceinline__ uint64_t kmajor_desc(uint32_t base, int kk) {
+    return ptx::make_smem_desc(base + (kk / 4) * ATOM_BYTES + (kk % 4) * 32, 16, 1024);
+}
+// the same tile read as an MN-major B operand (n = the HS columns, k = the 128 rows): k-step kk (16 rows)
+__device__ __forceinline__ uint64_t mnmajor_desc(uint32_t base, int kk) {
+    return ptx::make_smem_desc(base + kk * 2048, ATOM_BYTES, 1024);
+}
+
+template <int HS>
+__device__ __forceinline__ void load_tile(uint8_t* dst, const CUtensorMap* tm, uint64_t* bar, int col, int row) {
+#pragma unroll
+    for (int c = 0; c < HS / 64; c++) ptx::tma_load_2d(dst + c * ATOM_BYTES, tm, bar, col + 64 * c, row);
+}
+
+// write 8 bf16 into chunk `chunk16` (0..15 over the 128 columns) of row r of a [128 x 128] K-major tile
+__device__ __forceinline__ void store_chunk(uint8_t* tile, int r, int chunk16, const float* f) {
+    uint8_t* atom = tile + (chunk16 >> 3) * ATOM_BYTES + r * 128;
+    *reinterpret_cast<bf16x8*>(atom + (((chunk16 & 7) ^ (r & 7)) << 4)) = pack8(f);
+}
+
+// ====================================================================================== dK, dV
+template <int HS>
+struct DkvCfg {
+    static constexpr int RING = HS == 64 ? 2 : 1;
+    static constexpr int TILE = BT_ * HS * 2;
+    static constexpr int OFF_K = 0, OFF_V = TILE, OFF_RING = 2 * TILE;          // ring: [RING][Q, dO]
+    static constexpr int OFF_PT = OFF_RING + RING * 2 * TILE, OFF_DST = OFF_PT + BT_ * BT_ * 2;
+    static constexpr int OFF_LD = OFF_DST + BT_ * BT_ * 2;                       // float [2][2][128]
+    static constexpr int OFF_BAR = OFF_LD + 2 * 2 * 128 * 4;
+    static constexpr int SMEM_BYTES = OFF_BAR + 128;
+};
+
+template <int HS>
+__global__ void __launch_bounds__(THREADS, 1)
+attn_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_constant__ CUtensorMap tmDO,
+                       bf16* __restrict__ dqkv, const float* __restrict__ lse, const float* __restrict__ dvec, int T, int NH,
+                       int NKVH, float scale, int* status) {
+    using C = DkvCfg<HS>;
+    constexpr int RING = C::RING;
+    extern __shared__ __align__(1024) uint8_t smem[];
+    if (ptx::smem_u32(smem) & 1023u) {
+        if (threadIdx.x == 0 && status != nullptr) atomicCAS(status, 0, LLMK_ST_BOUNDS);
+        return;
+    }
+    uint8_t* sK = smem + C::OFF_K;
+    uint8_t* sV = smem + C::OFF_V;
+    uint8_t* sRing = smem + C::OFF_RING;
+    uint8_t* sPt = smem + C::OFF_PT;
+    uint8_t* sdSt = smem + C::OFF_DST;
+    float* sLD = reinterpret_cast<float*>(smem + C::OFF_LD);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + C::OFF_BAR);
+    uint64_t* kv_full = bars;         // [1]
+    uint64_t* ring_full = bars + 1;   // [2]
+    uint64_t* ring_empty = bars + 3;  // [2]
+    uint64_t* s_full = bars + 5;
+    uint64_t* p_full = bars + 6;
+    uint64_t* acc_done = bars + 7;
+    uint64_t* ld_full = bars + 8;     // [2] LSE / D vectors of a ring slot are in shared memory
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 10);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int kt = blockIdx.x, hk = blockIdx.y, b = blockIdx.z;
+    const int hr = NH / NKVH;
+    const int nq = T / BT_ - kt;
+    const int total = nq * hr;
+    const int row_base = b * T;
+    const int k_col = (NH + hk) * HS, v_col = (NH + NKVH + hk) * HS;
+    const float scale_log2 = scale * LOG2E;
+
+    if (threadIdx.x == 0) {
+        ptx::mbar_init(kv_full, 1);
+        for (int i = 0; i < 2; i++) {
+            ptx::mbar_init(&ring_full[i], 1);
+            ptx::mbar_init(&ring_empty[i], 1);
+            ptx::mbar_init(&ld_full[i], 1);
+        }
+        ptx::mbar_init(s_full, 1);
+        ptx::mbar_init(p_full, 4);
+        ptx::mbar_init(acc_done, 1);
+        *abort_flag = 0;
+        ptx::fence_barrier_init();
+    }
+    if (warp == 1) {
+        ptx::tmem_alloc(tmem_slot, TMEM_COLS);
+        ptx::tmem_relinquish();
+    }
+    ptx::tc_fence_before();
+    __syncthreads();
+    ptx::tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+    const uint32_t t_st = tmem_base, t_dpt = tmem_base + 128, t_dv = tmem_base + 256, t_dk = tmem_base + 256 + HS;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            ptx::mbar_arrive_expect_tx(kv_full, 2 * C::TILE);
+            load_tile<HS>(sK, &tmQKV, kv_full, k_col, row_base + kt * BT_);
+            load_tile<HS>(sV, &tmQKV, kv_full, v_col, row_base + kt * BT_);
+        }
+        __syncwarp();
+        for (int it = 0; it < total; it++) {
+            const int s = it % RING;
+            if (!ptx::mbar_wait(&ring_empty[s], ((it / RING) & 1) ^ 1, abort_flag, status, LLMK_ST_TIMEOUT_TMA_EMPTY, it)) break;
+            const int hq = hk * hr + it / nq, qt = kt + it % nq;
+            if (lane == 0) {
+                ptx::mbar_arrive_expect_tx(&ring_full[s], 2 * C::TILE);
+                load_tile<HS>(sRing + s * 2 * C::TILE, &tmQKV, &ring_full[s], hq * HS, row_base + qt * BT_);
+                load_tile<HS>(sRing + s * 2 * C::TILE + C::TILE, &tmDO, &ring_full[s], hq * HS, row_base + qt * BT_);
+            }
+            {   // log-sum-exp (in the exp2 domain) and D of the 128 queries of this tile, 4 per lane
+                float* sL = sLD + s * 256;
+                const size_t off = ((size_t)b * NH + hq) * T + qt * BT_;
+#pragma unroll
+                for (int i = 0; i < 4; i++) {
+                    sL[lane + 32 * i] = lse[off + lane + 32 * i] * LOG2E;
+                    sL[128 + lane + 32 * i] = dvec[off + lane + 32 * i];
+                }
+            }
+            __syncwarp();
+            if (lane == 0) ptx::mbar_arrive(&ld_full[s]);
+            __syncwarp();
+        }
+    } else if (warp == 1) {
+        constexpr uint32_t idesc_s = ptx::make_idesc_bf16(128, 128, 0, 0);
+        constexpr uint32_t idesc_acc = ptx::make_idesc_bf16(128, HS, 0, 1);
+        bool ok = ptx::mbar_wait(kv_full, 0, abort_flag, status, LLMK_ST_TIMEOUT_TMA_FULL, -1);
+        auto issue_s = [&](int it) -> bool {
+            const int s = it % RING;
+            if (!ptx::mbar_wait(&ring_full[s], (it / RING) & 1, abort_flag, status, LLMK_ST_TIMEOUT_TMA_FULL, it)) return false;
+            ptx::tc_fence_after();
+            if (lane == 0) {
+                const uint32_t k_addr = ptx::smem_u32(sK), v_addr = ptx::smem_u32(sV);
+                const uint32_t q_addr = ptx::smem_u32(sRing + s * 2 * C::TILE), do_addr = q_addr + C::TILE;
+#pragma unroll
+                for (int kk = 0; kk < HS / 16; kk++)
+                    ptx::mma_f16_ss(t_st, kmajor_desc(k_addr, kk), kmajor_desc(q_addr, kk), idesc_s, kk > 0 ? 1u : 0u);
+#pragma unroll
+                for (int kk = 0; kk < HS / 16; kk++)
+                    ptx::mma_f16_ss(t_dpt, kmajor_desc(v_addr, kk), kmajor_desc(do_addr, kk), idesc_s, kk > 0 ? 1u : 0u);
+                ptx::mma_commit(s_full);
+            }
+            __syncwarp();
+            return true;
+        };
+        auto issue_acc = [&](int it) {
+            const int s = it % RING;
+            if (lane == 0) {
+                const uint32_t q_addr = ptx::smem_u32(sRing + s * 2 * C::TILE), do_addr = q_addr + C::TILE;
+                const uint32_t pt_addr = ptx::smem_u32(sPt), dst_addr = ptx::smem_u32(sdSt);
+#pragma unroll
+                for (int kk = 0; kk < 8; kk++)
+                    ptx::mma_f16_ss(t_dv, kmajor_desc(pt_addr, kk), mnmajor_desc(do_addr, kk), idesc_acc, (it > 0 || kk > 0) ? 1u : 0u);
+#pragma unroll
+                for (int kk = 0; kk < 8; kk++)
+                    ptx::mma_f16_ss(t_dk, kmajor_desc(dst_addr, kk), mnmajor_desc(q_addr, kk), idesc_acc, (it > 0 || kk > 0) ? 1u : 0u);
+                ptx::mma_commit(&ring_empty[s]);
+                ptx::mma_commit(acc_done);
+            }
+            __syncwarp();
+        };
+        if (ok) ok = issue_s(0);
+        for (int it = 0; it < total && ok; it++) {
+            ok = ptx::mbar_wait(p_full, it & 1, abort_flag, status, LLMK_ST_TIMEOUT_ACC_EMPTY, it);
+            if (!ok) break;
+            ptx::tc_fence_after();
+            if (RING == 2) {
+                if (it + 1 < total) ok = issue_s(it + 1);   // next scores first, so the softmax can overlap the accumulation
+                if (!ok) break;
+                issue_acc(it);
+            } else {
+                issue_acc(it);
+                if (it + 1 < total) ok = issue_s(it + 1);
+            }
+        }
+    } else {
+        const int lane_group = warp & 3;
+        const int r = lane_group * 32 + lane;               // key row inside the tile
+        const uint32_t lane_off = (uint32_t)(lane_group * 32) << 16;
+        bool ok = true;
+        for (int it = 0; it < total && ok; it++) {
+            const int qt = kt + it % nq;
+            const int slot = it % RING;
+            const float* sL = sLD + slot * 256;
+            const float* sD = sL + 128;
+            ok = ptx::mbar_wait(&ld_full[slot], (it / RING) & 1, abort_flag, status, LLMK_ST_TIMEOUT_TMA_FULL, 3000 + it);
+            if (!ok) break;
+            ok = ptx::mbar_wait(s_full, it & 1, abort_flag, status, LLMK_ST_TIMEOUT_ACC_FULL, it);
+            if (!ok) break;
+            if (it > 0) {   // the previous accumulation MMAs have finished reading P^T / dS^T
+                ok = ptx::mbar_wait(acc_done, (it - 1) & 1, abort_flag, status, LLMK_ST_TIMEOUT_ACC_FULL, 1000 + it);
+                if (!ok) break;
+            }
+            ptx::tc_fence_after();
+            const bool diag = (qt == kt);
+#pragma unroll 1
+            for (int c4 = 0; c4 < 4; c4++) {
+                uint32_t vs[32], vd[32];
+                ptx::tmem_ld_32x32b_x32(t_st + lane_off + c4 * 32, vs);
+                ptx::tmem_ld_32x32b_x32(t_dpt + lane_off + c4 * 32, vd);
+                ptx::tmem_ld_wait();
+#pragma unroll
+                for (int q = 0; q < 4; q++) {
+                    float p[8], ds[8];
+#pragma unroll
+                    for (int i = 0; i < 8; i++) {
+                        const int c = c4 * 32 + q * 8 + i;   // query column
+                        float e = ex2(fmaf(__uint_as_float(vs[q * 8 + i]), scale_log2, -sL[c]));
+                        if (diag && r > c) e = 0.f;
+                        p[i] = e;
+                        ds[i] = e * (__uint_as_float(vd[q * 8 + i]) - sD[c]);
+                    }
+                    store_chunk(sPt, r, c4 * 4 + q, p);
+                    store_chunk(sdSt, r, c4 * 4 + q, ds);
+                }
+            }
+            ptx::tc_fence_before();
+            ptx::fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0) ptx::mbar_arrive(p_full);
+        }
+        if (ok) ok = ptx::mbar_wait(acc_done, (total - 1) & 1, abort_flag, status, LLMK_ST_TIMEOUT_ACC_FULL, 2000);
+        if (ok) {
+            ptx::tc_fence_after();
+            const int width = (NH + 2 * NKVH) * HS;
+            bf16* dk_row = dqkv + (size_t)(row_base + kt * BT_ + r) * width + k_col;
+            bf16* dv_row = dqkv + (size_t)(row_base + kt * BT_ + r) * width + v_col;
+#pragma unroll
+            for (int h4 = 0; h4 < HS / 32; h4++) {
+                uint32_t v[32];
+                ptx::tmem_ld_32x32b_x32(t_dk + lane_off + h4 * 32, v);
+                ptx::tmem_ld_wait();
+#pragma unroll
+                for (int q = 0; q < 4; q++) {
+                    float f[8];
+#pragma unroll
+                    for (int i = 0; i < 8; i++) f[i] = __uint_as_float(v[q * 8 + i]) * scale;
+                    st128(dk_row + h4 * 32 + q * 8, pack8(f));
+                }
+                ptx::tmem_ld_32x32b_x32(t_dv + lane_off + h4 * 32, v);
+                ptx::tmem_ld_wait();
+#pragma unroll
+                for (int q = 0; q < 4; q++) {
+                    float f[8];
+#pragma unroll
+                    for (int i = 0; i < 8; i++) f[i] = __uint_as_float(v[q * 8 + i]);
+                    st128(dv_row + h4 * 32 + q * 8, pack8(f));
+                }
+            }
+        }
+    }
+    ptx::tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        ptx::tc_fence_after();
+        ptx::tmem_dealloc(tmem_base, TMEM_COLS);
+    }
+}
+
+// ====================================================================================== dQ
+template <int HS>
+struct DqCfg {
+    static constexpr int TILE = BT_ * HS * 2;
+    static constexpr int OFF_Q = 0, OFF_DO = TILE, OFF_RING = 2 * TILE;   // ring: [2][K, V]
+    static constexpr int OFF_DS = OFF_RING + 4 * TILE;
+    static constexpr int OFF_BAR = OFF_DS + BT_ * BT_ * 2;
+    static constexpr int SMEM_BYTES = OFF_BAR + 128;
+};
+
+template <int HS>
+__global__ void __launch_bounds__(THREADS, 1)
+attn_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_constant__ CUtensorMap tmDO, bf16* __restrict__ dqkv,
+                      const float* __restrict__ lse, const float* __restrict__ dvec, int T, int NH, int NKVH, float scale,
+                      int* status) {
+    using C = DqCfg<HS>;
+    extern __shared__ __align__(1024) uint8_t smem[];
+    if (ptx::smem_u32(smem) & 1023u) {
+        if (threadIdx.x == 0 && status != nullptr) atomicCAS(status, 0, LLMK_ST_BOUNDS);
+        return;
+    }
+    uint8_t* sQ = smem + C::OFF_Q;
+    uint8_t* sdO = smem + C::OFF_DO;
+    uint8_t* sRing = smem + C::OFF_RING;
+    uint8_t* sdS = smem + C::OFF_DS;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + C::OFF_BAR);
+    uint64_t* q_full = bars;
+    uint64_t* ring_full = bars + 1;   // [2]
+    uint64_t* ring_empty = bars + 3;  // [2]
+    uint64_t* s_full = bars + 5;
+    uint64_t* p_full = bars + 6;
+    uint64_t* acc_done = bars + 7;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 8);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int qt = gridDim.x - 1 - blockIdx.x;
+    const int h = blockIdx.y, b = blockIdx.z;
+    const int hk = h / (NH / NKVH);
+    const int nkv = qt + 1;
+    const int row_base = b * T;
+    const int q_col = h * HS, k_col = (NH + hk) * HS, v_col = (NH + NKVH + hk) * HS;
+    const float scale_log2 = scale * LOG2E;
+
+    if (threadIdx.x == 0) {
+        ptx::mbar_init(q_full, 1);
+        for (int i = 0; i < 2; i++) {
+            ptx::mbar_init(&ring_full[i], 1);
+            ptx::mbar_init(&ring_empty[i], 1);
+        }
+        ptx::mbar_init(s_full, 1);
+        ptx::mbar_init(p_full, 4);
+        ptx::mbar_init(acc_done, 1);
+        *abort_flag = 0;
+        ptx::fence_barrier_init();
+    }
+    if (warp == 1) {
+        ptx::tmem_alloc(tmem_slot, TMEM_COLS);
+        ptx::tmem_relinquish();
+    }
+    ptx::tc_fence_before();
+    __syncthreads();
+    ptx::tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+    const uint32_t t_s = tmem_base, t_dp = tmem_base + 128, t_dq = tmem_base + 256;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            ptx::mbar_arrive_expect_tx(q_full, 2 * C::TILE);
+            load_tile<HS>(sQ, &tmQKV, q_full, q_col, row_base + qt * BT_);
+            load_tile<HS>(sdO, &tmDO, q_full, q_col, row_base + qt * BT_);
+        }
+        __syncwarp();
+        for (int j = 0; j < nkv; j++) {
+            const int s = j & 1;
+            if (!ptx::mbar_wait(&ring_empty[s], ((j >> 1) & 1) ^ 1, abort_flag, status, LLMK_ST_TIMEOUT_TMA_EMPTY, j)) break;
+            if (lane == 0) {
+                ptx::mbar_arrive_expect_tx(&ring_full[s], 2 * C::TILE);
+                load_tile<HS>(sRing + s * 2 * C::TILE, &tmQKV, &ring_full[s], k_col, row_base + j * BT_);
+                load_tile<HS>(sRing + s * 2 * C::TILE + C::TILE, &tmQKV, &ring_full[s], v_col, row_base + j * BT_);
+            }
+            __syncwarp();
+        }
+    } else if (warp == 1) {
+        constexpr uint32_t idesc_s = ptx::make_idesc_bf16(128, 128, 0, 0);
+        constexpr uint32_t idesc_acc = ptx::make_idesc_bf16(128, HS, 0, 1);
+        bool ok = ptx::mbar_wait(q_full, 0, abort_flag, status, LLMK_ST_TIMEOUT_TMA_FULL, -1);
+        auto issue_s = [&](int j) -> bool {
+            const int s = j & 1;
+            if (!ptx::mbar_wait(&ring_full[s], (j >> 1) & 1, abort_flag, status, LLMK_ST_TIMEOUT_TMA_FULL, j)) return false;
+            ptx::tc_fence_after();
+            if (lane == 0) {
+                const uint32_t q_addr = ptx::smem_u32(sQ), do_addr = ptx::smem_u32(sdO);
+                const uint32_t k_addr = ptx::smem_u32(sRing + s * 2 * C::TILE), v_addr = k_addr + C::TILE;
+#pragma unroll
+                for (int kk = 0; kk < HS / 16; kk++)
+                    ptx::mma_f16_ss(t_s, kmajor_desc(q_addr, kk), kmajor_desc(k_addr, kk), idesc_s, kk > 0 ? 1u : 0u);
+#pragma unroll
+                for (int kk = 0; kk < HS / 16; kk++)
+                    ptx::mma_f16_ss(t_dp, kmajor_desc(do_addr, kk), kmajor_desc(v_addr, kk), idesc_s, kk > 0 ? 1u : 0u);
+                ptx::mma_commit(s_full);
+            }
+            __syncwarp();
+            return true;
+        };
+        if (ok) ok = issue_s(0);
+        for (int j = 0; j < nkv && ok; j++) {
+            const int s = j & 1;
+            ok = ptx::mbar_wait(p_full, j & 1, abort_flag, status, LLMK_ST_TIMEOUT_ACC_EMPTY, j);
+            if (!ok) break;
+            ptx::tc_fence_after();
+            if (j + 1 < nkv) {
+                ok = issue_s(j + 1);
+                if (!ok) break;
+            }
+            if (lane == 0) {
+                const uint32_t ds_addr = ptx::smem_u32(sdS), k_addr = ptx::smem_u32(sRing + s * 2 * C::TILE);
+#pragma unroll
+                for (int kk = 0; kk < 8; kk++)
+                    ptx::mma_f16_ss(t_dq, kmajor_desc(ds_addr, kk), mnmajor_desc(k_addr, kk), idesc_acc, (j > 0 || kk > 0) ? 1u : 0u);
+                ptx::mma_commit(&ring_empty[s]);
+                ptx::mma_commit(acc_done);
+            }
+            __syncwarp();
+        }
+    } else {
+        const int lane_group = warp & 3;
+        const int r = lane_group * 32 + lane;   // query row inside the tile
+        const uint32_t lane_off = (uint32_t)(lane_group * 32) << 16;
+        const size_t roff = ((size_t)b * NH + h) * T + qt * BT_ + r;
+        const float Lr = lse[roff] * LOG2E, Dr = dvec[roff];
+        bool ok = true;
+        for (int j = 0; j < nkv && ok; j++) {
+            ok = ptx::mbar_wait(s_full, j & 1, abort_flag, status, LLMK_ST_TIMEOUT_ACC_FULL, j);
+            if (!ok) break;
+            if (j > 0) {
+                ok = ptx::mbar_wait(acc_done, (j - 1) & 1, abort_flag, status, LLMK_ST_TIMEOUT_ACC_FULL, 1000 + j);
+                if (!ok) break;
+            }
+            ptx::tc_fence_after();
+            const bool diag = (j == nkv - 1);
+#pragma unroll 1
+            for (int c4 = 0; c4 < 4; c4++) {
+                uint32_t vs[32], vd[32];
+                ptx::tmem_ld_32x32b_x32(t_s + lane_off + c4 * 32, vs);
+                ptx::tmem_ld_32x32b_x32(t_dp + lane_off + c4 * 32, vd);
+                ptx::tmem_ld_wait();
+#pragma unroll
+                for (int q = 0; q < 4; q++) {
+                    float ds[8];
+#pragma unroll
+                    for (int i = 0; i < 8; i++) {
+                        const int c = c4 * 32 + q * 8 + i;   // key column
+                        float e = ex2(fmaf(__uint_as_float(vs[q * 8 + i]), scale_log2, -Lr));
+                        if (diag && c > r) e = 0.f;
+                        ds[i] = e * (__uint_as_float(vd[q * 8 + i]) - Dr);
+                    }
+                    store_chunk(sdS, r, c4 * 4 + q, ds);
+                }
+            }
+            ptx::tc_fence_before();
+            ptx::fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0) ptx::mbar_arrive(p_full);
+        }
+        if (ok) ok = ptx::mbar_wait(acc_done, (nkv - 1) & 1, abort_flag, status, LLMK_ST_TIMEOUT_ACC_FULL, 2000);
+        if (ok) {
+            ptx::tc_fence_after();
+            const int width = (NH + 2 * NKVH) * HS;
+            bf16* dq_row = dqkv + (size_t)(row_base + qt * BT_ + r) * width + q_col;
+#pragma unroll
+            for (int h4 = 0; h4 < HS / 32; h4++) {
+                uint32_t v[32];
+                ptx::tmem_ld_32x32b_x32(t_dq + lane_off + h4 * 32, v);
+                ptx::tmem_ld_wait();
+#pragma unroll
+                for (int q = 0; q < 4; q++) {
+                    float f[8];
+#pragma unroll
+                    for (int i = 0; i < 8; i++) f[i] = __uint_as_float(v[q * 8 + i]) * scale;
+                    st128(dq_row + h4 * 32 + q * 8, pack8(f));
+                }
+            }
+        }
+    }
+    ptx::tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        ptx::tc_fence_after();
+        ptx::tmem_dealloc(tmem_base, TMEM_COLS);
+    }
+}
+
+template <int HS>
+static int launch(const CUtensorMap& tq, const CUtensorMap& tdo, bf16* dqkv, const float* lse, const float* dvec, int B, int T, int NH,
+                  int NKVH, int* status, cudaStream_t stream) {
+    static bool configured = false;
+    if (!configured) {
+        LLMK_CUDA_TRY(cudaFuncSetAttribute(attn_bwd_dkv_tc_kernel<HS>, cudaFuncAttributeMaxDynamicSharedMemorySize, DkvCfg<HS>::SMEM_BYTES));
+        LLMK_CUDA_TRY(cudaFuncSetAttribute(attn_bwd_dq_tc_kernel<HS>, cudaFuncAttributeMaxDynamicSharedMemorySize, DqCfg<HS>::SMEM_BYTES));
+        configured = true;
+    }
+    const float scale = 1.0f / sqrtf((float)HS);
+    attn_bwd_dkv_tc_kernel<HS><<<dim3(T / BT_, NKVH, B), THREADS, DkvCfg<HS>::SMEM_BYTES, stream>>>(tq, tdo, dqkv, lse, dvec, T, NH,
+                                                                                                  NKVH, scale, status);
+    LLMK_LAUNCH_CHECK();
+    attn_bwd_dq_tc_kernel<HS><<<dim3(T / BT_, NH, B), THREADS, DqCfg<HS>::SMEM_BYTES, stream>>>(tq, tdo, dqkv, lse, dvec, T, NH, NKVH,
+                                                                                              scale, status);
+    LLMK_LAUNCH_CHECK();
+    return LLMK_OK;
+}
+
+}  // namespace attn_bwd_tc
+}  // namespace llmk
+
+using namespace llmk;
+
+// dqkv (packed, fully overwritten) from dout [B*T, NH*HS]; `dvec` must already hold rowsum(dO*O) as [B,NH,T]
+// (llmk_attention_bwd_prep). T must be a multiple of 128.
+LLMK_API int llmk_attention_bwd_tc(void* dqkv, const void* dvec, const void* dout, const void* qkv, const void* lse, int B, int T,
+                                   int NH, int NKVH, int HS, int* status, void* stream_) {
+    cudaStream_t stream = (cudaStream_t)stream_;
+    if (T % 128 || NH % NKVH || (HS != 64 && HS != 128)) return LLMK_ERR_SHAPE;
+    const long width = (long)(NH + 2 * NKVH) * HS;
+    CUtensorMap tq, tdo;
+    int rc = gemm::make_tmap_2d(&tq, qkv, (uint64_t)width, (uint64_t)B * T, (uint64_t)width, 64, 128);
+    if (rc) return rc;
+    rc = gemm::make_tmap_2d(&tdo, dout, (uint64_t)NH * HS, (uint64_t)B * T, (uint64_t)NH * HS, 64, 128);
+    if (rc) return rc;
+    if (HS == 64)
+        return attn_bwd_tc::launch<64>(tq, tdo, (bf16*)dqkv, (const float*)lse, (const float*)dvec, B, T, NH, NKVH, status, stream);
+    return attn_bwd_tc::launch<128>(tq, tdo, (bf16*)dqkv, (const float*)lse, (const float*)dvec, B, T, NH, NKVH, status, stream);
+}

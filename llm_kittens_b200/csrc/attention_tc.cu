@@ -188,10 +188,11 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQKV, bf16* __restrict__
         constexpr uint32_t idesc_s = ptx::make_idesc_bf16(BQ, BKV, 0, 0);
         constexpr uint32_t idesc_o = ptx::make_idesc_bf16(BQ, HS, 0, 1);
         bool ok = ptx::mbar_wait(q_full, 0, abort_flag, status, LLMK_ST_TIMEOUT_TMA_FULL, -1);
-        for (int j = 0; j < nkv && ok; j++) {
+        // S(j+1) is issued BEFORE P V(j): the tensor core works through them in order, so the softmax of
+        // tile j+1 can start while P V(j) is still running.
+        auto issue_s = [&](int j) -> bool {
             const int s = j & 1;
-            ok = ptx::mbar_wait(&kv_full[s], (j >> 1) & 1, abort_flag, status, LLMK_ST_TIMEOUT_TMA_FULL, j);
-            if (!ok) break;
+            if (!ptx::mbar_wait(&kv_full[s], (j >> 1) & 1, abort_flag, status, LLMK_ST_TIMEOUT_TMA_FULL, j)) return false;
             ptx::tc_fence_after();
             if (lane == 0) {
                 const uint32_t q_addr = ptx::smem_u32(sQ), k_addr = ptx::smem_u32(sK + s * C::TILE_BYTES);
@@ -204,9 +205,19 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQKV, bf16* __restrict__
                 ptx::mma_commit(s_full);
             }
             __syncwarp();
+            return true;
+        };
+        if (ok) ok = issue_s(0);
+        for (int j = 0; j < nkv && ok; j++) {
+            const int s = j & 1;
+            // P(j) is in shared memory and S(j) has been consumed
             ok = ptx::mbar_wait(p_full, j & 1, abort_flag, status, LLMK_ST_TIMEOUT_ACC_EMPTY, j);
             if (!ok) break;
             ptx::tc_fence_after();
+            if (j + 1 < nkv) {
+                ok = issue_s(j + 1);
+                if (!ok) break;
+            }
             if (lane == 0) {
                 const uint32_t p_addr = ptx::smem_u32(sP), v_addr = ptx::smem_u32(sV + s * C::TILE_BYTES);
 #pragma unroll

@@ -24,8 +24,12 @@ def attention_fwd(qkv, B, T, NH, NKVH, HS, out=None, lse=None, impl=None):
     return out, lse
 
 
-def attention_bwd(dout, qkv, out, lse, B, T, NH, NKVH, HS, dqkv=None, dvec=None):
+def attention_bwd(dout, qkv, out, lse, B, T, NH, NKVH, HS, dqkv=None, dvec=None, impl=None):
     dqkv = torch.empty_like(qkv) if dqkv is None else dqkv
     dvec = torch.empty(B, NH, T, dtype=torch.float32, device=qkv.device) if dvec is None else dvec
-    N.call("llmk_attention_bwd", dqkv, dvec, dout, qkv, out, lse, B, T, NH, NKVH, HS)
+    if (impl or IMPL) == "tc" and T % 128 == 0:
+        N.call("llmk_attention_bwd_prep", dvec, dout, out, B, T, NH, HS)
+        N.call("llmk_attention_bwd_tc", dqkv, dvec, dout, qkv, lse, B, T, NH, NKVH, HS, N.status_word())
+    else:
+        N.call("llmk_attention_bwd", dqkv, dvec, dout, qkv, out, lse, B, T, NH, NKVH, HS)
     return dqkv

@@ -30,6 +30,7 @@ def bench_attention():
         tf = time_fn(lambda: attention.attention_fwd(qkv, B, T, NH, NKVH, HS, out=out, lse=lse))
         tfw = time_fn(lambda: attention.attention_fwd(qkv, B, T, NH, NKVH, HS, out=out, lse=lse, impl="warp"))
         tb = time_fn(lambda: attention.attention_bwd(dout, qkv, out, lse, B, T, NH, NKVH, HS, dqkv=dqkv, dvec=dvec))
+        tbw = time_fn(lambda: attention.attention_bwd(dout, qkv, out, lse, B, T, NH, NKVH, HS, dqkv=dqkv, dvec=dvec, impl="warp"))
         x = qkv.view(B, T, NH + 2 * NKVH, HS)
         q = x[:, :, :NH].transpose(1, 2).contiguous().requires_grad_(True)
         k = x[:, :, NH:NH + NKVH].transpose(1, 2).contiguous().requires_grad_(True)
@@ -40,7 +41,7 @@ def bench_attention():
         do = torch.randn_like(o)
         tsb = time_fn(lambda: torch.autograd.grad(o, (q, k, v), do, retain_graph=True))
         fl = 4.0 * B * NH * T * T * HS / 2
-        print(f"B{B} T{T} NH{NH} NKVH{NKVH} HS{HS:<14d} {tf:8.3f} (warp {tfw:.3f}) {fl / tf / 1e9:8.1f} {tb:8.3f} {2.5 * fl / tb / 1e9:8.1f} {ts:9.3f} {tsb:9.3f}")
+        print(f"B{B} T{T} NH{NH} NKVH{NKVH} HS{HS:<14d} {tf:8.3f} (warp {tfw:.3f}) {fl / tf / 1e9:8.1f} {tb:8.3f} (warp {tbw:.3f}) {2.5 * fl / tb / 1e9:8.1f} {ts:9.3f} {tsb:9.3f}")
     N.check_status()
 
 

@@ -208,7 +208,10 @@ def test_attention_fwd_bwd(B, T, NH, NKVH, HS):
     assert maxerr(lse, ref_lse) < 0.02
     dout = rnd(B, T, NH * HS)
     ref.backward(dout.float())
+    dqkv_w = attention.attention_bwd(dout, qkv, out, lse, B, T, NH, NKVH, HS, impl="warp")
+    assert maxerr(dqkv_w, qf.grad) < 0.08
     dqkv = attention.attention_bwd(dout, qkv, out, lse, B, T, NH, NKVH, HS)
+    _native.check_status()
     assert maxerr(dqkv, qf.grad) < 0.08
     dqkv2 = attention.attention_bwd(dout, qkv, out, lse, B, T, NH, NKVH, HS)
     assert torch.equal(dqkv, dqkv2)
