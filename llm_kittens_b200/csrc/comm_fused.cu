@@ -107,8 +107,8 @@ __global__ void wait_kernel(const int* my_ctrl, int slot, int epoch, int P, long
 // offset in the fp32 shard buffer, length); lengths are multiples of 8.
 __global__ void __launch_bounds__(TPB)
 rs_bucket_kernel(Peers grads, const int* my_ctrl, int slot, int epoch, const long long* __restrict__ segs,
-                 float* __restrict__ gshard, float* __restrict__ norm_partials, int P, float inv_p, long long limit_ns,
-                 int* status) {
+                 float* __restrict__ gshard, float* __restrict__ norm_partials, int P, float inv_p, int accumulate,
+                 long long limit_ns, int* status) {
     __shared__ float sh[32];
     const bool ok = wait_flags_block(my_ctrl, slot, epoch, P, limit_ns, status, slot);
     const long long* seg = segs + (size_t)blockIdx.y * 3;
@@ -136,6 +136,11 @@ rs_bucket_kernel(Peers grads, const int* my_ctrl, int slot, int epoch, const lon
                 nrm += acc[j] * acc[j];
             }
             float4* dst = reinterpret_cast<float4*>(gshard + s_off + i);
+            if (accumulate) {   // later micro-steps of a sharded-gradient step add to the running shard
+                const float4 o0 = dst[0], o1 = dst[1];
+                acc[0] += o0.x; acc[1] += o0.y; acc[2] += o0.z; acc[3] += o0.w;
+                acc[4] += o1.x; acc[5] += o1.y; acc[6] += o1.z; acc[7] += o1.w;
+            }
             dst[0] = make_float4(acc[0], acc[1], acc[2], acc[3]);
             dst[1] = make_float4(acc[4], acc[5], acc[6], acc[7]);
         }
@@ -177,6 +182,22 @@ norm_exchange_kernel(Peers ctrl, const float* __restrict__ partials, int n, int 
             scale_out[0] = (clip > 0.f && nv > clip) ? clip / nv : 1.0f;
             if (flag_out) flag_out[0] = 0;
         }
+    }
+}
+
+// All-gather of one bucket for sharded parameters: segment table int64[nseg][3] = (offset of the shard in
+// every rank's shard buffer, offset of the full slice in the local staging buffer, shard length);
+// blockIdx.z = source rank. Plain 128-bit peer loads, local stores.
+__global__ void __launch_bounds__(TPB)
+ag_bucket_kernel(Peers shards, bf16* __restrict__ staging, const long long* __restrict__ segs) {
+    const long long* seg = segs + (size_t)blockIdx.y * 3;
+    const size_t s_off = (size_t)seg[0], d_off = (size_t)seg[1], len = (size_t)seg[2];
+    const int r = blockIdx.z;
+    const bf16* src = static_cast<const bf16*>(shards.p[r]) + s_off;
+    bf16* dst = staging + d_off + (size_t)r * len;
+    for (size_t i = ((size_t)blockIdx.x * TPB + threadIdx.x) * 8; i < len; i += (size_t)gridDim.x * TPB * 8) {
+        const uint4 v = ld_volatile_v4(src + i);
+        *reinterpret_cast<uint4*>(dst + i) = v;
     }
 }
 
@@ -272,12 +293,23 @@ LLMK_API int llmk_comm_wait(const void* my_ctrl, int slot, int epoch, int P, lon
 
 // Reduce-scatter + 1/P scale + norm partials for one bucket. norm_partials must hold nseg * grid_x floats.
 LLMK_API int llmk_comm_rs_bucket(const long long* grad_ptrs, const void* my_ctrl, int slot, int epoch, const void* segs, int nseg,
-                                 void* gshard, void* norm_partials, int grid_x, int P, long limit_ns, int* status, void* stream) {
+                                 void* gshard, void* norm_partials, int grid_x, int P, int accumulate, long limit_ns, int* status,
+                                 void* stream) {
     if (P > MAXP || nseg <= 0 || grid_x <= 0) return LLMK_ERR_SHAPE;
     dim3 grid(grid_x, nseg);
     rs_bucket_kernel<<<grid, TPB, 0, (cudaStream_t)stream>>>(make_peers(grad_ptrs, P), (const int*)my_ctrl, slot, epoch,
                                                             (const long long*)segs, (float*)gshard, (float*)norm_partials, P,
-                                                            1.0f / (float)P, (long long)limit_ns, status);
+                                                            1.0f / (float)P, accumulate, (long long)limit_ns, status);
+    LLMK_LAUNCH_CHECK();
+    return LLMK_OK;
+}
+
+// Gather one bucket of sharded parameters from all ranks into the local staging buffer.
+LLMK_API int llmk_comm_ag_bucket(const long long* shard_ptrs, void* staging, const void* segs, int nseg, int grid_x, int P,
+                                 void* stream) {
+    if (P > MAXP || nseg <= 0 || grid_x <= 0) return LLMK_ERR_SHAPE;
+    ag_bucket_kernel<<<dim3(grid_x, nseg, P), TPB, 0, (cudaStream_t)stream>>>(make_peers(shard_ptrs, P), (bf16*)staging,
+                                                                            (const long long*)segs);
     LLMK_LAUNCH_CHECK();
     return LLMK_OK;
 }

@@ -57,6 +57,10 @@ class Transformer:
         self.is_llama = config.family == "llama3"
         # ZeRO-3 style hooks: called with the layer index right before a block's parameters are used
         self.param_hook: Callable[[int | None, str], None] | None = None
+        # sharded-gradient communication: called before a block's backward writes its gradients, and
+        # block buckets are handed over after every micro-step instead of only the last one
+        self.grad_hook: Callable[[int], None] | None = None
+        self.reduce_every_micro_step = False
 
     # ------------------------------------------------------------------ parameters
     def init_weights(self, seed: int = 42) -> None:
@@ -177,13 +181,14 @@ class Transformer:
             return 0 if r >= 2 else l
         return 0 if r >= 1 else l
 
-    def _block_forward(self, l: int, x: torch.Tensor) -> torch.Tensor:
-        """One transformer block; ``x`` is the residual stream input (BT, C); returns the output view."""
+    def _block_forward(self, l: int, x: torch.Tensor, phase: str = "forward") -> torch.Tensor:
+        """One transformer block; ``x`` is the residual stream input (BT, C); returns the output view.
+        ``phase`` is handed to the parameter hook: ``backward`` when the block is re-run for recomputation."""
         cfg, a, p = self.config, self.acts, self.p
         B, T = self.B, self.T
         k, n, gi = self._idx(l, "k"), self._idx(l, "n"), self._idx(l, "g")
         if self.param_hook:
-            self.param_hook(l, "forward")
+            self.param_hook(l, phase)
         ln1, ln2 = a["ln1"][n], a["ln2"][n]
         mean1 = None if self.is_llama else a["ln1_mean"][k]
         mean2 = None if self.is_llama else a["ln2_mean"][k]
@@ -301,11 +306,13 @@ class Transformer:
         for l in range(L - 1, -1, -1):
             if self.recompute >= 3:
                 x_in = a["block_in"][l]
-                self._block_forward(l, x_in)
+                self._block_forward(l, x_in, phase="backward")
             else:
                 x_in = a["encoded"] if l == 0 else a["res3"][l - 1]
                 if self.param_hook:
                     self.param_hook(l, "backward")
+            if self.grad_hook:
+                self.grad_hook(l)
             k, n, gi = self._idx(l, "k"), self._idx(l, "n"), self._idx(l, "g")
             ln1, ln2 = a["ln1"][n], a["ln2"][n]
             mean1 = None if self.is_llama else a["ln1_mean"][k]
@@ -336,7 +343,7 @@ class Transformer:
                 ew.dbias(g["qkvb"][l], dqkv, accumulate=True)
             self._norm_bwd(dres, g["ln1w"][l], None if self.is_llama else g["ln1b"][l], d_btc, x_in, p["ln1w"][l], mean1,
                            a["ln1_rstd"][k], accumulate=True)
-            if last_micro_step and bucket_ready is not None:
+            if (last_micro_step or self.reduce_every_micro_step) and bucket_ready is not None:
                 bucket_ready(l)
         if self.param_hook:
             self.param_hook(None, "embedding")

@@ -54,6 +54,10 @@ def make_comm(plan: ZeroPlan, model, world: int, rank: int, device: torch.device
         return SingleProcessComm(plan)
     if prefer in ("auto", "fused") and device.type == "cuda":
         try:
+            if plan.stage >= 2 and not plan._has_experts():
+                from .sharded import ShardedComm
+
+                return ShardedComm(plan, model, device)   # gradients (and parameters) really sharded
             from .fused import FusedComm
 
             return FusedComm(plan, model, device)

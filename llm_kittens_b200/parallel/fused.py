@@ -119,13 +119,13 @@ class FusedComm:
         table, nseg, base = self.buckets[layer]
         with torch.cuda.stream(self.stream):
             N.call("llmk_comm_rs_bucket", self.grad_ptrs, self.ctrl, slot, self.epoch, table, nseg, self.gshard,
-                   self.partials[base:], self.grid_x, self.world_size, self.limit_ns, N.status_word())
+                   self.partials[base:], self.grid_x, self.world_size, 0, self.limit_ns, N.status_word())
 
     def finish_reduce(self) -> None:
         if self.expert_table is not None:
             # epoch 0 is always satisfied: no peer is involved in this copy
             N.call("llmk_comm_rs_bucket", self.own_grad_ptr, self.ctrl, 0, 0, self.expert_table, int(self.expert_table.shape[0]),
-                   self.gshard, self.partials[self.expert_base:], self.grid_x, 1, self.limit_ns, N.status_word())
+                   self.gshard, self.partials[self.expert_base:], self.grid_x, 1, 0, self.limit_ns, N.status_word())
         torch.cuda.current_stream().wait_stream(self.stream)
 
     def norm_and_clip(self, clip: float, scale: torch.Tensor, norm: torch.Tensor, flag: torch.Tensor) -> None:

@@ -22,7 +22,7 @@ def save_checkpoint(output_dir: str, step: int, trainer, loader, world: int, ran
     model_path, state_path, done_path = formats.checkpoint_paths(output_dir, step, rank)
     cfg = trainer.model.config
     if rank == 0:
-        formats.write_model(model_path, cfg, trainer.model.params)
+        formats.write_model(model_path, cfg, trainer.full_params())
     formats.write_state(state_path, cfg.family, world, rank, step, trainer.m, trainer.v, trainer.master,
                         trainer.rng.state, trainer.rng_state_last_update,
                         loader.current_shard_idx if loader is not None else 0,

@@ -42,7 +42,9 @@ class Trainer:
         self.cuda = self.device.type == "cuda"
         self.plan = ZeroPlan(model.config, num_processes, rank, zero_stage)
         self.comm = comm if comm is not None else SingleProcessComm(self.plan)
-        self.use_master = use_master_weights and model.params.dtype != torch.float32
+        self.sharded_state = getattr(self.comm, "sharded_state", False)   # real ZeRO-2/3: the comm owns shard buffers
+        param_dtype = model.params.dtype if model.params is not None else torch.bfloat16
+        self.use_master = use_master_weights and param_dtype != torch.float32
         self.lr, self.wd, self.beta1, self.beta2, self.eps, self.grad_clip = learning_rate, weight_decay, beta1, beta2, eps, grad_clip
         self.step_count = 0
         self.rng = Xorshift(rng_state)
@@ -102,7 +104,9 @@ class Trainer:
 
     def _ensure_master(self) -> None:
         if self.use_master and not self._master_ready:
-            if self.native:
+            if self.sharded_state:
+                self.comm.master_from_shard(self.master)
+            elif self.native:
                 from ..ops import optim
 
                 optim.master_from_params(self.master, self.model.params, self.segs, self.max_len)
@@ -141,6 +145,8 @@ class Trainer:
         batches = list(micro_batches)
         accum = len(batches)
         for i, (x, y) in enumerate(batches):
+            if self.sharded_state:
+                self.comm.start_micro_step(i)
             model.forward(x, y, grad_accum_steps=accum, micro_step=i)
             model.backward(last_micro_step=(i == accum - 1), bucket_ready=self._bucket_ready)
         return accum
@@ -177,7 +183,10 @@ class Trainer:
         self._ensure_master()
         self.rng_state_last_update = self.rng.state
         seed = self.rng.u32()
-        if getattr(self.comm, "fused", False):
+        if self.sharded_state:
+            self.comm.adamw_shard(self.master, self.m, self.v, lr, self.beta1, self.beta2, self.step_count + 1, self.eps,
+                                  self.wd, self.scale, seed)
+        elif getattr(self.comm, "fused", False):
             self.comm.adamw_push(self.master, self.m, self.v, lr, self.beta1, self.beta2, self.step_count + 1, self.eps,
                                  self.wd, self.scale, seed)
         else:
@@ -211,6 +220,12 @@ class Trainer:
         self.model.forward(tokens, targets, grad_accum_steps=1, micro_step=0, compute_dlogits=False)
         return self.model.mean_loss()
 
+    def full_params(self) -> torch.Tensor:
+        """The complete bf16 parameter vector in checkpoint order (a collective when parameters are sharded)."""
+        if self.model.params is None:
+            return self.comm.materialize_params()
+        return self.model.params
+
     def restore_params_from_master(self) -> None:
         """Re-derive the bf16 parameters of this rank's shard from the fp32 master copy with the
         rounding noise of the last update (bit-exact resume), then gather the other shards."""
@@ -218,6 +233,10 @@ class Trainer:
             return
         rng = Xorshift(self.rng_state_last_update)
         seed = rng.u32()
+        if self.sharded_state:
+            self.comm.shard_from_master(self.master, seed)
+            self._master_ready = True
+            return
         if self.native:
             from ..ops import optim
 

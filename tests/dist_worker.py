@@ -5,9 +5,12 @@ modes:
   cpu_zero<k>      gloo, PyTorch oracle model in fp32, ZeRO stage k, library collectives
   gpu_library<k>   NCCL, CUDA model, ZeRO stage k, library collectives
   gpu_fused        NCCL bootstrap, CUDA model, ZeRO-1 through the fused peer-memory kernels
+  gpu_sharded<k>   ZeRO stage 2 / 3 with really sharded gradients / parameters (peer-memory kernels); every
+                   step is split into two micro-steps so that the shard accumulation is exercised
   gpu_moe_library1 / gpu_moe_fused   mixture-of-experts model, experts split over the ranks (peer-memory
                    dispatch / combine), dense parameters ZeRO-1 through library / fused communication
   cpu_fail_rank1   gloo; rank 1 raises before its first collective (failure-detection test)
+environment: LLMK_TEST_LAYERS (dense model depth, default 2), LLMK_TEST_RECOMPUTE (default 0)
 Each rank writes ``rank<r>.pt`` with its per-step losses / norms and a parameter checksum sample.
 """
 import datetime
@@ -26,7 +29,8 @@ from llm_kittens_b200.runtime.trainer import Trainer  # noqa: E402
 
 
 def tiny_config():
-    return ModelConfig(family="gpt2", max_seq_len=64, vocab_size=512, padded_vocab_size=512, num_layers=2, num_heads=2,
+    layers = int(os.environ.get("LLMK_TEST_LAYERS", "2"))
+    return ModelConfig(family="gpt2", max_seq_len=64, vocab_size=512, padded_vocab_size=512, num_layers=layers, num_heads=2,
                        num_kv_heads=2, channels=128, hidden_dim=512)
 
 
@@ -87,13 +91,17 @@ def main():
     else:
         from llm_kittens_b200.models.transformer import Transformer
 
-        model = Transformer(cfg, device=device, recompute=0)
+        model = Transformer(cfg, device=device, recompute=int(os.environ.get("LLMK_TEST_RECOMPUTE", "0")))
     model.init_weights(42)
     plan = ZeroPlan(cfg, world, rank, stage)
     if mode in ("gpu_fused", "gpu_moe_fused"):
         from llm_kittens_b200.parallel.fused import FusedComm
 
         comm = FusedComm(plan, model, device, timeout_ms=20000)
+    elif mode.startswith("gpu_sharded"):
+        from llm_kittens_b200.parallel.sharded import ShardedComm
+
+        comm = ShardedComm(plan, model, device, timeout_ms=20000)
     else:
         comm = LibraryComm(plan, None, device)
     trainer = Trainer(model, zero_stage=stage, use_master_weights=True, learning_rate=1e-3, weight_decay=0.1, comm=comm,
@@ -101,14 +109,17 @@ def main():
     losses, norms = [], []
     for x, y in global_batches(cfg, steps, world, B, T):
         xs, ys = x[rank * B:(rank + 1) * B].contiguous(), y[rank * B:(rank + 1) * B].contiguous()
-        r = trainer.train_step([(xs, ys)])
+        if mode.startswith("gpu_sharded"):
+            r = trainer.train_step([(xs[:1].contiguous(), ys[:1].contiguous()), (xs[1:].contiguous(), ys[1:].contiguous())])
+        else:
+            r = trainer.train_step([(xs, ys)])
         losses.append(r.loss)
         norms.append(r.grad_norm)
     if not cpu:
         from llm_kittens_b200.ops import _native
 
         _native.check_status()
-    torch.save({"losses": losses, "norms": norms, "params": model.params.float().cpu()}, os.path.join(out_dir, f"rank{rank}.pt"))
+    torch.save({"losses": losses, "norms": norms, "params": (trainer.full_params() if not cpu else model.params).float().cpu()}, os.path.join(out_dir, f"rank{rank}.pt"))
     dist.barrier()
     dist.destroy_process_group()
 

@@ -16,12 +16,12 @@ def _need_two_gpus():
         pytest.skip("needs two GPUs")
 
 
-def _run(mode, tmp_path):
+def _run(mode, tmp_path, **env):
     from test_dist_cpu import launch
 
-    d = tmp_path / mode
+    d = tmp_path / (mode + "".join(f"_{k}{v}" for k, v in env.items()))
     d.mkdir()
-    outs = launch(mode, d, extra_env={"NCCL_NVLS_ENABLE": "0", "TORCH_SYMM_MEM_DISABLE_MULTICAST": "1"})
+    outs = launch(mode, d, extra_env={"NCCL_NVLS_ENABLE": "0", "TORCH_SYMM_MEM_DISABLE_MULTICAST": "1", **env})
     for rc, out in outs:
         assert rc == 0, out[-3000:]
     return torch.load(d / "rank0.pt"), torch.load(d / "rank1.pt")
@@ -60,3 +60,21 @@ def test_expert_parallel_moe_matches_single_process(tmp_path):
         for a, b in zip(r0["losses"], ref):
             assert abs(a - b) < 0.03, (mode, r0["losses"], ref)
         assert r0["losses"][-1] < r0["losses"][0]
+
+
+@pytest.mark.parametrize("stage,recompute", [(2, 0), (3, 0), (3, 3)])
+def test_sharded_zero_stages_match_library(tmp_path, stage, recompute):
+    """Really sharded gradients (stage 2) and parameters (stage 3), two micro-steps per step, four blocks
+    (so that the two bucket slots are reused inside a micro-step): same training as the library path."""
+    _need_two_gpus()
+    env = {"LLMK_TEST_LAYERS": "4", "LLMK_TEST_RECOMPUTE": str(recompute)}
+    s0, s1 = _run(f"gpu_sharded{stage}", tmp_path, **env)
+    l0, _ = _run("gpu_library1", tmp_path, **env)
+    assert torch.equal(s0["params"], s1["params"])
+    assert s0["losses"] == s1["losses"]
+    for a, b in zip(s0["losses"], l0["losses"]):
+        assert abs(a - b) < 0.02, (s0["losses"], l0["losses"])
+    for a, b in zip(s0["norms"], l0["norms"]):
+        assert abs(a - b) < 0.03 * max(1.0, b)
+    assert (s0["params"] - l0["params"]).abs().max().item() < 0.02
+    assert s0["losses"][-1] < s0["losses"][0]
