@@ -125,6 +125,12 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQKV, bf16* __restrict__
     using C = Cfg<HS>;
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     uint8_t* smem = smem_raw;
+    {   // a failure already recorded in the status word (by an earlier CTA or kernel) makes the rest return at once
+        __shared__ int skip;
+        if (threadIdx.x == 0) skip = (status != nullptr && *reinterpret_cast<volatile int*>(status) != 0);
+        __syncthreads();
+        if (skip) return;
+    }
     if (ptx::smem_u32(smem) & 1023u) {  // swizzled tiles need a 1024-byte aligned window: refuse instead of corrupting
         if (threadIdx.x == 0 && status != nullptr) atomicCAS(status, 0, LLMK_ST_BOUNDS);
         return;
@@ -395,6 +401,12 @@ attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_con
                      int T, int NH, int NKVH, float scale_log2, int* status) {
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     uint8_t* smem = smem_raw;
+    {   // a failure already recorded in the status word (by an earlier CTA or kernel) makes the rest return at once
+        __shared__ int skip;
+        if (threadIdx.x == 0) skip = (status != nullptr && *reinterpret_cast<volatile int*>(status) != 0);
+        __syncthreads();
+        if (skip) return;
+    }
     if (ptx::smem_u32(smem) & 1023u) {
         if (threadIdx.x == 0 && status != nullptr) atomicCAS(status, 0, LLMK_ST_BOUNDS);
         return;
@@ -489,19 +501,19 @@ attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_con
             const uint64_t k_desc = ptx::make_smem_desc(ptx::smem_u32(sK), 16, 1024);
             const uint64_t p_desc = ptx::make_smem_desc(ptx::smem_u32(sP + i * P_BYTES), 16, 1024);
             const uint64_t v_desc = ptx::make_smem_desc(ptx::smem_u32(sV), ATOM_BYTES, 1024);
-            bool ok = ptx::mbar_wait(q_full, 0, abort_flag, status, LLMK_ST_TIMEOUT_TMA_FULL, -1);
+            bool ok = ptx::mbar_wait_spin(q_full, 0, abort_flag, status, LLMK_ST_TIMEOUT_TMA_FULL, -1);
             if (ni == 0) {
                 // idle half (sequence ends inside this block): still release the K/V stages for the other issuer
                 for (int j = 0; j < nmax && ok; j++) {
-                    ok = ptx::mbar_wait(&kv_full[j % STAGES], (j / STAGES) & 1, abort_flag, status, LLMK_ST_TIMEOUT_TMA_FULL, j);
+                    ok = ptx::mbar_wait_spin(&kv_full[j % STAGES], (j / STAGES) & 1, abort_flag, status, LLMK_ST_TIMEOUT_TMA_FULL, j);
                     if (ok) ptx::mbar_arrive(&kv_empty[j % STAGES]);
                 }
             }
             for (int j = 0; j <= ni && ok && ni > 0; j++) {
                 if (j < ni) {
                     const int s = j % STAGES;
-                    ok = ptx::mbar_wait(&kv_full[s], (j / STAGES) & 1, abort_flag, status, LLMK_ST_TIMEOUT_TMA_FULL, j);
-                    if (ok && j > 0) ok = ptx::mbar_wait(&s_free[i], (j - 1) & 1, abort_flag, status, LLMK_ST_TIMEOUT_ACC_EMPTY, 3000 + j);
+                    ok = ptx::mbar_wait_spin(&kv_full[s], (j / STAGES) & 1, abort_flag, status, LLMK_ST_TIMEOUT_TMA_FULL, j);
+                    if (ok && j > 0) ok = ptx::mbar_wait_spin(&s_free[i], (j - 1) & 1, abort_flag, status, LLMK_ST_TIMEOUT_ACC_EMPTY, 3000 + j);
                     if (!ok) break;
                     ptx::tc_fence_after();
                     const uint64_t kd = k_desc + (uint64_t)((s * TILE_BYTES) >> 4);
@@ -512,7 +524,7 @@ attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_con
                 }
                 if (j > 0) {
                     const int jj = j - 1, s = jj % STAGES;
-                    ok = ptx::mbar_wait(&p_full[i], jj & 1, abort_flag, status, LLMK_ST_TIMEOUT_ACC_EMPTY, jj);
+                    ok = ptx::mbar_wait_spin(&p_full[i], jj & 1, abort_flag, status, LLMK_ST_TIMEOUT_ACC_EMPTY, jj);
                     if (!ok) break;
                     ptx::tc_fence_after();
                     const uint64_t vd = v_desc + (uint64_t)((s * TILE_BYTES) >> 4);
@@ -601,6 +613,7 @@ attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_con
             __syncwarp();
             if (lane == 0) ptx::mbar_arrive(&p_full[half]);
         }
+
         if (ok) ok = ptx::mbar_wait(&o_full[half], (nkv - 1) & 1, abort_flag, status, LLMK_ST_TIMEOUT_ACC_FULL, 2000);
         if (ok) {
             // O -> bf16 -> this warpgroup's P buffer (128 rows x 128 B, swizzled like the tensor map) -> one TMA store

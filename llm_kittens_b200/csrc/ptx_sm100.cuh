@@ -101,6 +101,30 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
     }
 }
 
+// Same contract as mbar_wait, but the thread never suspends: it polls with test_wait. For MMA issuer threads,
+// whose tcgen05.commit arrivals were observed to be delivered late while the thread sat suspended in try_wait.
+__device__ __forceinline__ bool mbar_wait_spin(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int* status,
+                                               int code, int tag) {
+    if (mbar_poll(bar, parity)) return true;
+    const uint64_t t0 = globaltimer_ns();
+    uint32_t spins = 0;
+    while (true) {
+        if (mbar_poll(bar, parity)) return true;
+        if ((++spins & 0xfffu) == 0) {
+            if (*abort_flag) return false;
+            if (globaltimer_ns() - t0 > LLMK_WAIT_LIMIT_NS) {
+                *abort_flag = 1;
+                if (status != nullptr && atomicCAS(status, 0, code) == 0) {
+                    status[1] = tag;
+                    status[2] = (int)blockIdx.x;
+                    status[3] = (int)threadIdx.x;
+                }
+                return false;
+            }
+        }
+    }
+}
+
 // ------------------------------------------------------------------ proxies / fences
 __device__ __forceinline__ void fence_proxy_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 
