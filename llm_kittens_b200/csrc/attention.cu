@@ -265,27 +265,39 @@ attn_fwd_kernel(bf16* __restrict__ out, float* __restrict__ lse, const bf16* __r
 }
 
 // ================================================================== backward pre-pass: D = rowsum(dO * O)
-__global__ void attn_bwd_prep_kernel(float* __restrict__ dvec, const bf16* __restrict__ out, const bf16* __restrict__ dout,
-                                     int BT, int NH, int HS, int T) {
-    // one warp per (token, head)
-    const size_t w = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
-    const int lane = threadIdx.x & 31;
-    if (w >= (size_t)BT * NH) return;
-    const size_t bt = w / NH;
-    const int h = w % NH;
-    const bf16* o = out + (bt * NH + h) * HS;
-    const bf16* d = dout + (bt * NH + h) * HS;
+// HS/8 lanes per (batch, head, token) row, 16-byte loads; consecutive rows are consecutive tokens of one head,
+// so the fp32 results are written coalesced and every 128-byte line of O / dO is read by one lane group.
+template <int HS>
+__global__ void __launch_bounds__(256) attn_bwd_prep_kernel(float* __restrict__ dvec, const bf16* __restrict__ out,
+                                                            const bf16* __restrict__ dout, long rows, int NH, int T) {
+    constexpr int G = HS / 8;
+    const long row = ((long)blockIdx.x * blockDim.x + threadIdx.x) / G;   // = (b * NH + h) * T + t
+    const int sub = threadIdx.x % G;
     float acc = 0.f;
-    for (int c = lane * 2; c < HS; c += 64) {
-        const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(o + c));
-        const float2 e = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(d + c));
-        acc += a.x * e.x + a.y * e.y;
+    if (row < rows) {
+        const long bh = row / T;
+        const int t = (int)(row % T);
+        const long b = bh / NH;
+        const int h = (int)(bh % NH);
+        const size_t off = (((size_t)b * T + t) * NH + h) * HS + sub * 8;
+        float o[8], d[8];
+        unpack8(ld128_stream(out + off), o);
+        unpack8(ld128_stream(dout + off), d);
+#pragma unroll
+        for (int i = 0; i < 8; i++) acc = fmaf(o[i], d[i], acc);
     }
-    acc = warp_sum(acc);
-    if (lane == 0) {
-        const size_t b = bt / T, t = bt % T;
-        dvec[(b * NH + h) * T + t] = acc;
-    }
+#pragma unroll
+    for (int m = G / 2; m > 0; m >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, m);
+    if (row < rows && sub == 0) dvec[row] = acc;
+}
+
+static int launch_bwd_prep(float* dvec, const bf16* out, const bf16* dout, int B, int T, int NH, int HS, cudaStream_t stream) {
+    const long rows = (long)B * NH * T;
+    if (HS == 64) attn_bwd_prep_kernel<64><<<ceil_div(rows * 8, 256), 256, 0, stream>>>(dvec, out, dout, rows, NH, T);
+    else if (HS == 128) attn_bwd_prep_kernel<128><<<ceil_div(rows * 16, 256), 256, 0, stream>>>(dvec, out, dout, rows, NH, T);
+    else return LLMK_ERR_SHAPE;
+    LLMK_LAUNCH_CHECK();
+    return LLMK_OK;
 }
 
 // ================================================================== backward: dK, dV (KV-tile owned)
@@ -533,10 +545,7 @@ LLMK_API int llmk_attention_bwd(void* dqkv, void* dvec, const void* dout, const 
     if (T % 64 || NH % NKVH || (HS != 64 && HS != 128)) return LLMK_ERR_SHAPE;
     const float scale = 1.0f / sqrtf((float)HS);
     const float scale_log2 = 1.4426950408889634f * scale;
-    const long warps = (long)B * T * NH;
-    attn_bwd_prep_kernel<<<ceil_div(warps * 32, 256), 256, 0, stream>>>((float*)dvec, (const bf16*)out, (const bf16*)dout, B * T,
-                                                                       NH, HS, T);
-    LLMK_LAUNCH_CHECK();
+    if (int prc = launch_bwd_prep((float*)dvec, (const bf16*)out, (const bf16*)dout, B, T, NH, HS, stream)) return prc;
     dim3 gkv(T / BKV, NKVH, B), gq(T / BQ, NH, B);
     int rc;
     if (HS == 64) {
@@ -563,9 +572,5 @@ LLMK_API int llmk_attention_bwd(void* dqkv, void* dvec, const void* dout, const 
 // D = rowsum(dO * O) as [B, NH, T] fp32: the pre-pass shared by both backward implementations.
 LLMK_API int llmk_attention_bwd_prep(void* dvec, const void* dout, const void* out, int B, int T, int NH, int HS, void* stream_) {
     cudaStream_t stream = (cudaStream_t)stream_;
-    const long warps = (long)B * T * NH;
-    attn_bwd_prep_kernel<<<ceil_div(warps * 32, 256), 256, 0, stream>>>((float*)dvec, (const bf16*)out, (const bf16*)dout, B * T,
-                                                                       NH, HS, T);
-    LLMK_LAUNCH_CHECK();
-    return LLMK_OK;
+    return launch_bwd_prep((float*)dvec, (const bf16*)out, (const bf16*)dout, B, T, NH, HS, stream);
 }

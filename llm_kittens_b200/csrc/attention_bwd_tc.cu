@@ -47,6 +47,27 @@ template <int ROWS>
 __device__ __forceinline__ uint64_t mnmajor_desc(uint32_t base, int kk) {
     return ptx::make_smem_desc(base + kk * 2048, ROWS * 128, 1024);
 }
+// The same descriptors by arithmetic on a base descriptor built once per buffer (the start-address field holds
+// bytes / 16): inside the issue loops an operand then costs one 64-bit add instead of a rebuild.
+template <int ROWS>
+__device__ __forceinline__ uint64_t kmajor_step(uint64_t base_desc, int kk) {
+    return base_desc + (uint64_t)(((kk / 4) * (ROWS * 128) + (kk % 4) * 32) >> 4);
+}
+__device__ __forceinline__ uint64_t mnmajor_step(uint64_t base_desc, int kk) { return base_desc + (uint64_t)((kk * 2048) >> 4); }
+
+// Returns true (for the whole CTA) when the status word already holds a failure: the kernel then returns at once.
+__device__ __forceinline__ bool already_failed(const int* status) {
+    __shared__ int skip;
+    if (threadIdx.x == 0) skip = (status != nullptr && *reinterpret_cast<const volatile int*>(status) != 0);
+    __syncthreads();
+    return skip != 0;
+}
+
+// One 128-row x 64-column bf16 tile row (this thread's row r) into a TMA-store staging tile, 16-byte chunk `chunk`.
+__device__ __forceinline__ void stage_chunk(uint8_t* tile, int r, int chunk, const float* f) {
+    *reinterpret_cast<bf16x8*>(tile + r * 128 + ((chunk ^ (r & 7)) << 4)) = pack8(f);
+}
+
 template <int HS, int ROWS>
 __device__ __forceinline__ void load_tile(uint8_t* dst, const CUtensorMap* tm, uint64_t* bar, int col, int row) {
 #pragma unroll
@@ -82,11 +103,13 @@ struct DkvCfg {
 template <int HS>
 __global__ void __launch_bounds__(THREADS, Inner<HS>::CTAS)
 attn_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_constant__ CUtensorMap tmQKVin,
-                       const __grid_constant__ CUtensorMap tmDOin, bf16* __restrict__ dqkv, const float* __restrict__ lse,
-                       const float* __restrict__ dvec, int T, int NH, int NKVH, float scale, int* status) {
+                       const __grid_constant__ CUtensorMap tmDOin, const __grid_constant__ CUtensorMap tmDQKV,
+                       const float* __restrict__ lse, const float* __restrict__ dvec, int T, int NH, int NKVH, float scale,
+                       int* status) {
     using C = DkvCfg<HS>;
     constexpr int RING = C::RING, BN = C::BN;
     extern __shared__ __align__(1024) uint8_t smem[];
+    if (already_failed(status)) return;
     if (ptx::smem_u32(smem) & 1023u) {
         if (threadIdx.x == 0 && status != nullptr) atomicCAS(status, 0, LLMK_ST_BOUNDS);
         return;
@@ -105,7 +128,8 @@ attn_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_c
     uint64_t* p_full = bars + 6;
     uint64_t* acc_done = bars + 7;
     uint64_t* ld_full = bars + 8;     // [2] LSE / D vectors of a ring slot are in shared memory
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 10);
+    uint64_t* epi = bars + 10;        // dK / dV staged in shared memory
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 11);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -128,6 +152,7 @@ attn_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_c
         ptx::mbar_init(s_full, 1);
         ptx::mbar_init(p_full, 4);
         ptx::mbar_init(acc_done, 1);
+        ptx::mbar_init(epi, 4);
         *abort_flag = 0;
         ptx::fence_barrier_init();
     }
@@ -174,19 +199,23 @@ attn_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_c
         constexpr uint32_t idesc_s = ptx::make_idesc_bf16(BM, BN, 0, 0);
         constexpr uint32_t idesc_acc = ptx::make_idesc_bf16(BM, HS, 0, 1);
         bool ok = ptx::mbar_wait(kv_full, 0, abort_flag, status, LLMK_ST_TIMEOUT_TMA_FULL, -1);
+        // descriptors are built once; only lane 0 runs the issue loop (it shares its scheduler with softmax warps,
+        // so every instruction saved here shortens the critical path)
+        const uint64_t k_desc = kmajor_desc<BM>(ptx::smem_u32(sK), 0), v_desc = kmajor_desc<BM>(ptx::smem_u32(sV), 0);
+        const uint64_t pt_desc = kmajor_desc<BM>(ptx::smem_u32(sPt), 0), dst_desc = kmajor_desc<BM>(ptx::smem_u32(sdSt), 0);
+        const uint32_t ring_addr = ptx::smem_u32(sRing);
         auto issue_s = [&](int it) -> bool {
             const int s = it % RING;
             if (!ptx::mbar_wait(&ring_full[s], (it / RING) & 1, abort_flag, status, LLMK_ST_TIMEOUT_TMA_FULL, it)) return false;
             ptx::tc_fence_after();
             if (lane == 0) {
-                const uint32_t k_addr = ptx::smem_u32(sK), v_addr = ptx::smem_u32(sV);
-                const uint32_t q_addr = ptx::smem_u32(sRing + s * 2 * C::RT), do_addr = q_addr + C::RT;
+                const uint64_t q_desc = kmajor_desc<BN>(ring_addr + s * 2 * C::RT, 0), do_desc = kmajor_desc<BN>(ring_addr + s * 2 * C::RT + C::RT, 0);
 #pragma unroll
                 for (int kk = 0; kk < HS / 16; kk++)
-                    ptx::mma_f16_ss(t_st, kmajor_desc<BM>(k_addr, kk), kmajor_desc<BN>(q_addr, kk), idesc_s, kk > 0 ? 1u : 0u);
+                    ptx::mma_f16_ss(t_st, kmajor_step<BM>(k_desc, kk), kmajor_step<BN>(q_desc, kk), idesc_s, kk > 0 ? 1u : 0u);
 #pragma unroll
                 for (int kk = 0; kk < HS / 16; kk++)
-                    ptx::mma_f16_ss(t_dpt, kmajor_desc<BM>(v_addr, kk), kmajor_desc<BN>(do_addr, kk), idesc_s, kk > 0 ? 1u : 0u);
+                    ptx::mma_f16_ss(t_dpt, kmajor_step<BM>(v_desc, kk), kmajor_step<BN>(do_desc, kk), idesc_s, kk > 0 ? 1u : 0u);
                 ptx::mma_commit(s_full);
             }
             __syncwarp();
@@ -195,16 +224,13 @@ attn_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_c
         auto issue_acc = [&](int it) {
             const int s = it % RING;
             if (lane == 0) {
-                const uint32_t q_addr = ptx::smem_u32(sRing + s * 2 * C::RT), do_addr = q_addr + C::RT;
-                const uint32_t pt_addr = ptx::smem_u32(sPt), dst_addr = ptx::smem_u32(sdSt);
+                const uint64_t q_mn = mnmajor_desc<BN>(ring_addr + s * 2 * C::RT, 0), do_mn = mnmajor_desc<BN>(ring_addr + s * 2 * C::RT + C::RT, 0);
 #pragma unroll
                 for (int kk = 0; kk < BN / 16; kk++)
-                    ptx::mma_f16_ss(t_dv, kmajor_desc<BM>(pt_addr, kk), mnmajor_desc<BN>(do_addr, kk), idesc_acc,
-                                    (it > 0 || kk > 0) ? 1u : 0u);
+                    ptx::mma_f16_ss(t_dv, kmajor_step<BM>(pt_desc, kk), mnmajor_step(do_mn, kk), idesc_acc, (it > 0 || kk > 0) ? 1u : 0u);
 #pragma unroll
                 for (int kk = 0; kk < BN / 16; kk++)
-                    ptx::mma_f16_ss(t_dk, kmajor_desc<BM>(dst_addr, kk), mnmajor_desc<BN>(q_addr, kk), idesc_acc,
-                                    (it > 0 || kk > 0) ? 1u : 0u);
+                    ptx::mma_f16_ss(t_dk, kmajor_step<BM>(dst_desc, kk), mnmajor_step(q_mn, kk), idesc_acc, (it > 0 || kk > 0) ? 1u : 0u);
                 ptx::mma_commit(&ring_empty[s]);
                 ptx::mma_commit(acc_done);
             }
@@ -252,14 +278,18 @@ attn_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_c
                 ptx::tmem_ld_wait();
 #pragma unroll
                 for (int q = 0; q < 4; q++) {
-                    float p[8], ds[8];
+                    float p[8], ds[8], L[8], D[8];
+                    *reinterpret_cast<float4*>(L) = *reinterpret_cast<const float4*>(sL + c4 * 32 + q * 8);
+                    *reinterpret_cast<float4*>(L + 4) = *reinterpret_cast<const float4*>(sL + c4 * 32 + q * 8 + 4);
+                    *reinterpret_cast<float4*>(D) = *reinterpret_cast<const float4*>(sD + c4 * 32 + q * 8);
+                    *reinterpret_cast<float4*>(D + 4) = *reinterpret_cast<const float4*>(sD + c4 * 32 + q * 8 + 4);
 #pragma unroll
                     for (int i = 0; i < 8; i++) {
                         const int c = c4 * 32 + q * 8 + i;   // query column of the sub-tile
-                        float e = ex2(fmaf(__uint_as_float(vs[q * 8 + i]), scale_log2, -sL[c]));
+                        float e = ex2(fmaf(__uint_as_float(vs[q * 8 + i]), scale_log2, -L[i]));
                         if (diag && r > c + dq0) e = 0.f;     // key after query
                         p[i] = e;
-                        ds[i] = e * (__uint_as_float(vd[q * 8 + i]) - sD[c]);
+                        ds[i] = e * (__uint_as_float(vd[q * 8 + i]) - D[i]);
                     }
                     store_chunk(sPt, r, c4 * 4 + q, p);
                     store_chunk(sdSt, r, c4 * 4 + q, ds);
@@ -273,9 +303,9 @@ attn_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_c
         if (ok) ok = ptx::mbar_wait(acc_done, (total - 1) & 1, abort_flag, status, LLMK_ST_TIMEOUT_ACC_FULL, 2000);
         if (ok) {
             ptx::tc_fence_after();
-            const int width = (NH + 2 * NKVH) * HS;
-            bf16* dk_row = dqkv + (size_t)(row_base + kv0 + r) * width + k_col;
-            bf16* dv_row = dqkv + (size_t)(row_base + kv0 + r) * width + v_col;
+            // dK (scaled) and dV -> bf16 -> the P^T / dS^T buffers as [128 x 64] staging tiles per 64 columns -> TMA stores
+            uint8_t* stage_dk = sPt;    // HS/64 tiles of 16 KB each fit: BM*BN*2 >= BM*HS*2 for both head sizes
+            uint8_t* stage_dv = sdSt;
 #pragma unroll
             for (int h4 = 0; h4 < HS / 32; h4++) {
                 uint32_t v[32];
@@ -286,7 +316,7 @@ attn_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_c
                     float f[8];
 #pragma unroll
                     for (int i = 0; i < 8; i++) f[i] = __uint_as_float(v[q * 8 + i]) * scale;
-                    st128(dk_row + h4 * 32 + q * 8, pack8(f));
+                    stage_chunk(stage_dk + (h4 / 2) * (BM * 128), r, (h4 & 1) * 4 + q, f);
                 }
                 ptx::tmem_ld_32x32b_x32(t_dv + lane_off + h4 * 32, v);
                 ptx::tmem_ld_wait();
@@ -295,7 +325,21 @@ attn_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_c
                     float f[8];
 #pragma unroll
                     for (int i = 0; i < 8; i++) f[i] = __uint_as_float(v[q * 8 + i]);
-                    st128(dv_row + h4 * 32 + q * 8, pack8(f));
+                    stage_chunk(stage_dv + (h4 / 2) * (BM * 128), r, (h4 & 1) * 4 + q, f);
+                }
+            }
+            ptx::fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0) ptx::mbar_arrive(epi);
+            if (warp == 2 && lane == 0) {
+                if (ptx::mbar_wait(epi, 0, abort_flag, status, LLMK_ST_TIMEOUT_ACC_FULL, 4000)) {
+#pragma unroll
+                    for (int c = 0; c < HS / 64; c++) {
+                        ptx::tma_store_2d(&tmDQKV, stage_dk + c * (BM * 128), k_col + 64 * c, row_base + kv0);
+                        ptx::tma_store_2d(&tmDQKV, stage_dv + c * (BM * 128), v_col + 64 * c, row_base + kv0);
+                    }
+                    ptx::tma_store_commit();
+                    ptx::tma_store_wait_read<0>();
                 }
             }
         }
@@ -324,11 +368,13 @@ struct DqCfg {
 template <int HS>
 __global__ void __launch_bounds__(THREADS, Inner<HS>::CTAS)
 attn_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_constant__ CUtensorMap tmDO,
-                      const __grid_constant__ CUtensorMap tmQKVin, bf16* __restrict__ dqkv, const float* __restrict__ lse,
-                      const float* __restrict__ dvec, int T, int NH, int NKVH, float scale, int* status) {
+                      const __grid_constant__ CUtensorMap tmQKVin, const __grid_constant__ CUtensorMap tmDQKV,
+                      const float* __restrict__ lse, const float* __restrict__ dvec, int T, int NH, int NKVH, float scale,
+                      int* status) {
     using C = DqCfg<HS>;
     constexpr int BN = C::BN;
     extern __shared__ __align__(1024) uint8_t smem[];
+    if (already_failed(status)) return;
     if (ptx::smem_u32(smem) & 1023u) {
         if (threadIdx.x == 0 && status != nullptr) atomicCAS(status, 0, LLMK_ST_BOUNDS);
         return;
@@ -344,7 +390,8 @@ attn_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_co
     uint64_t* s_full = bars + 5;
     uint64_t* p_full = bars + 6;
     uint64_t* acc_done = bars + 7;
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 8);
+    uint64_t* epi = bars + 8;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 9);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -366,6 +413,7 @@ attn_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_co
         ptx::mbar_init(s_full, 1);
         ptx::mbar_init(p_full, 4);
         ptx::mbar_init(acc_done, 1);
+        ptx::mbar_init(epi, 4);
         *abort_flag = 0;
         ptx::fence_barrier_init();
     }
@@ -400,19 +448,21 @@ attn_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_co
         constexpr uint32_t idesc_s = ptx::make_idesc_bf16(BM, BN, 0, 0);
         constexpr uint32_t idesc_acc = ptx::make_idesc_bf16(BM, HS, 0, 1);
         bool ok = ptx::mbar_wait(q_full, 0, abort_flag, status, LLMK_ST_TIMEOUT_TMA_FULL, -1);
+        const uint64_t q_desc = kmajor_desc<BM>(ptx::smem_u32(sQ), 0), do_desc = kmajor_desc<BM>(ptx::smem_u32(sdO), 0);
+        const uint64_t ds_desc = kmajor_desc<BM>(ptx::smem_u32(sdS), 0);
+        const uint32_t ring_addr = ptx::smem_u32(sRing);
         auto issue_s = [&](int j) -> bool {
             const int s = j & 1;
             if (!ptx::mbar_wait(&ring_full[s], (j >> 1) & 1, abort_flag, status, LLMK_ST_TIMEOUT_TMA_FULL, j)) return false;
             ptx::tc_fence_after();
             if (lane == 0) {
-                const uint32_t q_addr = ptx::smem_u32(sQ), do_addr = ptx::smem_u32(sdO);
-                const uint32_t k_addr = ptx::smem_u32(sRing + s * 2 * C::RT), v_addr = k_addr + C::RT;
+                const uint64_t k_desc = kmajor_desc<BN>(ring_addr + s * 2 * C::RT, 0), v_desc = kmajor_desc<BN>(ring_addr + s * 2 * C::RT + C::RT, 0);
 #pragma unroll
                 for (int kk = 0; kk < HS / 16; kk++)
-                    ptx::mma_f16_ss(t_s, kmajor_desc<BM>(q_addr, kk), kmajor_desc<BN>(k_addr, kk), idesc_s, kk > 0 ? 1u : 0u);
+                    ptx::mma_f16_ss(t_s, kmajor_step<BM>(q_desc, kk), kmajor_step<BN>(k_desc, kk), idesc_s, kk > 0 ? 1u : 0u);
 #pragma unroll
                 for (int kk = 0; kk < HS / 16; kk++)
-                    ptx::mma_f16_ss(t_dp, kmajor_desc<BM>(do_addr, kk), kmajor_desc<BN>(v_addr, kk), idesc_s, kk > 0 ? 1u : 0u);
+                    ptx::mma_f16_ss(t_dp, kmajor_step<BM>(do_desc, kk), kmajor_step<BN>(v_desc, kk), idesc_s, kk > 0 ? 1u : 0u);
                 ptx::mma_commit(s_full);
             }
             __syncwarp();
@@ -429,11 +479,10 @@ attn_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_co
                 if (!ok) break;
             }
             if (lane == 0) {
-                const uint32_t ds_addr = ptx::smem_u32(sdS), k_addr = ptx::smem_u32(sRing + s * 2 * C::RT);
+                const uint64_t k_mn = mnmajor_desc<BN>(ring_addr + s * 2 * C::RT, 0);
 #pragma unroll
                 for (int kk = 0; kk < BN / 16; kk++)
-                    ptx::mma_f16_ss(t_dq, kmajor_desc<BM>(ds_addr, kk), mnmajor_desc<BN>(k_addr, kk), idesc_acc,
-                                    (j > 0 || kk > 0) ? 1u : 0u);
+                    ptx::mma_f16_ss(t_dq, kmajor_step<BM>(ds_desc, kk), mnmajor_step(k_mn, kk), idesc_acc, (j > 0 || kk > 0) ? 1u : 0u);
                 ptx::mma_commit(&ring_empty[s]);
                 ptx::mma_commit(acc_done);
             }
@@ -483,8 +532,7 @@ attn_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_co
         if (ok) ok = ptx::mbar_wait(acc_done, (nkv - 1) & 1, abort_flag, status, LLMK_ST_TIMEOUT_ACC_FULL, 2000);
         if (ok) {
             ptx::tc_fence_after();
-            const int width = (NH + 2 * NKVH) * HS;
-            bf16* dq_row = dqkv + (size_t)(row_base + q0 + r) * width + q_col;
+            // dQ (scaled) -> bf16 -> the dS buffer as [128 x 64] staging tiles -> TMA stores
 #pragma unroll
             for (int h4 = 0; h4 < HS / 32; h4++) {
                 uint32_t v[32];
@@ -495,7 +543,18 @@ attn_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_co
                     float f[8];
 #pragma unroll
                     for (int i = 0; i < 8; i++) f[i] = __uint_as_float(v[q * 8 + i]) * scale;
-                    st128(dq_row + h4 * 32 + q * 8, pack8(f));
+                    stage_chunk(sdS + (h4 / 2) * (BM * 128), r, (h4 & 1) * 4 + q, f);
+                }
+            }
+            ptx::fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0) ptx::mbar_arrive(epi);
+            if (warp == 2 && lane == 0) {
+                if (ptx::mbar_wait(epi, 0, abort_flag, status, LLMK_ST_TIMEOUT_ACC_FULL, 4000)) {
+#pragma unroll
+                    for (int c = 0; c < HS / 64; c++) ptx::tma_store_2d(&tmDQKV, sdS + c * (BM * 128), q_col + 64 * c, row_base + q0);
+                    ptx::tma_store_commit();
+                    ptx::tma_store_wait_read<0>();
                 }
             }
         }
@@ -523,17 +582,18 @@ static int launch(const void* qkv, const void* dout, bf16* dqkv, const float* ls
         configured = true;
     }
     const uint64_t width = (uint64_t)(NH + 2 * NKVH) * HS, rows = (uint64_t)B * T, cw = (uint64_t)NH * HS;
-    CUtensorMap tq, tq_in, tdo, tdo_in;
+    CUtensorMap tq, tq_in, tdo, tdo_in, tdqkv;
     int rc;
     if ((rc = gemm::make_tmap_2d(&tq, qkv, width, rows, width, 64, BM))) return rc;
     if ((rc = gemm::make_tmap_2d(&tq_in, qkv, width, rows, width, 64, BN))) return rc;
     if ((rc = gemm::make_tmap_2d(&tdo, dout, cw, rows, cw, 64, BM))) return rc;
     if ((rc = gemm::make_tmap_2d(&tdo_in, dout, cw, rows, cw, 64, BN))) return rc;
+    if ((rc = gemm::make_tmap_2d(&tdqkv, dqkv, width, rows, width, 64, BM))) return rc;
     const float scale = 1.0f / sqrtf((float)HS);
-    attn_bwd_dkv_tc_kernel<HS><<<dim3(T / BM, NKVH, B), THREADS, DkvCfg<HS>::SMEM_BYTES, stream>>>(tq, tq_in, tdo_in, dqkv, lse, dvec,
+    attn_bwd_dkv_tc_kernel<HS><<<dim3(T / BM, NKVH, B), THREADS, DkvCfg<HS>::SMEM_BYTES, stream>>>(tq, tq_in, tdo_in, tdqkv, lse, dvec,
                                                                                                  T, NH, NKVH, scale, status);
     LLMK_LAUNCH_CHECK();
-    attn_bwd_dq_tc_kernel<HS><<<dim3(T / BM, NH, B), THREADS, DqCfg<HS>::SMEM_BYTES, stream>>>(tq, tdo, tq_in, dqkv, lse, dvec, T, NH,
+    attn_bwd_dq_tc_kernel<HS><<<dim3(T / BM, NH, B), THREADS, DqCfg<HS>::SMEM_BYTES, stream>>>(tq, tdo, tq_in, tdqkv, lse, dvec, T, NH,
                                                                                              NKVH, scale, status);
     LLMK_LAUNCH_CHECK();
     return LLMK_OK;
