@@ -38,6 +38,7 @@ typedef __nv_bfloat16 bf16;
 
 // host: remembers the text of the last CUDA error seen by a launcher of this library
 void set_last_error(const char* what, cudaError_t e);
+int* current_status_word();   // device pointer registered with llmk_set_status_word for the current device, or nullptr
 
 #define LLMK_CUDA_TRY(expr)                                  \
     do {                                                     \

@@ -11,7 +11,7 @@
 //     fixed columns, so no atomics); warps are summed in fixed order into one partial per block in a
 //     global scratch buffer, and a second kernel sums the block partials in fixed order into the
 //     bf16 gradients (+=). The result is bit-reproducible run to run.
-#include "common.cuh"
+#include "ptx_sm100.cuh"
 
 namespace llmk {
 namespace norm {
@@ -349,6 +349,144 @@ norm_bwd_reg_kernel(bf16* __restrict__ dinp, float* __restrict__ scratch, const 
     }
 }
 
+// Backward with a bulk-copy ring: every warp owns rows and streams them (dout, inp and, when accumulating, the old
+// dinp) into its own shared-memory ring with cp.async.bulk, STAGES rows ahead, so that about
+// warps x STAGES x 3 x C x 2 bytes are in flight per SM whatever the register budget - the register-only kernel above
+// has a single row per warp in flight and reaches well under half of the copy bandwidth. The arithmetic and the
+// scratch layout are those of norm_bwd_reg_kernel. Every wait is bounded; a failure goes to `status`.
+template <int NVEC>
+struct BulkCfg {
+    static constexpr int C = NVEC * 256;
+    static constexpr int ROW = C * 2;
+    // narrow rows: 16 warps (two per scheduler hide the reduction latency) with a 2-deep ring; wide rows: 8 warps
+    static constexpr int WARPS = NVEC <= 3 ? 16 : 8;
+    static constexpr int STAGES = NVEC <= 3 ? 2 : (NVEC == 4 ? 4 : 3);
+    static constexpr int WARP_RING = STAGES * 3 * ROW;
+    static constexpr int OFF_BAR = WARPS * WARP_RING;
+    static constexpr int SMEM = OFF_BAR + WARPS * STAGES * 8;
+};
+
+template <bool RMS, int NVEC>
+__global__ void __launch_bounds__(BulkCfg<NVEC>::WARPS * 32, 1)
+norm_bwd_bulk_kernel(bf16* __restrict__ dinp, float* __restrict__ scratch, const bf16* __restrict__ dout,
+                     const bf16* __restrict__ inp, const bf16* __restrict__ weight, const float* __restrict__ mean,
+                     const float* __restrict__ rstd, int N, int accumulate_dinp, int* status) {
+    using B = BulkCfg<NVEC>;
+    constexpr int C = B::C, ROW = B::ROW, STAGES = B::STAGES, WARPS = B::WARPS;
+    constexpr int PLANES = RMS ? 1 : 2;
+    extern __shared__ __align__(128) uint8_t smem_raw[];
+    __shared__ int abort_word;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    uint8_t* ring = smem_raw + (size_t)warp * B::WARP_RING;
+    uint64_t* full = reinterpret_cast<uint64_t*>(smem_raw + B::OFF_BAR) + warp * STAGES;
+    volatile int* abort_flag = &abort_word;
+    if (threadIdx.x == 0) abort_word = 0;
+    if (lane == 0) {
+        for (int i = 0; i < STAGES; i++) ptx::mbar_init(&full[i], 1);
+    }
+    ptx::fence_barrier_init();
+    __syncthreads();
+
+    const int first = blockIdx.x * WARPS + warp, stride = gridDim.x * WARPS;
+    const int nrows = first < N ? (N - first + stride - 1) / stride : 0;
+    const uint32_t tx = (accumulate_dinp ? 3u : 2u) * ROW;
+    auto issue = [&](int i) {   // lane 0 only
+        const int st = i % STAGES;
+        const size_t off = (size_t)(first + (size_t)i * stride) * C;
+        uint8_t* dst = ring + st * 3 * ROW;
+        ptx::mbar_arrive_expect_tx(&full[st], tx);
+        ptx::bulk_load_1d(dst, dout + off, ROW, &full[st]);
+        ptx::bulk_load_1d(dst + ROW, inp + off, ROW, &full[st]);
+        if (accumulate_dinp) ptx::bulk_load_1d(dst + 2 * ROW, dinp + off, ROW, &full[st]);
+    };
+    if (lane == 0)
+        for (int i = 0; i < STAGES && i < nrows; i++) issue(i);
+
+    const float inv_c = 1.0f / (float)C;
+    float dw[NVEC][8], db[RMS ? 1 : NVEC][8];
+#pragma unroll
+    for (int k = 0; k < NVEC; k++)
+#pragma unroll
+        for (int j = 0; j < 8; j++) {
+            dw[k][j] = 0.f;
+            if (!RMS) db[k][j] = 0.f;
+        }
+
+    bool ok = true;
+    for (int i = 0; i < nrows; i++) {
+        const int st = i % STAGES;
+        const int row = first + i * stride;
+        ok = ptx::mbar_wait(&full[st], (i / STAGES) & 1, abort_flag, status, LLMK_ST_TIMEOUT_TMA_FULL, 8000 + st);
+        if (!ok) break;
+        const uint8_t* src = ring + st * 3 * ROW;
+        bf16x8 dv[NVEC], xv[NVEC], ov[NVEC];
+#pragma unroll
+        for (int k = 0; k < NVEC; k++) {
+            dv[k] = *reinterpret_cast<const bf16x8*>(src + (lane + 32 * k) * 16);
+            xv[k] = *reinterpret_cast<const bf16x8*>(src + ROW + (lane + 32 * k) * 16);
+            if (accumulate_dinp) ov[k] = *reinterpret_cast<const bf16x8*>(src + 2 * ROW + (lane + 32 * k) * 16);
+        }
+        __syncwarp();   // the stage has been copied into registers by every lane: refill it
+        if (lane == 0 && i + STAGES < nrows) issue(i + STAGES);
+        const float m = RMS ? 0.f : mean[row];
+        const float rs = rstd[row];
+        float s1 = 0.f, s2 = 0.f;
+#pragma unroll
+        for (int k = 0; k < NVEC; k++) {
+            float fd[8], fx[8], fw[8];
+            unpack8(dv[k], fd);
+            unpack8(xv[k], fx);
+            unpack8(ld128(weight + (lane + 32 * k) * 8), fw);
+#pragma unroll
+            for (int j = 0; j < 8; j++) {
+                const float n = (fx[j] - m) * rs;
+                const float dn = fd[j] * fw[j];
+                s1 += dn;
+                s2 += dn * n;
+                dw[k][j] += fd[j] * n;
+                if (!RMS) db[k][j] += fd[j];
+            }
+        }
+        s1 = warp_sum(s1) * inv_c;
+        s2 = warp_sum(s2) * inv_c;
+#pragma unroll
+        for (int k = 0; k < NVEC; k++) {
+            float fd[8], fx[8], fo[8], fw[8];
+            unpack8(dv[k], fd);
+            unpack8(xv[k], fx);
+            unpack8(ld128(weight + (lane + 32 * k) * 8), fw);
+            if (accumulate_dinp) unpack8(ov[k], fo);
+#pragma unroll
+            for (int j = 0; j < 8; j++) {
+                const float n = (fx[j] - m) * rs;
+                const float dn = fd[j] * fw[j];
+                const float d = RMS ? (dn - n * s2) * rs : (dn - s1 - n * s2) * rs;
+                fo[j] = accumulate_dinp ? fo[j] + d : d;
+            }
+            st128(dinp + (size_t)row * C + (lane + 32 * k) * 8, pack8(fo));
+        }
+    }
+    // all rings are idle now (every issued copy has been waited for): reuse them for the cross-warp reduction
+    __syncthreads();
+    if (*abort_flag) return;
+    float* sh = reinterpret_cast<float*>(smem_raw);   // [WARPS][PLANES][C]
+#pragma unroll
+    for (int k = 0; k < NVEC; k++)
+#pragma unroll
+        for (int j = 0; j < 8; j++) {
+            sh[(size_t)warp * PLANES * C + (lane + 32 * k) * 8 + j] = dw[k][j];
+            if (!RMS) sh[(size_t)warp * PLANES * C + C + (lane + 32 * k) * 8 + j] = db[k][j];
+        }
+    __syncthreads();
+    float* dst = scratch + (size_t)blockIdx.x * 2 * C;
+    for (int i = threadIdx.x; i < PLANES * C; i += blockDim.x) {
+        float acc = 0.f;
+#pragma unroll
+        for (int w = 0; w < WARPS; w++) acc += sh[(size_t)w * PLANES * C + i];
+        dst[i] = acc;
+    }
+}
+
 static int g_sms = 0;
 static int num_sms() {
     if (g_sms == 0) {
@@ -453,6 +591,24 @@ static int launch_bwd_reg(bf16* dinp, bf16* dweight, bf16* dbias, float* scratch
                           const bf16* weight, const float* mean, const float* rstd, int N, int accumulate_dinp,
                           cudaStream_t stream) {
     constexpr int C = NVEC * 256;
+    if constexpr (NVEC <= 5) {
+        using B = BulkCfg<NVEC>;
+        static_assert(B::OFF_BAR >= B::WARPS * 2 * C * 4, "the rings must be able to hold the final reduction buffer");
+        static bool bulk_configured = false;
+        if (!bulk_configured) {
+            LLMK_CUDA_TRY(cudaFuncSetAttribute(norm_bwd_bulk_kernel<RMS, NVEC>, cudaFuncAttributeMaxDynamicSharedMemorySize, B::SMEM));
+            bulk_configured = true;
+        }
+        int grid = num_sms();
+        const int need = ceil_div(N, B::WARPS);
+        if (grid > need) grid = need;
+        norm_bwd_bulk_kernel<RMS, NVEC><<<grid, B::WARPS * 32, B::SMEM, stream>>>(dinp, scratch, dout, inp, weight, mean, rstd, N,
+                                                                                 accumulate_dinp, current_status_word());
+        LLMK_LAUNCH_CHECK();
+        norm_bwd_finish_kernel<<<ceil_div(C, 32), dim3(32, 8), 0, stream>>>(dweight, dbias, scratch, grid, C);
+        LLMK_LAUNCH_CHECK();
+        return LLMK_OK;
+    }
     constexpr int SMEM = REG_WARPS * (RMS ? 1 : 2) * C * 4;
     static bool configured = false;
     if (!configured) {

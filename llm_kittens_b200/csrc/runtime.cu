@@ -8,9 +8,25 @@ static thread_local char g_last_error[512] = "";
 void set_last_error(const char* what, cudaError_t e) {
     snprintf(g_last_error, sizeof(g_last_error), "%s -> %s (%s)", what, cudaGetErrorName(e), cudaGetErrorString(e));
 }
+// Per-device status word (int32[4] in device memory) registered by the binding layer: kernels with bounded
+// waits whose C entry point has no status argument report their failures there.
+static int* g_status_word[64];
+int* current_status_word() {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+    return g_status_word[dev];
+}
 }  // namespace llmk
 
 using namespace llmk;
+
+LLMK_API int llmk_set_status_word(void* device_ptr) {
+    int dev = 0;
+    LLMK_CUDA_TRY(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64) return LLMK_ERR_SHAPE;
+    g_status_word[dev] = static_cast<int*>(device_ptr);
+    return LLMK_OK;
+}
 
 LLMK_API const char* llmk_last_error() { return g_last_error; }
 

@@ -117,6 +117,8 @@ def status_word() -> torch.Tensor:
     dev = torch.cuda.current_device()
     if dev not in _STATUS:
         _STATUS[dev] = torch.zeros(4, dtype=torch.int32, device=f"cuda:{dev}")
+        with torch.cuda.device(dev):
+            lib().llmk_set_status_word(ctypes.c_void_p(_STATUS[dev].data_ptr()))
     return _STATUS[dev]
 
 
