@@ -487,6 +487,111 @@ norm_bwd_bulk_kernel(bf16* __restrict__ dinp, float* __restrict__ scratch, const
     }
 }
 
+// Wide rows (C = NV * 2048): one 256-thread block per row, every thread owns NV 8-element column groups, so the
+// weight-gradient accumulators stay at NV * 8 registers per plane however wide the row is and no cross-warp
+// reduction of them is needed (each column has one owner per block). The next row is prefetched into registers
+// while the block reduces the current one. scratch layout [gridDim.x][2][C] as for the other kernels.
+template <bool RMS, int NV>
+__global__ void __launch_bounds__(256, NV <= 2 ? 2 : 1)
+norm_bwd_wide_kernel(bf16* __restrict__ dinp, float* __restrict__ scratch, const bf16* __restrict__ dout,
+                     const bf16* __restrict__ inp, const bf16* __restrict__ weight, const float* __restrict__ mean,
+                     const float* __restrict__ rstd, int N, int accumulate_dinp) {
+    constexpr int C = NV * 2048;
+    __shared__ float red[2][2][8];   // [parity][s1 | s2][warp]
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const float inv_c = 1.0f / (float)C;
+    float dw[NV][8], db[RMS ? 1 : NV][8], fw[NV][8];
+#pragma unroll
+    for (int k = 0; k < NV; k++) {
+        unpack8(ld128(weight + (threadIdx.x + 256 * k) * 8), fw[k]);
+#pragma unroll
+        for (int j = 0; j < 8; j++) {
+            dw[k][j] = 0.f;
+            if (!RMS) db[k][j] = 0.f;
+        }
+    }
+    bf16x8 dv[NV], xv[NV], ov[NV], dvn[NV], xvn[NV], ovn[NV];
+    auto load = [&](int row, bf16x8* d, bf16x8* x, bf16x8* o) {
+#pragma unroll
+        for (int k = 0; k < NV; k++) {
+            const size_t off = (size_t)row * C + (threadIdx.x + 256 * k) * 8;
+            d[k] = ld128_stream(dout + off);
+            x[k] = ld128_stream(inp + off);
+            if (accumulate_dinp) o[k] = ld128(dinp + off);
+        }
+    };
+    int row = blockIdx.x;
+    if (row < N) load(row, dv, xv, ov);
+    int par = 0;
+    for (; row < N; row += gridDim.x, par ^= 1) {
+        const int next = row + gridDim.x;
+        if (next < N) load(next, dvn, xvn, ovn);
+        const float m = RMS ? 0.f : mean[row];
+        const float rs = rstd[row];
+        float s1 = 0.f, s2 = 0.f;
+#pragma unroll
+        for (int k = 0; k < NV; k++) {
+            float fd[8], fx[8];
+            unpack8(dv[k], fd);
+            unpack8(xv[k], fx);
+#pragma unroll
+            for (int j = 0; j < 8; j++) {
+                const float n = (fx[j] - m) * rs;
+                const float dn = fd[j] * fw[k][j];
+                s1 += dn;
+                s2 += dn * n;
+                dw[k][j] += fd[j] * n;
+                if (!RMS) db[k][j] += fd[j];
+            }
+        }
+        s1 = warp_sum(s1);
+        s2 = warp_sum(s2);
+        if (lane == 0) {
+            red[par][0][warp] = s1;
+            red[par][1][warp] = s2;
+        }
+        __syncthreads();   // the other parity's slots are free again once every warp has passed this point
+        s1 = 0.f;
+        s2 = 0.f;
+#pragma unroll
+        for (int w = 0; w < 8; w++) {
+            s1 += red[par][0][w];
+            s2 += red[par][1][w];
+        }
+        s1 *= inv_c;
+        s2 *= inv_c;
+#pragma unroll
+        for (int k = 0; k < NV; k++) {
+            float fd[8], fx[8], fo[8];
+            unpack8(dv[k], fd);
+            unpack8(xv[k], fx);
+            if (accumulate_dinp) unpack8(ov[k], fo);
+#pragma unroll
+            for (int j = 0; j < 8; j++) {
+                const float n = (fx[j] - m) * rs;
+                const float dn = fd[j] * fw[k][j];
+                const float d = RMS ? (dn - n * s2) * rs : (dn - s1 - n * s2) * rs;
+                fo[j] = accumulate_dinp ? fo[j] + d : d;
+            }
+            st128(dinp + (size_t)row * C + (threadIdx.x + 256 * k) * 8, pack8(fo));
+        }
+#pragma unroll
+        for (int k = 0; k < NV; k++) {
+            dv[k] = dvn[k];
+            xv[k] = xvn[k];
+            ov[k] = ovn[k];
+        }
+    }
+    float* dst = scratch + (size_t)blockIdx.x * 2 * C;
+#pragma unroll
+    for (int k = 0; k < NV; k++)
+#pragma unroll
+        for (int j = 0; j < 8; j++) {
+            dst[(threadIdx.x + 256 * k) * 8 + j] = dw[k][j];
+            if (!RMS) dst[C + (threadIdx.x + 256 * k) * 8 + j] = db[k][j];
+        }
+}
+
 static int g_sms = 0;
 static int num_sms() {
     if (g_sms == 0) {
@@ -625,6 +730,19 @@ static int launch_bwd_reg(bf16* dinp, bf16* dweight, bf16* dbias, float* scratch
     LLMK_LAUNCH_CHECK();
     return LLMK_OK;
 }
+template <bool RMS, int NV>
+static int launch_bwd_wide(bf16* dinp, bf16* dweight, bf16* dbias, float* scratch, const bf16* dout, const bf16* inp,
+                           const bf16* weight, const float* mean, const float* rstd, int N, int accumulate_dinp,
+                           cudaStream_t stream) {
+    constexpr int C = NV * 2048;
+    int grid = num_sms() * (NV <= 2 ? 2 : 1);
+    if (grid > N) grid = N;
+    norm_bwd_wide_kernel<RMS, NV><<<grid, 256, 0, stream>>>(dinp, scratch, dout, inp, weight, mean, rstd, N, accumulate_dinp);
+    LLMK_LAUNCH_CHECK();
+    norm_bwd_finish_kernel<<<ceil_div(C, 32), dim3(32, 8), 0, stream>>>(dweight, dbias, scratch, grid, C);
+    LLMK_LAUNCH_CHECK();
+    return LLMK_OK;
+}
 }  // namespace norm
 }  // namespace llmk
 
@@ -635,6 +753,14 @@ int layernorm_bwd_impl(bf16* dinp, bf16* dweight, bf16* dbias, float* scratch, c
                        const bf16* weight, const float* mean, const float* rstd, int N, int C, int accumulate_dinp,
                        cudaStream_t stream) {
     if (C % 8 != 0 || C > 12288) return LLMK_ERR_SHAPE;
+    switch (C % 2048 == 0 ? C / 2048 : 0) {
+        case 1: return launch_bwd_wide<false, 1>(dinp, dweight, dbias, scratch, dout, inp, weight, mean, rstd, N, accumulate_dinp, stream);
+        case 2: return launch_bwd_wide<false, 2>(dinp, dweight, dbias, scratch, dout, inp, weight, mean, rstd, N, accumulate_dinp, stream);
+        case 3: return launch_bwd_wide<false, 3>(dinp, dweight, dbias, scratch, dout, inp, weight, mean, rstd, N, accumulate_dinp, stream);
+        case 4: return launch_bwd_wide<false, 4>(dinp, dweight, dbias, scratch, dout, inp, weight, mean, rstd, N, accumulate_dinp, stream);
+        case 6: return launch_bwd_wide<false, 6>(dinp, dweight, dbias, scratch, dout, inp, weight, mean, rstd, N, accumulate_dinp, stream);
+        default: break;
+    }
     switch (C % 256 == 0 ? C / 256 : 0) {
         case 1: return launch_bwd_reg<false, 1>(dinp, dweight, dbias, scratch, dout, inp, weight, mean, rstd, N, accumulate_dinp, stream);
         case 2: return launch_bwd_reg<false, 2>(dinp, dweight, dbias, scratch, dout, inp, weight, mean, rstd, N, accumulate_dinp, stream);
@@ -680,13 +806,26 @@ LLMK_API int llmk_rmsnorm_bwd(void* dinp, void* dweight, void* scratch, const vo
         return launch_bwd_reg<true, NV>((bf16*)dinp, (bf16*)dweight, nullptr, (float*)scratch, (const bf16*)dout,         \
                                         (const bf16*)inp, (const bf16*)weight, nullptr, (const float*)rstd, N,            \
                                         accumulate_dinp, stream);
+#define LLMK_RMS_WIDE_CASE(NV)                                                                                            \
+    case NV:                                                                                                              \
+        return launch_bwd_wide<true, NV>((bf16*)dinp, (bf16*)dweight, nullptr, (float*)scratch, (const bf16*)dout,        \
+                                         (const bf16*)inp, (const bf16*)weight, nullptr, (const float*)rstd, N,           \
+                                         accumulate_dinp, stream);
+    switch (C % 2048 == 0 ? C / 2048 : 0) {
+        LLMK_RMS_WIDE_CASE(1)
+        LLMK_RMS_WIDE_CASE(2)
+        LLMK_RMS_WIDE_CASE(3)
+        LLMK_RMS_WIDE_CASE(4)
+        LLMK_RMS_WIDE_CASE(6)
+        default: break;
+    }
+#undef LLMK_RMS_WIDE_CASE
     switch (C % 256 == 0 ? C / 256 : 0) {
         LLMK_RMS_BWD_CASE(1)
         LLMK_RMS_BWD_CASE(2)
         LLMK_RMS_BWD_CASE(3)
         LLMK_RMS_BWD_CASE(4)
-        LLMK_RMS_BWD_CASE(8)
-        LLMK_RMS_BWD_CASE(16)
+        LLMK_RMS_BWD_CASE(5)
         default: break;
     }
 #undef LLMK_RMS_BWD_CASE
