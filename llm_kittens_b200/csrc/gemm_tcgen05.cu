@@ -18,6 +18,8 @@
 //
 // No cluster launch and no multicast: each CTA loads its own tiles; reuse comes from the L2 through
 // the grouped tile order. Every wait is bounded (ptx::mbar_wait) and reports through `status`.
+#include <cstdlib>
+
 #include "ptx_sm100.cuh"
 
 namespace llmk {
@@ -26,32 +28,38 @@ namespace gemm {
 constexpr int BM = 128, BN = 256, BK = 64;
 // 4 pipeline stages when the epilogue needs one staging buffer per warp, 3 when it needs two (a second
 // output or a TMA-loaded auxiliary input tile).
-template <int EPI> struct Cfg;
+// PAIR: two CTAs of a cluster share one 256 x 256 tile (tcgen05 cta_group::2): each loads its own 128 rows of A and
+// half of B's 256 columns, which cuts the operand traffic from the L2 by a third and leaves room for 6 stages.
+template <int EPI, bool PAIR> struct Cfg;
 constexpr int A_STAGE_BYTES = BM * BK * 2;  // 16 KiB
-constexpr int B_STAGE_BYTES = BN * BK * 2;  // 32 KiB
-constexpr int STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
+template <bool PAIR> struct Geo {
+    static constexpr int BN_CTA = PAIR ? BN / 2 : BN;          // B columns this CTA keeps in shared memory
+    static constexpr int B_STAGE_BYTES = BN_CTA * BK * 2;      // 16 / 32 KiB
+    static constexpr int STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
+};
 constexpr int CHUNK_BYTES = 64 * BK * 2;          // one 64(MN) x 64(K) MN-major box = 8 KiB
 constexpr int STAGING_BYTES = 32 * 128;           // 32 rows x 64 bf16 per epilogue warp buffer
 constexpr int NUM_EPI_WARPS = 8;  // two per TMEM lane group; each takes alternate 64-column chunks
 constexpr int THREADS = 32 * (2 + NUM_EPI_WARPS);
-constexpr int MAX_STAGES = 4;
+constexpr int MAX_STAGES = 6;
 constexpr int GROUP_M = 8;
 constexpr int TMEM_COLS = 512;
 
 enum { MODE_NT = 0, MODE_NN = 1, MODE_TN = 2 };
 enum { EPI_BIAS = 1, EPI_GELU = 2, EPI_DGELU = 4, EPI_ADD = 8, EPI_PARTIAL = 16 };
 
-template <int EPI>
+template <int EPI, bool PAIR>
 struct Cfg {
     static constexpr bool DUAL = (EPI & (EPI_GELU | EPI_DGELU | EPI_ADD)) != 0;
-    static constexpr int STAGES = DUAL ? 3 : 4;
-    static constexpr int SMEM_MAIN = STAGES * STAGE_BYTES + NUM_EPI_WARPS * (DUAL ? 2 : 1) * STAGING_BYTES;
+    static constexpr int STAGES = PAIR ? (DUAL ? 5 : 6) : (DUAL ? 3 : 4);
+    static constexpr int SMEM_MAIN = STAGES * Geo<PAIR>::STAGE_BYTES + NUM_EPI_WARPS * (DUAL ? 2 : 1) * STAGING_BYTES;
     static constexpr int SMEM_BYTES = SMEM_MAIN + 1024 /*alignment slack*/ + 256 /*barriers*/;
 };
 
 struct Params {
     int M, N, K;
-    int tiles_m, tiles_n, splits, kb_total, kb_per_split;
+    int tiles_m, tiles_n, splits, kb_total, kb_per_split;   // tiles_m counts 256-row tiles when `pair`
+    int pair;
     const bf16* bias;  // [N]
     const bf16* aux;   // [M,N] pre-GELU input (DGELU) or addend (ADD; may alias C)
     float* partial;    // [splits, M, N] fp32 (PARTIAL)
@@ -71,21 +79,22 @@ __device__ __forceinline__ Work decode_unit(const Params& p, int u) {
     const int first_m = group * GROUP_M;
     const int gm = min(p.tiles_m - first_m, GROUP_M);
     const int r = tile - group * group_size;
-    w.m0 = (first_m + r % gm) * BM;
+    w.m0 = (first_m + r % gm) * (p.pair ? 2 * BM : BM);
     w.n0 = (r / gm) * BN;
     w.kb_begin = w.split * p.kb_per_split;
     w.kb_end = min(p.kb_total, w.kb_begin + p.kb_per_split);
     return w;
 }
 
-template <int MODE, int EPI>
+template <int MODE, int EPI, bool PAIR>
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
             const __grid_constant__ CUtensorMap tmC, const __grid_constant__ CUtensorMap tmX, const Params p) {
     // tmX: second output (GELU pre-activation) or auxiliary [M,N] input (DGELU / ADD); same geometry as tmC
-    constexpr int STAGES = Cfg<EPI>::STAGES;
-    constexpr int SMEM_MAIN = Cfg<EPI>::SMEM_MAIN;
-    constexpr bool DUAL = Cfg<EPI>::DUAL;
+    constexpr int STAGES = Cfg<EPI, PAIR>::STAGES;
+    constexpr int SMEM_MAIN = Cfg<EPI, PAIR>::SMEM_MAIN;
+    constexpr bool DUAL = Cfg<EPI, PAIR>::DUAL;
+    constexpr int STAGE_BYTES = Geo<PAIR>::STAGE_BYTES, BN_CTA = Geo<PAIR>::BN_CTA;
     constexpr bool A_MN = (MODE == MODE_TN);
     constexpr bool B_MN = (MODE != MODE_NT);
 
@@ -98,11 +107,14 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
     uint64_t* acc_full = bars + 2 * MAX_STAGES;        // [2]
     uint64_t* acc_empty = bars + 2 * MAX_STAGES + 2;   // [2]
     uint64_t* aux_bar = bars + 2 * MAX_STAGES + 4;     // [NUM_EPI_WARPS]
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * MAX_STAGES + 4 + NUM_EPI_WARPS);
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(aux_bar + NUM_EPI_WARPS);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int total_units = p.tiles_m * p.tiles_n * p.splits;
+    const int rank = PAIR ? (int)ptx::cluster_ctarank() : 0;                 // 0 = leader of the pair
+    const int unit0 = PAIR ? blockIdx.x / 2 : blockIdx.x;                      // first work unit of this CTA (pair)
+    const int unit_step = PAIR ? gridDim.x / 2 : gridDim.x;
 
     if (threadIdx.x == 0) {
         for (int i = 0; i < STAGES; i++) {
@@ -111,7 +123,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
         }
         for (int i = 0; i < 2; i++) {
             ptx::mbar_init(&acc_full[i], 1);
-            ptx::mbar_init(&acc_empty[i], NUM_EPI_WARPS);
+            ptx::mbar_init(&acc_empty[i], PAIR ? 2 * NUM_EPI_WARPS : NUM_EPI_WARPS);   // pair: both CTAs' epilogue warps
         }
         for (int i = 0; i < NUM_EPI_WARPS; i++) ptx::mbar_init(&aux_bar[i], 1);
         *abort_flag = 0;
@@ -122,11 +134,17 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
         if (DUAL) ptx::prefetch_tmap(&tmX);
     }
     if (warp == 1) {
-        ptx::tmem_alloc(tmem_slot, TMEM_COLS);
-        ptx::tmem_relinquish();
+        if (PAIR) {
+            ptx::tmem_alloc_pair(tmem_slot, TMEM_COLS);
+            ptx::tmem_relinquish_pair();
+        } else {
+            ptx::tmem_alloc(tmem_slot, TMEM_COLS);
+            ptx::tmem_relinquish();
+        }
     }
     ptx::tc_fence_before();
     __syncthreads();
+    if (PAIR) ptx::cluster_sync_all();   // the peer's barriers are initialised before anything can signal them
     ptx::tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
 
@@ -135,29 +153,33 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
         int s = 0;
         uint32_t ph = 0;
         bool ok = true;
-        for (int u = blockIdx.x; u < total_units && ok; u += gridDim.x) {
+        auto load = [&](void* dst, const CUtensorMap* tm, uint64_t* bar, int x, int y) {
+            if (PAIR) ptx::tma_load_2d_pair(dst, tm, bar, x, y);   // the bytes are credited to the leader's barrier
+            else ptx::tma_load_2d(dst, tm, bar, x, y);
+        };
+        for (int u = unit0; u < total_units && ok; u += unit_step) {
             const Work w = decode_unit(p, u);
+            const int m_own = w.m0 + rank * BM, n_own = w.n0 + rank * BN_CTA;
             for (int kb = w.kb_begin; kb < w.kb_end; kb++) {
                 ok = ptx::mbar_wait(&empty_bar[s], ph ^ 1, abort_flag, p.status, LLMK_ST_TIMEOUT_TMA_EMPTY, u);
                 if (!ok) break;
                 if (lane == 0) {
                     uint8_t* sA = smem + s * STAGE_BYTES;
                     uint8_t* sB = sA + A_STAGE_BYTES;
-                    ptx::mbar_arrive_expect_tx(&full_bar[s], STAGE_BYTES);
+                    // pair: only the leader arms its barrier, for the bytes of both CTAs
+                    if (rank == 0) ptx::mbar_arrive_expect_tx(&full_bar[s], (PAIR ? 2 : 1) * STAGE_BYTES);
                     const int k0 = kb * BK;
                     if (A_MN) {
 #pragma unroll
-                        for (int j = 0; j < BM / 64; j++)
-                            ptx::tma_load_2d(sA + j * CHUNK_BYTES, &tmA, &full_bar[s], w.m0 + 64 * j, k0);
+                        for (int j = 0; j < BM / 64; j++) load(sA + j * CHUNK_BYTES, &tmA, &full_bar[s], m_own + 64 * j, k0);
                     } else {
-                        ptx::tma_load_2d(sA, &tmA, &full_bar[s], k0, w.m0);
+                        load(sA, &tmA, &full_bar[s], k0, m_own);
                     }
                     if (B_MN) {
 #pragma unroll
-                        for (int j = 0; j < BN / 64; j++)
-                            ptx::tma_load_2d(sB + j * CHUNK_BYTES, &tmB, &full_bar[s], w.n0 + 64 * j, k0);
+                        for (int j = 0; j < BN_CTA / 64; j++) load(sB + j * CHUNK_BYTES, &tmB, &full_bar[s], n_own + 64 * j, k0);
                     } else {
-                        ptx::tma_load_2d(sB, &tmB, &full_bar[s], k0, w.n0);
+                        load(sB, &tmB, &full_bar[s], k0, n_own);
                     }
                 }
                 __syncwarp();
@@ -171,14 +193,17 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
                 if (++s == STAGES) { s = 0; ph ^= 1; }
             }
         }
-    } else if (warp == 1) {
-        // ------------------------------------------------------------ MMA issuer
-        constexpr uint32_t idesc = ptx::make_idesc_bf16(BM, BN, A_MN ? 1 : 0, B_MN ? 1 : 0);
+    } else if (warp == 1 && rank == 0) {
+        // ------------------------------------------------------------ MMA issuer (pair: the leader CTA only)
+        constexpr uint32_t idesc = ptx::make_idesc_bf16(PAIR ? 2 * BM : BM, BN, A_MN ? 1 : 0, B_MN ? 1 : 0);
+        const uint32_t a_addr0 = ptx::smem_u32(smem), b_addr0 = a_addr0 + A_STAGE_BYTES;
+        const uint64_t a_desc0 = A_MN ? ptx::make_smem_desc(a_addr0, CHUNK_BYTES, 1024) : ptx::make_smem_desc(a_addr0, 16, 1024);
+        const uint64_t b_desc0 = B_MN ? ptx::make_smem_desc(b_addr0, CHUNK_BYTES, 1024) : ptx::make_smem_desc(b_addr0, 16, 1024);
         int s = 0;
         uint32_t ph = 0;
         int it = 0;
         bool ok = true;
-        for (int u = blockIdx.x; u < total_units && ok; u += gridDim.x, it++) {
+        for (int u = unit0; u < total_units && ok; u += unit_step, it++) {
             const Work w = decode_unit(p, u);
             const int a = it & 1;
             const uint32_t acc_ph = (it >> 1) & 1;
@@ -191,26 +216,32 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
                 if (!ok) break;
                 ptx::tc_fence_after();
                 if (lane == 0) {
-                    const uint32_t a_addr = ptx::smem_u32(smem + s * STAGE_BYTES);
-                    const uint32_t b_addr = a_addr + A_STAGE_BYTES;
+                    // descriptors by arithmetic on the stage-0 ones (start-address field = bytes / 16): the issuer shares
+                    // its scheduler with two epilogue warps, so its instruction count per k-block is kept minimal
+                    const uint64_t ad = a_desc0 + (uint64_t)(s * (STAGE_BYTES >> 4));
+                    const uint64_t bd = b_desc0 + (uint64_t)(s * (STAGE_BYTES >> 4));
 #pragma unroll
                     for (int kk = 0; kk < BK / 16; kk++) {
-                        const uint64_t adesc = A_MN ? ptx::make_smem_desc(a_addr + kk * 2048, CHUNK_BYTES, 1024)
-                                                    : ptx::make_smem_desc(a_addr + kk * 32, 16, 1024);
-                        const uint64_t bdesc = B_MN ? ptx::make_smem_desc(b_addr + kk * 2048, CHUNK_BYTES, 1024)
-                                                    : ptx::make_smem_desc(b_addr + kk * 32, 16, 1024);
-                        ptx::mma_f16_ss(d_tmem, adesc, bdesc, idesc, (kb > w.kb_begin || kk > 0) ? 1u : 0u);
+                        const uint64_t adk = ad + (uint64_t)((A_MN ? kk * 2048 : kk * 32) >> 4);
+                        const uint64_t bdk = bd + (uint64_t)((B_MN ? kk * 2048 : kk * 32) >> 4);
+                        const uint32_t acc = (kb > w.kb_begin || kk > 0) ? 1u : 0u;
+                        if (PAIR) ptx::mma_f16_ss_pair(d_tmem, adk, bdk, idesc, acc);
+                        else ptx::mma_f16_ss(d_tmem, adk, bdk, idesc, acc);
                     }
-                    ptx::mma_commit(&empty_bar[s]);
+                    if (PAIR) ptx::mma_commit_pair(&empty_bar[s]);   // frees the stage in both CTAs
+                    else ptx::mma_commit(&empty_bar[s]);
                 }
                 __syncwarp();
                 if (++s == STAGES) { s = 0; ph ^= 1; }
             }
             if (!ok) break;
-            if (lane == 0) ptx::mma_commit(&acc_full[a]);
+            if (lane == 0) {
+                if (PAIR) ptx::mma_commit_pair(&acc_full[a]);
+                else ptx::mma_commit(&acc_full[a]);
+            }
             __syncwarp();
         }
-    } else {
+    } else if (warp >= 2) {
         // ------------------------------------------------------------ epilogue warps
         const int e = warp - 2;              // 0..7
         const int lane_group = warp & 3;     // TMEM lanes [32*lane_group, +32) are visible to this warp
@@ -221,11 +252,11 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
         uint32_t aux_ph = 0;
         int it = 0;
         bool ok = true;
-        for (int u = blockIdx.x; u < total_units && ok; u += gridDim.x, it++) {
+        for (int u = unit0; u < total_units && ok; u += unit_step, it++) {
             const Work w = decode_unit(p, u);
             const int a = it & 1;
             const uint32_t acc_ph = (it >> 1) & 1;
-            const int row0 = w.m0 + lane_group * 32;
+            const int row0 = w.m0 + rank * BM + lane_group * 32;
             if (AUX_IN && w.n0 + chunk_sel * 64 < p.N) {
                 // fetch the first aux tile while the main loop of this tile is still running
                 if (lane == 0) {
@@ -337,7 +368,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
             // accumulator fully read by this warp: hand it back to the MMA warp
             ptx::tc_fence_before();
             __syncwarp();
-            if (lane == 0) ptx::mbar_arrive(&acc_empty[a]);
+            if (lane == 0) {
+                if (PAIR) ptx::mbar_arrive_cluster(&acc_empty[a], 0);   // the leader's barrier counts both CTAs' warps
+                else ptx::mbar_arrive(&acc_empty[a]);
+            }
         }
         if (lane == 0) ptx::tma_store_wait_all<0>();
         __syncwarp();
@@ -346,9 +380,11 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
     // ---------------------------------------------------------------- teardown (all paths meet here)
     ptx::tc_fence_before();
     __syncthreads();
+    if (PAIR) ptx::cluster_sync_all();   // the leader's MMAs read the peer's shared memory and signal its barriers
     if (warp == 1) {
         ptx::tc_fence_after();
-        ptx::tmem_dealloc(tmem_base, TMEM_COLS);
+        if (PAIR) ptx::tmem_dealloc_pair(tmem_base, TMEM_COLS);
+        else ptx::tmem_dealloc(tmem_base, TMEM_COLS);
     }
 }
 
@@ -409,26 +445,83 @@ int make_tmap_2d(CUtensorMap* m, const void* ptr, uint64_t inner, uint64_t outer
 
 static int g_num_sms = 0;
 
+static int g_pair_clusters = -1;   // how many CTA pairs can be resident at once (0: pairs unavailable)
+
 template <int MODE, int EPI>
 static int launch(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmC, const CUtensorMap& tmX,
                   const Params& p, int max_ctas, cudaStream_t stream) {
-    constexpr int SMEM_BYTES = Cfg<EPI>::SMEM_BYTES;
-    static bool configured = false;
-    if (!configured) {
-        LLMK_CUDA_TRY(cudaFuncSetAttribute(gemm_kernel<MODE, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
-        configured = true;
-    }
     if (g_num_sms == 0) {
         int dev = 0;
         LLMK_CUDA_TRY(cudaGetDevice(&dev));
         LLMK_CUDA_TRY(cudaDeviceGetAttribute(&g_num_sms, cudaDevAttrMultiProcessorCount, dev));
     }
     const int units = p.tiles_m * p.tiles_n * p.splits;
+    if (p.pair) {
+        constexpr int SMEM_BYTES = Cfg<EPI, true>::SMEM_BYTES;
+        static bool configured = false;
+        if (!configured) {
+            LLMK_CUDA_TRY(cudaFuncSetAttribute(gemm_kernel<MODE, EPI, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+            configured = true;
+        }
+        int clusters = units < g_pair_clusters ? units : g_pair_clusters;
+        if (max_ctas > 0 && clusters > max_ctas / 2) clusters = max_ctas / 2 > 0 ? max_ctas / 2 : 1;
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(2 * clusters);
+        cfg.blockDim = dim3(THREADS);
+        cfg.dynamicSmemBytes = SMEM_BYTES;
+        cfg.stream = stream;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = 2;
+        attr[0].val.clusterDim.y = 1;
+        attr[0].val.clusterDim.z = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+        LLMK_CUDA_TRY(cudaLaunchKernelEx(&cfg, gemm_kernel<MODE, EPI, true>, tmA, tmB, tmC, tmX, p));
+        return LLMK_OK;
+    }
+    constexpr int SMEM_BYTES = Cfg<EPI, false>::SMEM_BYTES;
+    static bool configured = false;
+    if (!configured) {
+        LLMK_CUDA_TRY(cudaFuncSetAttribute(gemm_kernel<MODE, EPI, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+        configured = true;
+    }
     int grid = units < g_num_sms ? units : g_num_sms;
     if (max_ctas > 0 && grid > max_ctas) grid = max_ctas;
-    gemm_kernel<MODE, EPI><<<grid, THREADS, SMEM_BYTES, stream>>>(tmA, tmB, tmC, tmX, p);
+    gemm_kernel<MODE, EPI, false><<<grid, THREADS, SMEM_BYTES, stream>>>(tmA, tmB, tmC, tmX, p);
     LLMK_LAUNCH_CHECK();
     return LLMK_OK;
+}
+
+// Number of resident CTA pairs for the pair kernel (queried once; 0 disables the pair path).
+static int query_pair_clusters() {
+    if (g_pair_clusters >= 0) return g_pair_clusters;
+    g_pair_clusters = 0;
+    const char* env = getenv("LLMK_GEMM_PAIR");
+    if (env != nullptr && env[0] == '0') return 0;
+    constexpr int SMEM_BYTES = Cfg<0, true>::SMEM_BYTES;
+    if (cudaFuncSetAttribute(gemm_kernel<MODE_NT, 0, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES) != cudaSuccess) {
+        cudaGetLastError();
+        return 0;
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(2);
+    cfg.blockDim = dim3(THREADS);
+    cfg.dynamicSmemBytes = SMEM_BYTES;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    int n = 0;
+    if (cudaOccupancyMaxActiveClusters(&n, gemm_kernel<MODE_NT, 0, true>, &cfg) != cudaSuccess) {
+        cudaGetLastError();
+        return 0;
+    }
+    g_pair_clusters = n;
+    return n;
 }
 
 }  // namespace gemm
@@ -437,12 +530,15 @@ static int launch(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensor
 using namespace llmk;
 using namespace llmk::gemm;
 
+// How many CTA pairs the pair (cta_group::2) kernel keeps resident; 0 when that path is off (LLMK_GEMM_PAIR=0).
+LLMK_API int llmk_gemm_pair_clusters() { return query_pair_clusters(); }
+
 // Bytes of fp32 workspace that llmk_gemm needs for (mode, M, N, K) with the split count it will pick.
 LLMK_API long llmk_gemm_workspace_bytes(int mode, int M, int N, int K, int num_sms);
 
-static int pick_splits(int mode, int M, int N, int K, int num_sms) {
+static int pick_splits(int mode, int M, int N, int K, int num_sms, int tile_rows = BM) {
     if (mode != MODE_TN) return 1;
-    const int tiles = ceil_div(M, BM) * ceil_div(N, BN);
+    const int tiles = ceil_div(M, tile_rows) * ceil_div(N, BN);
     const int kb = ceil_div(K, BK);
     if (tiles >= 2 * num_sms) return 1;
     // pick the split count whose work units fill whole waves best; ties go to fewer splits
@@ -458,7 +554,10 @@ static int pick_splits(int mode, int M, int N, int K, int num_sms) {
 }
 
 long llmk_gemm_workspace_bytes(int mode, int M, int N, int K, int num_sms) {
-    const int s = pick_splits(mode, M, N, K, num_sms > 0 ? num_sms : 148);
+    // the larger of what the single-CTA and the pair kernel would pick (the choice is made at launch time)
+    int s = pick_splits(mode, M, N, K, num_sms > 0 ? num_sms : 148);
+    const int s2 = pick_splits(mode, M, N, K, (num_sms > 0 ? num_sms : 148) / 2, 2 * BM);
+    if (s2 > s) s = s2;
     return s > 1 ? (long)s * M * N * 4 : 0;
 }
 
@@ -471,6 +570,7 @@ LLMK_API int llmk_gemm(int mode, int epi, const void* A, const void* B, void* C,
                        int max_ctas, void* stream_) {
     cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
     if (M <= 0 || N <= 0 || K <= 0) return LLMK_ERR_SHAPE;
+    if (epi & EPI_PARTIAL) return LLMK_ERR_SHAPE;   // internal: chosen here when the K dimension is split
     if ((N % 8) || (K % 8 && mode != MODE_TN) || (mode == MODE_TN && (M % 8))) return LLMK_ERR_SHAPE;
     if ((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(B) | reinterpret_cast<uintptr_t>(C)) & 15)
         return LLMK_ERR_SHAPE;
@@ -481,7 +581,9 @@ LLMK_API int llmk_gemm(int mode, int epi, const void* A, const void* B, void* C,
     }
     Params p;
     p.M = M; p.N = N; p.K = K;
-    p.tiles_m = ceil_div(M, BM);
+    const int pair_clusters = query_pair_clusters();
+    p.pair = pair_clusters > 0 ? 1 : 0;
+    p.tiles_m = ceil_div(M, p.pair ? 2 * BM : BM);
     p.tiles_n = ceil_div(N, BN);
     p.kb_total = ceil_div(K, BK);
     p.splits = 1;
@@ -491,7 +593,9 @@ LLMK_API int llmk_gemm(int mode, int epi, const void* A, const void* B, void* C,
     p.status = status;
     bool split_accumulate = false;
     if (mode == MODE_TN && (epi == 0 || epi == EPI_ADD)) {
-        int s = pick_splits(mode, M, N, K, max_ctas > 0 && max_ctas < g_num_sms ? max_ctas : g_num_sms);
+        const int workers = p.pair ? pair_clusters : g_num_sms;
+        const int cap = max_ctas > 0 ? (p.pair ? (max_ctas / 2 > 0 ? max_ctas / 2 : 1) : max_ctas) : workers;
+        int s = pick_splits(mode, M, N, K, cap < workers ? cap : workers, p.pair ? 2 * BM : BM);
         if (s > 1) {
             if (workspace == nullptr || workspace_bytes < (long)s * M * N * 4) return LLMK_ERR_WORKSPACE;
             p.splits = s;
@@ -510,7 +614,7 @@ LLMK_API int llmk_gemm(int mode, int epi, const void* A, const void* B, void* C,
     if (mode == MODE_TN) rc = make_tmap_2d(&tmA, A, M, K, M, 64, BK);   // A[K,M], box 64(m) x 64(k)
     else rc = make_tmap_2d(&tmA, A, K, M, K, BK, BM);                    // A[M,K], box 64(k) x 128(m)
     if (rc) return rc;
-    if (mode == MODE_NT) rc = make_tmap_2d(&tmB, B, K, N, K, BK, BN);   // B[N,K], box 64(k) x 256(n)
+    if (mode == MODE_NT) rc = make_tmap_2d(&tmB, B, K, N, K, BK, p.pair ? BN / 2 : BN);   // B[N,K], box 64(k) x 256(n); pair: 128(n) per CTA
     else rc = make_tmap_2d(&tmB, B, N, K, N, 64, BK);                    // B[K,N], box 64(n) x 64(k)
     if (rc) return rc;
     rc = make_tmap_2d(&tmC, C, N, M, N, 64, 32);
