@@ -233,7 +233,7 @@ def main() -> int:
         e2e_value = tokens / (ms_e2e / 1e3)
         clocks = sampler.summary(t0, t3)
         h2d = accum * 2 * B * T * 4 * world
-        d2h = 12 * world
+        d2h = 16 * world
         out = {
             "metric": "train tokens/sec (GPT-2 124M, device-timed, max over ranks)",
             "value": round(value, 1), "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,

@@ -116,7 +116,11 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
     const int unit0 = PAIR ? blockIdx.x / 2 : blockIdx.x;                      // first work unit of this CTA (pair)
     const int unit_step = PAIR ? gridDim.x / 2 : gridDim.x;
 
+    // A failure already recorded in the status word (by an earlier kernel or CTA) makes this kernel skip its work,
+    // so that one timed-out wait is not followed by thousands more. A pair takes its leader's view.
+    __shared__ int skip_word;
     if (threadIdx.x == 0) {
+        skip_word = (p.status != nullptr && *reinterpret_cast<volatile int*>(p.status) != 0) ? 1 : 0;
         for (int i = 0; i < STAGES; i++) {
             ptx::mbar_init(&full_bar[i], 1);
             ptx::mbar_init(&empty_bar[i], 1);
@@ -147,8 +151,11 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
     if (PAIR) ptx::cluster_sync_all();   // the peer's barriers are initialised before anything can signal them
     ptx::tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    const bool skip = (PAIR ? ptx::ld_shared_cluster_u32(&skip_word, 0) : (uint32_t)skip_word) != 0;
 
-    if (warp == 0) {
+    if (skip) {
+        // nothing to do: fall through to the teardown
+    } else if (warp == 0) {
         // ------------------------------------------------------------ TMA producer
         int s = 0;
         uint32_t ph = 0;

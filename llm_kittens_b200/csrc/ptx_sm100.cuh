@@ -278,6 +278,18 @@ __device__ __forceinline__ void mma_commit_pair(uint64_t* bar) {
                  "h"((uint16_t)3)
                  : "memory");
 }
+// Read the 32-bit word at this shared-memory offset in CTA `cta` of the cluster.
+__device__ __forceinline__ uint32_t ld_shared_cluster_u32(const void* local_ptr, uint32_t cta) {
+    uint32_t v;
+    asm volatile(
+        "{\n\t.reg .b32 remAddr32;\n\t"
+        "mapa.shared::cluster.u32 remAddr32, %1, %2;\n\t"
+        "ld.shared::cluster.u32 %0, [remAddr32];\n\t}"
+        : "=r"(v)
+        : "r"(smem_u32(local_ptr)), "r"(cta)
+        : "memory");
+    return v;
+}
 // Arrive on the barrier at this offset in CTA `cta` of the cluster.
 __device__ __forceinline__ void mbar_arrive_cluster(uint64_t* bar, uint32_t cta) {
     asm volatile(

@@ -67,8 +67,8 @@ class Trainer:
         self.scale = torch.ones(1, dtype=torch.float32, device=dev)
         self.norm = torch.zeros(1, dtype=torch.float32, device=dev)
         self.flag = torch.zeros(1, dtype=torch.int32, device=dev)
-        self.readback = torch.zeros(3, dtype=torch.float32, device=dev)
-        self.readback_host = torch.zeros(3, dtype=torch.float32)
+        self.readback = torch.zeros(4, dtype=torch.float32, device=dev)
+        self.readback_host = torch.zeros(4, dtype=torch.float32)
         if self.cuda:
             self.readback_host = self.readback_host.pin_memory()
         if self.native:
@@ -195,14 +195,23 @@ class Trainer:
         self.step_count += 1
 
     def read_scalars(self) -> tuple[float, float, bool]:
-        """(mean loss, grad norm, non-finite flag): one device-to-host copy of 12 bytes, then a sync."""
+        """(mean loss, grad norm, non-finite flag): one device-to-host copy of 16 bytes, then a sync."""
         self.readback[0:1].copy_(self.model.acts["loss_acc"])
         self.readback[1:2].copy_(self.norm)
         self.readback[2:3].copy_(self.flag.float())
+        if self.native:
+            from ..ops import _native
+
+            # the kernels' bounded-wait status travels with the same copy: a recorded failure raises here
+            self.readback[3:4].copy_(_native.status_word()[0:1].float())
         self.readback_host.copy_(self.readback, non_blocking=True)
         if self.cuda:
             torch.cuda.current_stream().synchronize()
-        loss, norm, flag = self.readback_host.tolist()
+        loss, norm, flag, status = self.readback_host.tolist()
+        if status != 0.0:
+            from ..ops import _native
+
+            _native.check_status()
         return loss, norm, flag != 0.0
 
     def train_step(self, micro_batches, lr: float | None = None) -> StepResult:
