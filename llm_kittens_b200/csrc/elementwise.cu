@@ -148,11 +148,21 @@ __global__ void dbias_partial_kernel(float* __restrict__ partial, const bf16* __
     const int r0 = blockIdx.y * DB_ROWS;
     const int r1 = min(rows, r0 + DB_ROWS);
     if (c < OC) {
-        for (int r = r0 + threadIdx.y; r < r1; r += 8) {
-            float f[8];
-            unpack8(ld128_stream(dout + (size_t)r * OC + c), f);
+        // eight independent 16-byte loads in flight per thread (the chunk has 32 rows per row lane)
+        for (int r = r0 + threadIdx.y; r < r1; r += 64) {
+            bf16x8 v[8];
 #pragma unroll
-            for (int j = 0; j < 8; j++) acc[j] += f[j];
+            for (int u = 0; u < 8; u++)
+                if (r + 8 * u < r1) v[u] = ld128_stream(dout + (size_t)(r + 8 * u) * OC + c);
+#pragma unroll
+            for (int u = 0; u < 8; u++) {
+                if (r + 8 * u < r1) {
+                    float f[8];
+                    unpack8(v[u], f);
+#pragma unroll
+                    for (int j = 0; j < 8; j++) acc[j] += f[j];
+                }
+            }
         }
     }
 #pragma unroll
@@ -168,13 +178,22 @@ __global__ void dbias_partial_kernel(float* __restrict__ partial, const bf16* __
         }
     }
 }
+// block = 32 columns x 32 chunk lanes; lane y sums chunks y, y+32, ... and the lanes are added in a fixed order
 __global__ void dbias_finish_kernel(bf16* __restrict__ dbias, const float* __restrict__ partial, int chunks, int OC,
                                     int accumulate) {
-    const int c = blockIdx.x * blockDim.x + threadIdx.x;
-    if (c >= OC) return;
-    float s = accumulate ? __bfloat162float(dbias[c]) : 0.f;
-    for (int k = 0; k < chunks; k++) s += partial[(size_t)k * OC + c];
-    dbias[c] = __float2bfloat16_rn(s);
+    __shared__ float sh[32][33];
+    const int c = blockIdx.x * 32 + threadIdx.x;
+    float s = 0.f;
+    if (c < OC)
+        for (int k = threadIdx.y; k < chunks; k += 32) s += partial[(size_t)k * OC + c];
+    sh[threadIdx.y][threadIdx.x] = s;
+    __syncthreads();
+    if (threadIdx.y == 0 && c < OC) {
+        float t = accumulate ? __bfloat162float(dbias[c]) : 0.f;
+#pragma unroll
+        for (int y = 0; y < 32; y++) t += sh[y][threadIdx.x];
+        dbias[c] = __float2bfloat16_rn(t);
+    }
 }
 
 // ------------------------------------------------------------------ encoder
@@ -315,8 +334,8 @@ LLMK_API int llmk_dbias(void* dbias, void* scratch, const void* dout, int rows, 
     dim3 grid(ceil_div(OC, 256), chunks), block(32, 8);
     dbias_partial_kernel<<<grid, block, 0, (cudaStream_t)stream>>>((float*)scratch, (const bf16*)dout, rows, OC);
     LLMK_LAUNCH_CHECK();
-    dbias_finish_kernel<<<ceil_div(OC, 256), 256, 0, (cudaStream_t)stream>>>((bf16*)dbias, (const float*)scratch, chunks, OC,
-                                                                          accumulate);
+    dbias_finish_kernel<<<ceil_div(OC, 32), dim3(32, 32), 0, (cudaStream_t)stream>>>((bf16*)dbias, (const float*)scratch, chunks,
+                                                                                  OC, accumulate);
     LLMK_LAUNCH_CHECK();
     return LLMK_OK;
 }
