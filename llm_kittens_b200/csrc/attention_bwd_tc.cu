@@ -270,12 +270,9 @@ attn_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_c
             }
             ptx::tc_fence_after();
             const bool diag = dq0 < BM;                      // some (key, query) pairs of this sub-tile are masked
-#pragma unroll 1
-            for (int c4 = 0; c4 < BN / 32; c4++) {
-                uint32_t vs[32], vd[32];
-                ptx::tmem_ld_32x32b_x32(t_st + lane_off + c4 * 32, vs);
-                ptx::tmem_ld_32x32b_x32(t_dpt + lane_off + c4 * 32, vd);
-                ptx::tmem_ld_wait();
+            // the two TMEM loads of chunk c4+1 are issued before chunk c4 is processed (two register sets)
+            uint32_t vsA[32], vdA[32], vsB[32], vdB[32];
+            auto process = [&](int c4, const uint32_t (&vs)[32], const uint32_t (&vd)[32]) {
 #pragma unroll
                 for (int q = 0; q < 4; q++) {
                     float p[8], ds[8], L[8], D[8];
@@ -294,6 +291,18 @@ attn_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_c
                     store_chunk(sPt, r, c4 * 4 + q, p);
                     store_chunk(sdSt, r, c4 * 4 + q, ds);
                 }
+            };
+            ptx::tmem_ld_32x32b_x32(t_st + lane_off, vsA);
+            ptx::tmem_ld_32x32b_x32(t_dpt + lane_off, vdA);
+#pragma unroll
+            for (int c4 = 0; c4 < BN / 32; c4++) {
+                ptx::tmem_ld_wait();
+                if (c4 + 1 < BN / 32) {
+                    ptx::tmem_ld_32x32b_x32(t_st + lane_off + (c4 + 1) * 32, (c4 & 1) ? vsA : vsB);
+                    ptx::tmem_ld_32x32b_x32(t_dpt + lane_off + (c4 + 1) * 32, (c4 & 1) ? vdA : vdB);
+                }
+                if (c4 & 1) process(c4, vsB, vdB);
+                else process(c4, vsA, vdA);
             }
             ptx::tc_fence_before();
             ptx::fence_proxy_async_smem();
@@ -505,12 +514,8 @@ attn_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_co
             ptx::tc_fence_after();
             const int dk0 = j * BN - q0;            // first key of the sub-tile relative to the first query
             const bool diag = dk0 + BN > 0;         // reaches past the first query: some pairs are masked
-#pragma unroll 1
-            for (int c4 = 0; c4 < BN / 32; c4++) {
-                uint32_t vs[32], vd[32];
-                ptx::tmem_ld_32x32b_x32(t_s + lane_off + c4 * 32, vs);
-                ptx::tmem_ld_32x32b_x32(t_dp + lane_off + c4 * 32, vd);
-                ptx::tmem_ld_wait();
+            uint32_t vsA[32], vdA[32], vsB[32], vdB[32];
+            auto process = [&](int c4, const uint32_t (&vs)[32], const uint32_t (&vd)[32]) {
 #pragma unroll
                 for (int q = 0; q < 4; q++) {
                     float ds[8];
@@ -523,6 +528,18 @@ attn_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_co
                     }
                     store_chunk(sdS, r, c4 * 4 + q, ds);
                 }
+            };
+            ptx::tmem_ld_32x32b_x32(t_s + lane_off, vsA);
+            ptx::tmem_ld_32x32b_x32(t_dp + lane_off, vdA);
+#pragma unroll
+            for (int c4 = 0; c4 < BN / 32; c4++) {
+                ptx::tmem_ld_wait();
+                if (c4 + 1 < BN / 32) {
+                    ptx::tmem_ld_32x32b_x32(t_s + lane_off + (c4 + 1) * 32, (c4 & 1) ? vsA : vsB);
+                    ptx::tmem_ld_32x32b_x32(t_dp + lane_off + (c4 + 1) * 32, (c4 & 1) ? vdA : vdB);
+                }
+                if (c4 & 1) process(c4, vsB, vdB);
+                else process(c4, vsA, vdA);
             }
             ptx::tc_fence_before();
             ptx::fence_proxy_async_smem();
