@@ -27,7 +27,7 @@ int make_tmap_2d(CUtensorMap* m, const void* ptr, uint64_t inner, uint64_t outer
 namespace attn_bwd_tc {
 
 constexpr int BM = 128;  // rows of the tile a CTA owns
-constexpr int THREADS = 192;
+constexpr int THREADS = 320;   // producer, MMA issuer, and two softmax warps per TMEM lane group (they split the columns)
 constexpr float LOG2E = 1.4426950408889634f;
 
 __device__ __forceinline__ float ex2(float x) {
@@ -150,9 +150,9 @@ attn_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_c
             ptx::mbar_init(&ld_full[i], 1);
         }
         ptx::mbar_init(s_full, 1);
-        ptx::mbar_init(p_full, 4);
+        ptx::mbar_init(p_full, 8);
         ptx::mbar_init(acc_done, 1);
-        ptx::mbar_init(epi, 4);
+        ptx::mbar_init(epi, 8);
         *abort_flag = 0;
         ptx::fence_barrier_init();
     }
@@ -252,6 +252,7 @@ attn_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_c
         }
     } else {
         const int lane_group = warp & 3;
+        const int sub = (warp - 2) >> 2;                     // 0 / 1: which half of the columns this warp handles
         const int r = lane_group * 32 + lane;               // key row inside the tile
         const uint32_t lane_off = (uint32_t)(lane_group * 32) << 16;
         bool ok = true;
@@ -292,16 +293,20 @@ attn_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_c
                     store_chunk(sdSt, r, c4 * 4 + q, ds);
                 }
             };
-            ptx::tmem_ld_32x32b_x32(t_st + lane_off, vsA);
-            ptx::tmem_ld_32x32b_x32(t_dpt + lane_off, vdA);
+            // this warp's share of the sub-tile's columns: chunks [sub * NCH, (sub + 1) * NCH)
+            constexpr int NCH = BN / 64;
+            const int c_first = sub * NCH;
+            ptx::tmem_ld_32x32b_x32(t_st + lane_off + c_first * 32, vsA);
+            ptx::tmem_ld_32x32b_x32(t_dpt + lane_off + c_first * 32, vdA);
 #pragma unroll
-            for (int c4 = 0; c4 < BN / 32; c4++) {
+            for (int i4 = 0; i4 < NCH; i4++) {
+                const int c4 = c_first + i4;
                 ptx::tmem_ld_wait();
-                if (c4 + 1 < BN / 32) {
-                    ptx::tmem_ld_32x32b_x32(t_st + lane_off + (c4 + 1) * 32, (c4 & 1) ? vsA : vsB);
-                    ptx::tmem_ld_32x32b_x32(t_dpt + lane_off + (c4 + 1) * 32, (c4 & 1) ? vdA : vdB);
+                if (i4 + 1 < NCH) {
+                    ptx::tmem_ld_32x32b_x32(t_st + lane_off + (c4 + 1) * 32, (i4 & 1) ? vsA : vsB);
+                    ptx::tmem_ld_32x32b_x32(t_dpt + lane_off + (c4 + 1) * 32, (i4 & 1) ? vdA : vdB);
                 }
-                if (c4 & 1) process(c4, vsB, vdB);
+                if (i4 & 1) process(c4, vsB, vdB);
                 else process(c4, vsA, vdA);
             }
             ptx::tc_fence_before();
@@ -316,7 +321,7 @@ attn_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_c
             uint8_t* stage_dk = sPt;    // HS/64 tiles of 16 KB each fit: BM*BN*2 >= BM*HS*2 for both head sizes
             uint8_t* stage_dv = sdSt;
 #pragma unroll
-            for (int h4 = 0; h4 < HS / 32; h4++) {
+            for (int h4 = sub; h4 < HS / 32; h4 += 2) {
                 uint32_t v[32];
                 ptx::tmem_ld_32x32b_x32(t_dk + lane_off + h4 * 32, v);
                 ptx::tmem_ld_wait();
@@ -420,9 +425,9 @@ attn_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_co
             ptx::mbar_init(&ring_empty[i], 1);
         }
         ptx::mbar_init(s_full, 1);
-        ptx::mbar_init(p_full, 4);
+        ptx::mbar_init(p_full, 8);
         ptx::mbar_init(acc_done, 1);
-        ptx::mbar_init(epi, 4);
+        ptx::mbar_init(epi, 8);
         *abort_flag = 0;
         ptx::fence_barrier_init();
     }
@@ -499,6 +504,7 @@ attn_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_co
         }
     } else {
         const int lane_group = warp & 3;
+        const int sub = (warp - 2) >> 2;                     // 0 / 1: which half of the columns this warp handles
         const int r = lane_group * 32 + lane;   // query row inside the tile
         const uint32_t lane_off = (uint32_t)(lane_group * 32) << 16;
         const size_t roff = ((size_t)b * NH + h) * T + q0 + r;
@@ -529,16 +535,20 @@ attn_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_co
                     store_chunk(sdS, r, c4 * 4 + q, ds);
                 }
             };
-            ptx::tmem_ld_32x32b_x32(t_s + lane_off, vsA);
-            ptx::tmem_ld_32x32b_x32(t_dp + lane_off, vdA);
+            // this warp's share of the sub-tile's columns: chunks [sub * NCH, (sub + 1) * NCH)
+            constexpr int NCH = BN / 64;
+            const int c_first = sub * NCH;
+            ptx::tmem_ld_32x32b_x32(t_s + lane_off + c_first * 32, vsA);
+            ptx::tmem_ld_32x32b_x32(t_dp + lane_off + c_first * 32, vdA);
 #pragma unroll
-            for (int c4 = 0; c4 < BN / 32; c4++) {
+            for (int i4 = 0; i4 < NCH; i4++) {
+                const int c4 = c_first + i4;
                 ptx::tmem_ld_wait();
-                if (c4 + 1 < BN / 32) {
-                    ptx::tmem_ld_32x32b_x32(t_s + lane_off + (c4 + 1) * 32, (c4 & 1) ? vsA : vsB);
-                    ptx::tmem_ld_32x32b_x32(t_dp + lane_off + (c4 + 1) * 32, (c4 & 1) ? vdA : vdB);
+                if (i4 + 1 < NCH) {
+                    ptx::tmem_ld_32x32b_x32(t_s + lane_off + (c4 + 1) * 32, (i4 & 1) ? vsA : vsB);
+                    ptx::tmem_ld_32x32b_x32(t_dp + lane_off + (c4 + 1) * 32, (i4 & 1) ? vdA : vdB);
                 }
-                if (c4 & 1) process(c4, vsB, vdB);
+                if (i4 & 1) process(c4, vsB, vdB);
                 else process(c4, vsA, vdA);
             }
             ptx::tc_fence_before();
@@ -551,7 +561,7 @@ attn_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_co
             ptx::tc_fence_after();
             // dQ (scaled) -> bf16 -> the dS buffer as [128 x 64] staging tiles -> TMA stores
 #pragma unroll
-            for (int h4 = 0; h4 < HS / 32; h4++) {
+            for (int h4 = sub; h4 < HS / 32; h4 += 2) {
                 uint32_t v[32];
                 ptx::tmem_ld_32x32b_x32(t_dq + lane_off + h4 * 32, v);
                 ptx::tmem_ld_wait();
