@@ -17,6 +17,8 @@
 // attention_backward / attention_gqa_backward in the reference (llmc/attention.cuh:481-604,
 // llmc/attention_gqa.cuh:483-572). Warp roles as in the forward kernel (attention_tc.cu): warp 0 TMA
 // producer, warp 1 MMA issuer, warps 2-5 one row per thread. All waits are bounded.
+#include <cstdlib>
+
 #include "ptx_sm100.cuh"
 
 namespace llmk {
@@ -366,6 +368,261 @@ attn_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_c
     }
 }
 
+// ====================================================================================== dK, dV for HS = 64, pipelined
+// One CTA per SM and per 128-key tile; the scores S^T / dP^T of 64-query sub-tiles are double-buffered in TMEM and
+// two groups of eight softmax warps take alternate sub-tiles, so the tensor core computes the scores of sub-tile
+// it+1 while group (it & 1) turns those of sub-tile `it` into P^T / dS^T. Q / dO sub-tiles come through a 3-deep ring.
+// TMEM (512 columns): S^T[2] 0/64, dP^T[2] 128/192, dV 256, dK 320.
+namespace dkv2 {
+constexpr int HS = 64, BN = 64, RING = 3;
+constexpr int THREADS2 = 32 * (2 + 16);
+constexpr int TILE = BM * HS * 2;       // K or V: 16 KB
+constexpr int RT = BN * HS * 2;         // Q or dO sub-tile: 8 KB
+constexpr int PT = BM * BN * 2;         // P^T or dS^T: 16 KB
+constexpr int OFF_K = 0, OFF_V = TILE, OFF_RING = 2 * TILE;
+constexpr int OFF_PT = OFF_RING + RING * 2 * RT;          // [2]
+constexpr int OFF_DST = OFF_PT + 2 * PT;                  // [2]
+constexpr int OFF_LD = OFF_DST + 2 * PT;                  // float [RING][2][64]
+constexpr int OFF_BAR = OFF_LD + RING * 2 * 64 * 4;
+constexpr int SMEM_BYTES = OFF_BAR + 256;
+
+__global__ void __launch_bounds__(THREADS2, 1)
+attn_bwd_dkv2_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_constant__ CUtensorMap tmQKVin,
+                     const __grid_constant__ CUtensorMap tmDOin, const __grid_constant__ CUtensorMap tmDQKV,
+                     const float* __restrict__ lse, const float* __restrict__ dvec, int T, int NH, int NKVH, float scale,
+                     int* status) {
+    extern __shared__ __align__(1024) uint8_t smem[];
+    if (already_failed(status)) return;
+    if (ptx::smem_u32(smem) & 1023u) {
+        if (threadIdx.x == 0 && status != nullptr) atomicCAS(status, 0, LLMK_ST_BOUNDS);
+        return;
+    }
+    uint8_t* sK = smem + OFF_K;
+    uint8_t* sV = smem + OFF_V;
+    uint8_t* sRing = smem + OFF_RING;
+    uint8_t* sPt = smem + OFF_PT;
+    uint8_t* sdSt = smem + OFF_DST;
+    float* sLD = reinterpret_cast<float*>(smem + OFF_LD);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + OFF_BAR);
+    uint64_t* kv_full = bars;             // [1]
+    uint64_t* ring_full = bars + 1;       // [3]
+    uint64_t* ring_empty = bars + 4;      // [3]
+    uint64_t* ld_full = bars + 7;         // [3]
+    uint64_t* s_full = bars + 10;         // [2]
+    uint64_t* p_full = bars + 12;         // [2]
+    uint64_t* acc_done = bars + 14;       // [2]
+    uint64_t* epi = bars + 16;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 17);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int kt = blockIdx.x, hk = blockIdx.y, b = blockIdx.z;
+    const int hr = NH / NKVH;
+    const int kv0 = kt * BM;
+    const int nq = (T - kv0) / BN;
+    const int total = nq * hr;
+    const int row_base = b * T;
+    const int k_col = (NH + hk) * HS, v_col = (NH + NKVH + hk) * HS;
+    const float scale_log2 = scale * LOG2E;
+
+    if (threadIdx.x == 0) {
+        ptx::mbar_init(kv_full, 1);
+        for (int i = 0; i < RING; i++) {
+            ptx::mbar_init(&ring_full[i], 1);
+            ptx::mbar_init(&ring_empty[i], 1);
+            ptx::mbar_init(&ld_full[i], 1);
+        }
+        for (int i = 0; i < 2; i++) {
+            ptx::mbar_init(&s_full[i], 1);
+            ptx::mbar_init(&p_full[i], 8);
+            ptx::mbar_init(&acc_done[i], 1);
+        }
+        ptx::mbar_init(epi, 16);
+        *abort_flag = 0;
+        ptx::fence_barrier_init();
+    }
+    if (warp == 1) {
+        ptx::tmem_alloc(tmem_slot, 512);
+        ptx::tmem_relinquish();
+    }
+    ptx::tc_fence_before();
+    __syncthreads();
+    ptx::tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+    const uint32_t t_dv = tmem_base + 256, t_dk = tmem_base + 320;
+
+    if (warp == 0) {
+        // ------------------------------------------------------------ producer: K, V once; Q / dO ring; LSE / D vectors
+        if (lane == 0) {
+            ptx::mbar_arrive_expect_tx(kv_full, 2 * TILE);
+            load_tile<HS, BM>(sK, &tmQKV, kv_full, k_col, row_base + kv0);
+            load_tile<HS, BM>(sV, &tmQKV, kv_full, v_col, row_base + kv0);
+        }
+        __syncwarp();
+        for (int it = 0; it < total; it++) {
+            const int s = it % RING;
+            if (!ptx::mbar_wait(&ring_empty[s], ((it / RING) & 1) ^ 1, abort_flag, status, LLMK_ST_TIMEOUT_TMA_EMPTY, it)) break;
+            const int hq = hk * hr + it / nq, q0 = kv0 + (it % nq) * BN;
+            if (lane == 0) {
+                ptx::mbar_arrive_expect_tx(&ring_full[s], 2 * RT);
+                load_tile<HS, BN>(sRing + s * 2 * RT, &tmQKVin, &ring_full[s], hq * HS, row_base + q0);
+                load_tile<HS, BN>(sRing + s * 2 * RT + RT, &tmDOin, &ring_full[s], hq * HS, row_base + q0);
+            }
+            float* sL = sLD + s * 128;
+            const size_t off = ((size_t)b * NH + hq) * T + q0;
+#pragma unroll
+            for (int i = 0; i < BN / 32; i++) {
+                sL[lane + 32 * i] = lse[off + lane + 32 * i] * LOG2E;
+                sL[64 + lane + 32 * i] = dvec[off + lane + 32 * i];
+            }
+            __syncwarp();
+            if (lane == 0) ptx::mbar_arrive(&ld_full[s]);
+            __syncwarp();
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------ MMA issuer (lane 0)
+        if (lane == 0) {
+            constexpr uint32_t idesc_s = ptx::make_idesc_bf16(BM, BN, 0, 0);
+            constexpr uint32_t idesc_acc = ptx::make_idesc_bf16(BM, HS, 0, 1);
+            const uint64_t k_desc = kmajor_desc<BM>(ptx::smem_u32(sK), 0), v_desc = kmajor_desc<BM>(ptx::smem_u32(sV), 0);
+            const uint32_t ring_addr = ptx::smem_u32(sRing), pt_addr = ptx::smem_u32(sPt), dst_addr = ptx::smem_u32(sdSt);
+            bool ok = ptx::mbar_wait_spin(kv_full, 0, abort_flag, status, LLMK_ST_TIMEOUT_TMA_FULL, -1);
+            for (int it = 0; it <= total && ok; it++) {
+                if (it < total) {
+                    // scores of sub-tile `it` into buffer it & 1 (its previous reader, sub-tile it-2, finished before
+                    // P(it-2) was published, which the accumulation step below has already waited for)
+                    const int s = it % RING, bsel = it & 1;
+                    ok = ptx::mbar_wait_spin(&ring_full[s], (it / RING) & 1, abort_flag, status, LLMK_ST_TIMEOUT_TMA_FULL, it);
+                    if (!ok) break;
+                    ptx::tc_fence_after();
+                    const uint64_t q_desc = kmajor_desc<BN>(ring_addr + s * 2 * RT, 0), do_desc = kmajor_desc<BN>(ring_addr + s * 2 * RT + RT, 0);
+#pragma unroll
+                    for (int kk = 0; kk < HS / 16; kk++)
+                        ptx::mma_f16_ss(tmem_base + bsel * 64, kmajor_step<BM>(k_desc, kk), kmajor_step<BN>(q_desc, kk), idesc_s, kk > 0 ? 1u : 0u);
+#pragma unroll
+                    for (int kk = 0; kk < HS / 16; kk++)
+                        ptx::mma_f16_ss(tmem_base + 128 + bsel * 64, kmajor_step<BM>(v_desc, kk), kmajor_step<BN>(do_desc, kk), idesc_s, kk > 0 ? 1u : 0u);
+                    ptx::mma_commit(&s_full[bsel]);
+                }
+                if (it >= 1) {
+                    const int j = it - 1, s = j % RING, bsel = j & 1;
+                    ok = ptx::mbar_wait_spin(&p_full[bsel], (j >> 1) & 1, abort_flag, status, LLMK_ST_TIMEOUT_ACC_EMPTY, j);
+                    if (!ok) break;
+                    ptx::tc_fence_after();
+                    const uint64_t q_mn = mnmajor_desc<BN>(ring_addr + s * 2 * RT, 0), do_mn = mnmajor_desc<BN>(ring_addr + s * 2 * RT + RT, 0);
+                    const uint64_t pt_desc = kmajor_desc<BM>(pt_addr + bsel * PT, 0), dst_desc = kmajor_desc<BM>(dst_addr + bsel * PT, 0);
+#pragma unroll
+                    for (int kk = 0; kk < BN / 16; kk++)
+                        ptx::mma_f16_ss(t_dv, kmajor_step<BM>(pt_desc, kk), mnmajor_step(do_mn, kk), idesc_acc, (j > 0 || kk > 0) ? 1u : 0u);
+#pragma unroll
+                    for (int kk = 0; kk < BN / 16; kk++)
+                        ptx::mma_f16_ss(t_dk, kmajor_step<BM>(dst_desc, kk), mnmajor_step(q_mn, kk), idesc_acc, (j > 0 || kk > 0) ? 1u : 0u);
+                    ptx::mma_commit(&ring_empty[s]);
+                    ptx::mma_commit(&acc_done[bsel]);
+                }
+            }
+        }
+        __syncwarp();
+    } else {
+        // ------------------------------------------------------------ softmax warps: group g takes sub-tiles it with (it & 1) == g
+        const int w = warp - 2;                  // 0..15
+        const int g = w >> 3;                    // group
+        const int lane_group = warp & 3;
+        const int sub = (w >> 2) & 1;            // which 32 of the 64 query columns
+        const int r = lane_group * 32 + lane;    // key row inside the tile
+        const uint32_t lane_off = (uint32_t)(lane_group * 32) << 16;
+        uint8_t* myPt = sPt + g * PT;
+        uint8_t* mydSt = sdSt + g * PT;
+        const uint32_t t_st = tmem_base + g * 64 + sub * 32, t_dpt = tmem_base + 128 + g * 64 + sub * 32;
+        bool ok = true;
+        int last = -1;
+        for (int it = g; it < total && ok; it += 2) {
+            last = it;
+            const int dq0 = (it % nq) * BN;
+            const int slot = it % RING;
+            const float* sL = sLD + slot * 128 + sub * 32;
+            const float* sD = sL + 64;
+            ok = ptx::mbar_wait(&ld_full[slot], (it / RING) & 1, abort_flag, status, LLMK_ST_TIMEOUT_TMA_FULL, 3000 + it);
+            if (!ok) break;
+            ok = ptx::mbar_wait(&s_full[g], (it >> 1) & 1, abort_flag, status, LLMK_ST_TIMEOUT_ACC_FULL, it);
+            if (!ok) break;
+            if (it >= 2) {   // the accumulation MMAs of sub-tile it-2 have finished reading this group's P^T / dS^T
+                ok = ptx::mbar_wait(&acc_done[g], ((it >> 1) - 1) & 1, abort_flag, status, LLMK_ST_TIMEOUT_ACC_FULL, 1000 + it);
+                if (!ok) break;
+            }
+            ptx::tc_fence_after();
+            const bool diag = dq0 < BM;
+            uint32_t vs[32], vd[32];
+            ptx::tmem_ld_32x32b_x32(t_st + lane_off, vs);
+            ptx::tmem_ld_32x32b_x32(t_dpt + lane_off, vd);
+            ptx::tmem_ld_wait();
+#pragma unroll
+            for (int q = 0; q < 4; q++) {
+                float p[8], ds[8], L[8], D[8];
+                *reinterpret_cast<float4*>(L) = *reinterpret_cast<const float4*>(sL + q * 8);
+                *reinterpret_cast<float4*>(L + 4) = *reinterpret_cast<const float4*>(sL + q * 8 + 4);
+                *reinterpret_cast<float4*>(D) = *reinterpret_cast<const float4*>(sD + q * 8);
+                *reinterpret_cast<float4*>(D + 4) = *reinterpret_cast<const float4*>(sD + q * 8 + 4);
+#pragma unroll
+                for (int i = 0; i < 8; i++) {
+                    const int c = sub * 32 + q * 8 + i;   // query column of the sub-tile
+                    float e = ex2(fmaf(__uint_as_float(vs[q * 8 + i]), scale_log2, -L[i]));
+                    if (diag && r > c + dq0) e = 0.f;     // key after query
+                    p[i] = e;
+                    ds[i] = e * (__uint_as_float(vd[q * 8 + i]) - D[i]);
+                }
+                store_chunk(myPt, r, sub * 4 + q, p);
+                store_chunk(mydSt, r, sub * 4 + q, ds);
+            }
+            ptx::tc_fence_before();
+            ptx::fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0) ptx::mbar_arrive(&p_full[g]);
+        }
+        // every accumulation has to be complete: the commit of the last sub-tile covers all earlier MMAs
+        if (ok) ok = ptx::mbar_wait(&acc_done[(total - 1) & 1], ((total - 1) >> 1) & 1, abort_flag, status, LLMK_ST_TIMEOUT_ACC_FULL, 2000);
+        if (ok && total >= 2 && last >= 0)   // ... and this group's own buffers must be idle before they become staging space
+            ok = ptx::mbar_wait(&acc_done[g], (last >> 1) & 1, abort_flag, status, LLMK_ST_TIMEOUT_ACC_FULL, 2001);
+        if (ok) {
+            ptx::tc_fence_after();
+            // the 4 warps of a lane group take one 32-column chunk each: dK chunks 0/1 (scaled), dV chunks 0/1
+            const int part = w >> 2;                           // 0..3
+            const bool is_dk = part < 2;
+            const int h4 = part & 1;
+            uint8_t* stage = is_dk ? sPt : sdSt;               // [128 x 64] staging tile in buffer 0 of each
+            uint32_t v[32];
+            ptx::tmem_ld_32x32b_x32((is_dk ? t_dk : t_dv) + lane_off + h4 * 32, v);
+            ptx::tmem_ld_wait();
+            const float sc = is_dk ? scale : 1.0f;
+#pragma unroll
+            for (int q = 0; q < 4; q++) {
+                float f[8];
+#pragma unroll
+                for (int i = 0; i < 8; i++) f[i] = __uint_as_float(v[q * 8 + i]) * sc;
+                stage_chunk(stage, r, h4 * 4 + q, f);
+            }
+            ptx::fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0) ptx::mbar_arrive(epi);
+            if (warp == 2 && lane == 0) {
+                if (ptx::mbar_wait(epi, 0, abort_flag, status, LLMK_ST_TIMEOUT_ACC_FULL, 4000)) {
+                    ptx::tma_store_2d(&tmDQKV, sPt, k_col, row_base + kv0);
+                    ptx::tma_store_2d(&tmDQKV, sdSt, v_col, row_base + kv0);
+                    ptx::tma_store_commit();
+                    ptx::tma_store_wait_read<0>();
+                }
+            }
+        }
+    }
+    ptx::tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        ptx::tc_fence_after();
+        ptx::tmem_dealloc(tmem_base, 512);
+    }
+}
+}  // namespace dkv2
+
 // ====================================================================================== dQ
 template <int HS>
 struct DqCfg {
@@ -617,8 +874,24 @@ static int launch(const void* qkv, const void* dout, bf16* dqkv, const float* ls
     if ((rc = gemm::make_tmap_2d(&tdo_in, dout, cw, rows, cw, 64, BN))) return rc;
     if ((rc = gemm::make_tmap_2d(&tdqkv, dqkv, width, rows, width, 64, BM))) return rc;
     const float scale = 1.0f / sqrtf((float)HS);
-    attn_bwd_dkv_tc_kernel<HS><<<dim3(T / BM, NKVH, B), THREADS, DkvCfg<HS>::SMEM_BYTES, stream>>>(tq, tq_in, tdo_in, tdqkv, lse, dvec,
-                                                                                                 T, NH, NKVH, scale, status);
+    // The pipelined kernel has no second CTA on its SM to hide its prologue and epilogue behind, so it only pays off
+    // when a CTA loops over many sub-tiles (long sequences, grouped queries): measured 1.08 vs 1.12 ms at T=2048 with
+    // 4 query heads per KV head, but 1.00 vs 0.90 ms at T=1024 with one. LLMK_ATTN_BWD_DKV=1|2 forces a version.
+    static const char* dkv_env = getenv("LLMK_ATTN_BWD_DKV");
+    const bool long_loops = (T / 64) * (NH / NKVH) >= 64;
+    const bool use_v2 = dkv_env != nullptr ? dkv_env[0] == '2' : long_loops;
+    if (HS == 64 && use_v2) {
+        static bool configured2 = false;
+        if (!configured2) {
+            LLMK_CUDA_TRY(cudaFuncSetAttribute(dkv2::attn_bwd_dkv2_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, dkv2::SMEM_BYTES));
+            configured2 = true;
+        }
+        dkv2::attn_bwd_dkv2_kernel<<<dim3(T / BM, NKVH, B), dkv2::THREADS2, dkv2::SMEM_BYTES, stream>>>(tq, tq_in, tdo_in, tdqkv, lse, dvec, T,
+                                                                                                    NH, NKVH, scale, status);
+    } else {
+        attn_bwd_dkv_tc_kernel<HS><<<dim3(T / BM, NKVH, B), THREADS, DkvCfg<HS>::SMEM_BYTES, stream>>>(tq, tq_in, tdo_in, tdqkv, lse, dvec,
+                                                                                                     T, NH, NKVH, scale, status);
+    }
     LLMK_LAUNCH_CHECK();
     attn_bwd_dq_tc_kernel<HS><<<dim3(T / BM, NH, B), THREADS, DqCfg<HS>::SMEM_BYTES, stream>>>(tq, tdo, tq_in, tdqkv, lse, dvec, T, NH,
                                                                                              NKVH, scale, status);
