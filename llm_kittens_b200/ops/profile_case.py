@@ -3,7 +3,8 @@
     python -m llm_kittens_b200.ops.profile_case <case> [launches]
 
 cases: gemm_nt, gemm_nt_gelu, gemm_nn, gemm_tn, attn_fwd, attn_bwd, layernorm_fwd, layernorm_bwd,
-classifier, adamw. Each case allocates inputs larger than the L2 (but well under a few GB), runs
+classifier, adamw, comm_rs, comm_adamw_push (the peer-memory kernels with all ranks emulated on one GPU).
+Each case allocates inputs larger than the L2 (but well under a few GB), runs
 the op twice as warm-up and then `launches` (default 2) more times, and checks the status word.
 Used as ``ncu --set full --clock-control none -k regex:<kernel> -s <warm-up launches> -c 1 ...``.
 """
@@ -70,6 +71,31 @@ def build(case: str):
         segs, max_len = optim.make_segments([(0, 0, 0, n, True)])
         scale = torch.ones(1, device="cuda")
         return lambda: optim.adamw(p, master, g, m, v, segs, max_len, 1e-4, 0.9, 0.95, 1, 1e-8, 0.1, scale)
+    if case in ("comm_rs", "comm_adamw_push"):
+        # The peer-memory kernels with all P "ranks" emulated on this GPU in ONE launch: P local buffers stand for the
+        # peers' buffers and every flag is pre-set, so nothing waits. Shows the kernels' own load / reduce / store
+        # rates; the NVLink part cannot be profiled here (multi-rank programs are not run under the profiler).
+        import ctypes
+
+        P, L, C = 8, 12, 768
+        per_layer = 12 * C * C + 13 * C                       # one GPT-2 block's parameters
+        n = L * per_layer
+        shard = per_layer // P // 8 * 8
+        bufs = [_rnd(n, scale=0.01) for _ in range(P)]
+        ptrs = (ctypes.c_longlong * P)(*[int(b.data_ptr()) for b in bufs])
+        ctrl = torch.full((int(N.lib().llmk_comm_ctrl_ints()),), 1 << 20, dtype=torch.int32, device="cuda")
+        gshard = torch.zeros(L * shard, dtype=torch.float32, device="cuda")
+        if case == "comm_rs":
+            rows = [(l * per_layer, l * shard, shard) for l in range(L)]       # rank 0's slice of every block
+            table = torch.tensor(rows, dtype=torch.int64, device="cuda")
+            partials = torch.zeros(len(rows) * 64, dtype=torch.float32, device="cuda")
+            return lambda: N.call("llmk_comm_rs_bucket", ptrs, ctrl, 0, 1, table, len(rows), gshard, partials, 64, P, 0,
+                                  int(1e9), N.status_word())
+        m, v, master = (torch.zeros(L * shard, dtype=torch.float32, device="cuda") for _ in range(3))
+        segs = torch.tensor([(l * per_layer, l * shard, shard, 1) for l in range(L)], dtype=torch.int64, device="cuda")
+        scale = torch.ones(1, device="cuda")
+        return lambda: N.call("llmk_comm_adamw_push", ptrs, master, gshard, m, v, segs, L, shard, 1e-4, 0.9, 0.95, 0.1, 0.05, 1e-8,
+                              0.1, scale, 1234, P, 0)
     raise SystemExit(f"unknown case {case}")
 
 
