@@ -98,6 +98,12 @@ def launch_count() -> int:
     return _LAUNCHES
 
 
+def count_replayed(kernels: int) -> None:
+    """A captured CUDA graph with ``kernels`` of this library's kernels has been replayed once."""
+    global _LAUNCHES
+    _LAUNCHES += kernels
+
+
 def call(name: str, *args: Any) -> None:
     """Call ``int name(args..., void* stream)``; tensors become device pointers; raises on failure."""
     global _LAUNCHES

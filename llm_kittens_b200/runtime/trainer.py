@@ -47,6 +47,8 @@ class Trainer:
         self.use_master = use_master_weights and param_dtype != torch.float32
         self.lr, self.wd, self.beta1, self.beta2, self.eps, self.grad_clip = learning_rate, weight_decay, beta1, beta2, eps, grad_clip
         self.step_count = 0
+        self.use_cuda_graph = False
+        self._graph, self._graph_key, self._eager_steps = None, None, 0
         self.rng = Xorshift(rng_state)
         self.rng_state_last_update = rng_state
         n = self.plan.state_elements
@@ -144,11 +146,57 @@ class Trainer:
         self.begin_step()
         batches = list(micro_batches)
         accum = len(batches)
+        if self.use_cuda_graph and self._graph_usable(batches):
+            return self._accumulate_graph(batches)
         for i, (x, y) in enumerate(batches):
             if self.sharded_state:
                 self.comm.start_micro_step(i)
             model.forward(x, y, grad_accum_steps=accum, micro_step=i)
             model.backward(last_micro_step=(i == accum - 1), bucket_ready=self._bucket_ready)
+        self._eager_steps += 1
+        return accum
+
+    # ------------------------------------------------------------------ CUDA graph of one micro-step
+    def enable_cuda_graph(self, on: bool = True) -> None:
+        """Replay one captured forward+backward per micro-step instead of launching ~370 kernels from Python
+        (single-process training only: the communication paths use side streams and host-visible flags).
+        The first step with a given (B, T, accumulation) runs eagerly, the second one is captured."""
+        self.use_cuda_graph = bool(on)
+
+    def _graph_usable(self, batches) -> bool:
+        return (self.native and isinstance(self.comm, SingleProcessComm) and self._eager_steps > 0
+                and type(self.model).__name__ == "Transformer" and len({tuple(x.shape) for x, _ in batches}) == 1)
+
+    def _accumulate_graph(self, batches) -> int:
+        model = self.model
+        accum = len(batches)
+        key = (tuple(batches[0][0].shape), accum)
+        if self._graph_key != key:
+            B, T = key[0]
+            self._gx = torch.zeros(B, T, dtype=torch.int32, device=self.device)
+            self._gy = torch.zeros(B, T, dtype=torch.int32, device=self.device)
+            torch.cuda.synchronize(self.device)
+            from ..ops import _native
+
+            graph = torch.cuda.CUDAGraph()
+            before = _native.launch_count()
+            with torch.cuda.graph(graph):
+                # micro_step=1: the loss accumulator is cleared outside the graph, before the first micro-step
+                model.forward(self._gx, self._gy, grad_accum_steps=accum, micro_step=1)
+                model.backward(last_micro_step=True, bucket_ready=None)
+            # the capture recorded the kernels without running them; gradients and loss are still untouched
+            self._graph_kernels = _native.launch_count() - before
+            _native.count_replayed(-self._graph_kernels)   # they were recorded, not launched
+            self._graph, self._graph_key = graph, key
+        for i, (x, y) in enumerate(batches):
+            self._gx.copy_(x, non_blocking=True)
+            self._gy.copy_(y, non_blocking=True)
+            if i == 0:
+                model.acts["loss_acc"].zero_()
+            self._graph.replay()
+        from ..ops import _native
+
+        _native.count_replayed(self._graph_kernels * accum)
         return accum
 
     def begin_step(self) -> None:
