@@ -253,8 +253,7 @@ def train(args: TrainArgs, trainer_name: str) -> int:
             trainer.begin_step()
             for micro in range(grad_accum):
                 x, y = train_loader.next_batch()
-                model.forward(x, y, grad_accum_steps=grad_accum, micro_step=micro)
-                model.backward(last_micro_step=(micro == grad_accum - 1), bucket_ready=trainer._bucket_ready)
+                trainer.micro_step(x, y, micro, grad_accum)
         lr = sched.get(step)
         guards = args.skip_update_lossz != 0.0 or args.skip_update_gradz != 0.0
         if guards:

@@ -251,6 +251,9 @@ class ShardedComm:
     def reduce_bucket(self, grads, layer) -> None:
         """Reduce-scatter one bucket into the fp32 gradient shard; block buckets every micro-step (adding to
         the shard after the first), the non-block bucket once per step."""
+        if self.micro == 0 or self.epoch == 0:
+            raise RuntimeError("ShardedComm: begin_step() / start_micro_step() were not called (drive micro-steps through "
+                               "Trainer.micro_step)")
         if layer is None:
             slot, epoch, ptrs, acc = self.slot_globals, self.epoch, self.grad_global_ptrs, 0
         else:

@@ -21,8 +21,10 @@ def save_checkpoint(output_dir: str, step: int, trainer, loader, world: int, ran
     os.makedirs(output_dir, exist_ok=True)
     model_path, state_path, done_path = formats.checkpoint_paths(output_dir, step, rank)
     cfg = trainer.model.config
+    params = trainer.full_params()   # a collective when the parameters are sharded: every rank takes part
     if rank == 0:
-        formats.write_model(model_path, cfg, trainer.full_params())
+        formats.write_model(model_path, cfg, params)
+    del params
     formats.write_state(state_path, cfg.family, world, rank, step, trainer.m, trainer.v, trainer.master,
                         trainer.rng.state, trainer.rng_state_last_update,
                         loader.current_shard_idx if loader is not None else 0,

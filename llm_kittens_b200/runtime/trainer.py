@@ -149,12 +149,17 @@ class Trainer:
         if self.use_cuda_graph and self._graph_usable(batches):
             return self._accumulate_graph(batches)
         for i, (x, y) in enumerate(batches):
-            if self.sharded_state:
-                self.comm.start_micro_step(i)
-            model.forward(x, y, grad_accum_steps=accum, micro_step=i)
-            model.backward(last_micro_step=(i == accum - 1), bucket_ready=self._bucket_ready)
+            self.micro_step(x, y, i, accum)
         self._eager_steps += 1
         return accum
+
+    def micro_step(self, x, y, index: int, accum: int) -> None:
+        """Forward + backward of micro-batch ``index`` of ``accum`` (after :meth:`begin_step`). Loops that drive the
+        micro-steps themselves must go through here: the sharded communication path counts micro-steps."""
+        if self.sharded_state:
+            self.comm.start_micro_step(index)
+        self.model.forward(x, y, grad_accum_steps=accum, micro_step=index)
+        self.model.backward(last_micro_step=(index == accum - 1), bucket_ready=self._bucket_ready)
 
     # ------------------------------------------------------------------ CUDA graph of one micro-step
     def enable_cuda_graph(self, on: bool = True) -> None:

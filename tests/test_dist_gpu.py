@@ -78,3 +78,44 @@ def test_sharded_zero_stages_match_library(tmp_path, stage, recompute):
         assert abs(a - b) < 0.03 * max(1.0, b)
     assert (s0["params"] - l0["params"]).abs().max().item() < 0.02
     assert s0["losses"][-1] < s0["losses"][0]
+
+
+def test_cli_zero3_checkpoint_resume_two_gpus(tmp_path):
+    """Trainer CLI on two GPUs with really sharded parameters: checkpoint (a collective gather of the shards),
+    resume from it, and a bit-identical continuation of the logged losses."""
+    _need_two_gpus()
+    import shutil
+    import subprocess
+
+    from llm_kittens_b200.data import prepare
+    from llm_kittens_b200.utils.logger import parse_log
+    from test_dist_cpu import free_port
+
+    repo = os.path.dirname(HERE)
+    prepare.prepare_synthetic(str(tmp_path / "data"), 400_000, vocab_size=50257, seed=3)
+    common = ["-i", str(tmp_path / "data" / "synthetic_train_*.bin"), "-j", str(tmp_path / "data" / "synthetic_val_*.bin"),
+              "-e", "d6", "-b", "4", "-t", "64", "-d", "1024", "-x", "6", "-l", "1e-3", "-u", "2", "-q", "0.1", "-c", "0.1",
+              "-v", "3", "-m", "2", "-s", "0", "-h", "0", "-r", "0", "-z", "3", "-n", "3"]
+
+    def run(out_dir, extra):
+        cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2", "--master-addr", "127.0.0.1",
+               "--master-port", str(free_port()), "-m", "llm_kittens_b200.cli.train_gpt2cu", *common, "-o", str(out_dir), *extra]
+        env = dict(os.environ, PYTHONPATH=repo, NCCL_NVLS_ENABLE="0", TORCH_SYMM_MEM_DISABLE_MULTICAST="1")
+        r = subprocess.run(cmd, cwd=str(tmp_path), env=env, capture_output=True, text=True, timeout=600)
+        assert r.returncode == 0, (r.stdout[-2000:], r.stderr[-3000:])
+        return r.stdout
+
+    a = tmp_path / "a"
+    out = run(a, [])
+    assert "ShardedComm" in out
+    full = parse_log(str(a / "main.log"))["train"]
+    assert len(full) == 6 and os.path.exists(a / "DONE_00000003") and os.path.exists(a / "state_00000003_00001.bin")
+    b = tmp_path / "b"
+    shutil.copytree(a, b)
+    for name in os.listdir(b):
+        if "00000006" in name:
+            os.remove(b / name)
+    run(b, ["-y", "1"])
+    resumed = parse_log(str(b / "main.log"))["train"]
+    for s in sorted(full)[3:]:
+        assert resumed[s] == full[s], (s, resumed[s], full[s])
