@@ -38,6 +38,22 @@ __device__ __forceinline__ float ex2(float x) {
     return y;
 }
 
+// Two columns of the backward softmax with packed fp32 pairs: e = exp2(s * c + nl) (zero where masked) and
+// ds = e * (dp + nd). `nl` / `nd` hold the NEGATED log-sum-exp (exp2 domain) and D, so that the pair forms of
+// FMA / ADD / MUL (which take no operand negation) give the same roundings as the scalar s*c - L and dp - D.
+__device__ __forceinline__ void prob_pair(uint32_t s0, uint32_t s1, uint32_t dp0, uint32_t dp1, ptx::f32x2 c2, ptx::f32x2 nl,
+                                          ptx::f32x2 nd, bool mask0, bool mask1, float* p, float* ds) {
+    float x0, x1;
+    ptx::unpack2(ptx::fma2(ptx::pack2(__uint_as_float(s0), __uint_as_float(s1)), c2, nl), x0, x1);
+    float e0 = ex2(x0), e1 = ex2(x1);
+    if (mask0) e0 = 0.f;
+    if (mask1) e1 = 0.f;
+    p[0] = e0;
+    p[1] = e1;
+    const ptx::f32x2 t = ptx::add2(ptx::pack2(__uint_as_float(dp0), __uint_as_float(dp1)), nd);
+    ptx::unpack2(ptx::mul2(ptx::pack2(e0, e1), t), ds[0], ds[1]);
+}
+
 // [ROWS x cols] K-major A/B operand at `base`, stored as atoms of 64 columns (ROWS * 128 bytes each):
 // descriptor of k-step kk (16 columns)
 template <int ROWS>
@@ -189,8 +205,8 @@ attn_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_c
                 const size_t off = ((size_t)b * NH + hq) * T + q0;
 #pragma unroll
                 for (int i = 0; i < BN / 32; i++) {
-                    sL[lane + 32 * i] = lse[off + lane + 32 * i] * LOG2E;
-                    sL[128 + lane + 32 * i] = dvec[off + lane + 32 * i];
+                    sL[lane + 32 * i] = -lse[off + lane + 32 * i] * LOG2E;   // negated: the consumers add
+                    sL[128 + lane + 32 * i] = -dvec[off + lane + 32 * i];
                 }
             }
             __syncwarp();
@@ -257,6 +273,7 @@ attn_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_c
         const int sub = (warp - 2) >> 2;                     // 0 / 1: which half of the columns this warp handles
         const int r = lane_group * 32 + lane;               // key row inside the tile
         const uint32_t lane_off = (uint32_t)(lane_group * 32) << 16;
+        const ptx::f32x2 c2 = ptx::pack2(scale_log2, scale_log2);
         bool ok = true;
         for (int it = 0; it < total && ok; it++) {
             const int dq0 = (it % nq) * BN;                  // first query of the sub-tile relative to the first key
@@ -284,12 +301,10 @@ attn_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_c
                     *reinterpret_cast<float4*>(D) = *reinterpret_cast<const float4*>(sD + c4 * 32 + q * 8);
                     *reinterpret_cast<float4*>(D + 4) = *reinterpret_cast<const float4*>(sD + c4 * 32 + q * 8 + 4);
 #pragma unroll
-                    for (int i = 0; i < 8; i++) {
+                    for (int i = 0; i < 8; i += 2) {
                         const int c = c4 * 32 + q * 8 + i;   // query column of the sub-tile
-                        float e = ex2(fmaf(__uint_as_float(vs[q * 8 + i]), scale_log2, -L[i]));
-                        if (diag && r > c + dq0) e = 0.f;     // key after query
-                        p[i] = e;
-                        ds[i] = e * (__uint_as_float(vd[q * 8 + i]) - D[i]);
+                        prob_pair(vs[q * 8 + i], vs[q * 8 + i + 1], vd[q * 8 + i], vd[q * 8 + i + 1], c2, ptx::pack2(L[i], L[i + 1]),
+                                  ptx::pack2(D[i], D[i + 1]), diag && r > c + dq0, diag && r > c + 1 + dq0, p + i, ds + i);
                     }
                     store_chunk(sPt, r, c4 * 4 + q, p);
                     store_chunk(sdSt, r, c4 * 4 + q, ds);
@@ -472,8 +487,8 @@ attn_bwd_dkv2_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_con
             const size_t off = ((size_t)b * NH + hq) * T + q0;
 #pragma unroll
             for (int i = 0; i < BN / 32; i++) {
-                sL[lane + 32 * i] = lse[off + lane + 32 * i] * LOG2E;
-                sL[64 + lane + 32 * i] = dvec[off + lane + 32 * i];
+                sL[lane + 32 * i] = -lse[off + lane + 32 * i] * LOG2E;   // negated: the consumers add
+                sL[64 + lane + 32 * i] = -dvec[off + lane + 32 * i];
             }
             __syncwarp();
             if (lane == 0) ptx::mbar_arrive(&ld_full[s]);
@@ -534,6 +549,7 @@ attn_bwd_dkv2_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_con
         uint8_t* myPt = sPt + g * PT;
         uint8_t* mydSt = sdSt + g * PT;
         const uint32_t t_st = tmem_base + g * 64 + sub * 32, t_dpt = tmem_base + 128 + g * 64 + sub * 32;
+        const ptx::f32x2 c2 = ptx::pack2(scale_log2, scale_log2);
         bool ok = true;
         int last = -1;
         for (int it = g; it < total && ok; it += 2) {
@@ -564,12 +580,10 @@ attn_bwd_dkv2_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_con
                 *reinterpret_cast<float4*>(D) = *reinterpret_cast<const float4*>(sD + q * 8);
                 *reinterpret_cast<float4*>(D + 4) = *reinterpret_cast<const float4*>(sD + q * 8 + 4);
 #pragma unroll
-                for (int i = 0; i < 8; i++) {
+                for (int i = 0; i < 8; i += 2) {
                     const int c = sub * 32 + q * 8 + i;   // query column of the sub-tile
-                    float e = ex2(fmaf(__uint_as_float(vs[q * 8 + i]), scale_log2, -L[i]));
-                    if (diag && r > c + dq0) e = 0.f;     // key after query
-                    p[i] = e;
-                    ds[i] = e * (__uint_as_float(vd[q * 8 + i]) - D[i]);
+                    prob_pair(vs[q * 8 + i], vs[q * 8 + i + 1], vd[q * 8 + i], vd[q * 8 + i + 1], c2, ptx::pack2(L[i], L[i + 1]),
+                              ptx::pack2(D[i], D[i + 1]), diag && r > c + dq0, diag && r > c + 1 + dq0, p + i, ds + i);
                 }
                 store_chunk(myPt, r, sub * 4 + q, p);
                 store_chunk(mydSt, r, sub * 4 + q, ds);
@@ -766,6 +780,7 @@ attn_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_co
         const uint32_t lane_off = (uint32_t)(lane_group * 32) << 16;
         const size_t roff = ((size_t)b * NH + h) * T + q0 + r;
         const float Lr = lse[roff] * LOG2E, Dr = dvec[roff];
+        const ptx::f32x2 nl2 = ptx::pack2(-Lr, -Lr), nd2 = ptx::pack2(-Dr, -Dr), c2 = ptx::pack2(scale_log2, scale_log2);
         bool ok = true;
         for (int j = 0; j < nkv && ok; j++) {
             ok = ptx::mbar_wait(s_full, j & 1, abort_flag, status, LLMK_ST_TIMEOUT_ACC_FULL, j);
@@ -781,13 +796,12 @@ attn_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_co
             auto process = [&](int c4, const uint32_t (&vs)[32], const uint32_t (&vd)[32]) {
 #pragma unroll
                 for (int q = 0; q < 4; q++) {
-                    float ds[8];
+                    float ds[8], p[8];
 #pragma unroll
-                    for (int i = 0; i < 8; i++) {
+                    for (int i = 0; i < 8; i += 2) {
                         const int c = c4 * 32 + q * 8 + i;   // key column of the sub-tile
-                        float e = ex2(fmaf(__uint_as_float(vs[q * 8 + i]), scale_log2, -Lr));
-                        if (diag && c + dk0 > r) e = 0.f;     // key after query
-                        ds[i] = e * (__uint_as_float(vd[q * 8 + i]) - Dr);
+                        prob_pair(vs[q * 8 + i], vs[q * 8 + i + 1], vd[q * 8 + i], vd[q * 8 + i + 1], c2, nl2, nd2,
+                                  diag && c + dk0 > r, diag && c + 1 + dk0 > r, p + i, ds + i);
                     }
                     store_chunk(sdS, r, c4 * 4 + q, ds);
                 }

@@ -91,22 +91,29 @@ __device__ __forceinline__ float chunk_max(const uint32_t (&s)[32], int lane, fl
 template <int MODE>
 __device__ __forceinline__ float chunk_probs(const uint32_t (&s)[32], uint8_t* atom, int chunk_base, int r, int lane,
                                              float scale_log2, float neg_m) {
-    float s0 = 0.f, s1 = 0.f;
+    // packed fp32 pairs: one FMA-pipe instruction per two columns for the exponent argument and the row sum
+    const ptx::f32x2 c2 = ptx::pack2(scale_log2, scale_log2), m2 = ptx::pack2(neg_m, neg_m);
+    ptx::f32x2 sum2 = ptx::pack2(0.f, 0.f);
 #pragma unroll
     for (int q = 0; q < 4; q++) {
         float p[8];
 #pragma unroll
-        for (int i = 0; i < 8; i++) {
-            float e = 0.f;
+        for (int i = 0; i < 8; i += 2) {
+            float e0 = 0.f, e1 = 0.f;
             if (MODE != 2) {
-                e = ex2(fmaf(__uint_as_float(s[q * 8 + i]), scale_log2, neg_m));
-                if (MODE == 1 && q * 8 + i > lane) e = 0.f;
+                float x0, x1;
+                ptx::unpack2(ptx::fma2(ptx::pack2(__uint_as_float(s[q * 8 + i]), __uint_as_float(s[q * 8 + i + 1])), c2, m2), x0, x1);
+                e0 = ex2(x0);
+                e1 = ex2(x1);
+                if (MODE == 1 && q * 8 + i > lane) e0 = 0.f;
+                if (MODE == 1 && q * 8 + i + 1 > lane) e1 = 0.f;
             }
-            p[i] = e;
+            p[i] = e0;
+            p[i + 1] = e1;
         }
         if (MODE != 2) {
-            s0 += (p[0] + p[1]) + (p[2] + p[3]);
-            s1 += (p[4] + p[5]) + (p[6] + p[7]);
+#pragma unroll
+            for (int i = 0; i < 8; i += 2) sum2 = ptx::add2(sum2, ptx::pack2(p[i], p[i + 1]));
         }
         uint4 w;
         w.x = pack_trunc2(p[0], p[1]);
@@ -115,6 +122,8 @@ __device__ __forceinline__ float chunk_probs(const uint32_t (&s)[32], uint8_t* a
         w.w = pack_trunc2(p[6], p[7]);
         *reinterpret_cast<uint4*>(atom + (((chunk_base + q) ^ (r & 7)) << 4)) = w;
     }
+    float s0, s1;
+    ptx::unpack2(sum2, s0, s1);
     return s0 + s1;
 }
 
