@@ -413,3 +413,34 @@ def test_rng_matches_torch_and_state_round_trip():
     assert [y.u32() for _ in range(3)] == u and 0.0 <= Xorshift(5).f32() < 1.0
     logits = np.array([0.0, 10.0, 0.0], dtype=np.float32)
     assert sample_softmax(logits, 0.5) == 1 and sample_softmax(logits, 0.0) == 0 and sample_softmax(logits, 0.99999) == 2
+
+
+def test_check_cli_zero_layout_log_and_checkpoint(tmp_path, capsys):
+    """The run-validation commands (reference: dev/validate_zero_layout.py, dev/validate_training_log.py,
+    dev/compare_training_logs.py, dev/validate_llama_checkpoint_artifacts.py)."""
+    from llm_kittens_b200.cli import check
+
+    assert check.main(["zero-layout", "--models", "d12", "llama3.2:1B", "gpt3:c768", "--world", "1", "2", "4", "8"]) == 0
+    log = Logger(str(tmp_path), 0)
+    for s, l in enumerate([5.0, 4.0, 3.5]):
+        log.log_train(s, l, 1e-3, 1.0)
+    main_log = str(tmp_path / "main.log")
+    assert check.main(["log", main_log, "--final-step", "2", "--max-train-loss", "4.0"]) == 0
+    assert check.main(["log", main_log, "--final-step", "7"]) == 1
+    assert check.main(["compare", main_log, main_log]) == 0
+    # checkpoint directory: a model file of the right size, one state file, DONE marker
+    cfg = ModelConfig(family="gpt2", max_seq_len=64, vocab_size=100, padded_vocab_size=128, num_layers=1, num_heads=2,
+                      num_kv_heads=2, channels=64, hidden_dim=256)
+    n = cfg.num_parameters()
+    params = torch.zeros(n, dtype=torch.bfloat16)
+    model_path, state_path, done_path = formats.checkpoint_paths(str(tmp_path), 4, 0)
+    formats.write_model(model_path, cfg, params)
+    z = torch.zeros(n, dtype=torch.float32)
+    formats.write_state(state_path, cfg.family, 1, 0, 4, z, z, None, 1, 2, 0, 0, b"")
+    assert check.main(["checkpoint", str(tmp_path)]) == 1          # no DONE marker yet
+    open(done_path, "w").close()
+    assert check.main(["checkpoint", str(tmp_path)]) == 0
+    with open(model_path, "ab") as f:
+        f.write(b"\0\0")
+    assert check.main(["checkpoint", str(tmp_path), "--step", "4"]) == 1
+    capsys.readouterr()
