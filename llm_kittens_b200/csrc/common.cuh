@@ -122,17 +122,30 @@ __device__ __forceinline__ float fast_tanh(float x) {
     return y;
 }
 #define LLMK_GELU_K 0.7978845608028654f  // sqrt(2/pi)
+#define LLMK_GELU_KC (0.7978845608028654f * 0.044715f)
 // tanh.approx.f32 (one MUFU op, ~2^-11 relative error) is used by the fused GEMM epilogues and by the
-// stand-alone kernels alike, so a recomputed activation equals the one the forward pass produced.
+// stand-alone kernels alike, so a recomputed activation equals the one the forward pass produced. The GEMM
+// epilogues evaluate the same formulas two values at a time with packed fp32 instructions; every step below is
+// an explicitly rounded multiply / FMA in the same order as there, so both give the same bits.
+//   u = x * (K + K*c*x^2);  gelu = 0.5x + 0.5x * tanh(u)
 __device__ __forceinline__ float gelu_fwd(float x) {
-    float cube = 0.044715f * x * x * x;
-    return 0.5f * x * (1.0f + fast_tanh(LLMK_GELU_K * (x + cube)));
+    const float x2 = __fmul_rn(x, x);
+    const float inner = __fmaf_rn(x2, LLMK_GELU_KC, LLMK_GELU_K);
+    const float t = fast_tanh(__fmul_rn(x, inner));
+    const float hx = __fmul_rn(x, 0.5f);
+    return __fmaf_rn(hx, t, hx);
 }
+//   gelu' = 0.5(1+t) + 0.5x (1-t^2) u'  with u' = K + 3K*c*x^2, factored as (1+t) * (0.5 + 0.5x u' (1-t))
 __device__ __forceinline__ float gelu_grad(float x) {
-    float cube = 0.044715f * x * x * x;
-    float t = fast_tanh(LLMK_GELU_K * (x + cube));
-    float sech2 = 1.0f - t * t;
-    return 0.5f * (1.0f + t) + x * 0.5f * sech2 * LLMK_GELU_K * (1.0f + 3.0f * 0.044715f * x * x);
+    const float x2 = __fmul_rn(x, x);
+    const float inner = __fmaf_rn(x2, LLMK_GELU_KC, LLMK_GELU_K);
+    const float t = fast_tanh(__fmul_rn(x, inner));
+    const float du = __fmaf_rn(x2, 3.0f * LLMK_GELU_KC, LLMK_GELU_K);
+    const float a = __fadd_rn(t, 1.0f);
+    const float b = __fmaf_rn(t, -1.0f, 1.0f);
+    const float w = __fmul_rn(__fmul_rn(x, 0.5f), du);
+    const float z = __fmaf_rn(w, b, 0.5f);
+    return __fmul_rn(a, z);
 }
 
 // ---- counter-based random bits for stochastic rounding ------------------------------------------

@@ -56,6 +56,33 @@ struct Cfg {
     static constexpr int SMEM_BYTES = SMEM_MAIN + 1024 /*alignment slack*/ + 256 /*barriers*/;
 };
 
+// Packed-pair forms of gelu_fwd / gelu_grad (common.cuh): the same explicitly rounded operations in the same order,
+// two values per instruction, so the fused epilogues and the stand-alone kernels give identical bits.
+__device__ __forceinline__ ptx::f32x2 tanh2(ptx::f32x2 u) {
+    float u0, u1;
+    ptx::unpack2(u, u0, u1);
+    return ptx::pack2(fast_tanh(u0), fast_tanh(u1));
+}
+__device__ __forceinline__ ptx::f32x2 gelu_fwd2(ptx::f32x2 x) {
+    const ptx::f32x2 kc = ptx::pack2(LLMK_GELU_KC, LLMK_GELU_KC), k = ptx::pack2(LLMK_GELU_K, LLMK_GELU_K);
+    const ptx::f32x2 inner = ptx::fma2(ptx::mul2(x, x), kc, k);
+    const ptx::f32x2 t = tanh2(ptx::mul2(x, inner));
+    const ptx::f32x2 hx = ptx::mul2(x, ptx::pack2(0.5f, 0.5f));
+    return ptx::fma2(hx, t, hx);
+}
+__device__ __forceinline__ ptx::f32x2 gelu_grad2(ptx::f32x2 x) {
+    const ptx::f32x2 kc = ptx::pack2(LLMK_GELU_KC, LLMK_GELU_KC), k = ptx::pack2(LLMK_GELU_K, LLMK_GELU_K);
+    const ptx::f32x2 kc3 = ptx::pack2(3.0f * LLMK_GELU_KC, 3.0f * LLMK_GELU_KC);
+    const ptx::f32x2 one = ptx::pack2(1.0f, 1.0f), half = ptx::pack2(0.5f, 0.5f), minus = ptx::pack2(-1.0f, -1.0f);
+    const ptx::f32x2 x2 = ptx::mul2(x, x);
+    const ptx::f32x2 t = tanh2(ptx::mul2(x, ptx::fma2(x2, kc, k)));
+    const ptx::f32x2 du = ptx::fma2(x2, kc3, k);
+    const ptx::f32x2 a = ptx::add2(t, one);
+    const ptx::f32x2 b = ptx::fma2(t, minus, one);
+    const ptx::f32x2 w = ptx::mul2(ptx::mul2(x, half), du);
+    return ptx::mul2(a, ptx::fma2(w, b, half));
+}
+
 struct Params {
     int M, N, K;
     int tiles_m, tiles_n, splits, kb_total, kb_per_split;   // tiles_m counts 256-row tiles when `pair`
@@ -305,37 +332,55 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
                 }
                 bf16x8 res[8];
                 bf16x8 res2[(EPI & EPI_GELU) ? 8 : 1];
+                // both TMEM loads of the chunk and its bias are in flight before anything waits: a warp has only one other
+                // epilogue warp on its scheduler to hide latency behind, so the loads overlap each other instead
+                uint32_t vv[2][32];
+                ptx::tmem_ld_32x32b_x32(t_row + chunk * 64, vv[0]);
+                ptx::tmem_ld_32x32b_x32(t_row + chunk * 64 + 32, vv[1]);
+                bf16x8 bias_v[(EPI & EPI_BIAS) ? 8 : 1];
+                if (EPI & EPI_BIAS) {
+#pragma unroll
+                    for (int cc = 0; cc < 8; cc++)
+                        if (n_base + cc * 8 < p.N) bias_v[(EPI & EPI_BIAS) ? cc : 0] = *reinterpret_cast<const bf16x8*>(p.bias + n_base + cc * 8);
+                }
                 if (AUX_IN) {
                     ok = ptx::mbar_wait(&aux_bar[e], aux_ph, abort_flag, p.status, LLMK_ST_TIMEOUT_ACC_FULL, -2);
                     aux_ph ^= 1;
-                    if (!ok) break;
                 }
+                ptx::tmem_ld_wait();
+                if (!ok) break;
 #pragma unroll
                 for (int half = 0; half < 2; half++) {
-                    uint32_t v[32];
-                    ptx::tmem_ld_32x32b_x32(t_row + chunk * 64 + half * 32, v);
-                    ptx::tmem_ld_wait();
+                    const uint32_t (&v)[32] = vv[half];
                     const int col0 = n_base + half * 32;
 #pragma unroll
                     for (int q = 0; q < 4; q++) {
+                        // two values per FMA-pipe instruction: with K = 768 the epilogue of the GELU / dGELU GEMMs has as
+                        // many cycles of per-element math as the main loop has of MMA, so its instruction count matters
+                        ptx::f32x2 xp[4];
                         float x[8];
 #pragma unroll
-                        for (int j = 0; j < 8; j++) x[j] = __uint_as_float(v[q * 8 + j]);
+                        for (int j = 0; j < 4; j++) xp[j] = ptx::pack2(__uint_as_float(v[q * 8 + 2 * j]), __uint_as_float(v[q * 8 + 2 * j + 1]));
                         const int col = col0 + q * 8;
                         const int cc = half * 4 + q;
                         const uint32_t off = lane * 128 + ((cc ^ (lane & 7)) << 4);
                         if ((EPI & EPI_BIAS) && col < p.N) {
                             float b[8];
-                            unpack8(*reinterpret_cast<const bf16x8*>(p.bias + col), b);
+                            unpack8(bias_v[(EPI & EPI_BIAS) ? cc : 0], b);
 #pragma unroll
-                            for (int j = 0; j < 8; j++) x[j] += b[j];
+                            for (int j = 0; j < 4; j++) xp[j] = ptx::add2(xp[j], ptx::pack2(b[2 * j], b[2 * j + 1]));
                         }
                         if (AUX_IN) {
                             float g[8];
                             unpack8(*reinterpret_cast<const bf16x8*>(buf2 + off), g);
 #pragma unroll
-                            for (int j = 0; j < 8; j++) x[j] = (EPI & EPI_DGELU) ? x[j] * gelu_grad(g[j]) : x[j] + g[j];
+                            for (int j = 0; j < 4; j++) {
+                                const ptx::f32x2 gp = ptx::pack2(g[2 * j], g[2 * j + 1]);
+                                xp[j] = (EPI & EPI_DGELU) ? ptx::mul2(xp[j], gelu_grad2(gp)) : ptx::add2(xp[j], gp);
+                            }
                         }
+#pragma unroll
+                        for (int j = 0; j < 4; j++) ptx::unpack2(xp[j], x[2 * j], x[2 * j + 1]);
                         if (EPI & EPI_GELU) {
                             // the activation is computed from the ROUNDED pre-activation, so that recomputing
                             // it later from the stored bf16 tensor gives the same bits
@@ -343,7 +388,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
                             res2[(EPI & EPI_GELU) ? cc : 0] = pre;
                             unpack8(pre, x);
 #pragma unroll
-                            for (int j = 0; j < 8; j++) x[j] = gelu_fwd(x[j]);
+                            for (int j = 0; j < 4; j++) ptx::unpack2(gelu_fwd2(ptx::pack2(x[2 * j], x[2 * j + 1])), x[2 * j], x[2 * j + 1]);
                         }
                         res[cc] = pack8(x);
                     }
