@@ -87,6 +87,9 @@ struct Params {
     int M, N, K;
     int tiles_m, tiles_n, splits, kb_total, kb_per_split;   // tiles_m counts 256-row tiles when `pair`
     int pair;
+    // Grouped (batched) problems: `group_m` rows of C per group (0 = one problem). Group g of a tile is m0 / group_m.
+    // NT: B is [G*N, K] and bias [G*N]; NN: B is [G*K, N]; TN: A is [G*K, M_g], B is [G*K, N], C is [G*M_g, N].
+    int group_m;
     const bf16* bias;  // [N]
     const bf16* aux;   // [M,N] pre-GELU input (DGELU) or addend (ADD; may alias C)
     float* partial;    // [splits, M, N] fp32 (PARTIAL)
@@ -94,7 +97,7 @@ struct Params {
 };
 
 struct Work {
-    int m0, n0, kb_begin, kb_end, split;
+    int m0, n0, kb_begin, kb_end, split, g;
 };
 
 __device__ __forceinline__ Work decode_unit(const Params& p, int u) {
@@ -110,6 +113,7 @@ __device__ __forceinline__ Work decode_unit(const Params& p, int u) {
     w.n0 = (r / gm) * BN;
     w.kb_begin = w.split * p.kb_per_split;
     w.kb_end = min(p.kb_total, w.kb_begin + p.kb_per_split);
+    w.g = p.group_m > 0 ? w.m0 / p.group_m : 0;
     return w;
 }
 
@@ -203,17 +207,18 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
                     // pair: only the leader arms its barrier, for the bytes of both CTAs
                     if (rank == 0) ptx::mbar_arrive_expect_tx(&full_bar[s], (PAIR ? 2 : 1) * STAGE_BYTES);
                     const int k0 = kb * BK;
-                    if (A_MN) {
+                    if (A_MN) {   // TN: group g reads token rows [g*K, (g+1)*K) and its own M_g columns of A
 #pragma unroll
-                        for (int j = 0; j < BM / 64; j++) load(sA + j * CHUNK_BYTES, &tmA, &full_bar[s], m_own + 64 * j, k0);
+                        for (int j = 0; j < BM / 64; j++)
+                            load(sA + j * CHUNK_BYTES, &tmA, &full_bar[s], m_own - w.g * p.group_m + 64 * j, k0 + w.g * p.K);
                     } else {
                         load(sA, &tmA, &full_bar[s], k0, m_own);
                     }
-                    if (B_MN) {
+                    if (B_MN) {   // NN / TN: the rows of B are the K dimension, stacked per group
 #pragma unroll
-                        for (int j = 0; j < BN_CTA / 64; j++) load(sB + j * CHUNK_BYTES, &tmB, &full_bar[s], n_own + 64 * j, k0);
-                    } else {
-                        load(sB, &tmB, &full_bar[s], k0, n_own);
+                        for (int j = 0; j < BN_CTA / 64; j++) load(sB + j * CHUNK_BYTES, &tmB, &full_bar[s], n_own + 64 * j, k0 + w.g * p.K);
+                    } else {      // NT: the rows of B are the N dimension, stacked per group
+                        load(sB, &tmB, &full_bar[s], k0, n_own + w.g * p.N);
                     }
                 }
                 __syncwarp();
@@ -341,7 +346,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
                 if (EPI & EPI_BIAS) {
 #pragma unroll
                     for (int cc = 0; cc < 8; cc++)
-                        if (n_base + cc * 8 < p.N) bias_v[(EPI & EPI_BIAS) ? cc : 0] = *reinterpret_cast<const bf16x8*>(p.bias + n_base + cc * 8);
+                        if (n_base + cc * 8 < p.N) bias_v[(EPI & EPI_BIAS) ? cc : 0] = *reinterpret_cast<const bf16x8*>(p.bias + (size_t)w.g * p.N + n_base + cc * 8);
                 }
                 if (AUX_IN) {
                     ok = ptx::mbar_wait(&aux_bar[e], aux_ph, abort_flag, p.status, LLMK_ST_TIMEOUT_ACC_FULL, -2);
@@ -617,11 +622,13 @@ long llmk_gemm_workspace_bytes(int mode, int M, int N, int K, int num_sms) {
 // to C2, 4 multiply by GELU'(aux), 8 add aux). For mode TN, `epi` 8 means C += result and the
 // launcher may split K through `workspace`. All matrices are dense row-major bf16; K, N (and M for
 // TN) must be multiples of 8 so that every row starts on a 16-byte boundary.
-LLMK_API int llmk_gemm(int mode, int epi, const void* A, const void* B, void* C, void* C2, const void* bias,
-                       const void* aux, int M, int N, int K, void* workspace, long workspace_bytes, int* status,
-                       int max_ctas, void* stream_) {
+static int gemm_impl(int mode, int epi, const void* A, const void* B, void* C, void* C2, const void* bias, const void* aux,
+                     int M_group, int N, int K, int groups, void* workspace, long workspace_bytes, int* status, int max_ctas,
+                     void* stream_) {
     cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
-    if (M <= 0 || N <= 0 || K <= 0) return LLMK_ERR_SHAPE;
+    if (M_group <= 0 || N <= 0 || K <= 0 || groups <= 0) return LLMK_ERR_SHAPE;
+    if ((long)M_group * groups > 0x7fffffffL) return LLMK_ERR_SHAPE;
+    const int M = M_group * groups;   // rows of C over all groups
     if (epi & EPI_PARTIAL) return LLMK_ERR_SHAPE;   // internal: chosen here when the K dimension is split
     if ((N % 8) || (K % 8 && mode != MODE_TN) || (mode == MODE_TN && (M % 8))) return LLMK_ERR_SHAPE;
     if ((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(B) | reinterpret_cast<uintptr_t>(C)) & 15)
@@ -635,6 +642,13 @@ LLMK_API int llmk_gemm(int mode, int epi, const void* A, const void* B, void* C,
     p.M = M; p.N = N; p.K = K;
     const int pair_clusters = query_pair_clusters();
     p.pair = pair_clusters > 0 ? 1 : 0;
+    p.group_m = 0;
+    if (groups > 1) {
+        // a tile must not straddle two groups, and a k-block must not run into the next group's rows
+        if (M_group % (p.pair ? 2 * BM : BM)) return LLMK_ERR_SHAPE;
+        if (mode != MODE_NT && (K % BK)) return LLMK_ERR_SHAPE;
+        p.group_m = M_group;
+    }
     p.tiles_m = ceil_div(M, p.pair ? 2 * BM : BM);
     p.tiles_n = ceil_div(N, BN);
     p.kb_total = ceil_div(K, BK);
@@ -663,11 +677,13 @@ LLMK_API int llmk_gemm(int mode, int epi, const void* A, const void* B, void* C,
 
     CUtensorMap tmA, tmB, tmC, tmX;
     int rc;
-    if (mode == MODE_TN) rc = make_tmap_2d(&tmA, A, M, K, M, 64, BK);   // A[K,M], box 64(m) x 64(k)
+    // grouped problems stack their operands along the outer (row) dimension of each matrix
+    const uint64_t G = (uint64_t)groups;
+    if (mode == MODE_TN) rc = make_tmap_2d(&tmA, A, M_group, G * K, M_group, 64, BK);   // A[G*K,M_g], box 64(m) x 64(k)
     else rc = make_tmap_2d(&tmA, A, K, M, K, BK, BM);                    // A[M,K], box 64(k) x 128(m)
     if (rc) return rc;
-    if (mode == MODE_NT) rc = make_tmap_2d(&tmB, B, K, N, K, BK, p.pair ? BN / 2 : BN);   // B[N,K], box 64(k) x 256(n); pair: 128(n) per CTA
-    else rc = make_tmap_2d(&tmB, B, N, K, N, 64, BK);                    // B[K,N], box 64(n) x 64(k)
+    if (mode == MODE_NT) rc = make_tmap_2d(&tmB, B, K, G * N, K, BK, p.pair ? BN / 2 : BN);   // B[G*N,K], box 64(k) x 256(n); pair: 128(n) per CTA
+    else rc = make_tmap_2d(&tmB, B, N, G * K, N, 64, BK);                // B[G*K,N], box 64(n) x 64(k)
     if (rc) return rc;
     rc = make_tmap_2d(&tmC, C, N, M, N, 64, 32);
     if (rc) return rc;
@@ -703,4 +719,22 @@ LLMK_API int llmk_gemm(int mode, int epi, const void* A, const void* B, void* C,
         LLMK_LAUNCH_CHECK();
     }
     return LLMK_OK;
+}
+
+LLMK_API int llmk_gemm(int mode, int epi, const void* A, const void* B, void* C, void* C2, const void* bias,
+                       const void* aux, int M, int N, int K, void* workspace, long workspace_bytes, int* status,
+                       int max_ctas, void* stream_) {
+    return gemm_impl(mode, epi, A, B, C, C2, bias, aux, M, N, K, 1, workspace, workspace_bytes, status, max_ctas, stream_);
+}
+
+// `groups` independent problems of the same shape in ONE persistent launch (the experts of a mixture-of-experts
+// layer; same job as grouped_gemm of the reference, llmc/gemm_ext.cuh:132-158, for equal row counts). M, N, K are the
+// dimensions of one group; operands are stacked along their rows: NT: A [G*M,K], B [G*N,K], bias [G*N], C [G*M,N];
+// NN: A [G*M,K], B [G*K,N]; TN: A [G*K,M], B [G*K,N], C [G*M,N] (K = tokens of one group). M must be a multiple of the
+// tile height (256 with CTA pairs, else 128) and, for NN / TN, K a multiple of 64; otherwise LLMK_ERR_SHAPE is
+// returned and the caller launches the groups one by one. Workspace for TN: llmk_gemm_workspace_bytes(mode, G*M, N, K).
+LLMK_API int llmk_gemm_grouped(int mode, int epi, const void* A, const void* B, void* C, void* C2, const void* bias,
+                               const void* aux, int M, int N, int K, int groups, void* workspace, long workspace_bytes,
+                               int* status, int max_ctas, void* stream_) {
+    return gemm_impl(mode, epi, A, B, C, C2, bias, aux, M, N, K, groups, workspace, workspace_bytes, status, max_ctas, stream_);
 }

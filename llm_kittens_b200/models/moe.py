@@ -118,11 +118,12 @@ class MoETransformer(Transformer):
         self.exchange.sync(4 * l + 0)
         per = P * cap
         act_l = a["hid_act"][0 if self.recompute >= 1 else l]
-        for el in range(self.Eloc):
-            w1, b1, w2, b2 = self._expert_views(l, el)[:4]
-            rows = slice(el * per, (el + 1) * per)
-            gemm.gemm_nt(self.recv_x[l][rows], w1, bias=b1, out=act_l[rows], gelu_pre_out=a["hid_pre"][l][rows])
-            gemm.gemm_nt(act_l[rows], w2, bias=b2, out=a["y_loc"][rows])
+        # the local experts have equal row counts (P * capacity): one grouped launch per projection
+        G, loc = self.Eloc, slice(self.ep_rank * self.Eloc, (self.ep_rank + 1) * self.Eloc)
+        rows = slice(0, G * per)
+        gemm.gemm_nt(self.recv_x[l][rows], p["fcw"][l][loc], bias=p["fcb"][l][loc], out=act_l[rows],
+                     gelu_pre_out=a["hid_pre"][l][rows], groups=G)
+        gemm.gemm_nt(act_l[rows], p["fcprojw"][l][loc], bias=p["fcprojb"][l][loc], out=a["y_loc"][rows], groups=G)
         moe_ops.return_rows(self.back_y_ptrs[l], a["y_loc"], cfg.channels, E, cap, self.ep_rank, P)
         self.exchange.sync(4 * l + 1)
         moe_ops.combine(out, res2, self.back_y[l], a["top_idx"][l], a["slot"][l], a["top_w"][l], cap)
@@ -137,18 +138,20 @@ class MoETransformer(Transformer):
         self.exchange.sync(4 * l + 2)
         per = P * cap
         act_l = a["hid_act"][0 if self.recompute >= 1 else l]
-        for el in range(self.Eloc):
-            w1, b1, w2, b2, gw1, gb1, gw2, gb2 = self._expert_views(l, el)
-            rows = slice(el * per, (el + 1) * per)
-            dy, x = self.recv_dy[rows], self.recv_x[l][rows]
-            if self.recompute >= 1:
-                ew.gelu_fwd(a["hid_pre"][l][rows], out=act_l[rows])
-            gemm.gemm_tn(dy, act_l[rows], out=gw2, accumulate=True)
-            ew.dbias(gb2, dy, accumulate=True)
-            gemm.gemm_nn(dy, w2, out=a["d_hid"][rows], dgelu_of=a["hid_pre"][l][rows])
-            gemm.gemm_tn(a["d_hid"][rows], x, out=gw1, accumulate=True)
-            ew.dbias(gb1, a["d_hid"][rows], accumulate=True)
-            gemm.gemm_nn(a["d_hid"][rows], w1, out=a["y_loc"][rows])
+        G, loc = self.Eloc, slice(self.ep_rank * self.Eloc, (self.ep_rank + 1) * self.Eloc)
+        rows = slice(0, G * per)
+        dy, x, d_hid = self.recv_dy[rows], self.recv_x[l][rows], a["d_hid"][rows]
+        if self.recompute >= 1:
+            ew.gelu_fwd(a["hid_pre"][l][rows], out=act_l[rows])
+        gemm.gemm_tn(dy, act_l[rows], out=g["fcprojw"][l][loc], accumulate=True, groups=G)
+        gemm.gemm_nn(dy, p["fcprojw"][l][loc], out=d_hid, dgelu_of=a["hid_pre"][l][rows], groups=G)
+        gemm.gemm_tn(d_hid, x, out=g["fcw"][l][loc], accumulate=True, groups=G)
+        gemm.gemm_nn(d_hid, p["fcw"][l][loc], out=a["y_loc"][rows], groups=G)
+        for el in range(G):
+            gb1, gb2 = self._expert_views(l, el)[5], self._expert_views(l, el)[7]
+            r = slice(el * per, (el + 1) * per)
+            ew.dbias(gb2, dy[r], accumulate=True)
+            ew.dbias(gb1, d_hid[r], accumulate=True)
         moe_ops.return_rows(self.back_dx_ptrs, a["y_loc"], C, E, cap, self.ep_rank, P)
         self.exchange.sync(4 * l + 3)
         moe_ops.combine(d_ln2, None, self.back_dx, idx, slot, None, cap)

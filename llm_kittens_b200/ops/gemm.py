@@ -35,28 +35,66 @@ def workspace(nbytes: int) -> torch.Tensor:
     return ws
 
 
-def _gemm(mode, epi, a, b, c, c2, bias, aux, M, Nn, K):
+_TILE_ROWS = 0
+
+
+def tile_rows() -> int:
+    """Rows of C that one work unit of the kernel covers: 256 with CTA pairs, else 128."""
+    global _TILE_ROWS
+    if _TILE_ROWS == 0:
+        _TILE_ROWS = 256 if int(N.lib().llmk_gemm_pair_clusters()) > 0 else 128
+    return _TILE_ROWS
+
+
+def _gemm(mode, epi, a, b, c, c2, bias, aux, M, Nn, K, groups=1):
+    """``M``, ``Nn``, ``K`` are the dimensions of ONE group; operands of a grouped call are stacked along their rows."""
     for t, nm in ((a, "A"), (b, "B"), (c, "C")):
         N.require_cuda_tensor(t, torch.bfloat16, nm)
+    if groups > 1 and (M % tile_rows() or (mode != MODE_NT and K % 64)):
+        # a tile would straddle two groups: one launch per group on row slices of the stacked operands
+        a_rows, b_rows = (K, K) if mode == MODE_TN else (M, Nn if mode == MODE_NT else K)
+        for g in range(groups):
+            cut = lambda t, r: None if t is None else t[g * r:(g + 1) * r]
+            _gemm(mode, epi, cut(a, a_rows), cut(b, b_rows), cut(c, M), cut(c2, M), cut(bias, Nn) if bias is not None and bias.dim() == 1 else bias,
+                  cut(aux, M), M, Nn, K)
+        return c
     ws = None
     ws_bytes = 0
     if mode == MODE_TN:
-        ws_bytes = int(N.lib().llmk_gemm_workspace_bytes(mode, M, Nn, K, 0))
+        ws_bytes = int(N.lib().llmk_gemm_workspace_bytes(mode, M * groups, Nn, K, 0))
         if ws_bytes:
             ws = workspace(ws_bytes)
             ws_bytes = ws.numel()
-    N.call("llmk_gemm", mode, epi, a, b, c, c2, bias, aux, M, Nn, K, ws, ws_bytes, N.status_word(), _MAX_CTAS)
+    if groups > 1:
+        N.call("llmk_gemm_grouped", mode, epi, a, b, c, c2, bias, aux, M, Nn, K, groups, ws, ws_bytes, N.status_word(), _MAX_CTAS)
+    else:
+        N.call("llmk_gemm", mode, epi, a, b, c, c2, bias, aux, M, Nn, K, ws, ws_bytes, N.status_word(), _MAX_CTAS)
     return c
 
 
-def gemm_nt(a, b, bias=None, out=None, gelu_pre_out=None, add=None):
+def _flat2(t, groups):
+    """[G, R, C] (contiguous) -> [G*R, C]; 2-D tensors pass through."""
+    if t is None or t.dim() == 2 or groups == 1 and t.dim() <= 2:
+        return t
+    assert t.is_contiguous()
+    return t.view(-1, t.shape[-1])
+
+
+def gemm_nt(a, b, bias=None, out=None, gelu_pre_out=None, add=None, groups=1):
     """``out = a @ b.T (+ bias) (+ add)``; with ``gelu_pre_out`` the pre-activation goes there and
-    ``out`` gets tanh-GELU of it. ``a``: [M,K], ``b``: [N,K]."""
-    M, K = a.shape
-    Nn = b.shape[0]
-    assert b.shape[1] == K
+    ``out`` gets tanh-GELU of it. ``a``: [M,K], ``b``: [N,K].
+
+    ``groups`` > 1: that many independent problems in one launch (the experts of an MoE layer): ``a`` [G*M,K],
+    ``b`` [G,N,K] or [G*N,K], ``bias`` [G,N] or [G*N], ``out`` / ``gelu_pre_out`` / ``add`` [G*M,N]."""
+    b = _flat2(b, groups)
+    if bias is not None and bias.dim() == 2:
+        bias = bias.reshape(-1)
+    K = a.shape[1]
+    M = a.shape[0] // groups
+    Nn = b.shape[0] // groups
+    assert b.shape[1] == K and a.shape[0] == M * groups and b.shape[0] == Nn * groups
     if out is None:
-        out = torch.empty(M, Nn, dtype=torch.bfloat16, device=a.device)
+        out = torch.empty(M * groups, Nn, dtype=torch.bfloat16, device=a.device)
     epi = 0
     if bias is not None:
         epi |= EPI_BIAS
@@ -65,31 +103,38 @@ def gemm_nt(a, b, bias=None, out=None, gelu_pre_out=None, add=None):
         epi |= EPI_GELU
     if add is not None:
         epi |= EPI_ADD
-    return _gemm(MODE_NT, epi, a, b, out, gelu_pre_out, bias, add, M, Nn, K)
+    return _gemm(MODE_NT, epi, a, b, out, gelu_pre_out, bias, add, M, Nn, K, groups)
 
 
-def gemm_nn(a, b, out=None, dgelu_of=None, add=None):
-    """``out = a @ b`` with ``a``: [M,K], ``b``: [K,N]; optionally ``* gelu'(dgelu_of)`` or ``+ add``."""
-    M, K = a.shape
+def gemm_nn(a, b, out=None, dgelu_of=None, add=None, groups=1):
+    """``out = a @ b`` with ``a``: [M,K], ``b``: [K,N]; optionally ``* gelu'(dgelu_of)`` or ``+ add``.
+    ``groups`` > 1: ``a`` [G*M,K], ``b`` [G,K,N] or [G*K,N], ``out`` / aux [G*M,N]."""
+    b = _flat2(b, groups)
+    K = a.shape[1]
+    M = a.shape[0] // groups
     Nn = b.shape[1]
-    assert b.shape[0] == K
+    assert b.shape[0] == K * groups and a.shape[0] == M * groups
     if out is None:
-        out = torch.empty(M, Nn, dtype=torch.bfloat16, device=a.device)
+        out = torch.empty(M * groups, Nn, dtype=torch.bfloat16, device=a.device)
     epi = 0
     aux = None
     if dgelu_of is not None:
         epi, aux = EPI_DGELU, dgelu_of
     elif add is not None:
         epi, aux = EPI_ADD, add
-    return _gemm(MODE_NN, epi, a, b, out, None, None, aux, M, Nn, K)
+    return _gemm(MODE_NN, epi, a, b, out, None, None, aux, M, Nn, K, groups)
 
 
-def gemm_tn(a, b, out=None, accumulate=False):
-    """``out (+)= a.T @ b`` with ``a``: [K,M], ``b``: [K,N] (K = token dimension)."""
-    K, M = a.shape
+def gemm_tn(a, b, out=None, accumulate=False, groups=1):
+    """``out (+)= a.T @ b`` with ``a``: [K,M], ``b``: [K,N] (K = token dimension).
+    ``groups`` > 1: ``a`` [G*K,M], ``b`` [G*K,N], ``out`` [G,M,N] or [G*M,N]: group g uses rows [g*K,(g+1)*K)."""
+    M = a.shape[1]
+    K = a.shape[0] // groups
     Nn = b.shape[1]
-    assert b.shape[0] == K
+    assert b.shape[0] == K * groups and a.shape[0] == K * groups
     if out is None:
         assert not accumulate
-        out = torch.empty(M, Nn, dtype=torch.bfloat16, device=a.device)
-    return _gemm(MODE_TN, EPI_ADD if accumulate else 0, a, b, out, None, None, out if accumulate else None, M, Nn, K)
+        out = torch.empty(M * groups, Nn, dtype=torch.bfloat16, device=a.device)
+    out2 = _flat2(out, groups)
+    _gemm(MODE_TN, EPI_ADD if accumulate else 0, a, b, out2, None, None, out2 if accumulate else None, M, Nn, K, groups)
+    return out

@@ -89,3 +89,37 @@ def test_gemm_deterministic():
     o1 = gemm.gemm_tn(a, b).clone()
     o2 = gemm.gemm_tn(a, b)
     assert torch.equal(o1, o2)
+
+
+@pytest.mark.parametrize("G,M,N,K", [(4, 512, 512, 256), (3, 256, 1000, 192), (2, 200, 264, 128)])
+def test_gemm_grouped_matches_per_group_reference(G, M, N, K):
+    """One launch for G equal-shaped problems (MoE experts); the last shape has rows that are not a multiple of the
+    tile height, which takes the one-launch-per-group path of the wrapper."""
+    from llm_kittens_b200.ops import gemm, _native
+
+    # NT with bias + GELU: a [G*M,K], w [G,N,K], bias [G,N]
+    a, w, bias = _rand(G * M, K), _rand(G, N, K, scale=0.05), _rand(G, N)
+    pre = torch.empty(G * M, N, device="cuda", dtype=torch.bfloat16)
+    out = gemm.gemm_nt(a, w, bias=bias, gelu_pre_out=pre, groups=G)
+    for g in range(G):
+        ref = a[g * M:(g + 1) * M].float() @ w[g].float().T + bias[g].float()
+        _close(pre[g * M:(g + 1) * M], ref, 0.06)
+        _close(out[g * M:(g + 1) * M], _gelu(ref), 0.06)
+    # NN: dy [G*M,N] @ w [G,N,K] -> [G*M,K], with the dGELU factor
+    dy = _rand(G * M, N)
+    pre2 = _rand(G * M, K)
+    dx = gemm.gemm_nn(dy, w, dgelu_of=pre2, groups=G)
+    x = pre2.float().requires_grad_(True)
+    _gelu(x).sum().backward()
+    for g in range(G):
+        ref = (dy[g * M:(g + 1) * M].float() @ w[g].float()) * x.grad[g * M:(g + 1) * M]
+        _close(dx[g * M:(g + 1) * M], ref, 0.15)
+    # TN: per-group weight gradient dy_g^T @ a_g accumulated into [G,N,K]
+    dyw = _rand(G * M, N, scale=0.1)
+    gw = _rand(G, N, K)
+    gw0 = gw.clone()
+    gemm.gemm_tn(dyw, a, out=gw, accumulate=True, groups=G)
+    for g in range(G):
+        ref = gw0[g].float() + dyw[g * M:(g + 1) * M].float().T @ a[g * M:(g + 1) * M].float()
+        _close(gw[g], ref, 0.12)
+    _native.check_status()
