@@ -136,6 +136,46 @@ __global__ void rope_qk_kernel(bf16* __restrict__ qkv, const float2* __restrict_
     base[i1] = __float2bfloat16_rn(x0 * cs.y + x1 * cs.x);
 }
 
+// The same rotation with 16-byte accesses: a thread owns 8 pairs (half-split: 8 elements of each half of a head,
+// two loads and two stores; interleaved: 16 consecutive elements). Needs HS to be a multiple of 16.
+template <bool INTERLEAVED>
+__global__ void rope_qk_vec_kernel(bf16* __restrict__ qkv, const float2* __restrict__ freqs, int B, int T, int NH, int NKVH, int HS,
+                                   int inverse) {
+    const int half = HS / 2;
+    const int groups = half / 8;            // groups of 8 pairs per head
+    const int heads = NH + NKVH;
+    const size_t total = (size_t)B * T * heads * groups;
+    const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= total) return;
+    const int gi = idx % groups;
+    const int h = (idx / groups) % heads;
+    const size_t bt = idx / ((size_t)groups * heads);
+    const int t = bt % T;
+    const int width = (NH + 2 * NKVH) * HS;
+    bf16* base = qkv + bt * width + (size_t)h * HS;
+    bf16* p0 = INTERLEAVED ? base + 16 * gi : base + 8 * gi;
+    bf16* p1 = INTERLEAVED ? p0 + 8 : p0 + half;
+    float a[8], b[8];
+    unpack8(ld128(p0), a);
+    unpack8(ld128(p1), b);
+    const float4* f4 = reinterpret_cast<const float4*>(freqs + (size_t)t * half + 8 * gi);   // 8 (cos, sin) pairs = 64 bytes
+    float cs[16];
+#pragma unroll
+    for (int j = 0; j < 4; j++) *reinterpret_cast<float4*>(cs + 4 * j) = __ldg(f4 + j);
+#pragma unroll
+    for (int j = 0; j < 8; j++) {
+        // pair j of this group: interleaved -> elements (2j, 2j+1) of the 16; half-split -> (a[j], b[j])
+        float& x0r = INTERLEAVED ? (j < 4 ? a[2 * j] : b[2 * j - 8]) : a[j];
+        float& x1r = INTERLEAVED ? (j < 4 ? a[2 * j + 1] : b[2 * j - 7]) : b[j];
+        const float c = cs[2 * j], sn = inverse ? -cs[2 * j + 1] : cs[2 * j + 1];
+        const float x0 = x0r, x1 = x1r;
+        x0r = x0 * c - x1 * sn;
+        x1r = x0 * sn + x1 * c;
+    }
+    st128(p0, pack8(a));
+    st128(p1, pack8(b));
+}
+
 // ------------------------------------------------------------------ bias gradient (column sums)
 // stage 1: partial[chunk][c] = sum over the chunk's rows of dout[row][c]; stage 2 sums chunks in order.
 constexpr int DB_ROWS = 256;  // rows per chunk
@@ -320,6 +360,17 @@ LLMK_API int llmk_add(void* out, const void* a, const void* b, long n, void* str
 LLMK_API int llmk_rope_qk(void* qkv, const void* freqs, int B, int T, int NH, int NKVH, int HS, int interleaved, int inverse,
                           void* stream) {
     if (HS % 2) return LLMK_ERR_SHAPE;
+    if (HS % 16 == 0 && (reinterpret_cast<uintptr_t>(qkv) & 15) == 0 && (reinterpret_cast<uintptr_t>(freqs) & 15) == 0) {
+        const size_t groups = (size_t)B * T * (NH + NKVH) * (HS / 16);
+        if (interleaved)
+            rope_qk_vec_kernel<true><<<ceil_div((long)groups, TPB), TPB, 0, (cudaStream_t)stream>>>((bf16*)qkv, (const float2*)freqs, B, T,
+                                                                                                  NH, NKVH, HS, inverse);
+        else
+            rope_qk_vec_kernel<false><<<ceil_div((long)groups, TPB), TPB, 0, (cudaStream_t)stream>>>((bf16*)qkv, (const float2*)freqs, B, T,
+                                                                                                   NH, NKVH, HS, inverse);
+        LLMK_LAUNCH_CHECK();
+        return LLMK_OK;
+    }
     const size_t total = (size_t)B * T * (NH + NKVH) * (HS / 2);
     rope_qk_kernel<<<ceil_div((long)total, TPB), TPB, 0, (cudaStream_t)stream>>>((bf16*)qkv, (const float2*)freqs, B, T, NH,
                                                                                 NKVH, HS, interleaved, inverse);
