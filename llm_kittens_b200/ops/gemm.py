@@ -74,7 +74,7 @@ def _gemm(mode, epi, a, b, c, c2, bias, aux, M, Nn, K, groups=1):
 
 def _flat2(t, groups):
     """[G, R, C] (contiguous) -> [G*R, C]; 2-D tensors pass through."""
-    if t is None or t.dim() == 2 or groups == 1 and t.dim() <= 2:
+    if t is None or t.dim() == 2:
         return t
     assert t.is_contiguous()
     return t.view(-1, t.shape[-1])
