@@ -40,7 +40,7 @@ template <bool PAIR> struct Geo {
 constexpr int CHUNK_BYTES = 64 * BK * 2;          // one 64(MN) x 64(K) MN-major box = 8 KiB
 constexpr int STAGING_BYTES = 32 * 128;           // 32 rows x 64 bf16 per epilogue warp buffer
 constexpr int NUM_EPI_WARPS = 8;  // two per TMEM lane group; each takes alternate 64-column chunks
-constexpr int THREADS = 32 * (2 + NUM_EPI_WARPS);
+constexpr int MAX_EPI_WARPS = 16;
 constexpr int MAX_STAGES = 6;
 constexpr int GROUP_M = 8;
 constexpr int TMEM_COLS = 512;
@@ -52,8 +52,18 @@ template <int EPI, bool PAIR>
 struct Cfg {
     static constexpr bool DUAL = (EPI & (EPI_GELU | EPI_DGELU | EPI_ADD)) != 0;
     static constexpr int STAGES = PAIR ? (DUAL ? 5 : 6) : (DUAL ? 3 : 4);
-    static constexpr int SMEM_MAIN = STAGES * Geo<PAIR>::STAGE_BYTES + NUM_EPI_WARPS * (DUAL ? 2 : 1) * STAGING_BYTES;
-    static constexpr int SMEM_BYTES = SMEM_MAIN + 1024 /*alignment slack*/ + 256 /*barriers*/;
+    // Wide epilogue (pair kernel, dGELU): 16 epilogue warps, four per TMEM lane group, one 64-column chunk each per
+    // tile; the result overwrites the aux tile in its staging buffer. With K = 768 this epilogue sets the pace of the
+    // kernel and it is bound by latency, not by issue slots or a pipe, so twice the warps per scheduler helps
+    // (0.33 -> 0.28-0.30 ms at 65536 x 3072 x 768). The GELU epilogue with its two outputs did not gain from it:
+    // 0.317 ms with one staging buffer per warp (the second store waits for the first), 0.343 ms with two buffers and
+    // a 3-stage ring, against 0.29 ms with 8 warps.
+    static constexpr bool WIDE = PAIR && EPI == EPI_DGELU;
+    static constexpr int EPI_WARPS = WIDE ? 16 : NUM_EPI_WARPS;
+    static constexpr int NTHREADS = 32 * (2 + EPI_WARPS);
+    static constexpr int NBUF = (DUAL && !WIDE) ? 2 : 1;   // staging buffers per epilogue warp
+    static constexpr int SMEM_MAIN = STAGES * Geo<PAIR>::STAGE_BYTES + EPI_WARPS * NBUF * STAGING_BYTES;
+    static constexpr int SMEM_BYTES = SMEM_MAIN + 1024 /*alignment slack*/ + 512 /*barriers*/;
 };
 
 // Packed-pair forms of gelu_fwd / gelu_grad (common.cuh): the same explicitly rounded operations in the same order,
@@ -118,13 +128,15 @@ __device__ __forceinline__ Work decode_unit(const Params& p, int u) {
 }
 
 template <int MODE, int EPI, bool PAIR>
-__global__ void __launch_bounds__(THREADS, 1)
+__global__ void __launch_bounds__((Cfg<EPI, PAIR>::NTHREADS), 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
             const __grid_constant__ CUtensorMap tmC, const __grid_constant__ CUtensorMap tmX, const Params p) {
     // tmX: second output (GELU pre-activation) or auxiliary [M,N] input (DGELU / ADD); same geometry as tmC
     constexpr int STAGES = Cfg<EPI, PAIR>::STAGES;
     constexpr int SMEM_MAIN = Cfg<EPI, PAIR>::SMEM_MAIN;
     constexpr bool DUAL = Cfg<EPI, PAIR>::DUAL;
+    constexpr bool WIDE = Cfg<EPI, PAIR>::WIDE;
+    constexpr int EPI_WARPS = Cfg<EPI, PAIR>::EPI_WARPS;
     constexpr int STAGE_BYTES = Geo<PAIR>::STAGE_BYTES, BN_CTA = Geo<PAIR>::BN_CTA;
     constexpr bool A_MN = (MODE == MODE_TN);
     constexpr bool B_MN = (MODE != MODE_NT);
@@ -137,8 +149,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
     uint64_t* empty_bar = bars + MAX_STAGES;           // [MAX_STAGES]
     uint64_t* acc_full = bars + 2 * MAX_STAGES;        // [2]
     uint64_t* acc_empty = bars + 2 * MAX_STAGES + 2;   // [2]
-    uint64_t* aux_bar = bars + 2 * MAX_STAGES + 4;     // [NUM_EPI_WARPS]
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(aux_bar + NUM_EPI_WARPS);
+    uint64_t* aux_bar = bars + 2 * MAX_STAGES + 4;     // [MAX_EPI_WARPS]
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(aux_bar + MAX_EPI_WARPS);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -158,9 +170,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
         }
         for (int i = 0; i < 2; i++) {
             ptx::mbar_init(&acc_full[i], 1);
-            ptx::mbar_init(&acc_empty[i], PAIR ? 2 * NUM_EPI_WARPS : NUM_EPI_WARPS);   // pair: both CTAs' epilogue warps
+            ptx::mbar_init(&acc_empty[i], PAIR ? 2 * EPI_WARPS : EPI_WARPS);   // pair: both CTAs' epilogue warps
         }
-        for (int i = 0; i < NUM_EPI_WARPS; i++) ptx::mbar_init(&aux_bar[i], 1);
+        for (int i = 0; i < EPI_WARPS; i++) ptx::mbar_init(&aux_bar[i], 1);
         *abort_flag = 0;
         ptx::fence_barrier_init();
         ptx::prefetch_tmap(&tmA);
@@ -282,11 +294,13 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
         }
     } else if (warp >= 2) {
         // ------------------------------------------------------------ epilogue warps
-        const int e = warp - 2;              // 0..7
+        const int e = warp - 2;              // 0..EPI_WARPS-1
         const int lane_group = warp & 3;     // TMEM lanes [32*lane_group, +32) are visible to this warp
-        const int chunk_sel = e >> 2;        // this warp takes chunks with (chunk & 1) == chunk_sel
-        uint8_t* buf = staging + e * (DUAL ? 2 : 1) * STAGING_BYTES;  // output tile
-        uint8_t* buf2 = buf + STAGING_BYTES;                          // second output / aux input (DUAL only)
+        constexpr int CH_STEP = EPI_WARPS / 4;   // warps per lane group = stride over the 64-column chunks
+        const int chunk_sel = e >> 2;        // this warp takes chunks chunk_sel, chunk_sel + CH_STEP, ...
+        constexpr int NBUF = Cfg<EPI, PAIR>::NBUF;
+        uint8_t* buf = staging + e * NBUF * STAGING_BYTES;            // output tile
+        uint8_t* buf2 = NBUF == 2 ? buf + STAGING_BYTES : buf;        // second output / aux input (DUAL); wide dGELU: the same buffer
         constexpr bool AUX_IN = (EPI & (EPI_DGELU | EPI_ADD)) != 0;
         uint32_t aux_ph = 0;
         int it = 0;
@@ -299,6 +313,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
             if (AUX_IN && w.n0 + chunk_sel * 64 < p.N) {
                 // fetch the first aux tile while the main loop of this tile is still running
                 if (lane == 0) {
+                    if (WIDE) ptx::tma_store_wait_read<0>();   // wide dGELU: the buffer was the source of the previous tile's store
                     ptx::mbar_arrive_expect_tx(&aux_bar[e], STAGING_BYTES);
                     ptx::tma_load_2d(buf2, &tmX, &aux_bar[e], w.n0 + chunk_sel * 64, row0);
                 }
@@ -311,9 +326,41 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
             const bool row_ok = row < p.M;
             const uint32_t t_row = tmem_base + a * BN + ((uint32_t)(lane_group * 32) << 16);
 #pragma unroll 1
-            for (int chunk = chunk_sel; chunk < BN / 64; chunk += 2) {
+            for (int chunk = chunk_sel; chunk < BN / 64; chunk += CH_STEP) {
                 const int n_base = w.n0 + chunk * 64;
                 if (n_base >= p.N) break;
+                if constexpr (WIDE) {
+                    // dGELU, one chunk per warp and tile, 32 columns at a time: result = acc * GELU'(aux), written over the aux tile
+                    ok = ptx::mbar_wait(&aux_bar[e], aux_ph, abort_flag, p.status, LLMK_ST_TIMEOUT_ACC_FULL, -2);
+                    aux_ph ^= 1;
+                    if (!ok) break;
+#pragma unroll
+                    for (int half = 0; half < 2; half++) {
+                        uint32_t v[32];
+                        ptx::tmem_ld_32x32b_x32(t_row + chunk * 64 + half * 32, v);
+                        ptx::tmem_ld_wait();
+#pragma unroll
+                        for (int q = 0; q < 4; q++) {
+                            const int cc = half * 4 + q;
+                            const uint32_t off = lane * 128 + ((cc ^ (lane & 7)) << 4);
+                            float g[8], x[8];
+                            unpack8(*reinterpret_cast<const bf16x8*>(buf + off), g);
+#pragma unroll
+                            for (int j = 0; j < 4; j++) {
+                                const ptx::f32x2 acc2 = ptx::pack2(__uint_as_float(v[q * 8 + 2 * j]), __uint_as_float(v[q * 8 + 2 * j + 1]));
+                                ptx::unpack2(ptx::mul2(acc2, gelu_grad2(ptx::pack2(g[2 * j], g[2 * j + 1]))), x[2 * j], x[2 * j + 1]);
+                            }
+                            *reinterpret_cast<bf16x8*>(buf + off) = pack8(x);
+                        }
+                    }
+                    ptx::fence_proxy_async_smem();
+                    __syncwarp();
+                    if (lane == 0) {
+                        ptx::tma_store_2d(&tmC, buf, n_base, row0);
+                        ptx::tma_store_commit();
+                    }
+                    continue;
+                }
                 if (EPI & EPI_PARTIAL) {
 #pragma unroll
                     for (int half = 0; half < 2; half++) {
@@ -524,7 +571,7 @@ static int launch(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensor
         if (max_ctas > 0 && clusters > max_ctas / 2) clusters = max_ctas / 2 > 0 ? max_ctas / 2 : 1;
         cudaLaunchConfig_t cfg = {};
         cfg.gridDim = dim3(2 * clusters);
-        cfg.blockDim = dim3(THREADS);
+        cfg.blockDim = dim3(Cfg<EPI, true>::NTHREADS);
         cfg.dynamicSmemBytes = SMEM_BYTES;
         cfg.stream = stream;
         cudaLaunchAttribute attr[1];
@@ -545,7 +592,7 @@ static int launch(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensor
     }
     int grid = units < g_num_sms ? units : g_num_sms;
     if (max_ctas > 0 && grid > max_ctas) grid = max_ctas;
-    gemm_kernel<MODE, EPI, false><<<grid, THREADS, SMEM_BYTES, stream>>>(tmA, tmB, tmC, tmX, p);
+    gemm_kernel<MODE, EPI, false><<<grid, Cfg<EPI, false>::NTHREADS, SMEM_BYTES, stream>>>(tmA, tmB, tmC, tmX, p);
     LLMK_LAUNCH_CHECK();
     return LLMK_OK;
 }
@@ -563,7 +610,7 @@ static int query_pair_clusters() {
     }
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(2);
-    cfg.blockDim = dim3(THREADS);
+    cfg.blockDim = dim3(Cfg<0, true>::NTHREADS);
     cfg.dynamicSmemBytes = SMEM_BYTES;
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeClusterDimension;
