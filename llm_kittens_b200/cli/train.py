@@ -17,7 +17,7 @@ import torch
 
 from ..models.config import ModelConfig, config_from_descriptor
 from ..parallel import zero as zero_mod
-from ..utils import formats
+from ..utils import formats, nvtx
 from ..utils.logger import Logger
 from ..utils.outlier import OutlierDetector
 from ..utils.schedulers import LearningRateScheduler
@@ -185,6 +185,15 @@ def train(args: TrainArgs, trainer_name: str) -> int:
     sched = LearningRateScheduler(args.lr_scheduler_type, args.learning_rate, args.warmup_iterations, train_num_batches,
                                   args.final_learning_rate_frac)
 
+    # host watchdog (LLMK_WATCHDOG_SECONDS > 0): a step that takes longer than the deadline, or a peer whose heartbeat
+    # stops, ends this process with the exit code that the supervisor maps to "resume from the last checkpoint"
+    watchdog = None
+    deadline = float(os.environ.get("LLMK_WATCHDOG_SECONDS", "0") or 0)
+    if deadline > 0:
+        from ..runtime.watchdog import Watchdog, store_from_env
+        watchdog = Watchdog(rank, world, deadline, store=store_from_env(rank, world) if world > 1 else None)
+        watchdog.start()
+
     step = 0
     if resuming:
         step = load_checkpoint(args.output_log_dir, resume_step, trainer, train_loader, world, rank)
@@ -199,16 +208,21 @@ def train(args: TrainArgs, trainer_name: str) -> int:
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     total_ms, timed_steps = 0.0, 0
     losses_host = torch.empty(B * T, dtype=torch.float32).pin_memory()
+    nvtx.profiler_start()   # with LLMK_NVTX=1: the capture range of a profiler ends after the third step, as in the reference
+    first_loop_step = step
     while step <= train_num_batches:
         last_step = step == train_num_batches
+        if watchdog is not None:
+            watchdog.beat(step)
         # validation
         if step % max(1, args.val_loss_every) == 0 or last_step:
             val_loader.reset()
             acc = torch.zeros(1, device=device)
-            for _ in range(val_num_batches):
-                x, y = val_loader.next_batch()
-                model.forward(x, y, compute_dlogits=False)
-                acc += model.acts["loss_acc"]
+            with nvtx.nvtx_range("validation"):
+                for _ in range(val_num_batches):
+                    x, y = val_loader.next_batch()
+                    model.forward(x, y, compute_dlogits=False)
+                    acc += model.acts["loss_acc"]
             acc /= val_num_batches
             comm.all_reduce_scalar(acc, "avg")
             val_loss = float(acc.item())
@@ -239,12 +253,15 @@ def train(args: TrainArgs, trainer_name: str) -> int:
         # checkpoint
         if args.checkpoint_every > 0 and args.output_log_dir and ((step > 0 and step % args.checkpoint_every == 0) or last_step) \
                 and not (resuming and step == resume_step):
-            save_checkpoint(args.output_log_dir, step, trainer, train_loader, world, rank, comm)
+            with nvtx.nvtx_range("checkpoint"):
+                save_checkpoint(args.output_log_dir, step, trainer, train_loader, world, rank, comm)
             prune_checkpoints(args.output_log_dir, step, args.checkpoint_every, args.checkpoints_keep, args.major_checkpoint_every,
                               world, rank)
         if last_step:
             break
 
+        if step == first_loop_step + 3:
+            nvtx.profiler_stop()
         ev0.record()
         if args.overfit_single_batch and step > 0:
             batches = [(train_loader.inputs, train_loader.targets)] * grad_accum
@@ -295,6 +312,8 @@ def train(args: TrainArgs, trainer_name: str) -> int:
                       % (info["gpu_util"], info["mem_util"], info["clock_mhz"], info["max_clock_mhz"], info["power_w"],
                          info["power_limit_w"], info["temperature_c"], info["throttle_reasons"]))
         logger.log_train(step - 1, loss, lr, norm)
+    if watchdog is not None:
+        watchdog.stop()
     if timed_steps:
         printf0(rank, f"total average iteration time: {total_ms / timed_steps:f} ms")
     if world > 1:

@@ -21,6 +21,7 @@ import torch
 
 from ..parallel.comm import SingleProcessComm
 from ..parallel.zero import ZeroPlan
+from ..utils.nvtx import nvtx_range
 from ..utils.rand import Xorshift
 
 
@@ -158,8 +159,10 @@ class Trainer:
         micro-steps themselves must go through here: the sharded communication path counts micro-steps."""
         if self.sharded_state:
             self.comm.start_micro_step(index)
-        self.model.forward(x, y, grad_accum_steps=accum, micro_step=index)
-        self.model.backward(last_micro_step=(index == accum - 1), bucket_ready=self._bucket_ready)
+        with nvtx_range("forward"):
+            self.model.forward(x, y, grad_accum_steps=accum, micro_step=index)
+        with nvtx_range("backward_and_reduce"):
+            self.model.backward(last_micro_step=(index == accum - 1), bucket_ready=self._bucket_ready)
 
     # ------------------------------------------------------------------ CUDA graph of one micro-step
     def enable_cuda_graph(self, on: bool = True) -> None:
@@ -216,22 +219,27 @@ class Trainer:
     def update(self, lr: float | None = None, skip: bool = False) -> None:
         """Queue reduction -> norm -> clip -> AdamW -> parameter gather on the current stream (no host
         sync). With ``skip`` the optimizer part is left out; :meth:`apply_update` can run it later."""
-        for off, n in self.expert_ranges:
-            self.model.grads[off:off + n].mul_(1.0 / self.num_processes)
-        self.comm.finish_reduce()
-        self.comm.all_reduce_scalar(self.model.acts["loss_acc"], "avg")
-        if getattr(self.comm, "fused", False):
-            # the bucket kernels already left the norm partials of the averaged shard
-            self.comm.norm_and_clip(self.grad_clip, self.scale, self.norm, self.flag)
-        else:
-            self._local_norm2()
-            if self.plan.sharded:
-                self.comm.all_reduce_scalar(self.norm2, "sum")
-            self._clip()
+        with nvtx_range("reduce_and_grad_norm"):
+            for off, n in self.expert_ranges:
+                self.model.grads[off:off + n].mul_(1.0 / self.num_processes)
+            self.comm.finish_reduce()
+            self.comm.all_reduce_scalar(self.model.acts["loss_acc"], "avg")
+            if getattr(self.comm, "fused", False):
+                # the bucket kernels already left the norm partials of the averaged shard
+                self.comm.norm_and_clip(self.grad_clip, self.scale, self.norm, self.flag)
+            else:
+                self._local_norm2()
+                if self.plan.sharded:
+                    self.comm.all_reduce_scalar(self.norm2, "sum")
+                self._clip()
         if not skip:
             self.apply_update(lr)
 
     def apply_update(self, lr: float | None = None) -> None:
+        with nvtx_range("optimizer_update_and_gather"):
+            self._apply_update(lr)
+
+    def _apply_update(self, lr: float | None = None) -> None:
         lr = self.lr if lr is None else lr
         self._ensure_master()
         self.rng_state_last_update = self.rng.state
