@@ -147,3 +147,55 @@ def require_cuda_tensor(t: torch.Tensor, dtype: torch.dtype | None = None, name:
         raise NativeError(f"{name} must be contiguous")
     if dtype is not None and t.dtype != dtype:
         raise NativeError(f"{name} must be {dtype}, got {t.dtype}")
+
+
+# ---- guard regions around scratch buffers ---------------------------------------------------------------
+# compute-sanitizer is not available where this runs, so the scratch buffers that kernels write through raw
+# pointers (split-K partials, column-sum partials of the norm / bias gradients) can be allocated with a canary
+# page on each side; check_guards() verifies them on the host. Off by default (the buffers are then pooled and
+# oversized); LLMK_GUARD=1 or set_guards(True) turns it on, which the GPU tests do.
+_GUARD_BYTES = 4096
+_GUARD_VALUE = 0xA5
+_GUARDS_ON = os.environ.get("LLMK_GUARD", "0") not in ("", "0")
+_GUARDED: list[tuple[str, torch.Tensor, int]] = []   # (name, whole allocation, payload bytes)
+
+
+def set_guards(on: bool) -> None:
+    global _GUARDS_ON
+    _GUARDS_ON = bool(on)
+    if not on:
+        _GUARDED.clear()
+
+
+def guards_enabled() -> bool:
+    return _GUARDS_ON
+
+
+def scratch_buffer(pool: dict, nbytes: int, min_bytes: int, name: str) -> torch.Tensor:
+    """A uint8 device buffer of at least ``nbytes`` from ``pool`` (one per device). With guards on it is exactly
+    ``nbytes`` (rounded up to 256) between two canary regions, so that a kernel writing past its stated need is seen."""
+    dev = torch.cuda.current_device()
+    if not _GUARDS_ON:
+        s = pool.get(dev)
+        if s is None or s.numel() < nbytes:
+            s = torch.empty(max(nbytes, min_bytes), dtype=torch.uint8, device=f"cuda:{dev}")
+            pool[dev] = s
+        return s
+    payload = (max(nbytes, 1) + 255) // 256 * 256
+    key = (dev, "guarded", payload)
+    whole = pool.get(key)
+    if whole is None:
+        whole = torch.full((payload + 2 * _GUARD_BYTES,), _GUARD_VALUE, dtype=torch.uint8, device=f"cuda:{dev}")
+        pool[key] = whole
+        _GUARDED.append((f"{name}[{payload}]@cuda:{dev}", whole, payload))
+    return whole[_GUARD_BYTES:_GUARD_BYTES + payload]
+
+
+def check_guards() -> int:
+    """Synchronise and verify every canary region; returns the number of guarded buffers, raises on damage."""
+    for name, whole, payload in _GUARDED:
+        lo = whole[:_GUARD_BYTES]
+        hi = whole[_GUARD_BYTES + payload:]
+        if not bool((lo == _GUARD_VALUE).all().item()) or not bool((hi == _GUARD_VALUE).all().item()):
+            raise NativeError(f"guard region of scratch buffer {name} was overwritten")
+    return len(_GUARDED)

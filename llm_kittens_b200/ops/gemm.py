@@ -27,12 +27,7 @@ def set_max_ctas(n: int) -> None:
 
 
 def workspace(nbytes: int) -> torch.Tensor:
-    dev = torch.cuda.current_device()
-    ws = _WORKSPACE.get(dev)
-    if ws is None or ws.numel() < nbytes:
-        ws = torch.empty(max(nbytes, 64 << 20), dtype=torch.uint8, device=f"cuda:{dev}")
-        _WORKSPACE[dev] = ws
-    return ws
+    return N.scratch_buffer(_WORKSPACE, nbytes, 64 << 20, "split-K partials")
 
 
 _TILE_ROWS = 0

@@ -10,12 +10,7 @@ _SCRATCH: dict[int, torch.Tensor] = {}
 
 
 def _scratch(nbytes: int) -> torch.Tensor:
-    dev = torch.cuda.current_device()
-    s = _SCRATCH.get(dev)
-    if s is None or s.numel() < nbytes:
-        s = torch.empty(max(nbytes, 1 << 20), dtype=torch.uint8, device=f"cuda:{dev}")
-        _SCRATCH[dev] = s
-    return s
+    return N.scratch_buffer(_SCRATCH, nbytes, 1 << 20, "column-sum partials")
 
 
 def layernorm_fwd(inp, weight, bias, out=None, mean=None, rstd=None):

@@ -254,3 +254,37 @@ def test_adamw_and_norm():
     p2 = torch.empty_like(params)
     optim.params_from_master(p2, master, segs, max_len, 1234)
     assert torch.equal(p2, params)
+
+
+def test_scratch_buffers_stay_inside_their_guard_regions():
+    """The kernels that write scratch memory through raw pointers (split-K partials, column-sum partials) get
+    exactly-sized buffers between canary pages; the canaries must be intact afterwards. The damaged case is made on
+    the host (a tensor fill over the whole allocation), not by a kernel."""
+    import pytest as _pytest
+
+    from llm_kittens_b200.ops import _native, elementwise as ew, gemm, norm
+
+    _native.set_guards(True)
+    try:
+        for M, Nn, K in [(768, 768, 4096), (2304, 768, 8192), (520, 264, 1000), (3072, 768, 2048)]:
+            a, b = rnd(K, M, scale=0.1), rnd(K, Nn, scale=0.1)
+            out = gemm.gemm_tn(a, b)
+            assert maxerr(out, a.float().T @ b.float()) < 0.02 * K ** 0.5
+        for rows, C in [(1000, 768), (4096, 1024), (777, 2048), (512, 4096)]:
+            x, w, bb = rnd(rows, C), rnd(C, scale=0.5) + 1, rnd(C, scale=0.1)
+            _, mean, rstd = norm.layernorm_fwd(x, w, bb)
+            dinp = torch.zeros(rows, C, device="cuda", dtype=BF)
+            dw, db = torch.zeros(C, device="cuda", dtype=BF), torch.zeros(C, device="cuda", dtype=BF)
+            norm.layernorm_bwd(dinp, dw, db, rnd(rows, C), x, w, mean, rstd, accumulate_dinp=False)
+            _, rstd2 = norm.rmsnorm_fwd(x, w, 1e-5)
+            norm.rmsnorm_bwd(dinp, dw, rnd(rows, C), x, w, rstd2, accumulate_dinp=False)
+            ew.dbias(db, rnd(rows, C), accumulate=False)
+        assert _native.check_guards() >= 8
+        _native.check_status()
+        # host-made damage is reported
+        name, whole, payload = _native._GUARDED[0]
+        whole[-1:].fill_(0)
+        with _pytest.raises(_native.NativeError, match="guard region"):
+            _native.check_guards()
+    finally:
+        _native.set_guards(False)
