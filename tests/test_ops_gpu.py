@@ -288,3 +288,36 @@ def test_scratch_buffers_stay_inside_their_guard_regions():
             _native.check_guards()
     finally:
         _native.set_guards(False)
+
+
+def test_peer_flag_wait_runs_out_and_reports_status():
+    """Failure detection inside a kernel, without any fault: a wait on a peer flag that nothing sets gives up after its
+    limit (0.2 s here), records LLMK_ST_TIMEOUT_PEER with the silent peer's index in the status word and returns; the
+    host reads the word and raises; the context stays usable."""
+    import time
+
+    import pytest as _pytest
+
+    from llm_kittens_b200.ops import _native, gemm
+
+    lib = _native.lib()
+    ctrl = torch.zeros(int(lib.llmk_comm_ctrl_ints()), dtype=torch.int32, device="cuda")
+    _native.check_status()
+    # every flag of slot 0 already at the awaited epoch: returns at once, status stays clear
+    ctrl[:8] = 1
+    _native.call("llmk_comm_wait", ctrl, 0, 1, 2, int(2e8), _native.status_word())
+    _native.check_status()
+    # peer 1 never signals epoch 2
+    ctrl[0] = 2
+    torch.cuda.synchronize()
+    t0 = time.time()
+    _native.call("llmk_comm_wait", ctrl, 0, 2, 2, int(2e8), _native.status_word())
+    with _pytest.raises(_native.NativeError, match="status 5") as info:
+        _native.check_status()
+    waited = time.time() - t0
+    assert 0.15 < waited < 5.0, waited
+    assert "thread=1" in str(info.value)              # the peer that stayed silent
+    # the status word was reset by the check and the context still runs kernels
+    a, b = rnd(256, 128), rnd(256, 128, scale=0.05)
+    assert maxerr(gemm.gemm_nt(a, b), a.float() @ b.float().T) < 0.05
+    _native.check_status()
