@@ -188,6 +188,7 @@ def train(args: TrainArgs, trainer_name: str) -> int:
     # host watchdog (LLMK_WATCHDOG_SECONDS > 0): a step that takes longer than the deadline, or a peer whose heartbeat
     # stops, ends this process with the exit code that the supervisor maps to "resume from the last checkpoint"
     watchdog = None
+    rendezvous = os.environ.get("LLMK_WATCHDOG_RENDEZVOUS", "0") not in ("", "0")   # host-side meeting point before every step
     deadline = float(os.environ.get("LLMK_WATCHDOG_SECONDS", "0") or 0)
     if deadline > 0:
         from ..runtime.watchdog import Watchdog, store_from_env
@@ -214,6 +215,10 @@ def train(args: TrainArgs, trainer_name: str) -> int:
         last_step = step == train_num_batches
         if watchdog is not None:
             watchdog.beat(step)
+            if rendezvous:
+                # nothing of this rank is in flight here: a peer that left or hangs is noticed before the next launch
+                torch.cuda.synchronize()
+                watchdog.enter_step(step)
         # validation
         if step % max(1, args.val_loss_every) == 0 or last_step:
             val_loader.reset()

@@ -8,9 +8,12 @@ what that scheme lacks, entirely on the host (no kernel is involved, nothing can
 * every rank runs a daemon thread; the training loop calls :meth:`Watchdog.beat` once per step;
 * if the own step takes longer than ``deadline_s`` the thread reports it and ends the process with
   :data:`EXIT_RESUME` (75, EX_TEMPFAIL), which :mod:`llm_kittens_b200.cli.supervise` maps to "restart with -y 1";
-* with a ``torch.distributed`` key-value store, each beat also publishes ``hb/<rank> = step:time`` and the thread
+* with a ``torch.distributed`` key-value store, each beat also publishes ``hb/<rank> = step`` and the thread
   watches the other ranks: a peer whose heartbeat is older than ``deadline_s`` (it crashed, or hangs before its
   next collective) ends this process the same way, instead of leaving it blocked in the next collective.
+
+* :meth:`Watchdog.enter_step` is a bounded host-side rendezvous at a step boundary (``LLMK_WATCHDOG_RENDEZVOUS=1`` in
+  the trainers): a peer that left between steps is noticed before this rank launches its next kernel or collective.
 
 The in-kernel waits of the fused communication kernels are bounded separately (status word, see ``ops/_native``);
 the watchdog covers what happens between kernels and inside library collectives.
@@ -61,6 +64,36 @@ class Watchdog:
                 self.store.set(f"hb/{self.rank}", f"{step}")
             except Exception as e:   # the store's host (rank 0) is gone
                 self._fail(f"rank {self.rank}: heartbeat store unreachable ({type(e).__name__})")
+
+    def enter_step(self, step: int, timeout_s: float | None = None) -> bool:
+        """Host-side rendezvous at a step boundary, to be called when none of this rank's kernels or collectives is in
+        flight: publishes ``enter/<rank> = step`` and waits (bounded) until every peer has published a step >= ``step``.
+        A peer that left or hangs is thus noticed BEFORE the next kernel or collective is launched. Returns True when
+        all peers arrived; otherwise the failure handler runs (default: exit with :data:`EXIT_RESUME`) and False is
+        returned."""
+        if self.store is None or self.world == 1:
+            return True
+        timeout_s = self.deadline_s if timeout_s is None else timeout_s
+        try:
+            self.store.set(f"enter/{self.rank}", str(step))
+            t0 = self.clock()
+            missing = [r for r in range(self.world) if r != self.rank]
+            while True:
+                missing = [r for r in missing
+                           if not (self.store.check([f"enter/{r}"]) and int(self.store.get(f"enter/{r}").decode()) >= step)]
+                if not missing:
+                    self._last_beat = self.clock()
+                    return True
+                if self.clock() - t0 > timeout_s:
+                    break
+                self._sleep(min(0.01, self.poll_s))
+        except Exception as e:
+            self._fail(f"rank {self.rank}: heartbeat store unreachable at step {step} ({type(e).__name__})")
+            return False
+        self._fail(f"rank {self.rank}: rank(s) {missing} did not enter step {step} within {timeout_s:.1f} s")
+        return False
+
+    _sleep = staticmethod(time.sleep)
 
     def start(self) -> None:
         self._last_beat = self.clock()

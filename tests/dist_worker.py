@@ -107,7 +107,25 @@ def main():
     trainer = Trainer(model, zero_stage=stage, use_master_weights=True, learning_rate=1e-3, weight_decay=0.1, comm=comm,
                       num_processes=world, rank=rank)
     losses, norms = [], []
-    for x, y in global_batches(cfg, steps, world, B, T):
+    leave = "leave" in mode
+    if leave:
+        # A rank leaves BETWEEN steps with none of its kernels or collectives in flight; the others learn of it at the
+        # host-side step rendezvous, before they launch anything, and exit with the resume code.
+        from llm_kittens_b200.runtime.watchdog import EXIT_RESUME, Watchdog, store_from_env
+
+        def on_failure(msg):
+            torch.save({"outcome": "peer_left", "message": msg, "losses": losses}, os.path.join(out_dir, f"rank{rank}.pt"))
+            os._exit(EXIT_RESUME)
+
+        wd = Watchdog(rank, world, deadline_s=3.0, store=store_from_env(rank, world), on_failure=on_failure)
+    for step_index, (x, y) in enumerate(global_batches(cfg, steps, world, B, T)):
+        if leave:
+            if not cpu:
+                torch.cuda.synchronize()
+            if rank == 1 and step_index == 2:
+                torch.save({"outcome": "left", "losses": losses}, os.path.join(out_dir, f"rank{rank}.pt"))
+                os._exit(0)
+            wd.enter_step(step_index)
         xs, ys = x[rank * B:(rank + 1) * B].contiguous(), y[rank * B:(rank + 1) * B].contiguous()
         if mode.startswith("gpu_sharded"):
             r = trainer.train_step([(xs[:1].contiguous(), ys[:1].contiguous()), (xs[1:].contiguous(), ys[1:].contiguous())])

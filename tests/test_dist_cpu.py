@@ -77,3 +77,17 @@ def test_failed_rank_is_detected_by_the_survivor(tmp_path):
     assert outs[1][0] != 0 and "injected failure" in outs[1][1]
     survivor = torch.load(tmp_path / "rank0.pt")
     assert survivor["outcome"].startswith("error:")
+
+
+def test_rank_that_leaves_between_steps_is_noticed_before_the_next_launch(tmp_path):
+    """Rank 1 exits cleanly after two steps; rank 0 learns of it at the host-side step rendezvous (no collective of
+    step 2 is ever started) and exits with the code that the supervisor maps to a resume."""
+    from llm_kittens_b200.runtime.watchdog import EXIT_RESUME
+
+    outs = launch("cpu_leave1", tmp_path, timeout=180)
+    assert outs[1][0] == 0, outs[1][1][-2000:]
+    assert outs[0][0] == EXIT_RESUME, outs[0][1][-2000:]
+    r0, r1 = torch.load(tmp_path / "rank0.pt"), torch.load(tmp_path / "rank1.pt")
+    assert r1["outcome"] == "left" and r0["outcome"] == "peer_left"
+    assert "rank(s) [1] did not enter step 2" in r0["message"]
+    assert len(r0["losses"]) == 2 and r0["losses"] == r1["losses"]

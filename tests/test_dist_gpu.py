@@ -119,3 +119,19 @@ def test_cli_zero3_checkpoint_resume_two_gpus(tmp_path):
     resumed = parse_log(str(b / "main.log"))["train"]
     for s in sorted(full)[3:]:
         assert resumed[s] == full[s], (s, resumed[s], full[s])
+
+
+def test_rank_that_leaves_between_steps_is_noticed_on_the_host(tmp_path):
+    """The same scenario on two GPUs with NCCL (NVLS off): rank 1 leaves between steps with nothing in flight, rank 0
+    finds out at the host-side rendezvous before it launches step 2 and exits with the resume code."""
+    _need_two_gpus()
+    from test_dist_cpu import launch
+
+    from llm_kittens_b200.runtime.watchdog import EXIT_RESUME
+
+    outs = launch("gpu_leave1", tmp_path, extra_env={"NCCL_NVLS_ENABLE": "0", "TORCH_SYMM_MEM_DISABLE_MULTICAST": "1"}, timeout=240)
+    assert outs[1][0] == 0, outs[1][1][-2000:]
+    assert outs[0][0] == EXIT_RESUME, outs[0][1][-2000:]
+    r0, r1 = torch.load(tmp_path / "rank0.pt"), torch.load(tmp_path / "rank1.pt")
+    assert r1["outcome"] == "left" and r0["outcome"] == "peer_left"
+    assert len(r0["losses"]) == 2 and r0["losses"] == r1["losses"]

@@ -129,3 +129,17 @@ def test_nvtx_ranges_nest_and_can_be_switched_off():
         assert len(nvtx.recent()) == n
     finally:
         nvtx.set_enabled(False)
+
+
+def test_step_rendezvous_notices_a_rank_that_left_before_anything_is_launched():
+    now = [0.0]
+    store = FakeStore()
+    failures = []
+    wd = Watchdog(0, 2, deadline_s=2.0, store=store, on_failure=failures.append, clock=lambda: now[0])
+    wd._sleep = lambda s: now.__setitem__(0, now[0] + s)      # waiting advances the fake clock
+    store.set("enter/1", "3")
+    assert wd.enter_step(3) and not failures                  # the peer is already there
+    assert wd.enter_step(2) and not failures
+    assert not wd.enter_step(4)                               # the peer never publishes step 4
+    assert failures and "rank(s) [1] did not enter step 4" in failures[0]
+    assert 2.0 <= now[0] <= 2.2
