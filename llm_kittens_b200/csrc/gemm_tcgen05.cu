@@ -57,7 +57,8 @@ struct Cfg {
     // kernel and it is bound by latency, not by issue slots or a pipe, so twice the warps per scheduler helps
     // (0.33 -> 0.28-0.30 ms at 65536 x 3072 x 768). The GELU epilogue with its two outputs did not gain from it:
     // 0.317 ms with one staging buffer per warp (the second store waits for the first), 0.343 ms with two buffers and
-    // a 3-stage ring, against 0.29 ms with 8 warps.
+    // a 3-stage ring, against 0.29 ms with 8 warps. The plain and bias epilogues lost as well (qkv 0.16 -> 0.18 ms,
+    // lm-head 3.85 -> 4.02 ms with 16 warps and 5 stages).
     static constexpr bool WIDE = PAIR && EPI == EPI_DGELU;
     static constexpr int EPI_WARPS = WIDE ? 16 : NUM_EPI_WARPS;
     static constexpr int NTHREADS = 32 * (2 + EPI_WARPS);
