@@ -19,7 +19,7 @@ from ..models.config import ModelConfig, config_from_descriptor
 from ..parallel import zero as zero_mod
 from ..utils import formats, nvtx
 from ..utils.logger import Logger
-from ..utils.outlier import OutlierDetector
+from ..utils.outlier import NativeOutlierDetector as OutlierDetector
 from ..utils.schedulers import LearningRateScheduler
 from .flags import FlagError, TrainArgs, parse_flags
 

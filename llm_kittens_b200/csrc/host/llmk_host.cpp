@@ -595,3 +595,97 @@ HOST_API int llmk_tokenizer_decode(void* h, int id, uint8_t* out, int cap) {
     memcpy(out, s.data(), n);
     return (int)s.size();
 }
+
+// ---- learning-rate schedules (cosine, linear, constant, wsd) with linear warm-up (step + 1) / warmup; float32
+// arithmetic, the same curves as llmc/schedulers.h:19-98 of the reference. kind: 0 cosine, 1 linear, 2 constant, 3 wsd.
+// Returns NaN for a step beyond the schedule or an unknown kind.
+HOST_API float llmk_lr_get(int kind, float lr, int warmup, int total, float final_frac, int step) {
+    const float min_lr = lr * final_frac;
+    if (kind == 2) return lr;
+    if (kind < 0 || kind > 3) return NAN;
+    if (step < warmup) return lr * (float)(step + 1) / (float)warmup;
+    if (kind == 3) {
+        const int decay_point = (int)(0.8f * (float)total);
+        if (step < decay_point) return lr;
+        const float ratio = (float)(step - decay_point) / (float)(total - decay_point);
+        return min_lr + (1.0f - sqrtf(ratio)) * (lr - min_lr);
+    }
+    const float ratio = (float)(step - warmup) / (float)(total - warmup);
+    if (!(ratio >= 0.0f && ratio <= 1.0f)) return NAN;
+    if (kind == 0) {
+        const float coeff = 0.5f * (1.0f + cosf((float)M_PI * ratio));
+        return min_lr + coeff * (lr - min_lr);
+    }
+    return lr - ratio * (lr - min_lr);
+}
+
+// ---- outlier detector: z-score of a value against the previous 128 (double precision running sums); NaN until the
+// window is full (llmc/outlier_detector.h:16-70)
+struct OutlierDetector {
+    static constexpr int WINDOW = 128;
+    double buffer[WINDOW];
+    int count = 0, index = 0;
+    double sum = 0.0, sum_sq = 0.0;
+    double update(double v) {
+        if (count < WINDOW) {
+            buffer[count++] = v;
+            sum += v;
+            sum_sq += v * v;
+            return NAN;
+        }
+        const double old = buffer[index];
+        sum += v - old;
+        sum_sq += v * v - old * old;
+        buffer[index] = v;
+        index = (index + 1) % WINDOW;
+        const double mean = sum / WINDOW;
+        const double var = sum_sq / WINDOW - mean * mean;
+        const double sd = var > 0 ? sqrt(var) : 0.0;
+        return sd == 0.0 ? 0.0 : (v - mean) / sd;
+    }
+};
+HOST_API void* llmk_outlier_create() { return new OutlierDetector(); }
+HOST_API void llmk_outlier_destroy(void* h) { delete (OutlierDetector*)h; }
+HOST_API double llmk_outlier_update(void* h, double v) { return ((OutlierDetector*)h)->update(v); }
+
+// ---- logger: rank 0's main.log, opened per line in append mode (a crash loses nothing), wiped at creation unless
+// resuming; line formats as in llmc/logger.h:19-56 because log validators parse them
+struct HostLogger {
+    std::string path;
+    bool active = false;
+    void line(const char* text) {
+        if (!active) return;
+        FILE* f = fopen(path.c_str(), "a");
+        if (f == nullptr) return;
+        fputs(text, f);
+        fclose(f);
+    }
+};
+HOST_API void* llmk_logger_create(const char* dir, int rank, int resume) {
+    HostLogger* l = new HostLogger();
+    if (dir != nullptr && dir[0] != 0 && rank == 0) {
+        l->active = true;
+        l->path = std::string(dir) + "/main.log";
+        if (!resume) {
+            FILE* f = fopen(l->path.c_str(), "w");
+            if (f != nullptr) fclose(f);
+        }
+    }
+    return l;
+}
+HOST_API void llmk_logger_destroy(void* h) { delete (HostLogger*)h; }
+HOST_API void llmk_logger_eval(void* h, int step, float val) {
+    char buf[128];
+    snprintf(buf, sizeof buf, "s:%d eval:%.4f\n", step, val);
+    ((HostLogger*)h)->line(buf);
+}
+HOST_API void llmk_logger_val(void* h, int step, float val_loss) {
+    char buf[128];
+    snprintf(buf, sizeof buf, "s:%d tel:%.4f\n", step, val_loss);
+    ((HostLogger*)h)->line(buf);
+}
+HOST_API void llmk_logger_train(void* h, int step, float train_loss, float lr, float grad_norm) {
+    char buf[160];
+    snprintf(buf, sizeof buf, "s:%d trl:%.4f lr:%.6f norm:%.2f\n", step, train_loss, lr, grad_norm);
+    ((HostLogger*)h)->line(buf);
+}

@@ -53,6 +53,15 @@ _SIGNATURES = {
     "llmk_tokenizer_vocab_size": (c_int, [c_void_p]),
     "llmk_tokenizer_eot": (c_int, [c_void_p]),
     "llmk_tokenizer_decode": (c_int, [c_void_p, c_int, c_void_p, c_int]),
+    "llmk_lr_get": (c_float, [c_int, c_float, c_int, c_int, c_float, c_int]),
+    "llmk_outlier_create": (c_void_p, []),
+    "llmk_outlier_destroy": (None, [c_void_p]),
+    "llmk_outlier_update": (ctypes.c_double, [c_void_p, ctypes.c_double]),
+    "llmk_logger_create": (c_void_p, [c_char_p, c_int, c_int]),
+    "llmk_logger_destroy": (None, [c_void_p]),
+    "llmk_logger_eval": (None, [c_void_p, c_int, c_float]),
+    "llmk_logger_val": (None, [c_void_p, c_int, c_float]),
+    "llmk_logger_train": (None, [c_void_p, c_int, c_float, c_float, c_float]),
 }
 
 

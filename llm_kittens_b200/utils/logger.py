@@ -7,14 +7,33 @@ import os
 import re
 
 
+def _f32(x: float) -> float:
+    """The value as the reference's ``float`` arguments carry it (float32), so both writers print the same digits."""
+    import struct
+
+    return struct.unpack("f", struct.pack("f", float(x)))[0]
+
+
 class Logger:
-    def __init__(self, log_dir: str | None, process_rank: int = 0, resume: bool = False):
+    """Writes through the C++ host library (``llmk_logger_*``) when it is available, else with Python file I/O; the
+    bytes are the same."""
+
+    def __init__(self, log_dir: str | None, process_rank: int = 0, resume: bool = False, native: bool = True):
         self.active = log_dir is not None and process_rank == 0
         self.path = None
+        self._lib = self._h = None
         if self.active:
             os.makedirs(log_dir, exist_ok=True)
             self.path = os.path.join(log_dir, "main.log")
-            if not resume:
+            if native:
+                try:
+                    from . import hostlib
+
+                    self._lib = hostlib.lib()
+                    self._h = self._lib.llmk_logger_create(log_dir.encode(), 0, int(resume))
+                except Exception:
+                    self._lib = self._h = None
+            if self._h is None and not resume:
                 open(self.path, "w").close()
 
     def _append(self, line: str) -> None:
@@ -23,13 +42,29 @@ class Logger:
                 f.write(line)
 
     def log_eval(self, step: int, val: float) -> None:
-        self._append("s:%d eval:%.4f\n" % (step, val))
+        if self._h is not None:
+            self._lib.llmk_logger_eval(self._h, step, val)
+        else:
+            self._append("s:%d eval:%.4f\n" % (step, _f32(val)))
 
     def log_val(self, step: int, val_loss: float) -> None:
-        self._append("s:%d tel:%.4f\n" % (step, val_loss))
+        if self._h is not None:
+            self._lib.llmk_logger_val(self._h, step, val_loss)
+        else:
+            self._append("s:%d tel:%.4f\n" % (step, _f32(val_loss)))
 
     def log_train(self, step: int, train_loss: float, learning_rate: float, grad_norm: float) -> None:
-        self._append("s:%d trl:%.4f lr:%.6f norm:%.2f\n" % (step, train_loss, learning_rate, grad_norm))
+        if self._h is not None:
+            self._lib.llmk_logger_train(self._h, step, train_loss, learning_rate, grad_norm)
+        else:
+            self._append("s:%d trl:%.4f lr:%.6f norm:%.2f\n" % (step, _f32(train_loss), _f32(learning_rate), _f32(grad_norm)))
+
+    def __del__(self):
+        try:
+            if self._h is not None:
+                self._lib.llmk_logger_destroy(self._h)
+        except Exception:
+            pass
 
 
 _LINE = re.compile(r"^s:(\d+) (.*)$")

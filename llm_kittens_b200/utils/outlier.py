@@ -34,3 +34,22 @@ class OutlierDetector:
         if std == 0.0:
             return 0.0
         return (value - mean) / std
+
+
+class NativeOutlierDetector:
+    """The same detector inside the C++ host library (``llmk_outlier_*``)."""
+
+    def __init__(self):
+        from . import hostlib
+
+        self._lib = hostlib.lib()
+        self._h = self._lib.llmk_outlier_create()
+
+    def update(self, value: float) -> float:
+        return float(self._lib.llmk_outlier_update(self._h, float(value)))
+
+    def __del__(self):
+        try:
+            self._lib.llmk_outlier_destroy(self._h)
+        except Exception:
+            pass

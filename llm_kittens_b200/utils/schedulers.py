@@ -1,6 +1,7 @@
 """Learning-rate schedules with linear warm-up ``(step+1)/warmup``: cosine, linear, constant, wsd
 (constant, then ``1 - sqrt`` decay over the last 20 %). Same curves as the reference's
-llmc/schedulers.h:19-98; arithmetic is done in float32 like there."""
+llmc/schedulers.h:19-98; arithmetic is done in float32 like there. ``get`` evaluates the schedule in the C++ host
+library (``llmk_lr_get``); ``get_python`` is the same arithmetic in numpy float32, kept as the cross-check."""
 from __future__ import annotations
 
 import math
@@ -22,11 +23,24 @@ class LearningRateScheduler:
         self.warmup = int(warmup_iterations)
         self.total = int(train_num_batches)
         self.final_frac = f32(final_learning_rate_frac)
+        try:
+            from . import hostlib
+            self._native = hostlib.lib().llmk_lr_get
+        except Exception:   # no compiler / library on this machine: numpy path
+            self._native = None
 
     def _warm(self, step: int):
         return self.lr * f32(step + 1) / f32(self.warmup)
 
     def get(self, step: int) -> float:
+        if self._native is None:
+            return self.get_python(step)
+        v = float(self._native(self.TYPES.index(self.kind), float(self.lr), self.warmup, self.total, float(self.final_frac), int(step)))
+        if v != v:
+            raise ValueError("step beyond the schedule")
+        return v
+
+    def get_python(self, step: int) -> float:
         lr, min_lr = self.lr, self.lr * self.final_frac
         if self.kind == "constant":
             return float(lr)

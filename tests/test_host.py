@@ -444,3 +444,39 @@ def test_check_cli_zero_layout_log_and_checkpoint(tmp_path, capsys):
         f.write(b"\0\0")
     assert check.main(["checkpoint", str(tmp_path), "--step", "4"]) == 1
     capsys.readouterr()
+
+
+def test_native_scheduler_outlier_and_logger_match_the_python_versions(tmp_path):
+    """The C++ host library's schedules, outlier detector and logger against their Python restatements."""
+    import math
+    import random
+
+    from llm_kittens_b200.utils.outlier import NativeOutlierDetector, OutlierDetector
+    from llm_kittens_b200.utils.schedulers import LearningRateScheduler
+
+    for kind in LearningRateScheduler.TYPES:
+        s = LearningRateScheduler(kind, 6e-4, 70, 1000, 0.1)
+        assert s._native is not None
+        for step in list(range(0, 1001, 7)) + [69, 70, 71, 799, 800, 801, 1000]:
+            a, b = s.get(step), s.get_python(step)
+            assert abs(a - b) <= 2e-7 * max(abs(b), 1e-6) + 1e-10, (kind, step, a, b)
+    with pytest.raises(ValueError):
+        LearningRateScheduler("cosine", 1e-3, 10, 100, 0.0).get(101)
+    rnd_ = random.Random(0)
+    nat, py = NativeOutlierDetector(), OutlierDetector()
+    for i in range(400):
+        v = rnd_.gauss(3.0, 0.5) + (8.0 if i == 300 else 0.0)
+        za, zb = nat.update(v), py.update(v)
+        assert (math.isnan(za) and math.isnan(zb)) or abs(za - zb) < 1e-9
+        if i == 300:
+            assert za > 5.0
+    a_dir, b_dir = tmp_path / "native", tmp_path / "python"
+    for d, native in ((a_dir, True), (b_dir, False)):
+        lg = Logger(str(d), 0, native=native)
+        assert (lg._h is not None) == native
+        lg.log_val(0, 10.98765)
+        for st in range(3):
+            lg.log_train(st, 10.0 - st * 0.333333, 6e-4 * (st + 1) / 3, 1.2345 + st)
+        lg.log_eval(2, 0.2512)
+        Logger(str(d), 0, resume=True, native=native).log_train(3, 1.5, 1e-4, 0.5)
+    assert open(a_dir / "main.log", "rb").read() == open(b_dir / "main.log", "rb").read()
