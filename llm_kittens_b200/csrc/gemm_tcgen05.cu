@@ -11,13 +11,18 @@
 // matmul_backward in the reference (llmc/matmul.cuh:678-785, 1138-1201, 1238-1338), which has no
 // sm_100 path; this is a new design:
 //
-//   warp 0      : TMA producer  (4-stage ring of 128x64 A and 256x64 B tiles, mbarrier tx-count)
-//   warp 1      : MMA issuer    (one elected lane; 128x256x16 tcgen05.mma; commit -> stage release)
-//   warps 2..9  : epilogue      (tcgen05.ld 32 lanes x 32 columns -> math -> swizzled smem -> TMA store)
+//   warp 0      : TMA producer  (ring of 128x64 A and 256x64 B tiles, mbarrier tx-count)
+//   warp 1      : MMA issuer    (one elected lane; tcgen05.mma; commit -> stage release)
+//   warps 2..   : epilogue      (tcgen05.ld 32 lanes x 32 columns -> math -> swizzled smem -> TMA store);
+//                 8 warps, 16 for the dGELU epilogue
 //   TMEM        : 2 x 256 fp32 columns, so the epilogue of tile i overlaps the main loop of tile i+1.
 //
-// No cluster launch and no multicast: each CTA loads its own tiles; reuse comes from the L2 through
-// the grouped tile order. Every wait is bounded (ptx::mbar_wait) and reports through `status`.
+// Default: clusters of two CTAs (tcgen05.mma.cta_group::2, one 256x256 tile per pair, 256x256x16 MMAs issued by
+// the leader, each CTA loading its own 128 rows of A and its half of B; 5 or 6 stages of 32 KiB per CTA). The
+// single-CTA kernel (128x256 tile, 3 or 4 stages) remains as the fallback. No load uses cluster multicast: each CTA
+// loads its own tiles, reuse comes from the L2 through the grouped tile order; only tcgen05.commit is multicast
+// to the pair. Grouped (batched) problems of equal shape run in one launch (llmk_gemm_grouped).
+// Every wait is bounded (ptx::mbar_wait) and reports through `status`.
 #include <cstdlib>
 
 #include "ptx_sm100.cuh"
