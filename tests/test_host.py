@@ -480,3 +480,52 @@ def test_native_scheduler_outlier_and_logger_match_the_python_versions(tmp_path)
         lg.log_eval(2, 0.2512)
         Logger(str(d), 0, resume=True, native=native).log_train(3, 1.5, 1e-4, 0.5)
     assert open(a_dir / "main.log", "rb").read() == open(b_dir / "main.log", "rb").read()
+
+
+def test_grouped_gemm_wrapper_falls_back_to_one_launch_per_group(monkeypatch):
+    """Shape logic of ops/gemm.py on CPU tensors with the native call replaced by a recorder: rows that are not a
+    multiple of the tile height (or, for NN / TN, a K that is not a multiple of 64) must turn a grouped call into one
+    plain call per group on the right row slices; eligible shapes make ONE grouped call."""
+    from llm_kittens_b200.ops import _native, gemm
+
+    calls = []
+    monkeypatch.setattr(_native, "require_cuda_tensor", lambda *a, **k: None)
+    monkeypatch.setattr(_native, "status_word", lambda: None)
+    monkeypatch.setattr(_native, "call", lambda name, *a: calls.append((name, a)))
+    monkeypatch.setattr(gemm, "tile_rows", lambda: 256)
+
+    class FakeLib:
+        @staticmethod
+        def llmk_gemm_workspace_bytes(*a):
+            return 0
+
+    monkeypatch.setattr(_native, "lib", lambda: FakeLib)
+    bf = torch.bfloat16
+    G, M, N, K = 3, 512, 384, 128
+    a, w, bias = torch.zeros(G * M, K, dtype=bf), torch.zeros(G, N, K, dtype=bf), torch.zeros(G, N, dtype=bf)
+    out = gemm.gemm_nt(a, w, bias=bias, groups=G)
+    assert out.shape == (G * M, N) and len(calls) == 1 and calls[0][0] == "llmk_gemm_grouped"
+    assert calls[0][1][8:12] == (M, N, K, G)
+    calls.clear()
+    M2 = 200                                            # not a multiple of the tile height: three plain calls
+    a2 = torch.arange(G * M2 * K, dtype=torch.float32).reshape(G * M2, K).to(bf)
+    out2 = torch.zeros(G * M2, N, dtype=bf)
+    gemm.gemm_nt(a2, w, bias=bias, out=out2, groups=G)
+    assert [c[0] for c in calls] == ["llmk_gemm"] * G
+    for g, (_, args) in enumerate(calls):
+        A, B, C, bias_g = args[2], args[3], args[4], args[6]
+        assert A.data_ptr() == a2[g * M2:].data_ptr() and A.shape == (M2, K)
+        assert B.data_ptr() == w[g].data_ptr() and B.shape == (N, K)
+        assert C.data_ptr() == out2[g * M2:].data_ptr() and bias_g.data_ptr() == bias[g].data_ptr()
+        assert args[8:11] == (M2, N, K)
+    calls.clear()
+    # TN with K (tokens per group) not a multiple of 64: per-group calls on token slices, outputs [G, M, N]
+    Kt = 100
+    dy, x = torch.zeros(G * Kt, 256, dtype=bf), torch.zeros(G * Kt, N, dtype=bf)
+    gw = torch.zeros(G, 256, N, dtype=bf)
+    gemm.gemm_tn(dy, x, out=gw, accumulate=True, groups=G)
+    assert [c[0] for c in calls] == ["llmk_gemm"] * G
+    for g, (_, args) in enumerate(calls):
+        assert args[2].data_ptr() == dy[g * Kt:].data_ptr() and args[3].data_ptr() == x[g * Kt:].data_ptr()
+        assert args[4].data_ptr() == gw[g].data_ptr() and args[7].data_ptr() == gw[g].data_ptr()
+        assert args[8:11] == (256, N, Kt)
