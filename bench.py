@@ -21,6 +21,7 @@ from __future__ import annotations
 import argparse
 import json
 import os
+import re
 import statistics
 import subprocess
 import sys
@@ -34,12 +35,135 @@ PUBLISHED_TOKENS_PER_S = 212316.0  # reference's best published run (1x RTX 5090
 MICRO_B, SEQ_T, TOTAL_BATCH = 64, 1024, 524288
 
 
+REF_DIR = os.path.join(REPO, "baseline", "_ref")
+REF_STEP_LINE = re.compile(r"^step\s+(\d+)/\d+ \| train loss ([-\d.naninf]+) \| norm ([-\d.naninf]+) \| lr \S+ \| \(([\d.]+) ms \| (\d+) tok/s\)")
+
+
+def _write_reference_shard(path: str, num_tokens: int) -> None:
+    """One token shard in the reference's format (256 int32 header, magic 20240520, version 1, uint16 tokens):
+    ids uniform in [0, 50257) from seed 1337. Written under a temporary name and renamed, so that ranks which
+    all write the same bytes can race."""
+    import numpy as np
+
+    if os.path.exists(path):
+        return
+    os.makedirs(os.path.dirname(path), exist_ok=True)
+    header = np.zeros(256, dtype=np.int32)
+    header[0], header[1], header[2] = 20240520, 1, num_tokens
+    tokens = np.random.default_rng(1337).integers(0, 50257, size=num_tokens, dtype=np.uint16)
+    tmp = f"{path}.{os.getpid()}.tmp"
+    with open(tmp, "wb") as f:
+        f.write(header.tobytes())
+        f.write(tokens.tobytes())
+    os.replace(tmp, path)
+
+
 def reference_arm(args) -> int:
-    why = ("reference is a Makefile/nvcc project without setup.py or pyproject.toml (pip: 'not installable') and its "
-           "sources need ../ThunderKittens headers that are not on this machine; it also has no sm_100 kernel path")
-    if int(os.environ.get("RANK", "0")) == 0:
-        print(json.dumps({"impl": "reference", "unavailable": why}))
-    return 0
+    """Runs the reference's own PyTorch trainer, unmodified (`baseline/_ref/train_gpt2.py`, a byte copy of the
+    reference's `train_gpt2.py`), as a child process with the flags of its stock recipe
+    (`scripts/pyrun_gpt2_124M.sh`: d12, bf16 autocast, flash attention, TF32, torch.compile, DDP +
+    ZeroRedundancyOptimizer for N > 1) at micro-batch 64 x 1024 and 524,288 tokens per step, on a synthetic token
+    shard, for warmup + steps iterations, and turns the step lines that the trainer prints into the JSON line.
+    Every rank of the launcher runs one child, which inherits RANK / LOCAL_RANK / WORLD_SIZE / MASTER_*; nothing of
+    this package is imported by it. The trainer's own step time is host wall clock around a step that ends in
+    `torch.cuda.synchronize()`, and the step includes the host-to-device copy of every micro-batch and the
+    read-back of loss and norm, so it is the end-to-end figure and the only one the reference has."""
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+
+    def say(obj):
+        if rank == 0:
+            obj = {"impl": "reference", **obj}
+            print(json.dumps(obj), flush=True)
+        return 0
+
+    script = os.path.join(REF_DIR, "train_gpt2.py")
+    if not os.path.exists(script):
+        upstream = os.path.join(os.environ.get("LLMK_REFERENCE_ROOT", "/root/reference"), "train_gpt2.py")
+        if not os.path.exists(upstream):
+            return say({"unavailable": "baseline/_ref/train_gpt2.py (copy of the reference's PyTorch trainer) is missing"})
+        os.makedirs(REF_DIR, exist_ok=True)
+        tmp = f"{script}.{os.getpid()}.tmp"
+        with open(upstream, "rb") as src, open(tmp, "wb") as dst:
+            dst.write(src.read())
+        os.replace(tmp, script)
+    warmup = max(args.warmup, 3)
+    B, T, total = args.micro_batch, args.seq_len, args.total_batch
+    if total % (B * T * world) != 0:
+        return say({"unavailable": f"total batch {total} is not a multiple of {B}x{T}x{world}"})
+    iters = warmup + args.steps
+    work = os.path.join(os.environ.get("TMPDIR", "/tmp"), f"llmk_reference_arm_{os.environ.get('MASTER_PORT', 'single')}")
+    shard = os.path.join(work, f"synthetic_uniform_{iters}_train_000000.bin")
+    _write_reference_shard(shard, min((iters + 1) * total + 1, 200_000_000))
+    env = dict(os.environ)
+    env["PYTHONPATH"] = os.path.join(REPO, "baseline", "offline")   # tiktoken stand-in only; not this package
+    env.setdefault("MASTER_ADDR", "127.0.0.1")
+
+    def run(compile_flag: int):
+        cmd = [sys.executable, "-u", script, "--input_bin", shard, "--val_loss_every", "0", "--sample_every", "0",
+               "--write_tensors", "0", "--model", "d12", "--batch_size", str(B), "--sequence_length", str(T),
+               "--total_batch_size", str(total), "--dtype", "bfloat16", "--compile", str(compile_flag), "--tensorcores", "1",
+               "--flash", "1", "--num_iterations", str(iters), "--weight_decay", "0.1", "--zero_stage", "1",
+               "--learning_rate", "0.0006", "--warmup_iters", "700", "--learning_rate_decay_frac", "0.0",
+               "--overfit_single_batch", "0"]
+        proc = subprocess.Popen(cmd, cwd=work, env=env, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
+        steps, tail = [], []
+        killer = threading.Timer(float(os.environ.get("LLMK_REFERENCE_TIMEOUT_S", "1500")), proc.kill)
+        killer.start()
+        try:
+            for line in proc.stdout:
+                tail.append(line.rstrip())
+                del tail[:-30]
+                m = REF_STEP_LINE.match(line.strip())
+                if m:
+                    steps.append((time.time(), int(m.group(1)), float(m.group(2)), float(m.group(3)), float(m.group(4))))
+            rc = proc.wait()
+        finally:
+            killer.cancel()
+        return rc, steps, tail, cmd
+
+    sampler = ClockSampler(int(os.environ.get("LOCAL_RANK", "0")))
+    if rank == 0:
+        sampler.start()
+    compiled = 1
+    rc, steps, tail, cmd = run(1)
+    if rc != 0 or len(steps) < iters:
+        first_failure = " | ".join(tail[-4:])[-600:]
+        compiled = 0
+        rc, steps, tail, cmd = run(0)
+    if rank == 0:
+        sampler.stop()
+    if rc != 0 or len(steps) < iters:
+        return say({"unavailable": f"train_gpt2.py exited {rc} after {len(steps)} of {iters} steps: " + " | ".join(tail[-4:])[-600:]})
+    timed = steps[warmup:]
+    ms = sum(s[4] for s in timed)
+    value = total * len(timed) / (ms / 1e3)
+    accum = total // (B * T * world)
+    out = {
+        "metric": "train tokens/sec (GPT-2 124M, device-timed, max over ranks)",
+        "value": round(value, 1), "unit": "tokens/s", "n_gpus": world, "steps": len(timed), "warmup": warmup,
+        "ms_per_step": round(ms / len(timed), 3), "higher_is_better": True, "scaling": "strong",
+        "vs_baseline": round(value / PUBLISHED_TOKENS_PER_S, 3) if world == 1 else None,
+        "vs_baseline_is": "this value / the reference's published 212,316 tokens/s on one RTX 5090 (other hardware)",
+        "dtype": "bf16 autocast (fp32 parameters, TF32 elsewhere)", "data": "synthetic", "same_config": True,
+        "config": {"model": "gpt2-124M (d12: L12 H12 C768 V50257 T1024)", "global_batch": total, "micro_batch": B,
+                   "seq_len": T, "grad_accum_steps": accum,
+                   "parallelism": f"dp{world}" + ("-zero1 (DDP + ZeroRedundancyOptimizer)" if world > 1 else ""),
+                   "optimizer": "torch AdamW (fused), clip 1.0, cosine lr 6e-4 warmup 700, wd 0.1",
+                   "torch_compile": bool(compiled), "command": " ".join(cmd[2:]).replace(REPO + os.sep, ""),
+                   "timing": "the trainer's own per-step wall clock (rank 0, after torch.cuda.synchronize()), summed over the timed steps",
+                   "offline": "tiktoken replaced by a stand-in module (the GPT-2 vocabulary cannot be downloaded); the tokenizer is not used in a step",
+                   "l2": "working set per step far exceeds the 126 MB L2"},
+        "clocks": sampler.summary(steps[warmup - 1][0], steps[-1][0]) if rank == 0 else {},
+        "e2e": {"value": round(value, 1), "unit": "tokens/s", "ms_per_step": round(ms / len(timed), 3),
+                "h2d_bytes_per_step": accum * world * 2 * B * T * 8, "d2h_bytes_per_step": 8,
+                "api": "python train_gpt2.py (stock recipe); its step copies int64 tokens/targets to the device and reads loss and norm back"},
+        "gpu_launches": None,
+        "loss_at_step": [s[2] for s in timed], "grad_norm_last": timed[-1][3],
+    }
+    if not compiled:
+        out["config"]["torch_compile_failed_with"] = first_failure
+    return say(out)
 
 
 class ClockSampler:
@@ -186,15 +310,26 @@ def main() -> int:
     if args.impl == "ours" and world == 1 and args.cuda_graph:
         trainer.enable_cuda_graph(True)   # captured during the warm-up steps (the first one runs eagerly)
 
-    # synthetic uniform tokens: a pool of pinned host batches (e2e) and device copies (device-timed)
-    gen = torch.Generator().manual_seed(1337 + rank)
-    pool = 8
-    host = [(torch.randint(0, config.vocab_size, (B, T), generator=gen, dtype=torch.int32).pin_memory(),
-             torch.randint(0, config.vocab_size, (B, T), generator=gen, dtype=torch.int32).pin_memory()) for _ in range(pool)]
-    dev = [(x.to(device), y.to(device)) for x, y in host]
+    # synthetic uniform tokens: ONE global stream from seed 1337, the same at every N. Step s consumes tokens
+    # [s*total, (s+1)*total]; its chunk c (B*T tokens, targets shifted by one) goes to rank c % N as micro-step
+    # c // N, as a strided data loader would deal it. No step repeats a batch, so the loss and norm trajectories
+    # of 1, 2, 4 and 8 GPUs are the same up to summation order.
+    total_steps = args.warmup + 2 * args.steps
+    gen = torch.Generator().manual_seed(1337)
+    stream = torch.randint(0, config.vocab_size, (total_steps * args.total_batch + 1,), generator=gen, dtype=torch.int32)
+    host, dev = [], []
+    for s_ in range(total_steps):
+        hs = []
+        for m_ in range(accum):
+            o = s_ * args.total_batch + (m_ * world + rank) * B * T
+            hs.append((stream[o:o + B * T].view(B, T).clone().pin_memory(), stream[o + 1:o + 1 + B * T].view(B, T).clone().pin_memory()))
+        host.append(hs)
+    # device-resident copies for the device-timed region only (steps warmup .. warmup+steps-1)
+    dev = {s_: [(x.to(device), y.to(device)) for x, y in host[s_]] for s_ in range(args.warmup, args.warmup + args.steps)}
+    del stream
 
     def batches(src, step):
-        return [src[(step * accum + i) % pool] for i in range(accum)]
+        return src[step]
 
     from llm_kittens_b200.utils.schedulers import LearningRateScheduler
 
@@ -228,10 +363,13 @@ def main() -> int:
         step_no[0] += 1
 
     last = {}
+    losses, norms = [], []
 
     def e2e_step(i):
         r = trainer.train_step(batches(host, step_no[0]), lr=sched.get(step_no[0]))
         last["loss"], last["norm"] = r.loss, r.grad_norm
+        losses.append(round(r.loss, 5))
+        norms.append(round(r.grad_norm, 4))
         step_no[0] += 1
 
     for i in range(args.warmup):
@@ -265,7 +403,9 @@ def main() -> int:
             else f"train tokens/sec ({args.model}, device-timed, max over ranks)",
             "value": round(value, 1), "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": round(ms_dev / args.steps, 3), "higher_is_better": True, "scaling": "strong",
-            "vs_baseline": round(value / PUBLISHED_TOKENS_PER_S, 3) if args.model == "d12" else None, "dtype": "bf16",
+            "vs_baseline": round(value / PUBLISHED_TOKENS_PER_S, 3) if (args.model == "d12" and world == 1) else None,
+            "vs_baseline_is": "this value / the reference's published 212,316 tokens/s on one RTX 5090 (other hardware; "
+                              "N=1 only)", "per_gpu_value": round(value / world, 1), "dtype": "bf16",
             "data": "synthetic",
             "impl": args.impl,
             "config": {"model": "gpt2-124M (d12: L12 H12 C768 V50257/50304 T1024)" if args.model == "d12"
@@ -277,12 +417,16 @@ def main() -> int:
                        "comm": type(comm).__name__, "recompute": args.recompute,
                        "cuda_graph": bool(getattr(trainer, "_graph", None) is not None),
                        "l2": "working set per step (~20 GB activations, 250 MB weights) far exceeds the 126 MB L2; no flush needed",
-                       "weights": "random init N(0,0.02), seed 42"},
+                       "weights": "random init N(0,0.02), seed 42",
+                       "tokens": "one global uniform stream from seed 1337, dealt to ranks chunk by chunk; no batch repeats"},
             "clocks": clocks,
             "e2e": {"value": round(e2e_value, 1), "unit": "tokens/s", "ms_per_step": round(ms_e2e / args.steps, 3),
                     "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "api": "Trainer.train_step(pinned host batches)"},
             "gpu_launches": int(launches),
             "loss_first_warmup": first_loss, "loss_last": last.get("loss"), "grad_norm_last": last.get("norm"),
+            "loss_at_step": {"steps": f"0..{args.warmup - 1} (warm-up) and {args.warmup + args.steps}..{total_steps - 1} "
+                                      f"(end-to-end region; steps {args.warmup}..{args.warmup + args.steps - 1} are the "
+                                      "device-timed region, which reads nothing back)", "loss": losses, "grad_norm": norms},
         }
         print(json.dumps(out))
     if world > 1:
