@@ -286,6 +286,7 @@ def train(args: TrainArgs, trainer_name: str) -> int:
                 (args.skip_update_gradz != 0.0 and zgrad == zgrad and zgrad > args.skip_update_gradz)
             if skip:
                 printf0(rank, f"skipping update: loss z-score {zloss:.2f}, grad-norm z-score {zgrad:.2f}")
+                trainer.skip_update()
             else:
                 trainer.apply_update(lr)
         else:

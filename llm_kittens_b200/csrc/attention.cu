@@ -501,13 +501,12 @@ attn_bwd_dq_kernel(bf16* __restrict__ dqkv, const bf16* __restrict__ qkv, const 
 
 template <int HS>
 static int configure() {
-    static bool done = false;
-    if (!done) {
+    static PerDeviceOnce once_done;
+    if (once_done.first()) {
         LLMK_CUDA_TRY(cudaFuncSetAttribute(attn_fwd_kernel<HS>, cudaFuncAttributeMaxDynamicSharedMemorySize, 5 * 64 * HS * 2));
         LLMK_CUDA_TRY(cudaFuncSetAttribute(attn_bwd_dkv_kernel<HS>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                            6 * 64 * HS * 2 + 1024));
         LLMK_CUDA_TRY(cudaFuncSetAttribute(attn_bwd_dq_kernel<HS>, cudaFuncAttributeMaxDynamicSharedMemorySize, 6 * 64 * HS * 2));
-        done = true;
     }
     return LLMK_OK;
 }

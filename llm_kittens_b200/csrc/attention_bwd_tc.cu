@@ -871,15 +871,14 @@ template <int HS>
 static int launch(const void* qkv, const void* dout, bf16* dqkv, const float* lse, const float* dvec, int B, int T, int NH, int NKVH,
                   int* status, cudaStream_t stream) {
     constexpr int BN = Inner<HS>::BN;
-    static bool configured = false;
-    if (!configured) {
+    static PerDeviceOnce once_configured;
+    if (once_configured.first()) {
         LLMK_CUDA_TRY(cudaFuncSetAttribute(attn_bwd_dkv_tc_kernel<HS>, cudaFuncAttributeMaxDynamicSharedMemorySize, DkvCfg<HS>::SMEM_BYTES));
         LLMK_CUDA_TRY(cudaFuncSetAttribute(attn_bwd_dq_tc_kernel<HS>, cudaFuncAttributeMaxDynamicSharedMemorySize, DqCfg<HS>::SMEM_BYTES));
         LLMK_CUDA_TRY(cudaFuncSetAttribute(attn_bwd_dkv_tc_kernel<HS>, cudaFuncAttributePreferredSharedMemoryCarveout,
                                            cudaSharedmemCarveoutMaxShared));
         LLMK_CUDA_TRY(cudaFuncSetAttribute(attn_bwd_dq_tc_kernel<HS>, cudaFuncAttributePreferredSharedMemoryCarveout,
                                            cudaSharedmemCarveoutMaxShared));
-        configured = true;
     }
     const uint64_t width = (uint64_t)(NH + 2 * NKVH) * HS, rows = (uint64_t)B * T, cw = (uint64_t)NH * HS;
     CUtensorMap tq, tq_in, tdo, tdo_in, tdqkv;
@@ -897,10 +896,9 @@ static int launch(const void* qkv, const void* dout, bf16* dqkv, const float* ls
     const bool long_loops = (T / 64) * (NH / NKVH) >= 64;
     const bool use_v2 = dkv_env != nullptr ? dkv_env[0] == '2' : long_loops;
     if (HS == 64 && use_v2) {
-        static bool configured2 = false;
-        if (!configured2) {
+        static PerDeviceOnce once_configured2;
+        if (once_configured2.first()) {
             LLMK_CUDA_TRY(cudaFuncSetAttribute(dkv2::attn_bwd_dkv2_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, dkv2::SMEM_BYTES));
-            configured2 = true;
         }
         // this kernel steps over the queries 64 at a time: its own load maps, whatever sub-tile the others use
         CUtensorMap tq_in64, tdo_in64;

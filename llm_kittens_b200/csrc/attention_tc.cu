@@ -370,12 +370,11 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQKV, bf16* __restrict__
 
 template <int HS>
 static int launch(const CUtensorMap& tm, bf16* out, float* lse, int B, int T, int NH, int NKVH, int* status, cudaStream_t stream) {
-    static bool configured = false;
-    if (!configured) {
+    static PerDeviceOnce once_configured;
+    if (once_configured.first()) {
         LLMK_CUDA_TRY(cudaFuncSetAttribute(attn_fwd_tc_kernel<HS>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<HS>::SMEM_BYTES));
         LLMK_CUDA_TRY(cudaFuncSetAttribute(attn_fwd_tc_kernel<HS>, cudaFuncAttributePreferredSharedMemoryCarveout,
                                            cudaSharedmemCarveoutMaxShared));
-        configured = true;
     }
     const float scale_log2 = 1.4426950408889634f / sqrtf((float)HS);
     dim3 grid(T / BQ, NH, B);
@@ -666,10 +665,9 @@ attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_con
 
 static int launch(const CUtensorMap& tm, const CUtensorMap& tm_out, float* lse, int B, int T, int NH, int NKVH, int* status,
                   cudaStream_t stream) {
-    static bool configured = false;
-    if (!configured) {
+    static PerDeviceOnce once_configured;
+    if (once_configured.first()) {
         LLMK_CUDA_TRY(cudaFuncSetAttribute(attn_fwd_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
-        configured = true;
     }
     const float scale_log2 = 1.4426950408889634f / sqrtf((float)HS);
     dim3 grid((T + 2 * BQ - 1) / (2 * BQ), NH, B);

@@ -245,11 +245,10 @@ LLMK_API int llmk_fused_classifier(void* logits, void* losses, const void* targe
     const int* tg = (const int*)targets;
     const int slot_bytes = (Vp * 2 + 127) & ~127;
     if (2 * slot_bytes <= 220 * 1024) {
-        static bool configured = false;
-        if (!configured) {
+        static PerDeviceOnce once_configured;
+        if (once_configured.first()) {
             LLMK_CUDA_TRY(cudaFuncSetAttribute(fused_classifier_smem_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024));
             LLMK_CUDA_TRY(cudaFuncSetAttribute(fused_classifier_smem_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024));
-            configured = true;
         }
         int sms = 0, dev = 0;
         LLMK_CUDA_TRY(cudaGetDevice(&dev));

@@ -216,6 +216,9 @@ adamw_push_kernel(Peers params, float* __restrict__ master, const float* __restr
     const size_t p_off = (size_t)seg[0], s_off = (size_t)seg[1], len = (size_t)seg[2];
     const float wd = (seg[3] & 1) ? a.wd : 0.f;
     const float gs = grad_scale_ptr ? grad_scale_ptr[0] : 1.0f;
+    // the clip kernel writes scale 0 only for a non-finite gradient norm (0 * inf would poison m, v and the
+    // weights): the step is skipped here, and every rank's parameter buffer keeps last step's values
+    if (grad_scale_ptr && gs == 0.f) return;
     const bf16* my_params = static_cast<const bf16*>(params.p[my_rank]);
     for (size_t i = ((size_t)blockIdx.x * TPB + threadIdx.x) * 8; i < len; i += (size_t)gridDim.x * TPB * 8) {
         float g[8], mm[8], vv[8], old[8], pn[8];

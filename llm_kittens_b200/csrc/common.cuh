@@ -53,6 +53,31 @@ int* current_status_word();   // device pointer registered with llmk_set_status_
 
 static inline int ceil_div(long a, long b) { return (int)((a + b - 1) / b); }
 
+// Function attributes (opt-in shared memory, carve-out) and device properties belong to a DEVICE, while a
+// launcher's `static` lives once per process: a process that drives several GPUs has to configure each of
+// them. `first()` is true once per device (the device current at the call), so the usual
+// `static PerDeviceOnce once; if (once.first()) { cudaFuncSetAttribute(...); }` configures every device it meets.
+constexpr int LLMK_MAX_DEVICES = 64;
+struct PerDeviceOnce {
+    bool done[LLMK_MAX_DEVICES] = {};
+    bool first() {
+        int dev = 0;
+        if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= LLMK_MAX_DEVICES) return true;   // unknown: configure again
+        if (done[dev]) return false;
+        done[dev] = true;
+        return true;
+    }
+};
+
+// multiprocessor count of the current device (cached per device)
+static inline int sm_count_current_device() {
+    static int sms[LLMK_MAX_DEVICES] = {};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= LLMK_MAX_DEVICES) return 0;
+    if (sms[dev] == 0 && cudaDeviceGetAttribute(&sms[dev], cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) sms[dev] = 0;
+    return sms[dev];
+}
+
 // ---- 128-bit packed access -------------------------------------------------------------------
 struct alignas(16) bf16x8 {
     __nv_bfloat162 v[4];

@@ -553,25 +553,20 @@ int make_tmap_2d(CUtensorMap* m, const void* ptr, uint64_t inner, uint64_t outer
     return r == CUDA_SUCCESS ? LLMK_OK : LLMK_ERR_TMAP;
 }
 
-static int g_num_sms = 0;
-
-static int g_pair_clusters = -1;   // how many CTA pairs can be resident at once (0: pairs unavailable)
+static int query_pair_clusters();
 
 template <int MODE, int EPI>
 static int launch(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmC, const CUtensorMap& tmX,
                   const Params& p, int max_ctas, cudaStream_t stream) {
-    if (g_num_sms == 0) {
-        int dev = 0;
-        LLMK_CUDA_TRY(cudaGetDevice(&dev));
-        LLMK_CUDA_TRY(cudaDeviceGetAttribute(&g_num_sms, cudaDevAttrMultiProcessorCount, dev));
-    }
+    const int g_num_sms = sm_count_current_device();
+    if (g_num_sms <= 0) return LLMK_ERR_CUDA;
+    const int g_pair_clusters = p.pair ? query_pair_clusters() : 0;
     const int units = p.tiles_m * p.tiles_n * p.splits;
     if (p.pair) {
         constexpr int SMEM_BYTES = Cfg<EPI, true>::SMEM_BYTES;
-        static bool configured = false;
-        if (!configured) {
+        static PerDeviceOnce once_configured;
+        if (once_configured.first()) {
             LLMK_CUDA_TRY(cudaFuncSetAttribute(gemm_kernel<MODE, EPI, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
-            configured = true;
         }
         int clusters = units < g_pair_clusters ? units : g_pair_clusters;
         if (max_ctas > 0 && clusters > max_ctas / 2) clusters = max_ctas / 2 > 0 ? max_ctas / 2 : 1;
@@ -591,10 +586,9 @@ static int launch(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensor
         return LLMK_OK;
     }
     constexpr int SMEM_BYTES = Cfg<EPI, false>::SMEM_BYTES;
-    static bool configured = false;
-    if (!configured) {
+    static PerDeviceOnce once_configured;
+    if (once_configured.first()) {
         LLMK_CUDA_TRY(cudaFuncSetAttribute(gemm_kernel<MODE, EPI, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
-        configured = true;
     }
     int grid = units < g_num_sms ? units : g_num_sms;
     if (max_ctas > 0 && grid > max_ctas) grid = max_ctas;
@@ -603,9 +597,16 @@ static int launch(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensor
     return LLMK_OK;
 }
 
-// Number of resident CTA pairs for the pair kernel (queried once; 0 disables the pair path).
+// Number of resident CTA pairs for the pair kernel on the current device (queried once per device; 0 disables
+// the pair path).
 static int query_pair_clusters() {
-    if (g_pair_clusters >= 0) return g_pair_clusters;
+    static int cached[LLMK_MAX_DEVICES];
+    static bool known[LLMK_MAX_DEVICES] = {};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= LLMK_MAX_DEVICES) return 0;
+    if (known[dev]) return cached[dev];
+    known[dev] = true;
+    int& g_pair_clusters = cached[dev];
     g_pair_clusters = 0;
     const char* env = getenv("LLMK_GEMM_PAIR");
     if (env != nullptr && env[0] == '0') return 0;
@@ -686,11 +687,8 @@ static int gemm_impl(int mode, int epi, const void* A, const void* B, void* C, v
     if ((N % 8) || (K % 8 && mode != MODE_TN) || (mode == MODE_TN && (M % 8))) return LLMK_ERR_SHAPE;
     if ((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(B) | reinterpret_cast<uintptr_t>(C)) & 15)
         return LLMK_ERR_SHAPE;
-    if (g_num_sms == 0) {
-        int dev = 0;
-        LLMK_CUDA_TRY(cudaGetDevice(&dev));
-        LLMK_CUDA_TRY(cudaDeviceGetAttribute(&g_num_sms, cudaDevAttrMultiProcessorCount, dev));
-    }
+    const int g_num_sms = sm_count_current_device();
+    if (g_num_sms <= 0) return LLMK_ERR_CUDA;
     Params p;
     p.M = M; p.N = N; p.K = K;
     const int pair_clusters = query_pair_clusters();

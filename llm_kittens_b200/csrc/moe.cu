@@ -316,10 +316,9 @@ LLMK_API int llmk_moe_router_fwd(void* probs, void* top_idx, void* top_w, const 
                                  void* stream) {
     if (E > MAXE || K > MAXK || K > E || C % 8 || (long)E * C * 2 > 200 * 1024) return LLMK_ERR_SHAPE;
     const int smem = E * C * 2;
-    static bool configured = false;
-    if (!configured) {
+    static PerDeviceOnce once_configured;
+    if (once_configured.first()) {
         LLMK_CUDA_TRY(cudaFuncSetAttribute(router_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
-        configured = true;
     }
     router_fwd_kernel<<<ceil_div(N, 8), 256, smem, (cudaStream_t)stream>>>((float*)probs, (int*)top_idx, (float*)top_w,
                                                                           (const bf16*)x, (const bf16*)wr, N, C, E, K);

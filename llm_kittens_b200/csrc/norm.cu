@@ -631,11 +631,10 @@ static int launch_fwd(bf16* normed, float* mean, float* rstd, bf16* residual, co
 #undef LLMK_NORM_FWD_CASE
     }
     const int smem = FWD_WARPS * C * 2;
-    static bool configured = false;
-    if (!configured) {
+    static PerDeviceOnce once_configured;
+    if (once_configured.first()) {
         LLMK_CUDA_TRY(cudaFuncSetAttribute(norm_fwd_kernel<RMS, FUSED>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                            FWD_WARPS * 16384 * 2));
-        configured = true;
     }
     int grid = ceil_div(N, FWD_WARPS);
     const int cap = num_sms() * 32;
@@ -699,10 +698,9 @@ static int launch_bwd_reg(bf16* dinp, bf16* dweight, bf16* dbias, float* scratch
     if constexpr (NVEC <= 5) {
         using B = BulkCfg<NVEC>;
         static_assert(B::OFF_BAR >= B::WARPS * 2 * C * 4, "the rings must be able to hold the final reduction buffer");
-        static bool bulk_configured = false;
-        if (!bulk_configured) {
+        static PerDeviceOnce once_bulk_configured;
+        if (once_bulk_configured.first()) {
             LLMK_CUDA_TRY(cudaFuncSetAttribute(norm_bwd_bulk_kernel<RMS, NVEC>, cudaFuncAttributeMaxDynamicSharedMemorySize, B::SMEM));
-            bulk_configured = true;
         }
         int grid = num_sms();
         const int need = ceil_div(N, B::WARPS);
@@ -715,10 +713,9 @@ static int launch_bwd_reg(bf16* dinp, bf16* dweight, bf16* dbias, float* scratch
         return LLMK_OK;
     }
     constexpr int SMEM = REG_WARPS * (RMS ? 1 : 2) * C * 4;
-    static bool configured = false;
-    if (!configured) {
+    static PerDeviceOnce once_configured;
+    if (once_configured.first()) {
         LLMK_CUDA_TRY(cudaFuncSetAttribute(norm_bwd_reg_kernel<RMS, NVEC>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM));
-        configured = true;
     }
     int grid = num_sms() * 2;
     const int need = ceil_div(N, REG_WARPS);
@@ -769,11 +766,10 @@ int layernorm_bwd_impl(bf16* dinp, bf16* dweight, bf16* dbias, float* scratch, c
         case 5: return launch_bwd_reg<false, 5>(dinp, dweight, dbias, scratch, dout, inp, weight, mean, rstd, N, accumulate_dinp, stream);
         default: break;
     }
-    static bool configured = false;
-    if (!configured) {
+    static PerDeviceOnce once_configured;
+    if (once_configured.first()) {
         LLMK_CUDA_TRY(cudaFuncSetAttribute(norm_bwd_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                            BWD_WARPS * 2 * 6144 * 4));
-        configured = true;
     }
     const int smem = BWD_WARPS * 2 * C * 4;
     if (smem > BWD_WARPS * 2 * 6144 * 4) return LLMK_ERR_SHAPE;
@@ -829,11 +825,10 @@ LLMK_API int llmk_rmsnorm_bwd(void* dinp, void* dweight, void* scratch, const vo
         default: break;
     }
 #undef LLMK_RMS_BWD_CASE
-    static bool configured = false;
-    if (!configured) {
+    static PerDeviceOnce once_configured;
+    if (once_configured.first()) {
         LLMK_CUDA_TRY(cudaFuncSetAttribute(norm_bwd_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                            BWD_WARPS * 12288 * 4));
-        configured = true;
     }
     const int smem = BWD_WARPS * C * 4;
     const int grid = llmk_norm_bwd_blocks(N, C);

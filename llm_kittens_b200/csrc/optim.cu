@@ -68,7 +68,7 @@ __global__ void sum_partials_kernel(float* __restrict__ out, const float* __rest
 }
 
 // scale_out[0] = min(1, clip / sqrt(norm2)) ; norm_out[0] = sqrt(norm2). A non-finite norm gives scale 0
-// and raises flag_out[0] so the host can skip the step.
+// and raises flag_out[0]; the AdamW kernels skip their update when they read that zero.
 __global__ void clip_scale_kernel(float* scale_out, float* norm_out, int* flag_out, const float* norm2, float clip) {
     const float n2 = norm2[0];
     const float n = sqrtf(n2);
@@ -96,6 +96,9 @@ adamw_kernel(bf16* __restrict__ params, float* __restrict__ master, const G* __r
     const size_t p_off = (size_t)seg[0], g_off = (size_t)seg[1], s_off = (size_t)seg[2], len = (size_t)seg[3];
     const float wd = (seg[4] & 1) ? a.wd : 0.f;
     const float gs = grad_scale_ptr ? grad_scale_ptr[0] * grad_scale_host : grad_scale_host;
+    // the clip kernel writes scale 0 only for a non-finite gradient norm (0 * inf would poison m, v and the
+    // weights): such a step leaves the optimizer state and the parameters as they are
+    if (grad_scale_ptr && grad_scale_ptr[0] == 0.f) return;
     const float inv_b1c = 1.0f / a.beta1_corr, inv_b2c = 1.0f / a.beta2_corr;
     // four elements per thread and iteration: 8-byte bf16 and 16-byte fp32 accesses
     for (size_t i = ((size_t)blockIdx.x * TPB + threadIdx.x) * 4; i < len; i += (size_t)gridDim.x * TPB * 4) {

@@ -139,6 +139,12 @@ class FusedComm:
                int(seed) & 0xFFFFFFFF, self.world_size, self.rank)
         N.call("llmk_comm_signal", self.ctrl_ptrs, self.slot_params, self.rank, self.world_size, self.epoch)
 
+    def skip_update(self) -> None:
+        """A step whose update is skipped still has to tell the peers that this rank is done with the step: the
+        "parameters ready" flag is what the next ``begin_step`` of every rank waits for before it zeroes the
+        gradients that peers read. Queued after ``norm_and_clip``, it is ordered after every rank's gradient reads."""
+        N.call("llmk_comm_signal", self.ctrl_ptrs, self.slot_params, self.rank, self.world_size, self.epoch)
+
     # ------------------------------------------------------------------ library-style helpers
     def all_reduce_scalar(self, t: torch.Tensor, op: str = "sum") -> None:
         dist.all_reduce(t, op=dist.ReduceOp.SUM, group=self.group)

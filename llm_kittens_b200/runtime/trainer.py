@@ -126,6 +126,8 @@ class Trainer:
             optim.adamw(self.model.params, self.master, self.model.grads, self.m, self.v, self.segs, self.max_len, lr,
                         self.beta1, self.beta2, t, self.eps, self.wd, grad_scale_ptr=self.scale, seed=seed)
             return
+        if int(self.flag[0]) != 0:
+            return   # non-finite gradient norm: same as the kernels, state and parameters stay as they are
         b1c, b2c = 1.0 - self.beta1 ** t, 1.0 - self.beta2 ** t
         gs = self.scale[0]
         P, G = self.model.params, self.model.grads
@@ -235,6 +237,13 @@ class Trainer:
         if not skip:
             self.apply_update(lr)
 
+    def skip_update(self) -> None:
+        """The caller decided to leave the optimizer out of this step (after ``update(skip=True)``): tell the
+        communication path, whose peers otherwise wait for this rank's parameter push."""
+        hook = getattr(self.comm, "skip_update", None)
+        if hook is not None:
+            hook()
+
     def apply_update(self, lr: float | None = None) -> None:
         with nvtx_range("optimizer_update_and_gather"):
             self._apply_update(lr)
@@ -282,7 +291,8 @@ class Trainer:
         self.accumulate(micro_batches)
         self.update(lr)
         loss, norm, bad = self.read_scalars()
-        return StepResult(loss=loss, grad_norm=norm, lr=lr, skipped=False)
+        # a non-finite gradient norm makes the AdamW kernels leave state and parameters untouched
+        return StepResult(loss=loss, grad_norm=norm, lr=lr, skipped=bad)
 
     # ------------------------------------------------------------------ evaluation
     @torch.no_grad()

@@ -27,8 +27,11 @@ class DataLoader:
     def __init__(self, pattern: str, B: int, T: int, process_rank: int = 0, num_processes: int = 1, should_shuffle: bool = False,
                  ring: int = 2):
         """``ring``: number of pinned batch buffers that are cycled through. A batch handed out stays
-        untouched for the next ``ring - 1`` calls, so asynchronous host-to-device copies of up to that
-        many batches may be in flight (use ``grad_accum_steps + 1`` when a step ends with a sync)."""
+        untouched for the next ``ring - 1`` calls. Its consumer copies it to the device asynchronously, so
+        before a buffer is refilled the loader waits for a CUDA event that it recorded (on the stream current
+        at that time) when the consumer came back for the following batch, i.e. after that copy had been
+        queued: a loop that queues work faster than the GPU runs it is held back to ``ring - 1`` batches
+        ahead instead of overwriting tokens that have not been copied yet."""
         self.B, self.T = B, T
         self._lib = hostlib.lib()
         self._h = self._lib.llmk_loader_create(pattern.encode(), B, T, process_rank, num_processes, int(should_shuffle))
@@ -37,6 +40,8 @@ class DataLoader:
         self.should_shuffle = should_shuffle
         self._ring = [(_pinned((B, T), torch.int32), _pinned((B, T), torch.int32)) for _ in range(max(1, ring))]
         self._slot = 0
+        self._events = [None] * len(self._ring)
+        self._cuda = torch.cuda.is_available() and self._ring[0][0].is_pinned()
         self.inputs, self.targets = self._ring[0]
         self.num_tokens = int(self._lib.llmk_loader_num_tokens(self._h))
 
@@ -49,7 +54,14 @@ class DataLoader:
 
     def next_batch(self):
         """Advance to the next batch; returns the (pinned, recycled) ``inputs`` and ``targets`` tensors."""
+        if self._cuda:
+            # everything queued so far includes the upload of the batch handed out last
+            ev = self._events[self._slot] or torch.cuda.Event()
+            ev.record()
+            self._events[self._slot] = ev
         self._slot = (self._slot + 1) % len(self._ring)
+        if self._events[self._slot] is not None:
+            self._events[self._slot].synchronize()
         self.inputs, self.targets = self._ring[self._slot]
         if self._lib.llmk_loader_next(self._h, self.inputs.data_ptr(), self.targets.data_ptr()) != 0:
             raise hostlib.HostError(hostlib.last_error())

@@ -10,7 +10,8 @@ modes:
   gpu_moe_library1 / gpu_moe_fused   mixture-of-experts model, experts split over the ranks (peer-memory
                    dispatch / combine), dense parameters ZeRO-1 through library / fused communication
   cpu_fail_rank1   gloo; rank 1 raises before its first collective (failure-detection test)
-environment: LLMK_TEST_LAYERS (dense model depth, default 2), LLMK_TEST_RECOMPUTE (default 0)
+environment: LLMK_TEST_LAYERS (dense model depth, default 2), LLMK_TEST_RECOMPUTE (default 0),
+LLMK_TEST_SKIP_STEP (index of a step whose optimizer update is left out, as the z-score guards of the trainer do)
 Each rank writes ``rank<r>.pt`` with its per-step losses / norms and a parameter checksum sample.
 """
 import datetime
@@ -128,9 +129,19 @@ def main():
             wd.enter_step(step_index)
         xs, ys = x[rank * B:(rank + 1) * B].contiguous(), y[rank * B:(rank + 1) * B].contiguous()
         if mode.startswith("gpu_sharded"):
-            r = trainer.train_step([(xs[:1].contiguous(), ys[:1].contiguous()), (xs[1:].contiguous(), ys[1:].contiguous())])
+            micro = [(xs[:1].contiguous(), ys[:1].contiguous()), (xs[1:].contiguous(), ys[1:].contiguous())]
         else:
-            r = trainer.train_step([(xs, ys)])
+            micro = [(xs, ys)]
+        if step_index == int(os.environ.get("LLMK_TEST_SKIP_STEP", "-1")):
+            from llm_kittens_b200.runtime.trainer import StepResult
+
+            trainer.accumulate(micro)
+            trainer.update(1e-3, skip=True)
+            loss, norm, _ = trainer.read_scalars()
+            trainer.skip_update()
+            r = StepResult(loss=loss, grad_norm=norm, lr=1e-3, skipped=True)
+        else:
+            r = trainer.train_step(micro)
         losses.append(r.loss)
         norms.append(r.grad_norm)
     if not cpu:

@@ -40,7 +40,7 @@ def launch(mode, out_dir, world=2, extra_env=None, timeout=300):
     return outs
 
 
-def single_process_reference(steps=4):
+def single_process_reference(steps=4, skip_step=-1):
     sys.path.insert(0, HERE)
     from dist_worker import global_batches, tiny_config
     from llm_kittens_b200.oracle.torch_model import TorchTransformer
@@ -51,9 +51,16 @@ def single_process_reference(steps=4):
     model.init_weights(42)
     tr = Trainer(model, learning_rate=1e-3, weight_decay=0.1)
     losses = []
-    for x, y in global_batches(cfg, steps, 2, 2, 64):
+    for i, (x, y) in enumerate(global_batches(cfg, steps, 2, 2, 64)):
         # two micro-batches of the rank-local size == the data-parallel average over two ranks
-        losses.append(tr.train_step([(x[:2], y[:2]), (x[2:], y[2:])]).loss)
+        micro = [(x[:2], y[:2]), (x[2:], y[2:])]
+        if i == skip_step:
+            tr.accumulate(micro)
+            tr.update(1e-3, skip=True)
+            losses.append(tr.read_scalars()[0])
+            tr.skip_update()
+        else:
+            losses.append(tr.train_step(micro).loss)
     return losses, model.params.clone()
 
 
@@ -70,6 +77,45 @@ def test_zero_stages_match_single_process(tmp_path, stage):
     assert r0["losses"] == r1["losses"] and r0["norms"] == r1["norms"]
     assert (r0["params"] - ref_params).abs().max().item() < 1e-5
     assert r0["losses"][-1] < r0["losses"][0]
+
+
+def test_skipped_update_keeps_ranks_in_step(tmp_path):
+    """Step 1 runs reduction, norm and clip but no optimizer update (what the z-score guards do): the next steps
+    must run and match one process that skips the same step."""
+    outs = launch("cpu_zero1", tmp_path, extra_env={"LLMK_TEST_SKIP_STEP": "1"})
+    for rc, out in outs:
+        assert rc == 0, out
+    ref_losses, ref_params = single_process_reference(skip_step=1)
+    r0, r1 = torch.load(tmp_path / "rank0.pt"), torch.load(tmp_path / "rank1.pt")
+    assert torch.equal(r0["params"], r1["params"])
+    for a, b in zip(r0["losses"], ref_losses):
+        assert abs(a - b) < 1e-4
+    assert (r0["params"] - ref_params).abs().max().item() < 1e-5
+
+
+def test_non_finite_gradient_leaves_weights_and_optimizer_state_alone():
+    """An inf in a gradient (injected on the host after backward) gives a non-finite norm: the update is skipped,
+    reported as skipped, and nothing becomes NaN."""
+    sys.path.insert(0, HERE)
+    from dist_worker import global_batches, tiny_config
+    from llm_kittens_b200.oracle.torch_model import TorchTransformer
+    from llm_kittens_b200.runtime.trainer import Trainer
+
+    cfg = tiny_config()
+    model = TorchTransformer(cfg, device="cpu", dtype=torch.float32)
+    model.init_weights(42)
+    tr = Trainer(model, learning_rate=1e-3, weight_decay=0.1)
+    (x, y), (x2, y2) = global_batches(cfg, 2, 1, 2, 64)
+    tr.train_step([(x, y)])
+    before, m_before = model.params.clone(), tr.m.clone()
+    tr.accumulate([(x2, y2)])
+    model.grads[5] = float("inf")
+    tr.update(1e-3)
+    loss, norm, bad = tr.read_scalars()
+    assert bad and not torch.isfinite(torch.tensor(norm))
+    assert torch.equal(model.params, before) and torch.equal(tr.m, m_before)
+    r = tr.train_step([(x2, y2)])
+    assert not r.skipped and r.loss == r.loss and torch.isfinite(model.params).all()
 
 
 def test_failed_rank_is_detected_by_the_survivor(tmp_path):

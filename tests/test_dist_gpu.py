@@ -41,6 +41,19 @@ def test_fused_comm_matches_library_and_zero0(tmp_path):
     assert f0["losses"][-1] < f0["losses"][0]
 
 
+def test_fused_comm_survives_a_skipped_update(tmp_path):
+    """A step without optimizer update (z-score guards) must still raise the "parameters ready" flag: the steps
+    after it run without a bounded wait running out (the worker checks the status word) and train like the library
+    path that skips the same step."""
+    _need_two_gpus()
+    f0, f1 = _run("gpu_fused", tmp_path, LLMK_TEST_SKIP_STEP="1")
+    l0, _ = _run("gpu_library1", tmp_path, LLMK_TEST_SKIP_STEP="1")
+    assert torch.equal(f0["params"], f1["params"])
+    for a, b in zip(f0["losses"], l0["losses"]):
+        assert abs(a - b) < 0.02
+    assert (f0["params"] - l0["params"]).abs().max().item() < 0.02
+
+
 def test_expert_parallel_moe_matches_single_process(tmp_path):
     _need_two_gpus()
     from dist_worker import global_batches, tiny_moe_config

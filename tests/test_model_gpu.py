@@ -235,3 +235,61 @@ def test_cuda_graph_micro_step_matches_eager():
         results.append((losses, model.params.clone()))
     assert results[0][0] == results[1][0]
     assert torch.equal(results[0][1], results[1][1])
+
+
+def test_validation_loop_without_syncs_reads_every_batch_intact(tmp_path):
+    """A loop that queues forwards faster than the GPU runs them (d12-size model, two pinned ring slots, no sync
+    between batches) must see the same tokens as a loop that syncs after every batch: the loader may not refill a
+    pinned buffer whose upload has not run yet."""
+    from llm_kittens_b200.data import prepare
+    from llm_kittens_b200.models.config import config_from_descriptor
+    from llm_kittens_b200.models.transformer import Transformer
+    from llm_kittens_b200.utils.dataloader import DataLoader
+
+    B, T, nb = 16, 1024, 8
+    prepare.prepare_synthetic(str(tmp_path / "data"), 200_000, vocab_size=50257, seed=5)
+    pattern = str(tmp_path / "data" / "synthetic_train_*.bin")
+    cfg = config_from_descriptor("d12")
+    model = Transformer(cfg, device="cuda", recompute=0)
+    model.init_weights(42)
+
+    def run(sync_every_batch):
+        loader = DataLoader(pattern, B, T, 0, 1, should_shuffle=False, ring=2)
+        per_batch = torch.zeros(nb, device="cuda")
+        for i in range(nb):
+            x, y = loader.next_batch()
+            model.forward(x, y, compute_dlogits=False)
+            per_batch[i:i + 1].copy_(model.acts["loss_acc"])
+            if sync_every_batch:
+                torch.cuda.synchronize()
+        torch.cuda.synchronize()
+        loader.close()
+        return per_batch.cpu()
+
+    safe = run(True)
+    fast = run(False)
+    assert torch.equal(safe, fast), (safe, fast)
+    assert len(set(safe.tolist())) == nb    # the batches differ, so a duplicated batch would have shown
+
+
+def test_non_finite_gradient_skips_the_update_on_the_gpu():
+    """An inf written into a gradient on the host side of the step: the AdamW kernel reads the zero clip scale and
+    leaves master weights, moments and parameters as they were; the step is reported as skipped."""
+    from llm_kittens_b200.models.transformer import Transformer
+    from llm_kittens_b200.runtime.trainer import Trainer
+
+    cfg = small_gpt2()
+    model = Transformer(cfg, device="cuda", recompute=0)
+    model.init_weights(42)
+    tr = Trainer(model, learning_rate=1e-3, weight_decay=0.1)
+    x, y = batch(cfg, 4, 128)
+    tr.train_step([(x.cuda(), y.cuda())])
+    before, m_before, master_before = model.params.clone(), tr.m.clone(), tr.master.clone()
+    tr.accumulate([(x.cuda(), y.cuda())])
+    model.grads[7:8].fill_(float("inf"))
+    tr.update(1e-3)
+    loss, norm, bad = tr.read_scalars()
+    assert bad
+    assert torch.equal(model.params, before) and torch.equal(tr.m, m_before) and torch.equal(tr.master, master_before)
+    r = tr.train_step([(x.cuda(), y.cuda())])
+    assert not r.skipped and torch.isfinite(model.params.float()).all()
