@@ -892,7 +892,7 @@ static int launch(const void* qkv, const void* dout, bf16* dqkv, const float* ls
     // The pipelined kernel has no second CTA on its SM to hide its prologue and epilogue behind, so it only pays off
     // when a CTA loops over many sub-tiles (long sequences, grouped queries): measured 1.08 vs 1.12 ms at T=2048 with
     // 4 query heads per KV head, but 1.00 vs 0.90 ms at T=1024 with one. LLMK_ATTN_BWD_DKV=1|2 forces a version.
-    static const char* dkv_env = getenv("LLMK_ATTN_BWD_DKV");
+    const char* dkv_env = getenv("LLMK_ATTN_BWD_DKV");   // read on every call, so that one process can run both versions
     const bool long_loops = (T / 64) * (NH / NKVH) >= 64;
     const bool use_v2 = dkv_env != nullptr ? dkv_env[0] == '2' : long_loops;
     if (HS == 64 && use_v2) {

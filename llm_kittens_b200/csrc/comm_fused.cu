@@ -12,10 +12,11 @@
 //                         them in rank order in fp32, scales by 1/P, stores the averaged shard as fp32
 //                         and leaves a per-block partial of its squared norm
 //                         = reduce-scatter + scale + norm partial in one pass, overlapped with backward.
-//   norm_exchange_kernel  sums the partials in fixed order, writes the local sum into every peer's
-//                         control buffer, waits for the peers' sums, adds them in rank order (so every
-//                         rank gets the same bits) and produces the clip coefficient on the device
-//                         = the scalar all-reduce, without a library call.
+//   norm_exchange_kernel  sums the partials in fixed order, writes the local sum (and this rank's mean
+//                         loss) into every peer's control buffer, waits for the peers' values, adds them in
+//                         rank order (so every rank gets the same bits) and produces the clip coefficient
+//                         and the global mean loss on the device = the scalar all-reduces of a step,
+//                         without a library call.
 //   adamw_push_kernel     AdamW (+ stochastic rounding, fp32 master) on the rank's fp32 averaged shard,
 //                         each updated bf16 value stored straight into the parameter buffer of EVERY
 //                         rank (P2P stores) = optimizer + all-gather in one pass.
@@ -152,7 +153,8 @@ rs_bucket_kernel(Peers grads, const int* my_ctrl, int slot, int epoch, const lon
 // One block. Sums `n` partials, exchanges the sum with the peers, clip coefficient on the device.
 __global__ void __launch_bounds__(1024)
 norm_exchange_kernel(Peers ctrl, const float* __restrict__ partials, int n, int norm_slot, int my_rank, int P, int epoch,
-                     float clip, float* scale_out, float* norm_out, int* flag_out, long long limit_ns, int* status) {
+                     float clip, float* scale_out, float* norm_out, int* flag_out, float* loss_inout, long long limit_ns,
+                     int* status) {
     __shared__ float sh[32];
     float s = 0.f;
     for (int i = threadIdx.x; i < n; i += blockDim.x) s += partials[i];
@@ -160,6 +162,7 @@ norm_exchange_kernel(Peers ctrl, const float* __restrict__ partials, int n, int 
     if ((int)threadIdx.x < P) {
         float* dst_val = reinterpret_cast<float*>(static_cast<int*>(ctrl.p[threadIdx.x]) + NORM_VAL_OFFSET) + my_rank;
         *reinterpret_cast<volatile float*>(dst_val) = s;
+        if (loss_inout != nullptr) *reinterpret_cast<volatile float*>(dst_val + MAXP) = loss_inout[0];
         __threadfence_system();
         st_release_sys(static_cast<int*>(ctrl.p[threadIdx.x]) + norm_slot * MAXP + my_rank, epoch);
     }
@@ -170,6 +173,11 @@ norm_exchange_kernel(Peers ctrl, const float* __restrict__ partials, int n, int 
         if (ok) {
             const float* vals = reinterpret_cast<const float*>(my_ctrl + NORM_VAL_OFFSET);
             for (int r = 0; r < P; r++) total += ld_volatile_f32(vals + r);
+            if (loss_inout != nullptr) {   // mean over ranks of the ranks' mean losses, summed in rank order
+                float loss = 0.f;
+                for (int r = 0; r < P; r++) loss += ld_volatile_f32(vals + MAXP + r);
+                loss_inout[0] = loss / (float)P;
+            }
         } else {
             total = NAN;
         }
@@ -198,6 +206,41 @@ ag_bucket_kernel(Peers shards, bf16* __restrict__ staging, const long long* __re
     for (size_t i = ((size_t)blockIdx.x * TPB + threadIdx.x) * 8; i < len; i += (size_t)gridDim.x * TPB * 8) {
         const uint4 v = ld_volatile_v4(src + i);
         *reinterpret_cast<uint4*>(dst + i) = v;
+    }
+}
+
+// The same gather with its progress published: segment table int64[nseg][5] = (shard offset, staging offset of the
+// full slice, shard length, first flag of the tensor, chunks per shard). Block (x, segment, source rank) copies chunk x
+// (length / chunks consecutive elements) of that rank's shard and then release-stores `tick` into
+// flags[first + rank * chunks + x], which is flag (element offset inside the tensor) / (chunk length). A GEMM that
+// consumes the tensor polls exactly the flags that cover a tile (llmk_gemm_b_ready), so it can start on the first
+// chunks while the others are still crossing NVLink. Four 128-bit peer loads are in flight per thread.
+__global__ void __launch_bounds__(TPB)
+ag_bucket_flags_kernel(Peers shards, bf16* __restrict__ staging, const long long* __restrict__ segs, int* __restrict__ flags,
+                       int tick) {
+    const long long* seg = segs + (size_t)blockIdx.y * 5;
+    const size_t s_off = (size_t)seg[0], d_off = (size_t)seg[1], len = (size_t)seg[2];
+    const int first = (int)seg[3], cps = (int)seg[4];
+    const int r = blockIdx.z, x = blockIdx.x;
+    if (x >= cps) return;
+    const size_t chunk = len / cps;
+    const bf16* src = static_cast<const bf16*>(shards.p[r]) + s_off + (size_t)x * chunk;
+    bf16* dst = staging + d_off + (size_t)r * len + (size_t)x * chunk;
+    constexpr size_t STEP = (size_t)TPB * 8;
+    size_t i = (size_t)threadIdx.x * 8;
+    for (; i + 3 * STEP < chunk; i += 4 * STEP) {
+        const uint4 v0 = ld_volatile_v4(src + i), v1 = ld_volatile_v4(src + i + STEP);
+        const uint4 v2 = ld_volatile_v4(src + i + 2 * STEP), v3 = ld_volatile_v4(src + i + 3 * STEP);
+        *reinterpret_cast<uint4*>(dst + i) = v0;
+        *reinterpret_cast<uint4*>(dst + i + STEP) = v1;
+        *reinterpret_cast<uint4*>(dst + i + 2 * STEP) = v2;
+        *reinterpret_cast<uint4*>(dst + i + 3 * STEP) = v3;
+    }
+    for (; i < chunk; i += STEP) *reinterpret_cast<uint4*>(dst + i) = ld_volatile_v4(src + i);
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        __threadfence();
+        asm volatile("st.release.gpu.global.s32 [%0], %1;" ::"l"(flags + first + r * cps + x), "r"(tick) : "memory");
     }
 }
 
@@ -317,13 +360,25 @@ LLMK_API int llmk_comm_ag_bucket(const long long* shard_ptrs, void* staging, con
     return LLMK_OK;
 }
 
+// Gather with per-chunk flags (see ag_bucket_flags_kernel). `max_cps` = the largest "chunks per shard" in the table;
+// every shard length must be a multiple of 8 * its chunk count.
+LLMK_API int llmk_comm_ag_bucket_flags(const long long* shard_ptrs, void* staging, const void* segs, int nseg, int max_cps, int P,
+                                       void* flags, int tick, void* stream) {
+    if (P > MAXP || nseg <= 0 || max_cps <= 0 || flags == nullptr) return LLMK_ERR_SHAPE;
+    ag_bucket_flags_kernel<<<dim3(max_cps, nseg, P), TPB, 0, (cudaStream_t)stream>>>(make_peers(shard_ptrs, P), (bf16*)staging,
+                                                                                   (const long long*)segs, (int*)flags, tick);
+    LLMK_LAUNCH_CHECK();
+    return LLMK_OK;
+}
+
 LLMK_API int llmk_comm_norm_exchange(const long long* ctrl_ptrs, const void* partials, int n, int norm_slot, int my_rank, int P,
-                                     int epoch, float clip, void* scale_out, void* norm_out, void* flag_out, long limit_ns,
-                                     int* status, void* stream) {
+                                     int epoch, float clip, void* scale_out, void* norm_out, void* flag_out, void* loss_inout,
+                                     long limit_ns, int* status, void* stream) {
+    // loss_inout (optional): in = this rank's mean loss of the step, out = the mean over the P ranks
     if (P > MAXP) return LLMK_ERR_SHAPE;
     norm_exchange_kernel<<<1, 1024, 0, (cudaStream_t)stream>>>(make_peers(ctrl_ptrs, P), (const float*)partials, n, norm_slot,
                                                               my_rank, P, epoch, clip, (float*)scale_out, (float*)norm_out,
-                                                              (int*)flag_out, (long long)limit_ns, status);
+                                                              (int*)flag_out, (float*)loss_inout, (long long)limit_ns, status);
     LLMK_LAUNCH_CHECK();
     return LLMK_OK;
 }

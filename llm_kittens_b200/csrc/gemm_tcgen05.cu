@@ -110,7 +110,56 @@ struct Params {
     const bf16* aux;   // [M,N] pre-GELU input (DGELU) or addend (ADD; may alias C)
     float* partial;    // [splits, M, N] fp32 (PARTIAL)
     int* status;
+    // Operand readiness (both optional). A kernel that fills an operand while this GEMM already runs (a parameter
+    // all-gather into a staging buffer, a token dispatch into an expert's rows) publishes its progress in device
+    // memory; the producer warp acquire-polls, with a time limit, what covers a tile before its first TMA load of it.
+    //   b_ready: one int per `b_chunk` consecutive ELEMENTS of B (row-major, as stored); ready when >= b_tick.
+    //   a_ready: one int per `a_rows` consecutive ROWS of A; ready when >= a_need (an arrival counter).
+    const int* b_ready;
+    const int* a_ready;
+    long long b_chunk;
+    int b_tick, a_rows, a_need;
+    long long ready_limit_ns;
 };
+
+__device__ __forceinline__ int ld_acquire_sys_s32(const int* ptr) {
+    int v;
+    asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(ptr) : "memory");
+    return v;
+}
+
+// One thread: wait until flags[f0..f1] >= need (f < 64 is remembered in `done`, so every flag is polled once per
+// CTA). On expiry: abort flag, LLMK_ST_TIMEOUT_PEER in the status word, false. The flags may be written by another
+// kernel of this GPU or by a peer GPU, hence the system-scope acquire; the fence afterwards orders the TMA (async
+// proxy) reads of the data behind the flag after the acquire.
+__device__ __forceinline__ bool ready_wait(const int* flags, long long f0, long long f1, int need, uint64_t& done,
+                                           long long limit_ns, volatile int* abort_flag, int* status, int tag) {
+    for (long long f = f0; f <= f1; f++) {
+        if (f < 64 && ((done >> f) & 1ull)) continue;
+        if (ld_acquire_sys_s32(flags + f) < need) {
+            const uint64_t t0 = ptx::globaltimer_ns();
+            uint32_t spins = 0;
+            while (ld_acquire_sys_s32(flags + f) < need) {
+                if ((++spins & 15u) == 0) {
+                    if (*abort_flag) return false;
+                    if ((long long)(ptx::globaltimer_ns() - t0) > limit_ns) {
+                        *abort_flag = 1;
+                        if (status != nullptr && atomicCAS(status, 0, LLMK_ST_TIMEOUT_PEER) == 0) {
+                            status[1] = tag;
+                            status[2] = (int)blockIdx.x;
+                            status[3] = (int)f;
+                        }
+                        return false;
+                    }
+                }
+                __nanosleep(100);
+            }
+        }
+        if (f < 64) done |= 1ull << f;
+    }
+    asm volatile("fence.proxy.async.global;" ::: "memory");
+    return true;
+}
 
 struct Work {
     int m0, n0, kb_begin, kb_end, split, g;
@@ -213,10 +262,41 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
             if (PAIR) ptx::tma_load_2d_pair(dst, tm, bar, x, y);   // the bytes are credited to the leader's barrier
             else ptx::tma_load_2d(dst, tm, bar, x, y);
         };
+        uint64_t b_done = 0, a_done = 0;
         for (int u = unit0; u < total_units && ok; u += unit_step) {
             const Work w = decode_unit(p, u);
             const int m_own = w.m0 + rank * BM, n_own = w.n0 + rank * BN_CTA;
+            if (p.a_ready != nullptr && MODE != MODE_TN) {
+                // rows [m_own, m_own + BM) of A must have arrived
+                bool fl = true;
+                if (lane == 0)
+                    fl = ready_wait(p.a_ready, m_own / p.a_rows, (min(m_own + BM, p.M) - 1) / p.a_rows, p.a_need, a_done,
+                                    p.ready_limit_ns, abort_flag, p.status, 7000);
+                if (!__shfl_sync(0xffffffffu, fl, 0)) { ok = false; break; }
+            }
+            if (p.b_ready != nullptr && MODE == MODE_NT && n_own < p.N) {
+                // NT: this CTA's rows [n_own, n_own + BN_CTA) of B, all of K
+                bool fl = true;
+                if (lane == 0) {
+                    const long long e0 = (long long)(n_own + w.g * p.N) * p.K;
+                    const long long e1 = (long long)(min(n_own + BN_CTA, p.N) + w.g * p.N) * p.K - 1;
+                    fl = ready_wait(p.b_ready, e0 / p.b_chunk, e1 / p.b_chunk, p.b_tick, b_done, p.ready_limit_ns, abort_flag,
+                                    p.status, 7100);
+                }
+                if (!__shfl_sync(0xffffffffu, fl, 0)) { ok = false; break; }
+            }
             for (int kb = w.kb_begin; kb < w.kb_end; kb++) {
+                if (p.b_ready != nullptr && MODE == MODE_NN) {
+                    // NN: rows [k0, k0 + 64) of B (the K dimension), whole rows
+                    bool fl = true;
+                    if (lane == 0) {
+                        const long long r0 = (long long)kb * BK + (long long)w.g * p.K;
+                        const long long r1 = min((long long)(kb + 1) * BK, (long long)p.K) + (long long)w.g * p.K;
+                        fl = ready_wait(p.b_ready, r0 * p.N / p.b_chunk, (r1 * p.N - 1) / p.b_chunk, p.b_tick, b_done,
+                                        p.ready_limit_ns, abort_flag, p.status, 7200);
+                    }
+                    if (!__shfl_sync(0xffffffffu, fl, 0)) { ok = false; break; }
+                }
                 ok = ptx::mbar_wait(&empty_bar[s], ph ^ 1, abort_flag, p.status, LLMK_ST_TIMEOUT_TMA_EMPTY, u);
                 if (!ok) break;
                 if (lane == 0) {
@@ -676,9 +756,17 @@ long llmk_gemm_workspace_bytes(int mode, int M, int N, int K, int num_sms) {
 // to C2, 4 multiply by GELU'(aux), 8 add aux). For mode TN, `epi` 8 means C += result and the
 // launcher may split K through `workspace`. All matrices are dense row-major bf16; K, N (and M for
 // TN) must be multiples of 8 so that every row starts on a 16-byte boundary.
+struct Ready {
+    const int* b_ready = nullptr;
+    const int* a_ready = nullptr;
+    long long b_chunk = 1;
+    int b_tick = 0, a_rows = 1, a_need = 0;
+    long long limit_ns = 0;
+};
+
 static int gemm_impl(int mode, int epi, const void* A, const void* B, void* C, void* C2, const void* bias, const void* aux,
                      int M_group, int N, int K, int groups, void* workspace, long workspace_bytes, int* status, int max_ctas,
-                     void* stream_) {
+                     void* stream_, const Ready& ready = Ready()) {
     cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
     if (M_group <= 0 || N <= 0 || K <= 0 || groups <= 0) return LLMK_ERR_SHAPE;
     if ((long)M_group * groups > 0x7fffffffL) return LLMK_ERR_SHAPE;
@@ -708,6 +796,11 @@ static int gemm_impl(int mode, int epi, const void* A, const void* B, void* C, v
     p.aux = static_cast<const bf16*>(aux);
     p.partial = nullptr;
     p.status = status;
+    p.b_ready = ready.b_ready; p.a_ready = ready.a_ready;
+    p.b_chunk = ready.b_chunk > 0 ? ready.b_chunk : 1;
+    p.b_tick = ready.b_tick; p.a_rows = ready.a_rows > 0 ? ready.a_rows : 1; p.a_need = ready.a_need;
+    p.ready_limit_ns = ready.limit_ns > 0 ? ready.limit_ns : (long long)LLMK_WAIT_LIMIT_NS;
+    if ((p.b_ready != nullptr || p.a_ready != nullptr) && mode == MODE_TN) return LLMK_ERR_SHAPE;
     bool split_accumulate = false;
     if (mode == MODE_TN && (epi == 0 || epi == EPI_ADD)) {
         const int workers = p.pair ? pair_clusters : g_num_sms;
@@ -776,6 +869,23 @@ LLMK_API int llmk_gemm(int mode, int epi, const void* A, const void* B, void* C,
                        const void* aux, int M, int N, int K, void* workspace, long workspace_bytes, int* status,
                        int max_ctas, void* stream_) {
     return gemm_impl(mode, epi, A, B, C, C2, bias, aux, M, N, K, 1, workspace, workspace_bytes, status, max_ctas, stream_);
+}
+
+// llmk_gemm whose B operand (a weight matrix, NT or NN) is still being filled by another kernel: `b_ready` holds one
+// int per `b_chunk` consecutive elements of B, written (release) with `b_tick` once those elements are in place. The
+// producer warp of every CTA acquire-polls the flags that cover a B tile before its first load of it, for at most
+// `limit_ns` nanoseconds (then LLMK_ST_TIMEOUT_PEER in the status word and the kernel returns). This is the consumer
+// half of the tile-granular parameter all-gather (job of llmc/zero.cuh:543-578 followed by matmul_forward).
+LLMK_API int llmk_gemm_b_ready(int mode, int epi, const void* A, const void* B, void* C, void* C2, const void* bias,
+                               const void* aux, int M, int N, int K, void* workspace, long workspace_bytes, int* status,
+                               int max_ctas, const void* b_ready, long b_chunk, int b_tick, long limit_ns, void* stream_) {
+    Ready r;
+    r.b_ready = static_cast<const int*>(b_ready);
+    r.b_chunk = b_chunk;
+    r.b_tick = b_tick;
+    r.limit_ns = limit_ns;
+    if (b_ready != nullptr && b_chunk <= 0) return LLMK_ERR_SHAPE;
+    return gemm_impl(mode, epi, A, B, C, C2, bias, aux, M, N, K, 1, workspace, workspace_bytes, status, max_ctas, stream_, r);
 }
 
 // `groups` independent problems of the same shape in ONE persistent launch (the experts of a mixture-of-experts

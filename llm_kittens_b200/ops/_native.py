@@ -104,11 +104,49 @@ def count_replayed(kernels: int) -> None:
     _LAUNCHES += kernels
 
 
+# ---- step ledger: device time of every library call inside a running step ------------------------------------
+_LEDGER: list | None = None
+
+
+def ledger_start() -> None:
+    """From now on every :func:`call` is bracketed by two CUDA events on its stream (no synchronisation)."""
+    global _LEDGER
+    _LEDGER = []
+
+
+def ledger_stop() -> dict[str, tuple[int, float]]:
+    """Synchronise and return {label: (calls, total milliseconds)}. GEMM calls are labelled by layout, epilogue and
+    shape, other entry points by name."""
+    global _LEDGER
+    rows, _LEDGER = _LEDGER or [], None
+    torch.cuda.synchronize()
+    out: dict[str, tuple[int, float]] = {}
+    for label, e0, e1 in rows:
+        n, ms = out.get(label, (0, 0.0))
+        out[label] = (n + 1, ms + e0.elapsed_time(e1))
+    return out
+
+
+def _ledger_label(name: str, args) -> str:
+    if name in ("llmk_gemm", "llmk_gemm_grouped"):
+        mode, epi = args[0], args[1]
+        M, Nn, K = args[8], args[9], args[10]
+        return f"{name[5:]} {('NT', 'NN', 'TN')[mode]} epi={epi} {M}x{Nn}x{K}"
+    return name[5:]
+
+
 def call(name: str, *args: Any) -> None:
     """Call ``int name(args..., void* stream)``; tensors become device pointers; raises on failure."""
     global _LAUNCHES
     fn = getattr(lib(), name)
-    rc = fn(*[_conv(a) for a in args], stream_handle())
+    if _LEDGER is not None:
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        rc = fn(*[_conv(a) for a in args], stream_handle())
+        e1.record()
+        _LEDGER.append((_ledger_label(name, args), e0, e1))
+    else:
+        rc = fn(*[_conv(a) for a in args], stream_handle())
     _LAUNCHES += _KERNELS_PER_CALL.get(name, 1)
     if rc != 0:
         detail = lib().llmk_last_error().decode() if rc == -1 else ""

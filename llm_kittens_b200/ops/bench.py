@@ -100,8 +100,82 @@ def bench_gemm(BT=65536):
         print(f"{name:28s} {M:6d} {Nn:6d} {K:6d} {t:8.3f} {tf:8.1f} {tf / tf_peak:6.2f} {t_ref:9.3f} {t_ref / t:6.2f}")
 
 
+def step_ledger(model_desc="d12", B=64, T=1024, total_batch=524288):
+    """Where one optimizer step of the headline configuration spends its device time: the step runs eagerly with
+    every library call between two CUDA events (no profiler), so each kernel is timed inside the step, at the
+    clocks the step really runs at. Printed beside the same step without events and replayed from a CUDA graph."""
+    import subprocess
+    import threading
+    import time
+
+    from ..models.config import config_from_descriptor
+    from ..models.transformer import Transformer
+    from ..runtime.trainer import Trainer
+
+    cfg = config_from_descriptor(model_desc)
+    model = Transformer(cfg, device=torch.device("cuda"), recompute=0)
+    model.init_weights(42)
+    tr = Trainer(model, learning_rate=6e-4, weight_decay=0.1)
+    accum = total_batch // (B * T)
+    g = torch.Generator().manual_seed(1337)
+    batches = [(torch.randint(0, cfg.vocab_size, (B, T), generator=g, dtype=torch.int32).cuda(),
+                torch.randint(0, cfg.vocab_size, (B, T), generator=g, dtype=torch.int32).cuda()) for _ in range(accum)]
+    clocks = []
+    smi = subprocess.Popen(["nvidia-smi", "--query-gpu=clocks.sm,power.draw", "--format=csv,noheader,nounits", "-lms", "200",
+                            "-i", str(torch.cuda.current_device())], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+    threading.Thread(target=lambda: [clocks.append((time.time(), ln)) for ln in smi.stdout], daemon=True).start()
+
+    def step():
+        tr.accumulate(batches)
+        tr.update(6e-4)
+
+    def timed(n):
+        torch.cuda.synchronize()
+        w0 = time.time()
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s.record()
+        for _ in range(n):
+            step()
+        e.record()
+        torch.cuda.synchronize()
+        return s.elapsed_time(e) / n, w0, time.time()
+
+    def median_clock(w0, w1):
+        v = [float(ln.split(",")[0]) for ts, ln in clocks if w0 <= ts <= w1 and ln.strip()]
+        return statistics.median(v) if v else float("nan")
+
+    for _ in range(3):
+        step()
+    eager_ms, w0, w1 = timed(3)
+    eager_clk = median_clock(w0, w1)
+    N.ledger_start()
+    led_ms, w0, w1 = timed(2)
+    rows = N.ledger_stop()
+    led_clk = median_clock(w0, w1)
+    tr.enable_cuda_graph(True)
+    for _ in range(2):
+        step()
+    graph_ms, w0, w1 = timed(3)
+    graph_clk = median_clock(w0, w1)
+    smi.terminate()
+    N.check_status()
+    print(f"# step ledger: {model_desc} B={B} T={T} total batch {total_batch} ({accum} micro-steps), 1 GPU")
+    print(f"step, eager launches: {eager_ms:8.2f} ms   (median SM clock {eager_clk:.0f} MHz)")
+    print(f"step, eager + events: {led_ms:8.2f} ms   (median SM clock {led_clk:.0f} MHz)")
+    print(f"step, CUDA graph    : {graph_ms:8.2f} ms   (median SM clock {graph_clk:.0f} MHz)")
+    total = sum(ms for _, ms in rows.values()) / 2
+    print(f"{'entry point / GEMM shape':52s} {'calls/step':>10s} {'ms/step':>9s} {'share':>6s} {'us/call':>8s}")
+    for label, (n, ms) in sorted(rows.items(), key=lambda kv: -kv[1][1]):
+        print(f"{label:52s} {n // 2:10d} {ms / 2:9.3f} {ms / 2 / total:6.1%} {1e3 * ms / n:8.1f}")
+    print(f"{'sum of the bracketed calls':52s} {'':10s} {total:9.3f}")
+    print(f"{'outside the brackets (gaps, torch ops, events)':52s} {'':10s} {led_ms - total:9.3f}")
+
+
 def main(argv):
     what = argv[1] if len(argv) > 1 else "all"
+    if what == "ledger":
+        step_ledger()
+        return
     if what in ("gemm", "all"):
         bench_gemm()
     if what in ("attention", "all"):

@@ -30,6 +30,24 @@ def workspace(nbytes: int) -> torch.Tensor:
     return N.scratch_buffer(_WORKSPACE, nbytes, 64 << 20, "split-K partials")
 
 
+# Weights that another kernel is still filling while GEMMs already run on them (the tile-granular parameter gather of
+# ZeRO-3, parallel/sharded.py): data pointer of the weight view -> [flags tensor, first flag, elements per flag, tick,
+# time limit in ns]. A GEMM whose B operand is registered here polls the flags that cover each tile (llmk_gemm_b_ready).
+_B_READY: dict[int, list] = {}
+
+
+def register_b_ready(weight: torch.Tensor, flags: torch.Tensor, first_flag: int, chunk_elems: int, limit_ns: int) -> list:
+    """Returns the registry entry; the owner of the gather sets ``entry[3]`` (the tick) before every gather and may set
+    it to 0 to switch the polling off (flags are compared with ``>=``)."""
+    entry = [flags[int(first_flag):], int(first_flag), int(chunk_elems), 0, int(limit_ns)]
+    _B_READY[weight.data_ptr()] = entry
+    return entry
+
+
+def unregister_b_ready(weight: torch.Tensor) -> None:
+    _B_READY.pop(weight.data_ptr(), None)
+
+
 _TILE_ROWS = 0
 
 
@@ -60,8 +78,13 @@ def _gemm(mode, epi, a, b, c, c2, bias, aux, M, Nn, K, groups=1):
         if ws_bytes:
             ws = workspace(ws_bytes)
             ws_bytes = ws.numel()
+    ready = _B_READY.get(b.data_ptr()) if (_B_READY and mode != MODE_TN) else None
     if groups > 1:
         N.call("llmk_gemm_grouped", mode, epi, a, b, c, c2, bias, aux, M, Nn, K, groups, ws, ws_bytes, N.status_word(), _MAX_CTAS)
+    elif ready is not None and ready[3] > 0:
+        flags, first, chunk, tick, limit_ns = ready
+        N.call("llmk_gemm_b_ready", mode, epi, a, b, c, c2, bias, aux, M, Nn, K, ws, ws_bytes, N.status_word(), _MAX_CTAS,
+               flags, chunk, tick, limit_ns)
     else:
         N.call("llmk_gemm", mode, epi, a, b, c, c2, bias, aux, M, Nn, K, ws, ws_bytes, N.status_word(), _MAX_CTAS)
     return c

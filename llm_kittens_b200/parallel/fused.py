@@ -29,6 +29,13 @@ from ..ops import _native as N
 from .zero import ZeroPlan
 
 
+def comm_grid_x(max_segment_elems: int) -> int:
+    """Blocks per segment of the bucket kernels (``rs_bucket``, ``ag_bucket``): one per 256 KiB of the longest
+    segment, at least 8 (enough for the 14 MB buckets of GPT-2 124M) and at most 64 (Llama-3 8B: 436 MB per block,
+    ~390 blocks of 256 threads with up to eight 16-byte peer loads in flight per thread)."""
+    return int(min(64, max(8, (max_segment_elems * 2) // (256 * 1024))))
+
+
 class FusedComm:
     fused = True
 
@@ -71,7 +78,7 @@ class FusedComm:
         self.stream = torch.cuda.Stream(device=device)
         self.gshard = torch.zeros(plan.state_elements, dtype=torch.float32, device=device)
         # per-bucket segment tables (gradient offset of my slice, state offset, length)
-        self.grid_x = 8
+        self.grid_x = comm_grid_x(max(s.length for s in plan.segments))
         self.buckets = {}
         base = 0
         by_key = {}
@@ -128,9 +135,12 @@ class FusedComm:
                    self.gshard, self.partials[self.expert_base:], self.grid_x, 1, 0, self.limit_ns, N.status_word())
         torch.cuda.current_stream().wait_stream(self.stream)
 
-    def norm_and_clip(self, clip: float, scale: torch.Tensor, norm: torch.Tensor, flag: torch.Tensor) -> None:
+    def norm_and_clip(self, clip: float, scale: torch.Tensor, norm: torch.Tensor, flag: torch.Tensor,
+                      loss: torch.Tensor | None = None) -> None:
+        """Global gradient norm and clip coefficient; ``loss`` (one float, this rank's mean loss) comes back as the mean
+        over the ranks from the same exchange, so a step has no library all-reduce."""
         N.call("llmk_comm_norm_exchange", self.ctrl_ptrs, self.partials, self.num_partials, self.slot_norm, self.rank,
-               self.world_size, self.epoch, float(clip), scale, norm, flag, self.limit_ns, N.status_word())
+               self.world_size, self.epoch, float(clip), scale, norm, flag, loss, self.limit_ns, N.status_word())
 
     def adamw_push(self, master, m, v, lr, beta1, beta2, step, eps, wd, scale, seed) -> None:
         b1c, b2c = 1.0 - beta1 ** step, 1.0 - beta2 ** step

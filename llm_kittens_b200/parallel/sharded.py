@@ -15,7 +15,12 @@ so they save no memory. Here:
   rank's bf16 shard (symmetric memory). A block's parameters are gathered just in time into one of
   two staging slots by ``ag_bucket`` on a side stream, one block ahead of the compute in forward,
   backward and recompute; AdamW updates the shard in place and nothing is pushed. The non-block
-  tensors are gathered once per optimizer step into a persistent buffer.
+  tensors are gathered once per optimizer step into a persistent buffer. The gather of a block's weight
+  MATRICES is tile-granular: the gather kernel publishes one flag per chunk of each matrix as the chunk
+  lands (``ag_bucket_flags``), and the GEMMs that consume the matrix poll only the flags covering the
+  tile they are about to load (``llmk_gemm_b_ready``), so the compute stream never waits for a whole
+  bucket; only the small tensors of a block (norm weights, biases) are waited for with an event.
+  ``LLMK_AG_FLAGS=0`` restores the bucket-granular gather (one event per bucket).
 
 The model sees none of this except through its ``p`` / ``g`` dictionaries (per-layer views into the
 slots) and the ``param_hook`` / ``grad_hook`` / ``bucket_ready`` callbacks.
@@ -106,7 +111,9 @@ class ShardedComm:
             self.rs_tables[layer] = torch.tensor(rs_rows, dtype=torch.int64, device=device)
             self.ag_tables[layer] = torch.tensor(ag_rows, dtype=torch.int64, device=device)
         self.ag_full_table = torch.tensor(ag_full_rows, dtype=torch.int64, device=device)
-        self.grid_x = 8
+        from .fused import comm_grid_x
+
+        self.grid_x = comm_grid_x(max(s.length for s in plan.segments))
         max_rows = max(int(t.shape[0]) for t in self.rs_tables.values())
         self.partials = torch.zeros(max_rows * self.grid_x, dtype=torch.float32, device=device)  # unused by-product of rs_bucket
         rows = []
@@ -121,12 +128,15 @@ class ShardedComm:
         self.norm2 = torch.zeros(8, dtype=torch.float32, device=device)
 
         # ---- what the model sees
+        self.flagged = False
         if stage >= 3:
             self.param_slots = torch.empty(2 * self.block_size, dtype=torch.bfloat16, device=device)
             self.param_globals = torch.empty(self.global_size, dtype=torch.bfloat16, device=device)
             model.p = self._views(self.param_slots, self.param_globals)
             model.params = None           # no full parameter buffer any more
             model.param_hook = self._param_hook
+            if os.environ.get("LLMK_AG_FLAGS", "1") != "0":
+                self._setup_flagged_gather(model, by_key)
         del full
         model.g = self._views(self.grad_slots, self.grad_globals)
         model.grads = None
@@ -142,7 +152,9 @@ class ShardedComm:
         if (self.slot_done + L) * int(N.lib().llmk_comm_max_ranks()) > 2048:
             raise RuntimeError("too many layers for the control buffer of the fused communication path")
         self.stream = torch.cuda.Stream(device=device)       # reduce-scatter kernels
-        self.ag_stream = torch.cuda.Stream(device=device)    # parameter gathers
+        # parameter gathers: high priority, so that a gather which GEMMs are already polling for gets the next free
+        # thread slots of every SM (a GEMM CTA leaves most of an SM's thread and register budget unused)
+        self.ag_stream = torch.cuda.Stream(device=device, priority=-1)
         self._gathered = {}                # layer -> event of a queued gather not yet consumed
         self._resident = [None, None]      # layer whose parameters sit in each slot
         self._globals_stale = True
@@ -188,15 +200,83 @@ class ShardedComm:
         N.call("llmk_comm_signal", self.ctrl_ptrs, slot, self.rank, self.world_size, epoch)
 
     # ------------------------------------------------------------------ parameters (stage 3)
+    def _setup_flagged_gather(self, model, by_key) -> None:
+        """Split every block bucket into its weight matrices (gathered chunk by chunk with one flag per chunk, consumed
+        by GEMMs that poll those flags) and the small rest (norm weights, biases: gathered first, waited for with an
+        event). A matrix of ``size`` elements arrives as P shards of ``size / P``; each shard is cut into ``cps`` chunks
+        of about ``LLMK_AG_CHUNK_BYTES`` (default 1 MiB), so flag ``f`` of a matrix covers its elements
+        ``[f * chunk, (f + 1) * chunk)`` and a GEMM maps a tile to flags by one division."""
+        from ..ops import gemm
+
+        lay, P = self.plan.layout, self.world_size
+        target = max(4096, int(os.environ.get("LLMK_AG_CHUNK_BYTES", str(1 << 20)))) // 2   # elements
+        self.matrix_names, geometry, nflags = [], {}, 0
+        for nme in self.block_names:
+            spec = lay[nme].spec
+            per_layer = lay[nme].size
+            segs = by_key[(nme, 0)]
+            if len(spec.shape) != 2 or per_layer < 16384 or len(segs) != 1 or segs[0].length * P != per_layer:
+                continue
+            length = segs[0].length
+            cps = max(1, min(8, length // target))
+            while cps > 1 and length % (cps * 8):
+                cps -= 1
+            self.matrix_names.append(nme)
+            geometry[nme] = (cps, length // cps)
+        if not self.matrix_names:
+            return
+        for q in range(2):
+            for nme in self.matrix_names:
+                geometry[(q, nme)] = nflags
+                nflags += P * geometry[nme][0]
+        self.ag_flags = torch.zeros(nflags, dtype=torch.int32, device=self.device)
+        self.ag_small_tables, self.ag_flag_tables = {}, {}
+        for layer in range(self.L):
+            small, flagged = [], []
+            for nme in self.block_names:
+                base = (layer % 2) * self.block_size + self.block_off[nme]
+                for sg in by_key[(nme, layer)]:
+                    if nme in self.matrix_names:
+                        flagged.append((sg.state_off, base, sg.length, geometry[(layer % 2, nme)], geometry[nme][0]))
+                    else:
+                        small.append((sg.state_off, base, sg.length))
+            self.ag_small_tables[layer] = torch.tensor(small, dtype=torch.int64, device=self.device) if small else None
+            self.ag_flag_tables[layer] = torch.tensor(flagged, dtype=torch.int64, device=self.device)
+        self.ag_max_cps = max(geometry[n][0] for n in self.matrix_names)
+        # the consumers: one registry entry per (slot, matrix); layers l and l + 2 share the slot and its entry
+        self._ready_entries = {}
+        for q in range(min(2, self.L)):
+            for nme in self.matrix_names:
+                self._ready_entries[(q, nme)] = gemm.register_b_ready(model.p[nme][q], self.ag_flags, geometry[(q, nme)],
+                                                                     geometry[nme][1], self.limit_ns)
+        self._tick = 0
+        self._gathers_in_flight = []
+        self.flagged = True
+
     def _gather(self, layer, after: torch.cuda.Event) -> None:
         """Queue the gather of one bucket on the gather stream, after the compute recorded in ``after``."""
         table = self.ag_tables[layer]
         dst = self.param_globals if layer is None else self.param_slots
         with torch.cuda.stream(self.ag_stream):
             self.ag_stream.wait_event(after)
-            N.call("llmk_comm_ag_bucket", self.param_shard_ptrs, dst, table, int(table.shape[0]), self.grid_x, self.world_size)
-            ev = torch.cuda.Event()
-            ev.record()
+            if self.flagged and layer is not None:
+                small, flagged = self.ag_small_tables[layer], self.ag_flag_tables[layer]
+                if small is not None:
+                    N.call("llmk_comm_ag_bucket", self.param_shard_ptrs, dst, small, int(small.shape[0]), 2, self.world_size)
+                ev = torch.cuda.Event()
+                ev.record()           # the compute stream waits for the small tensors only
+                self._tick += 1
+                N.call("llmk_comm_ag_bucket_flags", self.param_shard_ptrs, dst, flagged, int(flagged.shape[0]), self.ag_max_cps,
+                       self.world_size, self.ag_flags, self._tick)
+                done = torch.cuda.Event()
+                done.record()
+                self._gathers_in_flight.append(done)
+                for nme in self.matrix_names:
+                    self._ready_entries[(layer % 2, nme)][3] = self._tick
+            else:
+                N.call("llmk_comm_ag_bucket", self.param_shard_ptrs, dst, table, int(table.shape[0]), self.grid_x, self.world_size)
+                ev = torch.cuda.Event()
+                ev.record()
         self._gathered[layer] = ev
         if layer is not None:
             self._resident[layer % 2] = layer
@@ -272,10 +352,17 @@ class ShardedComm:
     def finish_reduce(self) -> None:
         torch.cuda.current_stream().wait_stream(self.stream)
 
-    def norm_and_clip(self, clip, scale, norm, flag) -> None:
+    def norm_and_clip(self, clip, scale, norm, flag, loss=None) -> None:
+        if self.flagged:
+            # every gather of this step has been consumed tile by tile; before this rank tells the others (through the
+            # norm exchange) that its reads of their shards are over, the gather kernels themselves must have ended
+            cur = torch.cuda.current_stream()
+            for ev in self._gathers_in_flight:
+                cur.wait_event(ev)
+            self._gathers_in_flight.clear()
         optim.global_norm2(self.gshard, self.shard_segs, self.shard_max_len, out=self.norm2[:1], partials=self.norm_partials)
         N.call("llmk_comm_norm_exchange", self.ctrl_ptrs, self.norm2, 1, self.slot_norm, self.rank, self.world_size, self.epoch,
-               float(clip), scale, norm, flag, self.limit_ns, N.status_word())
+               float(clip), scale, norm, flag, loss, self.limit_ns, N.status_word())
 
     # ------------------------------------------------------------------ optimizer
     def adamw_shard(self, master, m, v, lr, beta1, beta2, step, eps, wd, scale, seed) -> None:

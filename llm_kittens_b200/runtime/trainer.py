@@ -225,11 +225,12 @@ class Trainer:
             for off, n in self.expert_ranges:
                 self.model.grads[off:off + n].mul_(1.0 / self.num_processes)
             self.comm.finish_reduce()
-            self.comm.all_reduce_scalar(self.model.acts["loss_acc"], "avg")
             if getattr(self.comm, "fused", False):
-                # the bucket kernels already left the norm partials of the averaged shard
-                self.comm.norm_and_clip(self.grad_clip, self.scale, self.norm, self.flag)
+                # the bucket kernels already left the norm partials of the averaged shard; the mean loss of the ranks
+                # travels with the norm exchange (no library collective in the step)
+                self.comm.norm_and_clip(self.grad_clip, self.scale, self.norm, self.flag, loss=self.model.acts["loss_acc"])
             else:
+                self.comm.all_reduce_scalar(self.model.acts["loss_acc"], "avg")
                 self._local_norm2()
                 if self.plan.sharded:
                     self.comm.all_reduce_scalar(self.norm2, "sum")

@@ -75,14 +75,21 @@ def test_expert_parallel_moe_matches_single_process(tmp_path):
         assert r0["losses"][-1] < r0["losses"][0]
 
 
-@pytest.mark.parametrize("stage,recompute", [(2, 0), (3, 0), (3, 3)])
-def test_sharded_zero_stages_match_library(tmp_path, stage, recompute):
+@pytest.mark.parametrize("stage,recompute,gather", [(2, 0, ""), (3, 0, ""), (3, 3, ""), (3, 0, "chunks"), (3, 3, "chunks"), (3, 0, "bucket")])
+def test_sharded_zero_stages_match_library(tmp_path, stage, recompute, gather):
     """Really sharded gradients (stage 2) and parameters (stage 3), two micro-steps per step, four blocks
-    (so that the two bucket slots are reused inside a micro-step): same training as the library path."""
+    (so that the two bucket slots are reused inside a micro-step): same training as the library path. Stage 3
+    gathers a block's weight matrices chunk by chunk while the GEMMs poll the chunk flags: run with the default chunk
+    size (one chunk per shard at this model size), with 8 KiB chunks (several flags per matrix, tiles that span
+    two chunks) and with the bucket-granular gather."""
     _need_two_gpus()
     env = {"LLMK_TEST_LAYERS": "4", "LLMK_TEST_RECOMPUTE": str(recompute)}
+    if gather == "chunks":
+        env["LLMK_AG_CHUNK_BYTES"] = "8192"
+    elif gather == "bucket":
+        env["LLMK_AG_FLAGS"] = "0"
     s0, s1 = _run(f"gpu_sharded{stage}", tmp_path, **env)
-    l0, _ = _run("gpu_library1", tmp_path, **env)
+    l0, _ = _run("gpu_library1", tmp_path, LLMK_TEST_LAYERS="4", LLMK_TEST_RECOMPUTE=str(recompute))
     assert torch.equal(s0["params"], s1["params"])
     assert s0["losses"] == s1["losses"]
     for a, b in zip(s0["losses"], l0["losses"]):

@@ -123,3 +123,42 @@ def test_gemm_grouped_matches_per_group_reference(G, M, N, K):
         ref = gw0[g].float() + dyw[g * M:(g + 1) * M].float().T @ a[g * M:(g + 1) * M].float()
         _close(gw[g], ref, 0.12)
     _native.check_status()
+
+
+def test_gemm_polls_readiness_flags_of_its_weight_operand():
+    """The consumer half of the tile-granular parameter gather: a GEMM whose weight is registered with per-chunk
+    flags gives the plain result when the flags carry the expected tick (NT and NN layouts, tiles that span chunk
+    borders), and when one chunk's flag never arrives the bounded wait runs out after the given limit: status 5
+    (peer flag timeout) is read by the host and the context stays usable."""
+    from llm_kittens_b200.ops import _native, gemm
+
+    torch.manual_seed(0)
+    M, Nn, K = 512, 640, 256
+    a = (torch.randn(M, K, device="cuda") * 0.1).to(torch.bfloat16)
+    w = (torch.randn(Nn, K, device="cuda") * 0.1).to(torch.bfloat16)
+    d = (torch.randn(M, Nn, device="cuda") * 0.1).to(torch.bfloat16)
+    chunk = 10240                       # elements per flag: 40 rows of the weight, so tiles straddle chunks
+    nflags = (Nn * K + chunk - 1) // chunk
+    flags = torch.zeros(nflags + 3, dtype=torch.int32, device="cuda")
+    entry = gemm.register_b_ready(w, flags, 3, chunk, int(0.2e9))
+    try:
+        plain_nt = gemm.gemm_nt(a, w.clone())
+        plain_nn = gemm.gemm_nn(d, w.clone())
+        entry[3] = 7
+        flags.fill_(7)
+        torch.cuda.synchronize()
+        assert torch.equal(gemm.gemm_nt(a, w), plain_nt)
+        assert torch.equal(gemm.gemm_nn(d, w), plain_nn)
+        _native.check_status()
+        # an older tick in one flag = a chunk that has not landed: nothing sets it, the wait must run out
+        flags[3 + nflags // 2] = 6
+        torch.cuda.synchronize()
+        gemm.gemm_nt(a, w)
+        torch.cuda.synchronize()
+        with pytest.raises(_native.NativeError, match="peer flag"):
+            _native.check_status()
+        flags.fill_(7)
+        assert torch.equal(gemm.gemm_nt(a, w), plain_nt)   # the context and the kernels still work
+        _native.check_status()
+    finally:
+        gemm.unregister_b_ready(w)

@@ -92,6 +92,41 @@ def test_ten_step_loss_parity(family):
     assert b.loss < 6.0
 
 
+def test_gpt2_124m_ten_step_loss_parity_full_size(capsys):
+    """The reference's whole-model gate at full size (test_gpt2.cu:257-347): GPT-2 124M (12 layers, 768 channels,
+    vocabulary 50257 padded to 50304), B=4, T=64, token ids uniform from seed 1337, the same batch for ten AdamW
+    steps at lr 1e-4, random init N(0, 0.02) with scaled residual projections; the bf16 CUDA path against the fp32
+    PyTorch model with the same initial parameters, per-step loss within 0.05."""
+    from llm_kittens_b200.models.config import config_from_descriptor
+    from llm_kittens_b200.models.transformer import Transformer
+    from llm_kittens_b200.oracle.torch_model import TorchTransformer
+    from llm_kittens_b200.runtime.trainer import Trainer
+
+    cfg = config_from_descriptor("d12")
+    assert (cfg.num_layers, cfg.channels, cfg.num_heads, cfg.vocab_size, cfg.padded_vocab_size) == (12, 768, 12, 50257, 50304)
+    model = Transformer(cfg, device="cuda", recompute=0)
+    model.init_weights(42)
+    oracle = TorchTransformer(cfg, device="cuda", dtype=torch.float32)
+    oracle.load_parameters(model.params.float())
+    g = torch.Generator().manual_seed(1337)
+    x = torch.randint(0, cfg.vocab_size, (4, 64), generator=g, dtype=torch.int32)
+    y = torch.randint(0, cfg.vocab_size, (4, 64), generator=g, dtype=torch.int32)
+    tr_n = Trainer(model, learning_rate=1e-4, weight_decay=0.0, use_master_weights=True)
+    tr_o = Trainer(oracle, learning_rate=1e-4, weight_decay=0.0)
+    ours, ref = [], []
+    for step in range(10):
+        a = tr_n.train_step([(x.pin_memory(), y.pin_memory())])
+        b = tr_o.train_step([(x, y)])
+        ours.append(a.loss)
+        ref.append(b.loss)
+        assert abs(a.loss - b.loss) < 0.05, (step, a.loss, b.loss)
+        assert abs(a.grad_norm - b.grad_norm) < 0.05 * max(1.0, b.grad_norm), (step, a.grad_norm, b.grad_norm)
+    assert ref[-1] < ref[0] - 1.0   # ten steps on one batch: the loss falls by more than one nat
+    with capsys.disabled():
+        print("\nGPT-2 124M B=4 T=64 ten-step losses, CUDA bf16:", [round(v, 4) for v in ours])
+        print("GPT-2 124M B=4 T=64 ten-step losses, fp32 oracle:", [round(v, 4) for v in ref])
+
+
 @pytest.mark.parametrize("family", ["gpt2", "llama3"])
 def test_recompute_levels_agree_and_are_deterministic(family):
     cfg = small_gpt2() if family == "gpt2" else small_llama()

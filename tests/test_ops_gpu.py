@@ -217,6 +217,37 @@ def test_attention_fwd_bwd(B, T, NH, NKVH, HS):
     assert torch.equal(dqkv, dqkv2)
 
 
+@pytest.mark.parametrize("dkv", ["", "1", "2"])
+@pytest.mark.parametrize("B,T,NH,NKVH,HS,scale", [(1, 1024, 8, 2, 64, 1.0), (1, 2048, 4, 1, 64, 1.0), (1, 2048, 12, 12, 64, 1.0),
+                                                  (1, 4096, 32, 8, 128, 1.0), (1, 1024, 12, 12, 64, 3.0), (1, 2048, 8, 2, 128, 3.0)])
+def test_attention_long_sequences(B, T, NH, NKVH, HS, scale, dkv, monkeypatch):
+    """The sequence lengths of the training configurations: many key tiles per query tile (the K/V ring wraps
+    around), grouped queries long enough for the pipelined dK/dV kernel (chosen by itself for (T/64)*(NH/NKVH) >= 64,
+    forced both ways through LLMK_ATTN_BWD_DKV), and inputs scaled so that logits reach +-30 and the row maximum
+    jumps by more than 2^8 between key tiles (the lazy rescale of the output accumulator fires)."""
+    from llm_kittens_b200.ops import _native, attention
+
+    if dkv:
+        monkeypatch.setenv("LLMK_ATTN_BWD_DKV", dkv)
+    else:
+        monkeypatch.delenv("LLMK_ATTN_BWD_DKV", raising=False)
+    torch.manual_seed(T + NH + HS)
+    qkv = rnd(B, T, (NH + 2 * NKVH) * HS, scale=scale)
+    out, lse = attention.attention_fwd(qkv, B, T, NH, NKVH, HS)
+    _native.check_status()
+    qf = qkv.float().requires_grad_(True)
+    ref, ref_lse = _ref_attention(qf, B, T, NH, NKVH, HS)
+    assert maxerr(out, ref) < (0.03 if scale == 1.0 else 0.05 * scale)   # outputs reach |5| at scale 3: one bf16 ulp there is 0.03
+    assert maxerr(lse, ref_lse) < 0.02 * max(1.0, scale * scale)
+    dout = rnd(B, T, NH * HS)
+    ref.backward(dout.float())
+    dqkv = attention.attention_bwd(dout, qkv, out, lse, B, T, NH, NKVH, HS)
+    _native.check_status()
+    assert maxerr(dqkv, qf.grad) < 0.08 * max(1.0, scale * scale)
+    dqkv2 = attention.attention_bwd(dout, qkv, out, lse, B, T, NH, NKVH, HS)
+    assert torch.equal(dqkv, dqkv2)
+
+
 def test_adamw_and_norm():
     from llm_kittens_b200.ops import optim
 
