@@ -82,6 +82,20 @@ __device__ __forceinline__ bool already_failed(const int* status) {
 }
 
 // One 128-row x 64-column bf16 tile row (this thread's row r) into a TMA-store staging tile, 16-byte chunk `chunk`.
+// Backward of interleaved-pair RoPE on 8 consecutive head columns (4 pairs): the transpose rotation of the forward
+// one, so the gradients leave the kernel with respect to the un-rotated q / k that the QKV projection produced.
+// `fr` = the 4 (cos, sin) entries of this token's row of the frequency table that belong to the pairs.
+__device__ __forceinline__ void rope_inverse8(float* f, const float2* __restrict__ fr) {
+    const float4 a = __ldg(reinterpret_cast<const float4*>(fr)), b = __ldg(reinterpret_cast<const float4*>(fr) + 1);
+    const float c[4] = {a.x, a.z, b.x, b.z}, sn[4] = {a.y, a.w, b.y, b.w};
+#pragma unroll
+    for (int j = 0; j < 4; j++) {
+        const float x0 = f[2 * j], x1 = f[2 * j + 1];
+        f[2 * j] = x0 * c[j] + x1 * sn[j];
+        f[2 * j + 1] = x1 * c[j] - x0 * sn[j];
+    }
+}
+
 __device__ __forceinline__ void stage_chunk(uint8_t* tile, int r, int chunk, const float* f) {
     *reinterpret_cast<bf16x8*>(tile + r * 128 + ((chunk ^ (r & 7)) << 4)) = pack8(f);
 }
@@ -125,7 +139,7 @@ __global__ void __launch_bounds__(THREADS, Inner<HS>::CTAS)
 attn_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_constant__ CUtensorMap tmQKVin,
                        const __grid_constant__ CUtensorMap tmDOin, const __grid_constant__ CUtensorMap tmDQKV,
                        const float* __restrict__ lse, const float* __restrict__ dvec, int T, int NH, int NKVH, float scale,
-                       int* status) {
+                       int* status, const float2* __restrict__ rope) {
     using C = DkvCfg<HS>;
     constexpr int RING = C::RING, BN = C::BN;
     extern __shared__ __align__(1024) uint8_t smem[];
@@ -349,6 +363,7 @@ attn_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_c
                     float f[8];
 #pragma unroll
                     for (int i = 0; i < 8; i++) f[i] = __uint_as_float(v[q * 8 + i]) * scale;
+                    if (rope != nullptr) rope_inverse8(f, rope + (size_t)(kv0 + r) * (HS / 2) + h4 * 16 + q * 4);
                     stage_chunk(stage_dk + (h4 / 2) * (BM * 128), r, (h4 & 1) * 4 + q, f);
                 }
                 ptx::tmem_ld_32x32b_x32(t_dv + lane_off + h4 * 32, v);
@@ -407,7 +422,7 @@ __global__ void __launch_bounds__(THREADS2, 1)
 attn_bwd_dkv2_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_constant__ CUtensorMap tmQKVin,
                      const __grid_constant__ CUtensorMap tmDOin, const __grid_constant__ CUtensorMap tmDQKV,
                      const float* __restrict__ lse, const float* __restrict__ dvec, int T, int NH, int NKVH, float scale,
-                     int* status) {
+                     int* status, const float2* __restrict__ rope) {
     extern __shared__ __align__(1024) uint8_t smem[];
     if (already_failed(status)) return;
     if (ptx::smem_u32(smem) & 1023u) {
@@ -615,6 +630,7 @@ attn_bwd_dkv2_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_con
                 float f[8];
 #pragma unroll
                 for (int i = 0; i < 8; i++) f[i] = __uint_as_float(v[q * 8 + i]) * sc;
+                if (is_dk && rope != nullptr) rope_inverse8(f, rope + (size_t)(kv0 + r) * 32 + h4 * 16 + q * 4);
                 stage_chunk(stage, r, h4 * 4 + q, f);
             }
             ptx::fence_proxy_async_smem();
@@ -657,7 +673,7 @@ __global__ void __launch_bounds__(THREADS, Inner<HS>::CTAS)
 attn_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_constant__ CUtensorMap tmDO,
                       const __grid_constant__ CUtensorMap tmQKVin, const __grid_constant__ CUtensorMap tmDQKV,
                       const float* __restrict__ lse, const float* __restrict__ dvec, int T, int NH, int NKVH, float scale,
-                      int* status) {
+                      int* status, const float2* __restrict__ rope) {
     using C = DqCfg<HS>;
     constexpr int BN = C::BN;
     extern __shared__ __align__(1024) uint8_t smem[];
@@ -843,6 +859,7 @@ attn_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_co
                     float f[8];
 #pragma unroll
                     for (int i = 0; i < 8; i++) f[i] = __uint_as_float(v[q * 8 + i]) * scale;
+                    if (rope != nullptr) rope_inverse8(f, rope + (size_t)(q0 + r) * (HS / 2) + h4 * 16 + q * 4);
                     stage_chunk(sdS + (h4 / 2) * (BM * 128), r, (h4 & 1) * 4 + q, f);
                 }
             }
@@ -869,7 +886,7 @@ attn_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_co
 
 template <int HS>
 static int launch(const void* qkv, const void* dout, bf16* dqkv, const float* lse, const float* dvec, int B, int T, int NH, int NKVH,
-                  int* status, cudaStream_t stream) {
+                  int* status, const float2* rope, cudaStream_t stream) {
     constexpr int BN = Inner<HS>::BN;
     static PerDeviceOnce once_configured;
     if (once_configured.first()) {
@@ -905,14 +922,14 @@ static int launch(const void* qkv, const void* dout, bf16* dqkv, const float* ls
         if ((rc = gemm::make_tmap_2d(&tq_in64, qkv, width, rows, width, 64, 64))) return rc;
         if ((rc = gemm::make_tmap_2d(&tdo_in64, dout, cw, rows, cw, 64, 64))) return rc;
         dkv2::attn_bwd_dkv2_kernel<<<dim3(T / BM, NKVH, B), dkv2::THREADS2, dkv2::SMEM_BYTES, stream>>>(tq, tq_in64, tdo_in64, tdqkv, lse, dvec,
-                                                                                                    T, NH, NKVH, scale, status);
+                                                                                                    T, NH, NKVH, scale, status, rope);
     } else {
         attn_bwd_dkv_tc_kernel<HS><<<dim3(T / BM, NKVH, B), THREADS, DkvCfg<HS>::SMEM_BYTES, stream>>>(tq, tq_in, tdo_in, tdqkv, lse, dvec,
-                                                                                                     T, NH, NKVH, scale, status);
+                                                                                                     T, NH, NKVH, scale, status, rope);
     }
     LLMK_LAUNCH_CHECK();
     attn_bwd_dq_tc_kernel<HS><<<dim3(T / BM, NH, B), THREADS, DqCfg<HS>::SMEM_BYTES, stream>>>(tq, tdo, tq_in, tdqkv, lse, dvec, T, NH,
-                                                                                             NKVH, scale, status);
+                                                                                             NKVH, scale, status, rope);
     LLMK_LAUNCH_CHECK();
     return LLMK_OK;
 }
@@ -924,11 +941,29 @@ using namespace llmk;
 
 // dqkv (packed, fully overwritten) from dout [B*T, NH*HS]; `dvec` must already hold rowsum(dO*O) as [B,NH,T]
 // (llmk_attention_bwd_prep). T must be a multiple of 128.
-LLMK_API int llmk_attention_bwd_tc(void* dqkv, const void* dvec, const void* dout, const void* qkv, const void* lse, int B, int T,
-                                   int NH, int NKVH, int HS, int* status, void* stream_) {
+static int attention_bwd_tc_impl(void* dqkv, const void* dvec, const void* dout, const void* qkv, const void* lse, int B, int T,
+                                 int NH, int NKVH, int HS, int* status, const void* rope, void* stream_) {
     cudaStream_t stream = (cudaStream_t)stream_;
     if (T % 128 || NH % NKVH || (HS != 64 && HS != 128)) return LLMK_ERR_SHAPE;
+    if (reinterpret_cast<uintptr_t>(rope) & 15) return LLMK_ERR_SHAPE;
     if (HS == 64)
-        return attn_bwd_tc::launch<64>(qkv, dout, (bf16*)dqkv, (const float*)lse, (const float*)dvec, B, T, NH, NKVH, status, stream);
-    return attn_bwd_tc::launch<128>(qkv, dout, (bf16*)dqkv, (const float*)lse, (const float*)dvec, B, T, NH, NKVH, status, stream);
+        return attn_bwd_tc::launch<64>(qkv, dout, (bf16*)dqkv, (const float*)lse, (const float*)dvec, B, T, NH, NKVH, status,
+                                       (const float2*)rope, stream);
+    return attn_bwd_tc::launch<128>(qkv, dout, (bf16*)dqkv, (const float*)lse, (const float*)dvec, B, T, NH, NKVH, status,
+                                    (const float2*)rope, stream);
+}
+
+LLMK_API int llmk_attention_bwd_tc(void* dqkv, const void* dvec, const void* dout, const void* qkv, const void* lse, int B, int T,
+                                   int NH, int NKVH, int HS, int* status, void* stream_) {
+    return attention_bwd_tc_impl(dqkv, dvec, dout, qkv, lse, B, T, NH, NKVH, HS, status, nullptr, stream_);
+}
+
+// The same with the backward of RoPE folded into the dQ and dK output tiles: `qkv` holds ROTATED q and k (as the QKV
+// projection with the RoPE epilogue wrote them), `rope` is the [T, HS/2] (cos, sin) table of interleaved pairs, and the
+// dq / dk columns of `dqkv` come out as gradients of the un-rotated projections. Same job as the in-tile inverse
+// rotation of the reference's GQA backward (llmc/attention_gqa.cuh:184-227).
+LLMK_API int llmk_attention_bwd_tc_rope(void* dqkv, const void* dvec, const void* dout, const void* qkv, const void* lse, int B,
+                                        int T, int NH, int NKVH, int HS, int* status, const void* rope, void* stream_) {
+    if (rope == nullptr) return LLMK_ERR_SHAPE;
+    return attention_bwd_tc_impl(dqkv, dvec, dout, qkv, lse, B, T, NH, NKVH, HS, status, rope, stream_);
 }

@@ -210,25 +210,30 @@ ag_bucket_kernel(Peers shards, bf16* __restrict__ staging, const long long* __re
 }
 
 // The same gather with its progress published: segment table int64[nseg][5] = (shard offset, staging offset of the
-// full slice, shard length, first flag of the tensor, chunks per shard). Block (x, segment, source rank) copies chunk x
-// (length / chunks consecutive elements) of that rank's shard and then release-stores `tick` into
-// flags[first + rank * chunks + x], which is flag (element offset inside the tensor) / (chunk length). A GEMM that
-// consumes the tensor polls exactly the flags that cover a tile (llmk_gemm_b_ready), so it can start on the first
-// chunks while the others are still crossing NVLink. Four 128-bit peer loads are in flight per thread.
+// full slice, shard length, first flag of the tensor, chunks per shard). A chunk (length / chunks consecutive elements
+// of one rank's shard) is copied by `bpc` blocks (blockIdx.x = chunk * bpc + part); the block that finishes a chunk
+// last (an arrival counter per flag, left at zero again) release-stores `tick` into flags[first + rank * chunks +
+// chunk], which is flag (element offset inside the tensor) / (chunk length). A GEMM that consumes the tensor polls
+// exactly the flags that cover a tile (llmk_gemm_b_ready), so it can start on the first chunks while the others are
+// still crossing NVLink. Four 128-bit peer loads are in flight per thread.
 __global__ void __launch_bounds__(TPB)
 ag_bucket_flags_kernel(Peers shards, bf16* __restrict__ staging, const long long* __restrict__ segs, int* __restrict__ flags,
-                       int tick) {
+                       int* __restrict__ arrivals, int bpc, int tick) {
     const long long* seg = segs + (size_t)blockIdx.y * 5;
     const size_t s_off = (size_t)seg[0], d_off = (size_t)seg[1], len = (size_t)seg[2];
     const int first = (int)seg[3], cps = (int)seg[4];
-    const int r = blockIdx.z, x = blockIdx.x;
+    const int r = blockIdx.z, x = blockIdx.x / bpc, part = blockIdx.x - x * bpc;
     if (x >= cps) return;
     const size_t chunk = len / cps;
-    const bf16* src = static_cast<const bf16*>(shards.p[r]) + s_off + (size_t)x * chunk;
-    bf16* dst = staging + d_off + (size_t)r * len + (size_t)x * chunk;
+    // this block's part of the chunk: whole 128-bit words, the last part takes the remainder
+    const size_t words = chunk / 8, per = (words + bpc - 1) / bpc;
+    const size_t w0 = min(words, (size_t)part * per), w1 = min(words, w0 + per);
+    const bf16* src = static_cast<const bf16*>(shards.p[r]) + s_off + (size_t)x * chunk + w0 * 8;
+    bf16* dst = staging + d_off + (size_t)r * len + (size_t)x * chunk + w0 * 8;
+    const size_t n = (w1 - w0) * 8;
     constexpr size_t STEP = (size_t)TPB * 8;
     size_t i = (size_t)threadIdx.x * 8;
-    for (; i + 3 * STEP < chunk; i += 4 * STEP) {
+    for (; i + 3 * STEP < n; i += 4 * STEP) {
         const uint4 v0 = ld_volatile_v4(src + i), v1 = ld_volatile_v4(src + i + STEP);
         const uint4 v2 = ld_volatile_v4(src + i + 2 * STEP), v3 = ld_volatile_v4(src + i + 3 * STEP);
         *reinterpret_cast<uint4*>(dst + i) = v0;
@@ -236,11 +241,16 @@ ag_bucket_flags_kernel(Peers shards, bf16* __restrict__ staging, const long long
         *reinterpret_cast<uint4*>(dst + i + 2 * STEP) = v2;
         *reinterpret_cast<uint4*>(dst + i + 3 * STEP) = v3;
     }
-    for (; i < chunk; i += STEP) *reinterpret_cast<uint4*>(dst + i) = ld_volatile_v4(src + i);
+    for (; i < n; i += STEP) *reinterpret_cast<uint4*>(dst + i) = ld_volatile_v4(src + i);
     __syncthreads();
     if (threadIdx.x == 0) {
+        const int f = first + r * cps + x;
         __threadfence();
-        asm volatile("st.release.gpu.global.s32 [%0], %1;" ::"l"(flags + first + r * cps + x), "r"(tick) : "memory");
+        if (atomicAdd(arrivals + f, 1) == bpc - 1) {
+            arrivals[f] = 0;
+            __threadfence();
+            asm volatile("st.release.gpu.global.s32 [%0], %1;" ::"l"(flags + f), "r"(tick) : "memory");
+        }
     }
 }
 
@@ -361,12 +371,13 @@ LLMK_API int llmk_comm_ag_bucket(const long long* shard_ptrs, void* staging, con
 }
 
 // Gather with per-chunk flags (see ag_bucket_flags_kernel). `max_cps` = the largest "chunks per shard" in the table;
-// every shard length must be a multiple of 8 * its chunk count.
+// every shard length must be a multiple of 8 * its chunk count. `flags` and `arrivals` hold one int per chunk of every
+// tensor and rank (arrivals start at zero and are left at zero); `bpc` blocks share one chunk.
 LLMK_API int llmk_comm_ag_bucket_flags(const long long* shard_ptrs, void* staging, const void* segs, int nseg, int max_cps, int P,
-                                       void* flags, int tick, void* stream) {
-    if (P > MAXP || nseg <= 0 || max_cps <= 0 || flags == nullptr) return LLMK_ERR_SHAPE;
-    ag_bucket_flags_kernel<<<dim3(max_cps, nseg, P), TPB, 0, (cudaStream_t)stream>>>(make_peers(shard_ptrs, P), (bf16*)staging,
-                                                                                   (const long long*)segs, (int*)flags, tick);
+                                       void* flags, void* arrivals, int bpc, int tick, void* stream) {
+    if (P > MAXP || nseg <= 0 || max_cps <= 0 || bpc <= 0 || flags == nullptr || arrivals == nullptr) return LLMK_ERR_SHAPE;
+    ag_bucket_flags_kernel<<<dim3(max_cps * bpc, nseg, P), TPB, 0, (cudaStream_t)stream>>>(
+        make_peers(shard_ptrs, P), (bf16*)staging, (const long long*)segs, (int*)flags, (int*)arrivals, bpc, tick);
     LLMK_LAUNCH_CHECK();
     return LLMK_OK;
 }

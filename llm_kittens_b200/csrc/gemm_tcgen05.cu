@@ -51,7 +51,7 @@ constexpr int GROUP_M = 8;
 constexpr int TMEM_COLS = 512;
 
 enum { MODE_NT = 0, MODE_NN = 1, MODE_TN = 2 };
-enum { EPI_BIAS = 1, EPI_GELU = 2, EPI_DGELU = 4, EPI_ADD = 8, EPI_PARTIAL = 16 };
+enum { EPI_BIAS = 1, EPI_GELU = 2, EPI_DGELU = 4, EPI_ADD = 8, EPI_PARTIAL = 16, EPI_ROPE = 32 };
 
 template <int EPI, bool PAIR>
 struct Cfg {
@@ -120,6 +120,11 @@ struct Params {
     long long b_chunk;
     int b_tick, a_rows, a_need;
     long long ready_limit_ns;
+    // EPI_ROPE: rotate the q and k heads of a packed QKV projection in the epilogue. Row r of C is token r % rope_T;
+    // columns [0, rope_cols) are heads of rope_hs columns whose interleaved pairs (2i, 2i+1) turn by the angle in
+    // rope[token][i] = (cos, sin); the columns after them (v) pass through.
+    const float2* rope;
+    int rope_T, rope_cols, rope_hs;
 };
 
 __device__ __forceinline__ int ld_acquire_sys_s32(const int* ptr) {
@@ -508,6 +513,22 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
 #pragma unroll
                             for (int j = 0; j < 4; j++) xp[j] = ptx::add2(xp[j], ptx::pack2(b[2 * j], b[2 * j + 1]));
                         }
+                        if ((EPI & EPI_ROPE) && n_base < p.rope_cols) {
+                            // 8 columns = 4 pairs of one head; the accumulators are rotated in fp32 and rounded once
+                            const int tok = (row_ok ? row : 0) % p.rope_T;
+                            const float4* fr = reinterpret_cast<const float4*>(p.rope + (size_t)tok * (p.rope_hs >> 1) +
+                                                                               (((n_base % p.rope_hs) + half * 32 + q * 8) >> 1));
+                            const float4 f0 = __ldg(fr), f1 = __ldg(fr + 1);
+                            const ptx::f32x2 cs[4] = {ptx::pack2(f0.x, f0.x), ptx::pack2(f0.z, f0.z), ptx::pack2(f1.x, f1.x), ptx::pack2(f1.z, f1.z)};
+                            const float sn[4] = {f0.y, f0.w, f1.y, f1.w};
+#pragma unroll
+                            for (int j = 0; j < 4; j++) {
+                                float x0, x1;
+                                ptx::unpack2(xp[j], x0, x1);
+                                // (x0, x1) -> (x0 c - x1 s, x1 c + x0 s)
+                                xp[j] = ptx::fma2(xp[j], cs[j], ptx::pack2(-x1 * sn[j], x0 * sn[j]));
+                            }
+                        }
                         if (AUX_IN) {
                             float g[8];
                             unpack8(*reinterpret_cast<const bf16x8*>(buf2 + off), g);
@@ -762,6 +783,8 @@ struct Ready {
     long long b_chunk = 1;
     int b_tick = 0, a_rows = 1, a_need = 0;
     long long limit_ns = 0;
+    const float2* rope = nullptr;
+    int rope_T = 1, rope_cols = 0, rope_hs = 64;
 };
 
 static int gemm_impl(int mode, int epi, const void* A, const void* B, void* C, void* C2, const void* bias, const void* aux,
@@ -801,6 +824,12 @@ static int gemm_impl(int mode, int epi, const void* A, const void* B, void* C, v
     p.b_tick = ready.b_tick; p.a_rows = ready.a_rows > 0 ? ready.a_rows : 1; p.a_need = ready.a_need;
     p.ready_limit_ns = ready.limit_ns > 0 ? ready.limit_ns : (long long)LLMK_WAIT_LIMIT_NS;
     if ((p.b_ready != nullptr || p.a_ready != nullptr) && mode == MODE_TN) return LLMK_ERR_SHAPE;
+    p.rope = ready.rope; p.rope_T = ready.rope_T; p.rope_cols = ready.rope_cols; p.rope_hs = ready.rope_hs;
+    if (epi & EPI_ROPE) {
+        if (p.rope == nullptr || mode != MODE_NT || p.rope_T <= 0 || (p.rope_hs != 64 && p.rope_hs != 128) ||
+            p.rope_cols % p.rope_hs || p.rope_cols > N || (reinterpret_cast<uintptr_t>(p.rope) & 15))
+            return LLMK_ERR_SHAPE;
+    }
     bool split_accumulate = false;
     if (mode == MODE_TN && (epi == 0 || epi == EPI_ADD)) {
         const int workers = p.pair ? pair_clusters : g_num_sms;
@@ -847,6 +876,7 @@ static int gemm_impl(int mode, int epi, const void* A, const void* B, void* C, v
     LLMK_GEMM_CASE(MODE_NT, EPI_BIAS | EPI_GELU)
     LLMK_GEMM_CASE(MODE_NT, EPI_ADD)
     LLMK_GEMM_CASE(MODE_NT, EPI_BIAS | EPI_ADD)
+    LLMK_GEMM_CASE(MODE_NT, EPI_ROPE)
     LLMK_GEMM_CASE(MODE_NN, 0)
     LLMK_GEMM_CASE(MODE_NN, EPI_DGELU)
     LLMK_GEMM_CASE(MODE_NN, EPI_ADD)
@@ -886,6 +916,24 @@ LLMK_API int llmk_gemm_b_ready(int mode, int epi, const void* A, const void* B, 
     r.limit_ns = limit_ns;
     if (b_ready != nullptr && b_chunk <= 0) return LLMK_ERR_SHAPE;
     return gemm_impl(mode, epi, A, B, C, C2, bias, aux, M, N, K, 1, workspace, workspace_bytes, status, max_ctas, stream_, r);
+}
+
+// QKV projection with RoPE in the epilogue: C = A B^T where C is a packed [tokens, (NH + 2 NKVH) * HS] tensor; the
+// q and k heads (the first `rope_cols` columns) are rotated by the (cos, sin) table `rope` [T, HS/2] (interleaved
+// pairs) before they are rounded to bf16, v passes through. Row r is token r % T. Optional `b_ready` as in
+// llmk_gemm_b_ready. Same job as the in-tile rotation of the reference's GQA attention (llmc/tk/attention_gqa_h100.cuh:66-83),
+// moved to where the values are still in fp32 registers.
+LLMK_API int llmk_gemm_qkv_rope(const void* A, const void* B, void* C, int M, int N, int K, const void* rope, int T, int rope_cols,
+                                int HS, int* status, int max_ctas, const void* b_ready, long b_chunk, int b_tick, long limit_ns,
+                                void* stream_) {
+    Ready r;
+    r.b_ready = static_cast<const int*>(b_ready);
+    r.b_chunk = b_chunk > 0 ? b_chunk : 1;
+    r.b_tick = b_tick;
+    r.limit_ns = limit_ns;
+    r.rope = static_cast<const float2*>(rope);
+    r.rope_T = T; r.rope_cols = rope_cols; r.rope_hs = HS;
+    return gemm_impl(MODE_NT, EPI_ROPE, A, B, C, nullptr, nullptr, nullptr, M, N, K, 1, nullptr, 0, status, max_ctas, stream_, r);
 }
 
 // `groups` independent problems of the same shape in ONE persistent launch (the experts of a mixture-of-experts

@@ -20,6 +20,8 @@ CUDA stream. The schedule plays the role of gpt2_forward / gpt2_backward_and_red
 """
 from __future__ import annotations
 
+import os
+
 import math
 from typing import Callable
 
@@ -61,6 +63,13 @@ class Transformer:
         # block buckets are handed over after every micro-step instead of only the last one
         self.grad_hook: Callable[[int], None] | None = None
         self.reduce_every_micro_step = False
+        # Bandwidth-shaped side work of the backward pass (bias-gradient column sums, the D = rowsum(dO * O) pre-pass of
+        # attention) runs on a second stream beside the GEMMs that follow it: those are tensor-bound and leave most of
+        # the memory system idle. LLMK_SIDE_STREAM=0 keeps everything on one stream.
+        self.side = None
+        if self.device.type == "cuda" and os.environ.get("LLMK_SIDE_STREAM", "1") != "0":
+            self.side = torch.cuda.Stream(device=self.device)
+        self._side_busy = False
 
     # ------------------------------------------------------------------ parameters
     def init_weights(self, seed: int = 42) -> None:
@@ -172,6 +181,33 @@ class Transformer:
         else:
             norm_ops.layernorm_bwd(dinp, dw, db, dout, x, w, mean, rstd, accumulate_dinp=accumulate)
 
+    def _fork(self, fn) -> None:
+        """Run ``fn`` on the side stream, ordered after everything queued so far on the current stream."""
+        if self.side is None:
+            fn()
+            return
+        ev = torch.cuda.Event()
+        ev.record()
+        self.side.wait_event(ev)
+        with torch.cuda.stream(self.side):
+            fn()
+        self._side_busy = True
+
+    def _join(self) -> None:
+        """The current stream waits for the side work: before anything overwrites what that work reads, and before its
+        results (bias gradients, D) are used."""
+        if self._side_busy:
+            torch.cuda.current_stream().wait_stream(self.side)
+            self._side_busy = False
+
+    def _fused_rope(self) -> bool:
+        """Llama with interleaved pairs on the tcgen05 attention path: RoPE lives in the QKV projection's epilogue and
+        its backward in the output tiles of the attention backward kernels; no separate pass over QKV or dQKV. The
+        half-split pair convention and sequence lengths that fall back to the warp-level attention kernels keep the
+        stand-alone rotation kernel."""
+        return (self.is_llama and self.rope_interleaved and attn_ops.fused_rope_available(self.T)
+                and self.config.head_size in (64, 128) and os.environ.get("LLMK_FUSED_ROPE", "1") != "0")
+
     def _idx(self, l: int, kind: str) -> int:
         """Index of layer ``l`` in a per-layer activation given the recompute level."""
         r = self.recompute
@@ -194,9 +230,14 @@ class Transformer:
         mean2 = None if self.is_llama else a["ln2_mean"][k]
         self._norm_fwd(x, p["ln1w"][l], None if self.is_llama else p["ln1b"][l], ln1, mean1, a["ln1_rstd"][k])
         qkv = a["qkv"][k]
-        gemm.gemm_nt(ln1, p["qkvw"][l], bias=None if self.is_llama else p["qkvb"][l], out=qkv)
-        if self.is_llama:
-            ew.rope_qk_(qkv, a["rope"], B, T, cfg.num_heads, cfg.num_kv_heads, cfg.head_size, self.rope_interleaved)
+        if self._fused_rope():
+            # RoPE in the projection's epilogue: q and k are rotated while still fp32 accumulators
+            gemm.gemm_qkv_rope(ln1, p["qkvw"][l], a["rope"], T, (cfg.num_heads + cfg.num_kv_heads) * cfg.head_size, cfg.head_size,
+                               out=qkv)
+        else:
+            gemm.gemm_nt(ln1, p["qkvw"][l], bias=None if self.is_llama else p["qkvb"][l], out=qkv)
+            if self.is_llama:
+                ew.rope_qk_(qkv, a["rope"], B, T, cfg.num_heads, cfg.num_kv_heads, cfg.head_size, self.rope_interleaved)
         attn_ops.attention_fwd(qkv, B, T, cfg.num_heads, cfg.num_kv_heads, cfg.head_size, out=a["atty"][k], lse=a["lse"][k])
         res2 = a["res2"][k]
         gemm.gemm_nt(a["atty"][k], p["attprojw"][l], bias=None if self.is_llama else p["attprojb"][l], out=res2, add=x)
@@ -239,12 +280,12 @@ class Transformer:
             if 1 <= self.recompute < 3:
                 ew.gelu_fwd(a["fch"][k], out=act)
             d_fch = a["d_wide"].view(-1)[: BT * H].view(BT, H)
+            self._fork(lambda: ew.dbias(g["fcprojb"][l], dres, accumulate=True))
             gemm.gemm_tn(dres, act, out=g["fcprojw"][l], accumulate=True)
-            ew.dbias(g["fcprojb"][l], dres, accumulate=True)
             gemm.gemm_nn(dres, p["fcprojw"][l], out=d_fch, dgelu_of=a["fch"][k])
+            self._fork(lambda: ew.dbias(g["fcb"][l], d_fch, accumulate=True))
             gemm.gemm_nn(d_fch, p["fcw"][l], out=d_ln2)
             gemm.gemm_tn(d_fch, ln2, out=g["fcw"][l], accumulate=True)
-            ew.dbias(g["fcb"][l], d_fch, accumulate=True)
 
     # ------------------------------------------------------------------ forward
     def forward(self, tokens: torch.Tensor, targets: torch.Tensor | None = None, grad_accum_steps: int = 1,
@@ -322,25 +363,36 @@ class Transformer:
             if self.recompute == 2:
                 self._norm_fwd(res2, p["ln2w"][l], None if self.is_llama else p["ln2b"][l], ln2, mean2, a["ln2_rstd"][k])
             self._mlp_backward(l, k, gi, dres, d_btc, ln2)
+            self._join()   # the column sums over dres are done before the norm backward adds to it
             self._norm_bwd(dres, g["ln2w"][l], None if self.is_llama else g["ln2b"][l], d_btc, res2, p["ln2w"][l], mean2,
                            a["ln2_rstd"][k], accumulate=True)
             # ---- attention
             gemm.gemm_nn(dres, p["attprojw"][l], out=d_btc)
+            prep = [False]
+
+            def attention_side_work():
+                prep[0] = attn_ops.attention_bwd_prep(d_btc, a["atty"][k], a["dvec"], B, T, cfg.num_heads, cfg.head_size)
+                if not self.is_llama:
+                    ew.dbias(g["attprojb"][l], dres, accumulate=True)
+
+            self._fork(attention_side_work)
             gemm.gemm_tn(dres, a["atty"][k], out=g["attprojw"][l], accumulate=True)
-            if not self.is_llama:
-                ew.dbias(g["attprojb"][l], dres, accumulate=True)
+            self._join()   # D is needed now, and the next kernel overwrites the buffer that the MLP's column sum read
             dqkv = a["d_wide"].view(-1)[: BT * QW].view(BT, QW)
+            fused_rope = self._fused_rope()
             attn_ops.attention_bwd(d_btc, a["qkv"][k], a["atty"][k], a["lse"][k], B, T, cfg.num_heads, cfg.num_kv_heads,
-                                   cfg.head_size, dqkv=dqkv, dvec=a["dvec"])
-            if self.is_llama:
+                                   cfg.head_size, dqkv=dqkv, dvec=a["dvec"], rope=a["rope"] if fused_rope else None,
+                                   prep_done=prep[0])
+            if self.is_llama and not fused_rope:
                 ew.rope_qk_(dqkv, a["rope"], B, T, cfg.num_heads, cfg.num_kv_heads, cfg.head_size, self.rope_interleaved,
                             inverse=True)
             if self.recompute == 2:
                 self._norm_fwd(x_in, p["ln1w"][l], None if self.is_llama else p["ln1b"][l], ln1, mean1, a["ln1_rstd"][k])
+            if not self.is_llama:
+                self._fork(lambda: ew.dbias(g["qkvb"][l], dqkv, accumulate=True))
             gemm.gemm_nn(dqkv, p["qkvw"][l], out=d_btc)
             gemm.gemm_tn(dqkv, ln1, out=g["qkvw"][l], accumulate=True)
-            if not self.is_llama:
-                ew.dbias(g["qkvb"][l], dqkv, accumulate=True)
+            self._join()   # bias gradients of this block are complete before its bucket is handed over
             self._norm_bwd(dres, g["ln1w"][l], None if self.is_llama else g["ln1b"][l], d_btc, x_in, p["ln1w"][l], mean1,
                            a["ln1_rstd"][k], accumulate=True)
             if (last_micro_step or self.reduce_every_micro_step) and bucket_ready is not None:

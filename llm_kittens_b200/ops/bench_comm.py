@@ -102,6 +102,8 @@ def main() -> int:
         gx = comm_grid_x(max(r[2] for r in rs_rows))
         partials = torch.zeros(len(rs_rows) * gx, dtype=torch.float32, device=dev)
         flags = torch.zeros(nflags, dtype=torch.int32, device=dev)
+        arrivals = torch.zeros(nflags, dtype=torch.int32, device=dev)
+        bpc = max(1, min(16, 600 // max(1, nflags)))
         scale = torch.ones(1, device=dev)
         max_cps = max(r[4] for r in flag_rows)
 
@@ -123,7 +125,7 @@ def main() -> int:
 
         def agf():
             tick[0] += 1
-            N.call("llmk_comm_ag_bucket_flags", pshard_ptrs, params, flag_t, len(flag_rows), max_cps, P, flags, tick[0])
+            N.call("llmk_comm_ag_bucket_flags", pshard_ptrs, params, flag_t, len(flag_rows), max_cps, P, flags, arrivals, bpc, tick[0])
 
         bytes_in = (P - 1) * shard_n * 2          # what one GPU pulls (rs, ag) or pushes (adamw_push) per direction
         t_rs = timed(rs, before=signal)

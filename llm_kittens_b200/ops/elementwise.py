@@ -7,6 +7,8 @@ import torch
 from . import _native as N
 from .norm import _scratch
 
+_DBIAS_SCRATCH: dict[int, torch.Tensor] = {}
+
 
 def gelu_fwd(inp, out=None):
     out = torch.empty_like(inp) if out is None else out
@@ -80,7 +82,9 @@ def rope_qk_(qkv, freqs, B, T, NH, NKVH, HS, interleaved=True, inverse=False):
 def dbias(dbias_t, dout, accumulate=True):
     rows, OC = dout.shape
     nbytes = int(N.lib().llmk_dbias_scratch_bytes(rows, OC))
-    N.call("llmk_dbias", dbias_t, _scratch(nbytes), dout, rows, OC, int(accumulate))
+    # partial sums of its own: the model runs these column sums on a side stream while norm kernels use theirs
+    N.call("llmk_dbias", dbias_t, N.scratch_buffer(_DBIAS_SCRATCH, nbytes, 1 << 20, "bias-gradient partials"), dout, rows, OC,
+           int(accumulate))
     return dbias_t
 
 

@@ -124,6 +124,25 @@ def gemm_nt(a, b, bias=None, out=None, gelu_pre_out=None, add=None, groups=1):
     return _gemm(MODE_NT, epi, a, b, out, gelu_pre_out, bias, add, M, Nn, K, groups)
 
 
+def gemm_qkv_rope(a, w, rope, T, rope_cols, HS, out=None):
+    """QKV projection with RoPE applied in the epilogue: ``out = a @ w.T`` ([M, (NH + 2*NKVH)*HS] packed q | k | v), the
+    first ``rope_cols`` columns (q and k heads of ``HS`` columns) rotated by ``rope`` [T, HS/2, 2] (cos, sin of
+    interleaved pairs) for token ``row % T`` before rounding; v is stored as is."""
+    M, K = a.shape
+    Nn = w.shape[0]
+    for t, nm in ((a, "A"), (w, "B")):
+        N.require_cuda_tensor(t, torch.bfloat16, nm)
+    if out is None:
+        out = torch.empty(M, Nn, dtype=torch.bfloat16, device=a.device)
+    ready = _B_READY.get(w.data_ptr()) if _B_READY else None
+    if ready is not None and ready[3] > 0:
+        flags, _, chunk, tick, limit_ns = ready
+    else:
+        flags, chunk, tick, limit_ns = None, 1, 0, 0
+    N.call("llmk_gemm_qkv_rope", a, w, out, M, Nn, K, rope, T, rope_cols, HS, N.status_word(), _MAX_CTAS, flags, chunk, tick, limit_ns)
+    return out
+
+
 def gemm_nn(a, b, out=None, dgelu_of=None, add=None, groups=1):
     """``out = a @ b`` with ``a``: [M,K], ``b``: [K,N]; optionally ``* gelu'(dgelu_of)`` or ``+ add``.
     ``groups`` > 1: ``a`` [G*M,K], ``b`` [G,K,N] or [G*K,N], ``out`` / aux [G*M,N]."""

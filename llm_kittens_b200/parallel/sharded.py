@@ -230,6 +230,9 @@ class ShardedComm:
                 geometry[(q, nme)] = nflags
                 nflags += P * geometry[nme][0]
         self.ag_flags = torch.zeros(nflags, dtype=torch.int32, device=self.device)
+        self.ag_arrivals = torch.zeros(nflags, dtype=torch.int32, device=self.device)
+        # blocks per chunk: about 600 blocks per gather, so that enough peer loads are in flight to fill the links
+        self.ag_bpc = max(1, min(16, 600 // max(1, P * sum(geometry[n][0] for n in self.matrix_names))))
         self.ag_small_tables, self.ag_flag_tables = {}, {}
         for layer in range(self.L):
             small, flagged = [], []
@@ -267,7 +270,7 @@ class ShardedComm:
                 ev.record()           # the compute stream waits for the small tensors only
                 self._tick += 1
                 N.call("llmk_comm_ag_bucket_flags", self.param_shard_ptrs, dst, flagged, int(flagged.shape[0]), self.ag_max_cps,
-                       self.world_size, self.ag_flags, self._tick)
+                       self.world_size, self.ag_flags, self.ag_arrivals, self.ag_bpc, self._tick)
                 done = torch.cuda.Event()
                 done.record()
                 self._gathers_in_flight.append(done)

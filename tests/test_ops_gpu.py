@@ -248,6 +248,47 @@ def test_attention_long_sequences(B, T, NH, NKVH, HS, scale, dkv, monkeypatch):
     assert torch.equal(dqkv, dqkv2)
 
 
+def _rope_ref(x, table, B, T, heads, HS, inverse=False):
+    """fp32 rotation of the first ``heads`` heads of a packed [B*T, W] tensor, interleaved pairs."""
+    x = x.float().clone().view(B, T, -1)
+    part = x[..., : heads * HS].reshape(B, T, heads, HS // 2, 2)
+    cos, sin = table[..., 0][None, :, None, :], table[..., 1][None, :, None, :]
+    if inverse:
+        sin = -sin
+    x0, x1 = part[..., 0], part[..., 1]
+    rot = torch.stack([x0 * cos - x1 * sin, x0 * sin + x1 * cos], dim=-1)
+    x[..., : heads * HS] = rot.reshape(B, T, heads * HS)
+    return x.view(B * T, -1)
+
+
+@pytest.mark.parametrize("B,T,NH,NKVH,HS,C", [(2, 128, 4, 2, 64, 256), (1, 256, 8, 2, 128, 512), (1, 1024, 8, 2, 64, 512)])
+def test_rope_in_the_qkv_projection_and_in_the_attention_backward(B, T, NH, NKVH, HS, C):
+    """RoPE folded into the QKV GEMM's epilogue equals projection followed by an fp32 rotation; the attention backward
+    with the table returns dq / dk already rotated back, equal to the plain backward followed by the inverse rotation."""
+    from llm_kittens_b200.ops import _native, attention, elementwise as ew, gemm
+
+    torch.manual_seed(B * T + HS)
+    W = (NH + 2 * NKVH) * HS
+    x, w = rnd(B * T, C), rnd(W, C, scale=0.05)
+    table = ew.rope_tables(T, HS, 500000.0, False)
+    fused = gemm.gemm_qkv_rope(x, w, table, T, (NH + NKVH) * HS, HS)
+    _native.check_status()
+    ref = _rope_ref(x.float() @ w.float().T, table, B, T, NH + NKVH, HS)
+    assert maxerr(fused, ref) < 0.03
+    unfused = ew.rope_qk_(gemm.gemm_nt(x, w), table, B, T, NH, NKVH, HS, interleaved=True)
+    assert maxerr(fused, unfused) < 0.03
+    # backward
+    qkv = fused.view(B, T, W)
+    out, lse = attention.attention_fwd(qkv, B, T, NH, NKVH, HS)
+    dout = rnd(B, T, NH * HS)
+    plain = attention.attention_bwd(dout, qkv, out, lse, B, T, NH, NKVH, HS)
+    want = _rope_ref(plain.view(B * T, W), table, B, T, NH + NKVH, HS, inverse=True)
+    got = attention.attention_bwd(dout, qkv, out, lse, B, T, NH, NKVH, HS, rope=table)
+    _native.check_status()
+    assert maxerr(got.view(B * T, W), want) < 0.02 * max(1.0, want.abs().max().item())
+    assert torch.equal(got.view(B * T, W)[:, (NH + NKVH) * HS:], plain.view(B * T, W)[:, (NH + NKVH) * HS:])   # dv untouched
+
+
 def test_adamw_and_norm():
     from llm_kittens_b200.ops import optim
 
