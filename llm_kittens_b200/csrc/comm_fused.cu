@@ -68,9 +68,11 @@ __device__ __forceinline__ unsigned long long now_ns() {
 __device__ __forceinline__ bool wait_flags_block(const int* my_ctrl, int slot, int epoch, int P, long long limit_ns,
                                                  int* status, int tag) {
     __shared__ int sh_ok;
-    if (threadIdx.x == 0) sh_ok = 1;
+    // a failure already recorded by an earlier wait ends this one at once: one lost peer costs one time limit, not one
+    // per kernel that would have waited for it
+    if (threadIdx.x == 0) sh_ok = (status != nullptr && *reinterpret_cast<volatile int*>(status) != 0) ? 0 : 1;
     __syncthreads();
-    if ((int)threadIdx.x < P) {
+    if (sh_ok != 0 && (int)threadIdx.x < P) {
         const int* f = my_ctrl + slot * MAXP + threadIdx.x;
         const unsigned long long t0 = now_ns();
         unsigned int spins = 0;

@@ -398,6 +398,113 @@ LLMK_API int llmk_encoder_fwd(void* out, const void* tokens, const void* wte, co
     LLMK_LAUNCH_CHECK();
     return LLMK_OK;
 }
+// ------------------------------------------------------------------ bucketing positions by token id
+// Stable least-significant-digit radix sort of (token id, position) pairs, 9 bits per pass, on the device and without
+// a library: the embedding gradient sums the rows of each token id in ascending position order, which is what makes
+// it deterministic (job of the host-side bucket construction in the reference, llmc/encoder.cuh:169-234).
+// Per pass: (1) one 512-bin histogram per tile of 2048 pairs, (2) an exclusive scan over (digit, tile), (3) a
+// stable scatter: one warp walks its tile in order, a pair's rank inside its digit = pairs of that digit in earlier
+// tiles (scan) + earlier in this tile (running count in shared memory) + in lower lanes (match_any).
+namespace bucket {
+constexpr int BITS = 9, BINS = 1 << BITS, TILE = 2048;
+
+__global__ void __launch_bounds__(256)
+hist_kernel(int* __restrict__ hist, const int* __restrict__ keys, int n, int shift, int ntiles) {
+    __shared__ int h[BINS];
+    for (int i = threadIdx.x; i < BINS; i += blockDim.x) h[i] = 0;
+    __syncthreads();
+    const int base = blockIdx.x * TILE;
+    for (int i = threadIdx.x; i < TILE && base + i < n; i += blockDim.x) atomicAdd(&h[(keys[base + i] >> shift) & (BINS - 1)], 1);
+    __syncthreads();
+    for (int i = threadIdx.x; i < BINS; i += blockDim.x) hist[i * ntiles + blockIdx.x] = h[i];
+}
+
+// exclusive prefix sum of `m` ints in place, one block of 1024 threads (each thread owns a contiguous stretch)
+__global__ void __launch_bounds__(1024)
+scan_kernel(int* __restrict__ data, int m) {
+    __shared__ int part[1024];
+    const int per = (m + 1023) / 1024;
+    const int lo = min(m, (int)threadIdx.x * per), hi = min(m, lo + per);
+    int s = 0;
+    for (int i = lo; i < hi; i++) s += data[i];
+    part[threadIdx.x] = s;
+    __syncthreads();
+    for (int o = 1; o < 1024; o <<= 1) {
+        const int v = threadIdx.x >= o ? part[threadIdx.x - o] : 0;
+        __syncthreads();
+        part[threadIdx.x] += v;
+        __syncthreads();
+    }
+    int run = part[threadIdx.x] - s;
+    for (int i = lo; i < hi; i++) {
+        const int v = data[i];
+        data[i] = run;
+        run += v;
+    }
+}
+
+// vals_in == nullptr: the value of pair i is i (first pass)
+__global__ void __launch_bounds__(32)
+scatter_kernel(int* __restrict__ keys_out, int* __restrict__ vals_out, const int* __restrict__ keys_in,
+               const int* __restrict__ vals_in, const int* __restrict__ offsets, int n, int shift, int ntiles) {
+    __shared__ int running[BINS];
+    const int lane = threadIdx.x;
+    for (int i = lane; i < BINS; i += 32) running[i] = offsets[i * ntiles + blockIdx.x];
+    __syncwarp();
+    const int base = blockIdx.x * TILE;
+    for (int it = 0; it < TILE / 32; it++) {
+        const int i = base + it * 32 + lane;
+        const bool live = i < n;
+        const unsigned active = __ballot_sync(0xffffffffu, live);
+        if (live) {
+            const int key = keys_in[i];
+            const int d = (key >> shift) & (BINS - 1);
+            const unsigned same = __match_any_sync(active, d);
+            const int rank = __popc(same & ((1u << lane) - 1u));
+            const int dst = running[d] + rank;
+            keys_out[dst] = key;
+            vals_out[dst] = vals_in != nullptr ? vals_in[i] : i;
+            __syncwarp(active);
+            if (rank == 0) running[d] += __popc(same);   // the lowest lane of each digit group
+        }
+        __syncwarp();
+    }
+}
+}  // namespace bucket
+
+// sorted_tok / sorted_pos (n ints each) = positions 0..n-1 ordered by (tokens[pos], pos). `scratch`: at least
+// llmk_bucket_sort_scratch_ints(n) ints. `max_token` bounds the keys (number of 9-bit passes).
+LLMK_API long llmk_bucket_sort_scratch_ints(int n) { return 2L * n + (long)bucket::BINS * ceil_div(n, bucket::TILE); }
+LLMK_API int llmk_bucket_sort(void* sorted_tok, void* sorted_pos, const void* tokens, int n, int max_token, void* scratch,
+                              void* stream) {
+    if (n <= 0 || max_token <= 0) return LLMK_ERR_SHAPE;
+    cudaStream_t st = (cudaStream_t)stream;
+    const int ntiles = ceil_div(n, bucket::TILE);
+    if ((long)bucket::BINS * ntiles > (1L << 24)) return LLMK_ERR_SHAPE;
+    int passes = 1;
+    while (passes * bucket::BITS < 31 && (max_token >> (passes * bucket::BITS)) > 0) passes++;
+    int* tmp_k = (int*)scratch;
+    int* tmp_v = tmp_k + n;
+    int* hist = tmp_v + n;
+    const int* kin = (const int*)tokens;
+    const int* vin = nullptr;
+    for (int p = 0; p < passes; p++) {
+        // ping-pong so that the last pass lands in the output arrays
+        const bool to_out = ((passes - 1 - p) % 2) == 0;
+        int* kout = to_out ? (int*)sorted_tok : tmp_k;
+        int* vout = to_out ? (int*)sorted_pos : tmp_v;
+        bucket::hist_kernel<<<ntiles, 256, 0, st>>>(hist, kin, n, p * bucket::BITS, ntiles);
+        LLMK_LAUNCH_CHECK();
+        bucket::scan_kernel<<<1, 1024, 0, st>>>(hist, bucket::BINS * ntiles);
+        LLMK_LAUNCH_CHECK();
+        bucket::scatter_kernel<<<ntiles, 32, 0, st>>>(kout, vout, kin, vin, hist, n, p * bucket::BITS, ntiles);
+        LLMK_LAUNCH_CHECK();
+        kin = kout;
+        vin = vout;
+    }
+    return LLMK_OK;
+}
+
 // dwte += scatter of dout rows by token, dwpe += sum over batch (dwpe may be null for models without wpe).
 LLMK_API int llmk_encoder_bwd(void* dwte, void* dwpe, const void* dout, const void* sorted_tok, const void* sorted_pos, int B,
                               int T, int C, void* stream) {

@@ -918,6 +918,24 @@ LLMK_API int llmk_gemm_b_ready(int mode, int epi, const void* A, const void* B, 
     return gemm_impl(mode, epi, A, B, C, C2, bias, aux, M, N, K, 1, workspace, workspace_bytes, status, max_ctas, stream_, r);
 }
 
+// llmk_gemm_grouped whose A rows are still arriving (the token dispatch of an expert-parallel mixture of experts):
+// `a_ready` holds one int per `a_rows` consecutive rows of A (NT / NN), ready when >= `a_need`; the producer warp
+// polls, for at most limit_ns, only the entries that cover the M tile it is about to load. The counterpart of the
+// per-block release stores of llmk_moe_dispatch_signal (jobs of llmc/moe.cuh:121-237 + llmc/gemm_ext.cuh:132-158 +
+// llmc/distributed_ext.cuh:28-41 without a barrier between them).
+LLMK_API int llmk_gemm_grouped_a_ready(int mode, int epi, const void* A, const void* B, void* C, void* C2, const void* bias,
+                                       const void* aux, int M, int N, int K, int groups, void* workspace, long workspace_bytes,
+                                       int* status, int max_ctas, const void* a_ready, int a_rows, int a_need, long limit_ns,
+                                       void* stream_) {
+    Ready r;
+    r.a_ready = static_cast<const int*>(a_ready);
+    r.a_rows = a_rows;
+    r.a_need = a_need;
+    r.limit_ns = limit_ns;
+    if (a_ready != nullptr && a_rows <= 0) return LLMK_ERR_SHAPE;
+    return gemm_impl(mode, epi, A, B, C, C2, bias, aux, M, N, K, groups, workspace, workspace_bytes, status, max_ctas, stream_, r);
+}
+
 // QKV projection with RoPE in the epilogue: C = A B^T where C is a packed [tokens, (NH + 2 NKVH) * HS] tensor; the
 // q and k heads (the first `rope_cols` columns) are rotated by the (cos, sin) table `rope` [T, HS/2] (interleaved
 // pairs) before they are rounded to bf16, v passes through. Row r is token r % T. Optional `b_ready` as in

@@ -11,7 +11,12 @@
 //     the rank that owns the expert (or read from / written to the local one when that rank is this
 //     rank) through a table of peer pointers, so there is no packed send buffer and no collective
 //     call; padded capacity slots are zero-filled by the sender so they add nothing to any gradient;
-//   * every token row of the combine is produced by exactly one warp (no atomic adds).
+//   * every token row of the combine is produced by exactly one warp (no atomic adds);
+//   * there is no layer-wide barrier between the stages. The kernel that finishes a block of rows publishes it with a
+//     release store into the consumer rank's arrival table, and the consumer waits inside the kernel that needs the
+//     rows: the grouped expert GEMM's producer warp polls only the entries that cover the M tile it is about to load
+//     (rows of one source rank), the combine kernel polls the owners' "returned" entries before its first load.
+//     An entry holds the number of the exchange (a counter that only grows), so nothing is ever reset.
 //
 // Buffer layouts (C channels, cap = capacity per (source rank, expert), Eloc experts per rank):
 //   owner side   recv[e_local][src][cap][C]   rows routed to local expert e_local by rank src
@@ -28,6 +33,59 @@ constexpr int MAXK = 4;
 struct Peers {
     void* p[MAXP];
 };
+
+__device__ __forceinline__ void st_release_sys(int* ptr, int v) {
+    asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(ptr), "r"(v) : "memory");
+}
+__device__ __forceinline__ int ld_acquire_sys(const int* ptr) {
+    int v;
+    asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(ptr) : "memory");
+    return v;
+}
+__device__ __forceinline__ unsigned long long now_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+
+// The CTA that finishes a kernel's work last (an arrival counter in local memory, left at zero again) returns true
+// in thread 0, after a system-scope fence that covers the stores of every CTA (each fenced before it arrived).
+__device__ __forceinline__ bool last_cta_done(int* counter, int total) {
+    __syncthreads();
+    if (threadIdx.x != 0) return false;
+    __threadfence_system();
+    if (atomicAdd(counter, 1) != total - 1) return false;
+    *counter = 0;
+    __threadfence_system();
+    return true;
+}
+
+// Threads 0..n-1 of the block poll flags[0..n) until each is >= need, for at most limit_ns; false (to every thread)
+// when the time ran out: LLMK_ST_TIMEOUT_PEER goes to the status word and the caller skips its work.
+__device__ __forceinline__ bool wait_entries_block(const int* flags, int n, int need, long long limit_ns, int* status, int tag) {
+    __shared__ int sh_ok;
+    // a failure already recorded (by an earlier kernel or block) ends this wait at once
+    if (threadIdx.x == 0) sh_ok = (status != nullptr && *reinterpret_cast<volatile int*>(status) != 0) ? 0 : 1;
+    __syncthreads();
+    if (sh_ok != 0 && (int)threadIdx.x < n) {
+        const unsigned long long t0 = now_ns();
+        unsigned int spins = 0;
+        while (ld_acquire_sys(flags + threadIdx.x) < need) {
+            if ((++spins & 31u) == 0 && (long long)(now_ns() - t0) > limit_ns) {
+                sh_ok = 0;
+                if (status != nullptr && atomicCAS(status, 0, LLMK_ST_TIMEOUT_PEER) == 0) {
+                    status[1] = tag;
+                    status[2] = (int)blockIdx.x;
+                    status[3] = (int)threadIdx.x;
+                }
+                break;
+            }
+            __nanosleep(64);
+        }
+    }
+    __syncthreads();
+    return sh_ok != 0;
+}
 
 // ------------------------------------------------------------------ router
 // One warp per token: logits = x . Wr^T (fp32), softmax over E, top-K (ties -> lower expert index),
@@ -165,8 +223,13 @@ dispatch_kernel(Peers recv, const bf16* __restrict__ x, const int* __restrict__ 
     }
 }
 // Zero the unused slots [counts[e], cap) of this rank's block in every expert's receive buffer.
+// `arrive` (optional): the owners' arrival tables. This kernel runs after dispatch_kernel on the same stream, so when
+// its last CTA is done every row of this rank has been stored: that CTA release-stores `epoch` into entry
+// [e_local * P + my_rank] of the owner of every expert, which is entry (first row of the block) / cap of the
+// owner's receive buffer, the index the expert GEMM derives from the rows of a tile.
 __global__ void __launch_bounds__(256)
-zero_pad_kernel(Peers recv, const int* __restrict__ counts, int E, int C, int cap, int Eloc, int my_rank, int P) {
+zero_pad_kernel(Peers recv, const int* __restrict__ counts, int E, int C, int cap, int Eloc, int my_rank, int P, Peers arrive,
+                int arrive_off, int* done_counter, int epoch) {
     const int e = blockIdx.y;
     const int owner = e / Eloc, el = e % Eloc;
     const int first = counts[e];
@@ -177,13 +240,20 @@ zero_pad_kernel(Peers recv, const int* __restrict__ counts, int E, int C, int ca
     for (int i = 0; i < 4; i++) z.v[i] = __floats2bfloat162_rn(0.f, 0.f);
     for (size_t i = begin + ((size_t)blockIdx.x * blockDim.x + threadIdx.x) * 8; i < end; i += (size_t)gridDim.x * blockDim.x * 8)
         st128(base + i, z);
+    if (done_counter != nullptr && last_cta_done(done_counter, gridDim.x * gridDim.y)) {
+        for (int ee = 0; ee < E; ee++)
+            st_release_sys(static_cast<int*>(arrive.p[ee / Eloc]) + arrive_off + (ee % Eloc) * P + my_rank, epoch);
+    }
 }
 
 // ------------------------------------------------------------------ return (all-to-all back)
 // Owner side: copy the block of rows that rank `src` sent to local expert `el` back into that rank's
 // `back[e][cap][C]` buffer. grid = (chunks, P, Eloc).
+// `arrive` (optional): the source ranks' arrival tables; the CTA that finishes the block of (src, el) last
+// release-stores `epoch` into entry [arrive_off + e] of rank src (e = this rank's global expert index).
 __global__ void __launch_bounds__(256)
-return_kernel(Peers back, const bf16* __restrict__ y, int C, int cap, int Eloc, int my_rank, int P) {
+return_kernel(Peers back, const bf16* __restrict__ y, int C, int cap, int Eloc, int my_rank, int P, Peers arrive, int arrive_off,
+              int* done_counters, int epoch) {
     const int src = blockIdx.y, el = blockIdx.z;
     const int e = my_rank * Eloc + el;
     const bf16* from = y + (((size_t)el * P + src) * cap) * C;
@@ -191,14 +261,20 @@ return_kernel(Peers back, const bf16* __restrict__ y, int C, int cap, int Eloc, 
     const size_t n = (size_t)cap * C;
     for (size_t i = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) * 8; i < n; i += (size_t)gridDim.x * blockDim.x * 8)
         st128(to + i, ld128(from + i));
+    if (done_counters != nullptr && last_cta_done(done_counters + el * P + src, gridDim.x))
+        st_release_sys(static_cast<int*>(arrive.p[src]) + arrive_off + e, epoch);
 }
 
 // ------------------------------------------------------------------ combine
 // out[t] = base[t] + sum_k w[t,k] * back[e(t,k)][slot(t,k)]   (dropped assignments contribute 0).
 // With `weights == nullptr` the rows are summed unweighted (input-gradient gather in backward).
+// `returned` (optional): this rank's arrival entries of the E experts; every block waits (bounded) until each holds
+// `epoch`, i.e. until every owner has stored the rows of this rank into `back`.
 __global__ void __launch_bounds__(256)
 combine_kernel(bf16* __restrict__ out, const bf16* __restrict__ base, const bf16* __restrict__ back, const int* __restrict__ top_idx,
-               const int* __restrict__ slot, const float* __restrict__ weights, int N, int K, int C, int cap) {
+               const int* __restrict__ slot, const float* __restrict__ weights, int N, int K, int C, int cap,
+               const int* __restrict__ returned, int E, int epoch, long long limit_ns, int* status) {
+    if (returned != nullptr && !wait_entries_block(returned, E, epoch, limit_ns, status, 300)) return;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const size_t t = (size_t)blockIdx.x * (blockDim.x >> 5) + warp;
     if (t >= (size_t)N) return;
@@ -343,14 +419,43 @@ LLMK_API int llmk_moe_dispatch(const long long* recv_ptrs, const void* x, const 
     dispatch_kernel<<<ceil_div((long)N * K, 8), 256, 0, st>>>(recv, (const bf16*)x, (const int*)top_idx, (const int*)slot,
                                                              (const float*)top_w, N, K, C, cap, Eloc, my_rank, P, scale_by_weight);
     LLMK_LAUNCH_CHECK();
-    zero_pad_kernel<<<dim3(32, E), 256, 0, st>>>(recv, (const int*)counts, E, C, cap, Eloc, my_rank, P);
+    zero_pad_kernel<<<dim3(32, E), 256, 0, st>>>(recv, (const int*)counts, E, C, cap, Eloc, my_rank, P, recv, 0, nullptr, 0);
+    LLMK_LAUNCH_CHECK();
+    return LLMK_OK;
+}
+// Dispatch that publishes its completion: `arrive_ptrs` = the P ranks' arrival tables (int), `arrive_off` the first
+// entry of this exchange in them, `done_counter` one zeroed int of local scratch, `epoch` the number of the exchange.
+LLMK_API int llmk_moe_dispatch_signal(const long long* recv_ptrs, const void* x, const void* top_idx, const void* slot,
+                                      const void* top_w, const void* counts, int N, int K, int C, int E, int cap, int my_rank, int P,
+                                      int scale_by_weight, const long long* arrive_ptrs, int arrive_off, void* done_counter,
+                                      int epoch, void* stream) {
+    if (P > MAXP || E % P || C % 8 || arrive_ptrs == nullptr || done_counter == nullptr) return LLMK_ERR_SHAPE;
+    cudaStream_t st = (cudaStream_t)stream;
+    const Peers recv = make_peers(recv_ptrs, P);
+    const int Eloc = E / P;
+    dispatch_kernel<<<ceil_div((long)N * K, 8), 256, 0, st>>>(recv, (const bf16*)x, (const int*)top_idx, (const int*)slot,
+                                                             (const float*)top_w, N, K, C, cap, Eloc, my_rank, P, scale_by_weight);
+    LLMK_LAUNCH_CHECK();
+    zero_pad_kernel<<<dim3(32, E), 256, 0, st>>>(recv, (const int*)counts, E, C, cap, Eloc, my_rank, P, make_peers(arrive_ptrs, P),
+                                                 arrive_off, (int*)done_counter, epoch);
     LLMK_LAUNCH_CHECK();
     return LLMK_OK;
 }
 LLMK_API int llmk_moe_return(const long long* back_ptrs, const void* y, int C, int E, int cap, int my_rank, int P, void* stream) {
     if (P > MAXP || E % P) return LLMK_ERR_SHAPE;
+    const Peers back = make_peers(back_ptrs, P);
+    return_kernel<<<dim3(32, P, E / P), 256, 0, (cudaStream_t)stream>>>(back, (const bf16*)y, C, cap, E / P, my_rank, P, back, 0,
+                                                                      nullptr, 0);
+    LLMK_LAUNCH_CHECK();
+    return LLMK_OK;
+}
+// Return that publishes each (source rank, local expert) block as it completes; `done_counters`: Eloc * P zeroed ints.
+LLMK_API int llmk_moe_return_signal(const long long* back_ptrs, const void* y, int C, int E, int cap, int my_rank, int P,
+                                    const long long* arrive_ptrs, int arrive_off, void* done_counters, int epoch, void* stream) {
+    if (P > MAXP || E % P || arrive_ptrs == nullptr || done_counters == nullptr) return LLMK_ERR_SHAPE;
     return_kernel<<<dim3(32, P, E / P), 256, 0, (cudaStream_t)stream>>>(make_peers(back_ptrs, P), (const bf16*)y, C, cap, E / P,
-                                                                      my_rank, P);
+                                                                      my_rank, P, make_peers(arrive_ptrs, P), arrive_off,
+                                                                      (int*)done_counters, epoch);
     LLMK_LAUNCH_CHECK();
     return LLMK_OK;
 }
@@ -358,7 +463,19 @@ LLMK_API int llmk_moe_combine(void* out, const void* base, const void* back, con
                               const void* weights, int N, int K, int C, int cap, void* stream) {
     combine_kernel<<<ceil_div(N, 8), 256, 0, (cudaStream_t)stream>>>((bf16*)out, (const bf16*)base, (const bf16*)back,
                                                                     (const int*)top_idx, (const int*)slot, (const float*)weights,
-                                                                    N, K, C, cap);
+                                                                    N, K, C, cap, nullptr, 0, 0, 0, nullptr);
+    LLMK_LAUNCH_CHECK();
+    return LLMK_OK;
+}
+// Combine that first waits (inside the kernel, for at most limit_ns) until `returned[0..E)` all hold `epoch`.
+LLMK_API int llmk_moe_combine_wait(void* out, const void* base, const void* back, const void* top_idx, const void* slot,
+                                   const void* weights, int N, int K, int C, int cap, const void* returned, int E, int epoch,
+                                   long limit_ns, int* status, void* stream) {
+    if (returned == nullptr || E <= 0 || E > MAXE) return LLMK_ERR_SHAPE;
+    combine_kernel<<<ceil_div(N, 8), 256, 0, (cudaStream_t)stream>>>((bf16*)out, (const bf16*)base, (const bf16*)back,
+                                                                    (const int*)top_idx, (const int*)slot, (const float*)weights,
+                                                                    N, K, C, cap, (const int*)returned, E, epoch,
+                                                                    (long long)limit_ns, status);
     LLMK_LAUNCH_CHECK();
     return LLMK_OK;
 }

@@ -10,6 +10,9 @@ semantics:
 * dispatch / combine are direct row stores / loads through a table of peer pointers: rank r owns
   experts ``[r*E/P, (r+1)*E/P)`` and receives rows in ``recv[e_local][src][cap][C]``; padded slots are
   zeroed by the sender. With one process the same kernels run on a single-entry table;
+* no barrier separates dispatch, expert GEMMs, return and combine: each producer publishes its blocks
+  in the consumer's arrival table and each consumer waits inside its kernel for exactly what it reads
+  (the grouped GEMM per M tile, i.e. per source rank; the combine for its owners);
 * expert ``y = GELU(x W1^T + b1) W2^T + b2`` = two tcgen05 GEMMs per local expert on its row block;
 * output ``res3 = res2 + sum_k w_k y_k``; auxiliary loss ``coef * E * sum_e density_e^2`` (density =
   mean router probability per expert on this rank) is added to the reported loss and to the router
@@ -35,8 +38,14 @@ class LocalExchange:
 
     world_size, rank = 1, 0
 
+    limit_ns = int(2e9)
+
     def alloc(self, numel: int, device) -> tuple[torch.Tensor, object]:
         t = torch.zeros(numel, dtype=BF16, device=device)
+        return t, moe_ops.ptr_table([t])
+
+    def arrival_table(self, entries: int, device=None):
+        t = torch.zeros(entries, dtype=torch.int32, device=device)
         return t, moe_ops.ptr_table([t])
 
     def sync(self, tag: int) -> None:
@@ -96,6 +105,11 @@ class MoETransformer(Transformer):
         self.recv_dy = t.view(rows, C)
         t, self.back_dx_ptrs = self.exchange.alloc(E * cap * C, dev)
         self.back_dx = t.view(E * cap, C)
+        # arrival tables: E entries per (layer, exchange), exchange 0 = tokens out, 1 = expert outputs back,
+        # 2 = output gradients out, 3 = input gradients back; the values are exchange numbers that only grow
+        self.arrive, self.arrive_ptrs = self.exchange.arrival_table(L * 4 * E, dev)
+        self.done = torch.zeros(1 + Eloc * P, dtype=i32, device=dev)
+        self._epoch = 0
 
     def _dense_mlp_buffers(self) -> bool:
         return False
@@ -113,20 +127,23 @@ class MoETransformer(Transformer):
         moe_ops.router_fwd(ln2, p["routerw"][l], K, a["probs"][l], a["top_idx"][l], a["top_w"][l])
         moe_ops.assign_slots(a["top_idx"][l], E, cap, a["slot"][l], a["counts"][l])
         moe_ops.density(a["probs"][l], cfg.aux_loss_coef * self._loss_scale, a["density"][l], a["aux_acc"], accumulate=True)
-        moe_ops.dispatch(self.recv_x_ptrs[l], ln2, a["top_idx"][l], a["slot"][l], a["top_w"][l], a["counts"][l], E, cap,
-                         self.ep_rank, P, scale_by_weight=False)
-        self.exchange.sync(4 * l + 0)
+        ep, lim = self._epoch, self.exchange.limit_ns
+        r_out, r_back = (4 * l + 0) * E, (4 * l + 1) * E
+        moe_ops.dispatch_signal(self.recv_x_ptrs[l], ln2, a["top_idx"][l], a["slot"][l], a["top_w"][l], a["counts"][l], E, cap,
+                                self.ep_rank, P, False, self.arrive_ptrs, r_out, self.done[0:1], ep)
         per = P * cap
         act_l = a["hid_act"][0 if self.recompute >= 1 else l]
         # the local experts have equal row counts (P * capacity): one grouped launch per projection
         G, loc = self.Eloc, slice(self.ep_rank * self.Eloc, (self.ep_rank + 1) * self.Eloc)
         rows = slice(0, G * per)
+        # every M tile of the first GEMM waits only for the source rank whose rows it loads
         gemm.gemm_nt(self.recv_x[l][rows], p["fcw"][l][loc], bias=p["fcb"][l][loc], out=act_l[rows],
-                     gelu_pre_out=a["hid_pre"][l][rows], groups=G)
+                     gelu_pre_out=a["hid_pre"][l][rows], groups=G, a_ready=(self.arrive[r_out:], cap, ep, lim))
         gemm.gemm_nt(act_l[rows], p["fcprojw"][l][loc], bias=p["fcprojb"][l][loc], out=a["y_loc"][rows], groups=G)
-        moe_ops.return_rows(self.back_y_ptrs[l], a["y_loc"], cfg.channels, E, cap, self.ep_rank, P)
-        self.exchange.sync(4 * l + 1)
-        moe_ops.combine(out, res2, self.back_y[l], a["top_idx"][l], a["slot"][l], a["top_w"][l], cap)
+        moe_ops.return_signal(self.back_y_ptrs[l], a["y_loc"], cfg.channels, E, cap, self.ep_rank, P, self.arrive_ptrs, r_back,
+                              self.done[1:], ep)
+        moe_ops.combine_wait(out, res2, self.back_y[l], a["top_idx"][l], a["slot"][l], a["top_w"][l], cap,
+                             self.arrive[r_back:], E, ep, lim)
 
     def _mlp_backward(self, l, k, gi, dres, d_ln2, ln2):
         a, p, g, cfg = self.acts, self.p, self.g, self.config
@@ -134,8 +151,10 @@ class MoETransformer(Transformer):
         N = self.B * self.T
         idx, slot, w = a["top_idx"][l], a["slot"][l], a["top_w"][l]
         moe_ops.combine_dweight(dres, self.back_y[l], idx, slot, cap, dw=a["dw"])
-        moe_ops.dispatch(self.recv_dy_ptrs, dres, idx, slot, w, a["counts"][l], E, cap, self.ep_rank, P, scale_by_weight=True)
-        self.exchange.sync(4 * l + 2)
+        ep, lim = self._epoch, self.exchange.limit_ns
+        r_out, r_back = (4 * l + 2) * E, (4 * l + 3) * E
+        moe_ops.dispatch_signal(self.recv_dy_ptrs, dres, idx, slot, w, a["counts"][l], E, cap, self.ep_rank, P, True,
+                                self.arrive_ptrs, r_out, self.done[0:1], ep)
         per = P * cap
         act_l = a["hid_act"][0 if self.recompute >= 1 else l]
         G, loc = self.Eloc, slice(self.ep_rank * self.Eloc, (self.ep_rank + 1) * self.Eloc)
@@ -143,8 +162,10 @@ class MoETransformer(Transformer):
         dy, x, d_hid = self.recv_dy[rows], self.recv_x[l][rows], a["d_hid"][rows]
         if self.recompute >= 1:
             ew.gelu_fwd(a["hid_pre"][l][rows], out=act_l[rows])
+        # the first consumer of dy waits tile by tile for its source ranks; the products after it find dy complete
+        gemm.gemm_nn(dy, p["fcprojw"][l][loc], out=d_hid, dgelu_of=a["hid_pre"][l][rows], groups=G,
+                     a_ready=(self.arrive[r_out:], cap, ep, lim))
         gemm.gemm_tn(dy, act_l[rows], out=g["fcprojw"][l][loc], accumulate=True, groups=G)
-        gemm.gemm_nn(dy, p["fcprojw"][l][loc], out=d_hid, dgelu_of=a["hid_pre"][l][rows], groups=G)
         gemm.gemm_tn(d_hid, x, out=g["fcw"][l][loc], accumulate=True, groups=G)
         gemm.gemm_nn(d_hid, p["fcw"][l][loc], out=a["y_loc"][rows], groups=G)
         for el in range(G):
@@ -152,9 +173,8 @@ class MoETransformer(Transformer):
             r = slice(el * per, (el + 1) * per)
             ew.dbias(gb2, dy[r], accumulate=True)
             ew.dbias(gb1, d_hid[r], accumulate=True)
-        moe_ops.return_rows(self.back_dx_ptrs, a["y_loc"], C, E, cap, self.ep_rank, P)
-        self.exchange.sync(4 * l + 3)
-        moe_ops.combine(d_ln2, None, self.back_dx, idx, slot, None, cap)
+        moe_ops.return_signal(self.back_dx_ptrs, a["y_loc"], C, E, cap, self.ep_rank, P, self.arrive_ptrs, r_back, self.done[1:], ep)
+        moe_ops.combine_wait(d_ln2, None, self.back_dx, idx, slot, None, cap, self.arrive[r_back:], E, ep, lim)
         # router: gradient through the renormalised top-k weights plus the load-balance term
         aux_scale = cfg.aux_loss_coef * E * 2.0 / N * self._loss_scale
         dlog = moe_ops.router_bwd(a["probs"][l], idx, w, a["dw"], slot, a["density"][l], aux_scale, dlogits=a["dlogits"])
@@ -169,6 +189,7 @@ class MoETransformer(Transformer):
     # ------------------------------------------------------------------ forward wrapper: aux-loss bookkeeping
     def forward(self, tokens, targets=None, grad_accum_steps: int = 1, micro_step: int = 0, compute_dlogits: bool = True):
         self.allocate(*tokens.shape)
+        self._epoch += 1          # number of this micro-step's exchanges (forward and backward)
         self._loss_scale = 1.0 / grad_accum_steps
         if micro_step == 0:
             self.acts["aux_acc"].zero_()

@@ -54,7 +54,8 @@ def lib() -> ctypes.CDLL:
                     _build.build()
                 handle = ctypes.CDLL(str(path))
                 handle.llmk_last_error.restype = ctypes.c_char_p
-                for fn in ("llmk_gemm_workspace_bytes", "llmk_norm_bwd_scratch_bytes", "llmk_dbias_scratch_bytes"):
+                for fn in ("llmk_gemm_workspace_bytes", "llmk_norm_bwd_scratch_bytes", "llmk_dbias_scratch_bytes",
+                           "llmk_bucket_sort_scratch_ints"):
                     getattr(handle, fn).restype = ctypes.c_long
                 handle.llmk_optim_grid_x.argtypes = [ctypes.c_long]
                 _LIB = handle
@@ -88,7 +89,7 @@ def _conv(a: Any):
 
 # kernels launched by one call of a library entry point (default 1); used for the launch counter
 _KERNELS_PER_CALL = {"llmk_layernorm_bwd": 2, "llmk_rmsnorm_bwd": 2, "llmk_dbias": 2, "llmk_attention_bwd": 3, "llmk_attention_bwd_tc": 2,
-                     "llmk_encoder_bwd": 2, "llmk_global_norm2": 2}
+                     "llmk_encoder_bwd": 2, "llmk_global_norm2": 2, "llmk_bucket_sort": 6, "llmk_moe_dispatch_signal": 2, "llmk_moe_dispatch": 2}
 _LAUNCHES = 0
 
 

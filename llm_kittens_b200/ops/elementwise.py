@@ -96,10 +96,30 @@ def encoder_fwd(tokens, wte, wpe, out=None):
     return out
 
 
+_BUCKETS: dict[tuple, tuple] = {}
+
+
+def bucket_sort(tokens: torch.Tensor, max_token: int):
+    """(sorted token ids, positions) of the flattened int32 ``tokens``, ordered by (token id, position): the
+    framework's own stable radix sort on the device (no library sort, no allocation after the first call for a
+    given size). The returned tensors are reused by the next call with the same number of tokens."""
+    n = tokens.numel()
+    key = (tokens.device.index, n)
+    if key not in _BUCKETS:
+        dev = tokens.device
+        ints = int(N.lib().llmk_bucket_sort_scratch_ints(n))
+        _BUCKETS[key] = (torch.empty(n, dtype=torch.int32, device=dev), torch.empty(n, dtype=torch.int32, device=dev),
+                         torch.empty(ints, dtype=torch.int32, device=dev))
+    st, sp, scratch = _BUCKETS[key]
+    N.call("llmk_bucket_sort", st, sp, tokens, n, int(max_token), scratch)
+    return st, sp
+
+
 def encoder_bwd(dwte, dwpe, dout, tokens):
     """Deterministic: positions are bucketed by token id with a stable device sort, then each token's
     rows are summed in ascending position order."""
     B, T = tokens.shape
     C = dwte.shape[1]
-    sorted_tok, sorted_pos = torch.sort(tokens.reshape(-1), stable=True)
-    N.call("llmk_encoder_bwd", dwte, dwpe, dout, sorted_tok.to(torch.int32), sorted_pos.to(torch.int32), B, T, C)
+    N.require_cuda_tensor(tokens, torch.int32, "tokens")
+    sorted_tok, sorted_pos = bucket_sort(tokens, dwte.shape[0])
+    N.call("llmk_encoder_bwd", dwte, dwpe, dout, sorted_tok, sorted_pos, B, T, C)

@@ -59,8 +59,10 @@ def tile_rows() -> int:
     return _TILE_ROWS
 
 
-def _gemm(mode, epi, a, b, c, c2, bias, aux, M, Nn, K, groups=1):
-    """``M``, ``Nn``, ``K`` are the dimensions of ONE group; operands of a grouped call are stacked along their rows."""
+def _gemm(mode, epi, a, b, c, c2, bias, aux, M, Nn, K, groups=1, a_ready=None):
+    """``M``, ``Nn``, ``K`` are the dimensions of ONE group; operands of a grouped call are stacked along their rows.
+    ``a_ready`` = (int32 tensor, rows per entry, needed value, time limit in ns): the rows of A are still arriving and
+    entry ``row // rows_per_entry`` tells when a block of them is complete (NT / NN only)."""
     for t, nm in ((a, "A"), (b, "B"), (c, "C")):
         N.require_cuda_tensor(t, torch.bfloat16, nm)
     if groups > 1 and (M % tile_rows() or (mode != MODE_NT and K % 64)):
@@ -68,8 +70,9 @@ def _gemm(mode, epi, a, b, c, c2, bias, aux, M, Nn, K, groups=1):
         a_rows, b_rows = (K, K) if mode == MODE_TN else (M, Nn if mode == MODE_NT else K)
         for g in range(groups):
             cut = lambda t, r: None if t is None else t[g * r:(g + 1) * r]
+            ar = None if a_ready is None else (a_ready[0][g * (M // a_ready[1]):], *a_ready[1:])
             _gemm(mode, epi, cut(a, a_rows), cut(b, b_rows), cut(c, M), cut(c2, M), cut(bias, Nn) if bias is not None and bias.dim() == 1 else bias,
-                  cut(aux, M), M, Nn, K)
+                  cut(aux, M), M, Nn, K, a_ready=ar)
         return c
     ws = None
     ws_bytes = 0
@@ -79,7 +82,13 @@ def _gemm(mode, epi, a, b, c, c2, bias, aux, M, Nn, K, groups=1):
             ws = workspace(ws_bytes)
             ws_bytes = ws.numel()
     ready = _B_READY.get(b.data_ptr()) if (_B_READY and mode != MODE_TN) else None
-    if groups > 1:
+    if a_ready is not None:
+        if mode == MODE_TN or M % a_ready[1]:
+            raise N.NativeError("gemm: a_ready needs an NT / NN product whose group rows are whole flag blocks")
+        flags, rows_per, need, limit_ns = a_ready
+        N.call("llmk_gemm_grouped_a_ready", mode, epi, a, b, c, c2, bias, aux, M, Nn, K, groups, ws, ws_bytes, N.status_word(),
+               _MAX_CTAS, flags, rows_per, need, limit_ns)
+    elif groups > 1:
         N.call("llmk_gemm_grouped", mode, epi, a, b, c, c2, bias, aux, M, Nn, K, groups, ws, ws_bytes, N.status_word(), _MAX_CTAS)
     elif ready is not None and ready[3] > 0:
         flags, first, chunk, tick, limit_ns = ready
@@ -98,7 +107,7 @@ def _flat2(t, groups):
     return t.view(-1, t.shape[-1])
 
 
-def gemm_nt(a, b, bias=None, out=None, gelu_pre_out=None, add=None, groups=1):
+def gemm_nt(a, b, bias=None, out=None, gelu_pre_out=None, add=None, groups=1, a_ready=None):
     """``out = a @ b.T (+ bias) (+ add)``; with ``gelu_pre_out`` the pre-activation goes there and
     ``out`` gets tanh-GELU of it. ``a``: [M,K], ``b``: [N,K].
 
@@ -121,7 +130,7 @@ def gemm_nt(a, b, bias=None, out=None, gelu_pre_out=None, add=None, groups=1):
         epi |= EPI_GELU
     if add is not None:
         epi |= EPI_ADD
-    return _gemm(MODE_NT, epi, a, b, out, gelu_pre_out, bias, add, M, Nn, K, groups)
+    return _gemm(MODE_NT, epi, a, b, out, gelu_pre_out, bias, add, M, Nn, K, groups, a_ready=a_ready)
 
 
 def gemm_qkv_rope(a, w, rope, T, rope_cols, HS, out=None):
@@ -143,7 +152,7 @@ def gemm_qkv_rope(a, w, rope, T, rope_cols, HS, out=None):
     return out
 
 
-def gemm_nn(a, b, out=None, dgelu_of=None, add=None, groups=1):
+def gemm_nn(a, b, out=None, dgelu_of=None, add=None, groups=1, a_ready=None):
     """``out = a @ b`` with ``a``: [M,K], ``b``: [K,N]; optionally ``* gelu'(dgelu_of)`` or ``+ add``.
     ``groups`` > 1: ``a`` [G*M,K], ``b`` [G,K,N] or [G*K,N], ``out`` / aux [G*M,N]."""
     b = _flat2(b, groups)
@@ -159,7 +168,7 @@ def gemm_nn(a, b, out=None, dgelu_of=None, add=None, groups=1):
         epi, aux = EPI_DGELU, dgelu_of
     elif add is not None:
         epi, aux = EPI_ADD, add
-    return _gemm(MODE_NN, epi, a, b, out, None, None, aux, M, Nn, K, groups)
+    return _gemm(MODE_NN, epi, a, b, out, None, None, aux, M, Nn, K, groups, a_ready=a_ready)
 
 
 def gemm_tn(a, b, out=None, accumulate=False, groups=1):

@@ -41,6 +41,28 @@ def dispatch(recv_ptrs, x, top_idx, slot, top_w, counts, E, cap, rank=0, P=1, sc
     N.call("llmk_moe_dispatch", recv_ptrs, x, top_idx, slot, top_w, counts, Nn, K, x.shape[1], E, cap, rank, P, int(scale_by_weight))
 
 
+def dispatch_signal(recv_ptrs, x, top_idx, slot, top_w, counts, E, cap, rank, P, scale_by_weight, arrive_ptrs, arrive_off, done, epoch):
+    """:func:`dispatch` whose last block release-stores ``epoch`` into entry ``arrive_off + e_local * P + rank`` of the
+    owner of every expert (``arrive_ptrs``: the ranks' arrival tables; ``done``: one zeroed int32 of local scratch)."""
+    Nn, K = top_idx.shape
+    N.call("llmk_moe_dispatch_signal", recv_ptrs, x, top_idx, slot, top_w, counts, Nn, K, x.shape[1], E, cap, rank, P,
+           int(scale_by_weight), arrive_ptrs, arrive_off, done, epoch)
+
+
+def return_signal(back_ptrs, y, C, E, cap, rank, P, arrive_ptrs, arrive_off, done, epoch):
+    """:func:`return_rows` that publishes every (source rank, local expert) block with a release store of ``epoch`` into
+    entry ``arrive_off + e`` of the source rank's arrival table (``done``: ``E/P * P`` zeroed int32 of local scratch)."""
+    N.call("llmk_moe_return_signal", back_ptrs, y, C, E, cap, rank, P, arrive_ptrs, arrive_off, done, epoch)
+
+
+def combine_wait(out, base, back, top_idx, slot, weights, cap, returned, E, epoch, limit_ns):
+    """:func:`combine` that first waits inside the kernel (bounded) until ``returned[0:E]`` all hold ``epoch``."""
+    Nn, K = top_idx.shape
+    N.call("llmk_moe_combine_wait", out, base, back, top_idx, slot, weights, Nn, K, out.shape[1], cap, returned, E, epoch, limit_ns,
+           N.status_word())
+    return out
+
+
 def return_rows(back_ptrs, y, C, E, cap, rank=0, P=1):
     N.call("llmk_moe_return", back_ptrs, y, C, E, cap, rank, P)
 

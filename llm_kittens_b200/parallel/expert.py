@@ -1,12 +1,14 @@
 """Expert-parallel exchange for the mixture-of-experts model: symmetric (peer-mapped) buffers plus
-the flag protocol that turns the dispatch / return kernels of ``csrc/moe.cu`` into an all-to-all.
+the arrival tables that turn the dispatch / return kernels of ``csrc/moe.cu`` into an all-to-all.
 
 A buffer allocated here exists on every rank at a known peer address, so a source rank stores its
-routed rows directly into the owner's receive buffer. ``sync(tag)`` is the hand-over point: each
-rank release-stores an epoch flag into every peer's control buffer after its stores, then waits
-(bounded, on the device, no host sync) until all peers' flags for that tag have arrived. The
-library equivalent would be one ``all_to_all_single`` per direction and layer
-(reference primitive: llmc/distributed_ext.cuh:27-48).
+routed rows directly into the owner's receive buffer. There is no barrier between the stages of a
+layer: the dispatch kernel's last block release-stores the number of the exchange into the owners'
+arrival tables (``arrival_table``), the expert GEMM's producer warp waits only for the entries of
+the rows it is about to load, the return kernel publishes each (source, expert) block the same way
+and the combine kernel waits for its owners inside the kernel. ``sync(tag)`` (a device-side barrier
+over all ranks: signal + bounded wait) remains for set-up and tests. The library equivalent would be
+one ``all_to_all_single`` per direction and layer (reference primitive: llmc/distributed_ext.cuh:27-48).
 """
 from __future__ import annotations
 
@@ -49,6 +51,14 @@ class PeerExchange:
     def alloc(self, numel: int, device=None):
         t, ptrs = self._alloc(numel, torch.bfloat16)
         t.zero_()
+        return t, ptrs
+
+    def arrival_table(self, entries: int, device=None):
+        """Zeroed int32 table in symmetric memory + the host array of the ranks' pointers to it."""
+        t, ptrs = self._alloc(entries, torch.int32)
+        t.zero_()
+        torch.cuda.synchronize(self.device)
+        dist.barrier(group=self.group)
         return t, ptrs
 
     def sync(self, tag: int) -> None:

@@ -156,6 +156,22 @@ def test_dbias_and_encoder():
     assert torch.equal(dwte, dwte2)
 
 
+@pytest.mark.parametrize("n,V", [(65536, 50304), (5000, 128256), (2048, 300), (33, 7), (131072, 50304)])
+def test_bucket_sort_is_a_stable_sort_by_token(n, V):
+    """The device radix sort that buckets positions by token id gives exactly the stable sort (token, position),
+    for sizes that are not whole tiles and for vocabularies that need one, two and (hypothetically) more digit passes."""
+    from llm_kittens_b200.ops import elementwise as ew
+
+    g = torch.Generator(device="cuda").manual_seed(n)
+    tok = torch.randint(0, V, (n,), generator=g, device="cuda", dtype=torch.int32)
+    tok[: n // 3] = tok[0]                    # a heavy hitter, as natural text has
+    st, sp = ew.bucket_sort(tok, V)
+    ref_tok, ref_pos = torch.sort(tok, stable=True)
+    assert torch.equal(st, ref_tok) and torch.equal(sp.long(), ref_pos)
+    st2, sp2 = ew.bucket_sort(tok, 1 << 20)    # three passes
+    assert torch.equal(st2, ref_tok) and torch.equal(sp2.long(), ref_pos)
+
+
 @pytest.mark.parametrize("rows,V,Vp", [(64, 50257, 50304), (16, 1000, 1024), (8, 128256, 128256)])
 def test_fused_classifier(rows, V, Vp):
     from llm_kittens_b200.ops import classifier
@@ -276,7 +292,7 @@ def test_rope_in_the_qkv_projection_and_in_the_attention_backward(B, T, NH, NKVH
     ref = _rope_ref(x.float() @ w.float().T, table, B, T, NH + NKVH, HS)
     assert maxerr(fused, ref) < 0.03
     unfused = ew.rope_qk_(gemm.gemm_nt(x, w), table, B, T, NH, NKVH, HS, interleaved=True)
-    assert maxerr(fused, unfused) < 0.03
+    assert maxerr(fused, unfused) < 0.05   # the unfused path rounds to bf16 twice
     # backward
     qkv = fused.view(B, T, W)
     out, lse = attention.attention_fwd(qkv, B, T, NH, NKVH, HS)
