@@ -236,7 +236,8 @@ def main() -> int:
     ap.add_argument("--seq-len", type=int, default=SEQ_T)
     ap.add_argument("--total-batch", type=int, default=TOTAL_BATCH)
     ap.add_argument("--cuda-graph", type=int, default=1,
-                    help="1 GPU only: replay a captured forward+backward per micro-step (0 = launch every kernel from Python)")
+                    help="replay captured forward+backward graphs per micro-step where the communication path allows it "
+                         "(one process, fused ZeRO-1); 0 = launch every kernel from Python")
     args = ap.parse_args()
     if args.impl == "reference":
         return reference_arm(args)
@@ -307,8 +308,9 @@ def main() -> int:
     comm = make_comm(plan, model, world, rank, device, prefer=args.comm if args.impl == "ours" else "library")
     trainer = Trainer(model, zero_stage=zero, use_master_weights=True, learning_rate=6e-4, weight_decay=0.1, comm=comm,
                       num_processes=world, rank=rank)
-    if args.impl == "ours" and world == 1 and args.cuda_graph:
-        trainer.enable_cuda_graph(True)   # captured during the warm-up steps (the first one runs eagerly)
+    if args.impl == "ours" and args.cuda_graph:
+        # captured during the warm-up steps (the first one runs eagerly); used by one process and by the fused ZeRO-1 path
+        trainer.enable_cuda_graph(True)
 
     # synthetic uniform tokens: ONE global stream from seed 1337, the same at every N. Step s consumes tokens
     # [s*total, (s+1)*total]; its chunk c (B*T tokens, targets shifted by one) goes to rank c % N as micro-step

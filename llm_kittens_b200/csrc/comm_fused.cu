@@ -95,7 +95,10 @@ __device__ __forceinline__ bool wait_flags_block(const int* my_ctrl, int slot, i
 
 // ctrl[dst][slot][my_rank] = epoch for every dst (release at system scope: everything this rank wrote
 // before this kernel is visible to a peer that acquires the flag)
-__global__ void signal_kernel(Peers ctrl, int slot, int my_rank, int P, int epoch) {
+// `epoch_ptr` (optional): the epoch is read from device memory instead, so that a captured CUDA graph of a step can be
+// replayed with a counter that the host bumps between replays.
+__global__ void signal_kernel(Peers ctrl, int slot, int my_rank, int P, int epoch, const int* __restrict__ epoch_ptr) {
+    if (epoch_ptr != nullptr) epoch = *epoch_ptr;
     if ((int)threadIdx.x < P) {
         __threadfence_system();
         st_release_sys(static_cast<int*>(ctrl.p[threadIdx.x]) + slot * MAXP + my_rank, epoch);
@@ -111,8 +114,9 @@ __global__ void wait_kernel(const int* my_ctrl, int slot, int epoch, int P, long
 __global__ void __launch_bounds__(TPB)
 rs_bucket_kernel(Peers grads, const int* my_ctrl, int slot, int epoch, const long long* __restrict__ segs,
                  float* __restrict__ gshard, float* __restrict__ norm_partials, int P, float inv_p, int accumulate,
-                 long long limit_ns, int* status) {
+                 long long limit_ns, int* status, const int* __restrict__ epoch_ptr) {
     __shared__ float sh[32];
+    if (epoch_ptr != nullptr) epoch = *epoch_ptr;
     const bool ok = wait_flags_block(my_ctrl, slot, epoch, P, limit_ns, status, slot);
     const long long* seg = segs + (size_t)blockIdx.y * 3;
     const size_t g_off = (size_t)seg[0], s_off = (size_t)seg[1], len = (size_t)seg[2];
@@ -337,7 +341,15 @@ LLMK_API int llmk_comm_ctrl_ints() { return CTRL_INTS; }
 // `ptrs`: host array of P device pointers (one per rank, this rank's own included).
 LLMK_API int llmk_comm_signal(const long long* ctrl_ptrs, int slot, int my_rank, int P, int epoch, void* stream) {
     if (P > MAXP || slot < 0 || (slot + 1) * MAXP > NORM_VAL_OFFSET) return LLMK_ERR_SHAPE;
-    signal_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(make_peers(ctrl_ptrs, P), slot, my_rank, P, epoch);
+    signal_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(make_peers(ctrl_ptrs, P), slot, my_rank, P, epoch, nullptr);
+    LLMK_LAUNCH_CHECK();
+    return LLMK_OK;
+}
+
+// The same with the epoch taken from device memory when the kernel runs (for launches recorded in a CUDA graph).
+LLMK_API int llmk_comm_signal_dev(const long long* ctrl_ptrs, int slot, int my_rank, int P, const void* epoch_ptr, void* stream) {
+    if (P > MAXP || slot < 0 || (slot + 1) * MAXP > NORM_VAL_OFFSET || epoch_ptr == nullptr) return LLMK_ERR_SHAPE;
+    signal_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(make_peers(ctrl_ptrs, P), slot, my_rank, P, 0, (const int*)epoch_ptr);
     LLMK_LAUNCH_CHECK();
     return LLMK_OK;
 }
@@ -357,7 +369,21 @@ LLMK_API int llmk_comm_rs_bucket(const long long* grad_ptrs, const void* my_ctrl
     dim3 grid(grid_x, nseg);
     rs_bucket_kernel<<<grid, TPB, 0, (cudaStream_t)stream>>>(make_peers(grad_ptrs, P), (const int*)my_ctrl, slot, epoch,
                                                             (const long long*)segs, (float*)gshard, (float*)norm_partials, P,
-                                                            1.0f / (float)P, accumulate, (long long)limit_ns, status);
+                                                            1.0f / (float)P, accumulate, (long long)limit_ns, status, nullptr);
+    LLMK_LAUNCH_CHECK();
+    return LLMK_OK;
+}
+
+// The same with the epoch taken from device memory when the kernel runs (for launches recorded in a CUDA graph).
+LLMK_API int llmk_comm_rs_bucket_dev(const long long* grad_ptrs, const void* my_ctrl, int slot, const void* epoch_ptr,
+                                     const void* segs, int nseg, void* gshard, void* norm_partials, int grid_x, int P,
+                                     int accumulate, long limit_ns, int* status, void* stream) {
+    if (P > MAXP || nseg <= 0 || grid_x <= 0 || epoch_ptr == nullptr) return LLMK_ERR_SHAPE;
+    dim3 grid(grid_x, nseg);
+    rs_bucket_kernel<<<grid, TPB, 0, (cudaStream_t)stream>>>(make_peers(grad_ptrs, P), (const int*)my_ctrl, slot, 0,
+                                                            (const long long*)segs, (float*)gshard, (float*)norm_partials, P,
+                                                            1.0f / (float)P, accumulate, (long long)limit_ns, status,
+                                                            (const int*)epoch_ptr);
     LLMK_LAUNCH_CHECK();
     return LLMK_OK;
 }

@@ -75,6 +75,10 @@ class FusedComm:
         L = plan.config.num_layers
         self.slot_params, self.slot_norm = L + 1, L + 2
         self.epoch = 0
+        # the same counter on the device: the bucket kernels read it when they run, so a micro-step recorded in a CUDA
+        # graph can be replayed every step (the host bumps both copies in begin_step)
+        self.epoch_dev = torch.zeros(1, dtype=torch.int32, device=device)
+        self.graph_capturable = True
         self.stream = torch.cuda.Stream(device=device)
         self.gshard = torch.zeros(plan.state_elements, dtype=torch.float32, device=device)
         # per-bucket segment tables (gradient offset of my slice, state offset, length)
@@ -117,16 +121,22 @@ class FusedComm:
         if self.epoch > 0:
             N.call("llmk_comm_wait", self.ctrl, self.slot_params, self.epoch, self.world_size, self.limit_ns, N.status_word())
         self.epoch += 1
+        self.epoch_dev.add_(1)
 
     def reduce_bucket(self, grads: torch.Tensor, layer) -> None:
         slot = self.plan.config.num_layers if layer is None else layer
-        N.call("llmk_comm_signal", self.ctrl_ptrs, slot, self.rank, self.world_size, self.epoch)
+        N.call("llmk_comm_signal_dev", self.ctrl_ptrs, slot, self.rank, self.world_size, self.epoch_dev)
         self._event.record()
         self.stream.wait_event(self._event)
         table, nseg, base = self.buckets[layer]
         with torch.cuda.stream(self.stream):
-            N.call("llmk_comm_rs_bucket", self.grad_ptrs, self.ctrl, slot, self.epoch, table, nseg, self.gshard,
+            N.call("llmk_comm_rs_bucket_dev", self.grad_ptrs, self.ctrl, slot, self.epoch_dev, table, nseg, self.gshard,
                    self.partials[base:], self.grid_x, self.world_size, 0, self.limit_ns, N.status_word())
+
+    def join_buckets(self) -> None:
+        """The current stream waits for the bucket kernels queued so far (the end of a captured micro-step: every
+        stream that forked from the capturing stream has to come back to it)."""
+        torch.cuda.current_stream().wait_stream(self.stream)
 
     def finish_reduce(self) -> None:
         if self.expert_table is not None:

@@ -168,45 +168,59 @@ class Trainer:
 
     # ------------------------------------------------------------------ CUDA graph of one micro-step
     def enable_cuda_graph(self, on: bool = True) -> None:
-        """Replay one captured forward+backward per micro-step instead of launching ~370 kernels from Python
-        (single-process training only: the communication paths use side streams and host-visible flags).
-        The first step with a given (B, T, accumulation) runs eagerly, the second one is captured."""
+        """Replay captured forward+backward graphs per micro-step instead of launching ~370 kernels from Python: one
+        graph for the micro-steps that only accumulate, one for the last micro-step of a step, which also holds the
+        per-bucket "ready" signals and reduce-scatter kernels of the fused ZeRO-1 path (they read the step's epoch
+        from device memory). One process, or several with ``FusedComm``; the first step with a given
+        (B, T, accumulation) runs eagerly, the second one is captured."""
         self.use_cuda_graph = bool(on)
 
     def _graph_usable(self, batches) -> bool:
-        return (self.native and isinstance(self.comm, SingleProcessComm) and self._eager_steps > 0
+        comm_ok = isinstance(self.comm, SingleProcessComm) or getattr(self.comm, "graph_capturable", False)
+        return (self.native and comm_ok and self._eager_steps > 0
                 and type(self.model).__name__ == "Transformer" and len({tuple(x.shape) for x, _ in batches}) == 1)
 
     def _accumulate_graph(self, batches) -> int:
         model = self.model
         accum = len(batches)
         key = (tuple(batches[0][0].shape), accum)
+        from ..ops import _native
+
+        with_comm = not isinstance(self.comm, SingleProcessComm)
         if self._graph_key != key:
             B, T = key[0]
             self._gx = torch.zeros(B, T, dtype=torch.int32, device=self.device)
             self._gy = torch.zeros(B, T, dtype=torch.int32, device=self.device)
             torch.cuda.synchronize(self.device)
-            from ..ops import _native
 
-            graph = torch.cuda.CUDAGraph()
-            before = _native.launch_count()
-            with torch.cuda.graph(graph):
-                # micro_step=1: the loss accumulator is cleared outside the graph, before the first micro-step
-                model.forward(self._gx, self._gy, grad_accum_steps=accum, micro_step=1)
-                model.backward(last_micro_step=True, bucket_ready=None)
-            # the capture recorded the kernels without running them; gradients and loss are still untouched
-            self._graph_kernels = _native.launch_count() - before
-            _native.count_replayed(-self._graph_kernels)   # they were recorded, not launched
-            self._graph, self._graph_key = graph, key
+            def capture(last: bool):
+                graph = torch.cuda.CUDAGraph()
+                before = _native.launch_count()
+                with torch.cuda.graph(graph):
+                    # micro_step=1: the loss accumulator is cleared outside the graph, before the first micro-step
+                    model.forward(self._gx, self._gy, grad_accum_steps=accum, micro_step=1)
+                    model.backward(last_micro_step=last, bucket_ready=self._bucket_ready if (last and with_comm) else None)
+                    if last and with_comm:
+                        self.comm.join_buckets()
+                # the capture recorded the kernels without running them; gradients and loss are still untouched
+                kernels = _native.launch_count() - before
+                _native.count_replayed(-kernels)   # they were recorded, not launched
+                return graph, kernels
+
+            self._graph_last, self._graph_last_kernels = capture(True)
+            if with_comm and accum > 1:
+                self._graph, self._graph_kernels = capture(False)
+            else:
+                self._graph, self._graph_kernels = self._graph_last, self._graph_last_kernels
+            self._graph_key = key
         for i, (x, y) in enumerate(batches):
             self._gx.copy_(x, non_blocking=True)
             self._gy.copy_(y, non_blocking=True)
             if i == 0:
                 model.acts["loss_acc"].zero_()
-            self._graph.replay()
-        from ..ops import _native
-
-        _native.count_replayed(self._graph_kernels * accum)
+            last = i == accum - 1
+            (self._graph_last if last else self._graph).replay()
+            _native.count_replayed(self._graph_last_kernels if last else self._graph_kernels)
         return accum
 
     def begin_step(self) -> None:

@@ -11,7 +11,7 @@ modes:
                    dispatch / combine), dense parameters ZeRO-1 through library / fused communication
   cpu_fail_rank1   gloo; rank 1 raises before its first collective (failure-detection test)
 environment: LLMK_TEST_LAYERS (dense model depth, default 2), LLMK_TEST_RECOMPUTE (default 0),
-LLMK_TEST_SKIP_STEP (index of a step whose optimizer update is left out, as the z-score guards of the trainer do)
+LLMK_TEST_GRAPH (replay the micro-step from CUDA graphs), LLMK_TEST_SKIP_STEP (index of a step whose optimizer update is left out, as the z-score guards of the trainer do)
 Each rank writes ``rank<r>.pt`` with its per-step losses / norms and a parameter checksum sample.
 """
 import datetime
@@ -107,6 +107,8 @@ def main():
         comm = LibraryComm(plan, None, device)
     trainer = Trainer(model, zero_stage=stage, use_master_weights=True, learning_rate=1e-3, weight_decay=0.1, comm=comm,
                       num_processes=world, rank=rank)
+    if os.environ.get("LLMK_TEST_GRAPH"):
+        trainer.enable_cuda_graph(True)   # step 0 runs eagerly, step 1 is captured, the later steps replay
     losses, norms = [], []
     leave = "leave" in mode
     if leave:

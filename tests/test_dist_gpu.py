@@ -41,6 +41,18 @@ def test_fused_comm_matches_library_and_zero0(tmp_path):
     assert f0["losses"][-1] < f0["losses"][0]
 
 
+def test_fused_comm_micro_step_replayed_from_cuda_graphs(tmp_path):
+    """The fused ZeRO-1 micro-step (forward, backward, per-bucket signals and reduce-scatter kernels that read the
+    step's epoch from device memory) captured once and replayed: the same losses, norms and parameters as eager
+    launches, bit for bit (the kernels and their order are the same)."""
+    _need_two_gpus()
+    e0, e1 = _run("gpu_fused", tmp_path)
+    g0, g1 = _run("gpu_fused", tmp_path, LLMK_TEST_GRAPH="1")
+    assert torch.equal(g0["params"], g1["params"])
+    assert g0["losses"] == e0["losses"] and g0["norms"] == e0["norms"]
+    assert torch.equal(g0["params"], e0["params"])
+
+
 def test_fused_comm_survives_a_skipped_update(tmp_path):
     """A step without optimizer update (z-score guards) must still raise the "parameters ready" flag: the steps
     after it run without a bounded wait running out (the worker checks the status word) and train like the library
