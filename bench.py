@@ -281,9 +281,10 @@ def main() -> int:
 
         exchange = None
         if world > 1:
-            from llm_kittens_b200.parallel.expert import PeerExchange
+            from llm_kittens_b200.parallel.expert import LibraryExchange, PeerExchange
 
-            exchange = PeerExchange(device)
+            # --comm library: experts' rows through all_to_all_single (NCCL), dense gradients through NCCL collectives
+            exchange = LibraryExchange(device) if args.comm == "library" else PeerExchange(device)
         model = MoETransformer(config, device=device, recompute=args.recompute, exchange=exchange)
     else:
         from llm_kittens_b200.models.transformer import Transformer
@@ -416,7 +417,8 @@ def main() -> int:
                        "micro_batch": B, "seq_len": T, "grad_accum_steps": accum,
                        "parallelism": f"dp{world}" + (f"-zero{zero}" if world > 1 else ""),
                        "optimizer": "AdamW fp32 m/v + fp32 master, bf16 params/grads, clip 1.0, cosine lr 6e-4 warmup 700",
-                       "comm": type(comm).__name__, "recompute": args.recompute,
+                       "comm": type(comm).__name__ + (f" + {type(getattr(model, 'exchange', None)).__name__}"
+                                                      if config.family == "moe" else ""), "recompute": args.recompute,
                        "cuda_graph": bool(getattr(trainer, "_graph", None) is not None),
                        "l2": "working set per step (~20 GB activations, 250 MB weights) far exceeds the 126 MB L2; no flush needed",
                        "weights": "random init N(0,0.02), seed 42",

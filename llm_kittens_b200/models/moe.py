@@ -110,6 +110,12 @@ class MoETransformer(Transformer):
         self.arrive, self.arrive_ptrs = self.exchange.arrival_table(L * 4 * E, dev)
         self.done = torch.zeros(1 + Eloc * P, dtype=i32, device=dev)
         self._epoch = 0
+        self.library = bool(getattr(self.exchange, "library", False))
+        if self.library:
+            # baseline route: a packed send buffer [E][cap][C] and a receive buffer in the collective's order
+            self.a2a_send = torch.zeros(E * cap, C, dtype=BF16, device=dev)
+            self.a2a_recv = torch.zeros(rows, C, dtype=BF16, device=dev)
+            self.a2a_send_ptrs = moe_ops.ptr_table([self.a2a_send])
 
     def _dense_mlp_buffers(self) -> bool:
         return False
@@ -121,6 +127,26 @@ class MoETransformer(Transformer):
         return (p["fcw"][l][e], p["fcb"][l][e], p["fcprojw"][l][e], p["fcprojb"][l][e],
                 g["fcw"][l][e], g["fcb"][l][e], g["fcprojw"][l][e], g["fcprojb"][l][e])
 
+    # ---- baseline route through all_to_all_single (LibraryExchange) -------------------------------------------------
+    def _library_out(self, x, idx, slot, w, counts, recv_rows, scale_by_weight):
+        """rows of ``x`` -> this rank's packed [E][cap][C] send buffer -> all-to-all -> ``recv_rows`` [el][src][cap][C]."""
+        E, P, cap, Eloc = self.E, self.P, self.cap, self.Eloc
+        moe_ops.dispatch(self.a2a_send_ptrs, x, idx, slot, w, counts, E, cap, 0, 1, scale_by_weight=scale_by_weight)
+        if Eloc == 1:
+            self.exchange.all_to_all(recv_rows, self.a2a_send)           # [src][1][cap] is [1][src][cap]
+        else:
+            self.exchange.all_to_all(self.a2a_recv, self.a2a_send)       # [src][el][cap][C]
+            recv_rows.view(Eloc, P, cap, -1).copy_(self.a2a_recv.view(P, Eloc, cap, -1).transpose(0, 1))
+
+    def _library_back(self, y_rows, back):
+        """``y_rows`` [el][src][cap][C] -> all-to-all -> ``back`` [e][cap][C] on the source ranks."""
+        P, cap, Eloc = self.P, self.cap, self.Eloc
+        if Eloc == 1:
+            self.exchange.all_to_all(back, y_rows)
+        else:
+            self.a2a_recv.view(P, Eloc, cap, -1).copy_(y_rows.view(Eloc, P, cap, -1).transpose(0, 1))
+            self.exchange.all_to_all(back, self.a2a_recv)
+
     def _mlp_forward(self, l, k, gi, ln2, res2, out):
         a, p, cfg = self.acts, self.p, self.config
         E, K, P, cap = self.E, self.K, self.P, self.cap
@@ -129,8 +155,12 @@ class MoETransformer(Transformer):
         moe_ops.density(a["probs"][l], cfg.aux_loss_coef * self._loss_scale, a["density"][l], a["aux_acc"], accumulate=True)
         ep, lim = self._epoch, self.exchange.limit_ns
         r_out, r_back = (4 * l + 0) * E, (4 * l + 1) * E
-        moe_ops.dispatch_signal(self.recv_x_ptrs[l], ln2, a["top_idx"][l], a["slot"][l], a["top_w"][l], a["counts"][l], E, cap,
-                                self.ep_rank, P, False, self.arrive_ptrs, r_out, self.done[0:1], ep)
+        lib = self.library
+        if lib:
+            self._library_out(ln2, a["top_idx"][l], a["slot"][l], a["top_w"][l], a["counts"][l], self.recv_x[l], False)
+        else:
+            moe_ops.dispatch_signal(self.recv_x_ptrs[l], ln2, a["top_idx"][l], a["slot"][l], a["top_w"][l], a["counts"][l], E, cap,
+                                    self.ep_rank, P, False, self.arrive_ptrs, r_out, self.done[0:1], ep)
         per = P * cap
         act_l = a["hid_act"][0 if self.recompute >= 1 else l]
         # the local experts have equal row counts (P * capacity): one grouped launch per projection
@@ -138,8 +168,13 @@ class MoETransformer(Transformer):
         rows = slice(0, G * per)
         # every M tile of the first GEMM waits only for the source rank whose rows it loads
         gemm.gemm_nt(self.recv_x[l][rows], p["fcw"][l][loc], bias=p["fcb"][l][loc], out=act_l[rows],
-                     gelu_pre_out=a["hid_pre"][l][rows], groups=G, a_ready=(self.arrive[r_out:], cap, ep, lim))
+                     gelu_pre_out=a["hid_pre"][l][rows], groups=G,
+                     a_ready=None if lib else (self.arrive[r_out:], cap, ep, lim))
         gemm.gemm_nt(act_l[rows], p["fcprojw"][l][loc], bias=p["fcprojb"][l][loc], out=a["y_loc"][rows], groups=G)
+        if lib:
+            self._library_back(a["y_loc"], self.back_y[l])
+            moe_ops.combine(out, res2, self.back_y[l], a["top_idx"][l], a["slot"][l], a["top_w"][l], cap)
+            return
         moe_ops.return_signal(self.back_y_ptrs[l], a["y_loc"], cfg.channels, E, cap, self.ep_rank, P, self.arrive_ptrs, r_back,
                               self.done[1:], ep)
         moe_ops.combine_wait(out, res2, self.back_y[l], a["top_idx"][l], a["slot"][l], a["top_w"][l], cap,
@@ -153,8 +188,12 @@ class MoETransformer(Transformer):
         moe_ops.combine_dweight(dres, self.back_y[l], idx, slot, cap, dw=a["dw"])
         ep, lim = self._epoch, self.exchange.limit_ns
         r_out, r_back = (4 * l + 2) * E, (4 * l + 3) * E
-        moe_ops.dispatch_signal(self.recv_dy_ptrs, dres, idx, slot, w, a["counts"][l], E, cap, self.ep_rank, P, True,
-                                self.arrive_ptrs, r_out, self.done[0:1], ep)
+        lib = self.library
+        if lib:
+            self._library_out(dres, idx, slot, w, a["counts"][l], self.recv_dy, True)
+        else:
+            moe_ops.dispatch_signal(self.recv_dy_ptrs, dres, idx, slot, w, a["counts"][l], E, cap, self.ep_rank, P, True,
+                                    self.arrive_ptrs, r_out, self.done[0:1], ep)
         per = P * cap
         act_l = a["hid_act"][0 if self.recompute >= 1 else l]
         G, loc = self.Eloc, slice(self.ep_rank * self.Eloc, (self.ep_rank + 1) * self.Eloc)
@@ -164,7 +203,7 @@ class MoETransformer(Transformer):
             ew.gelu_fwd(a["hid_pre"][l][rows], out=act_l[rows])
         # the first consumer of dy waits tile by tile for its source ranks; the products after it find dy complete
         gemm.gemm_nn(dy, p["fcprojw"][l][loc], out=d_hid, dgelu_of=a["hid_pre"][l][rows], groups=G,
-                     a_ready=(self.arrive[r_out:], cap, ep, lim))
+                     a_ready=None if lib else (self.arrive[r_out:], cap, ep, lim))
         gemm.gemm_tn(dy, act_l[rows], out=g["fcprojw"][l][loc], accumulate=True, groups=G)
         gemm.gemm_tn(d_hid, x, out=g["fcw"][l][loc], accumulate=True, groups=G)
         gemm.gemm_nn(d_hid, p["fcw"][l][loc], out=a["y_loc"][rows], groups=G)
@@ -173,8 +212,13 @@ class MoETransformer(Transformer):
             r = slice(el * per, (el + 1) * per)
             ew.dbias(gb2, dy[r], accumulate=True)
             ew.dbias(gb1, d_hid[r], accumulate=True)
-        moe_ops.return_signal(self.back_dx_ptrs, a["y_loc"], C, E, cap, self.ep_rank, P, self.arrive_ptrs, r_back, self.done[1:], ep)
-        moe_ops.combine_wait(d_ln2, None, self.back_dx, idx, slot, None, cap, self.arrive[r_back:], E, ep, lim)
+        if lib:
+            self._library_back(a["y_loc"], self.back_dx)
+            moe_ops.combine(d_ln2, None, self.back_dx, idx, slot, None, cap)
+        else:
+            moe_ops.return_signal(self.back_dx_ptrs, a["y_loc"], C, E, cap, self.ep_rank, P, self.arrive_ptrs, r_back,
+                                  self.done[1:], ep)
+            moe_ops.combine_wait(d_ln2, None, self.back_dx, idx, slot, None, cap, self.arrive[r_back:], E, ep, lim)
         # router: gradient through the renormalised top-k weights plus the load-balance term
         aux_scale = cfg.aux_loss_coef * E * 2.0 / N * self._loss_scale
         dlog = moe_ops.router_bwd(a["probs"][l], idx, w, a["dw"], slot, a["density"][l], aux_scale, dlogits=a["dlogits"])

@@ -67,3 +67,37 @@ class PeerExchange:
         self.epochs[tag] = e
         N.call("llmk_comm_signal", self.ctrl_ptrs, tag, self.rank, self.world_size, e)
         N.call("llmk_comm_wait", self.ctrl, tag, e, self.world_size, self.limit_ns, N.status_word())
+
+
+class LibraryExchange:
+    """The baseline the peer-memory exchange is measured against: the same dispatch / combine kernels, but rows travel
+    through a packed send buffer and one ``torch.distributed.all_to_all_single`` (NCCL) per direction and layer, the
+    collective the reference's primitive wraps (llmc/distributed_ext.cuh:27-48). The model checks ``library`` and takes
+    the collective route; buffers are ordinary device tensors."""
+
+    library = True
+    limit_ns = int(2e9)
+
+    def __init__(self, device: torch.device, group=None):
+        self.device = device
+        self.group = group if group is not None else dist.group.WORLD
+        self.world_size = dist.get_world_size(self.group)
+        self.rank = dist.get_rank(self.group)
+
+    def alloc(self, numel: int, device=None):
+        from ..ops import moe as moe_ops
+
+        t = torch.zeros(numel, dtype=torch.bfloat16, device=self.device)
+        return t, moe_ops.ptr_table([t])
+
+    def arrival_table(self, entries: int, device=None):
+        from ..ops import moe as moe_ops
+
+        t = torch.zeros(entries, dtype=torch.int32, device=self.device)
+        return t, moe_ops.ptr_table([t])
+
+    def all_to_all(self, recv: torch.Tensor, send: torch.Tensor) -> None:
+        dist.all_to_all_single(recv.view(-1), send.view(-1), group=self.group)
+
+    def sync(self, tag: int) -> None:
+        pass

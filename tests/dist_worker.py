@@ -7,6 +7,7 @@ modes:
   gpu_fused        NCCL bootstrap, CUDA model, ZeRO-1 through the fused peer-memory kernels
   gpu_sharded<k>   ZeRO stage 2 / 3 with really sharded gradients / parameters (peer-memory kernels); every
                    step is split into two micro-steps so that the shard accumulation is exercised
+  gpu_moe_a2a1     the same with the experts' rows exchanged through all_to_all_single (the measured baseline)
   gpu_moe_library1 / gpu_moe_fused   mixture-of-experts model, experts split over the ranks (peer-memory
                    dispatch / combine), dense parameters ZeRO-1 through library / fused communication
   cpu_fail_rank1   gloo; rank 1 raises before its first collective (failure-detection test)
@@ -82,9 +83,11 @@ def main():
     stage = int(mode[-1]) if mode[-1].isdigit() else 1
     if moe:
         from llm_kittens_b200.models.moe import MoETransformer
-        from llm_kittens_b200.parallel.expert import PeerExchange
+        from llm_kittens_b200.parallel.expert import LibraryExchange, PeerExchange
 
-        model = MoETransformer(cfg, device=device, recompute=0, exchange=PeerExchange(device, timeout_ms=20000))
+        # gpu_moe_a2a1: the baseline exchange through all_to_all_single
+        exchange = LibraryExchange(device) if "a2a" in mode else PeerExchange(device, timeout_ms=20000)
+        model = MoETransformer(cfg, device=device, recompute=0, exchange=exchange)
     elif cpu:
         from llm_kittens_b200.oracle.torch_model import TorchTransformer
 

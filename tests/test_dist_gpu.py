@@ -79,7 +79,7 @@ def test_expert_parallel_moe_matches_single_process(tmp_path):
     ref = []
     for x, y in global_batches(cfg, 3, 2, 2, 128):
         ref.append(tr.train_step([(x[:2].contiguous(), y[:2].contiguous()), (x[2:].contiguous(), y[2:].contiguous())]).loss)
-    for mode in ("gpu_moe_library1", "gpu_moe_fused"):
+    for mode in ("gpu_moe_library1", "gpu_moe_fused", "gpu_moe_a2a1"):
         r0, r1 = _run(mode, tmp_path)
         assert r0["losses"] == r1["losses"]
         for a, b in zip(r0["losses"], ref):
