@@ -9,6 +9,14 @@
 * ``checkpoint DIR [--step N]`` — header / size / DONE-marker checks of a checkpoint directory
   (``dev/validate_llama_checkpoint_artifacts.py``).
 
+* ``write-debug-state MODEL_BIN OUT [--batch B] [--seq T] [--seed S]`` — runs the fp32 PyTorch model on one batch of
+  seeded tokens and writes inputs, targets, logits, loss and every gradient (the artefact that the reference's
+  ``train_gpt2.py`` writes for its C tests, train_gpt2.py:395-524).
+* ``debug-state MODEL_BIN DEBUG_STATE [--device cuda|cpu] [--logit-tol X] [--loss-tol X]`` — the whole-model gate on
+  exported artefacts (jobs of ``dev/cuda/gpt2_validate.cu:12-101`` and ``test_gpt2.cu:168-229``): loads the model file,
+  runs forward + backward of the framework's model (the CUDA path on a GPU, else the PyTorch model) on the stored
+  batch and compares logits, loss and every gradient tensor with the stored values, tensor by tensor.
+
 Every command prints its findings and exits 1 if there are any.
 """
 from __future__ import annotations
@@ -102,6 +110,76 @@ def check_checkpoint(directory: str, step: int | None = None) -> list[str]:
     return problems
 
 
+def write_debug_state(model_path: str, out_path: str, B: int = 4, T: int = 64, seed: int = 1337) -> None:
+    import numpy as np
+    import torch
+
+    from ..oracle.torch_model import TorchTransformer
+
+    cfg, params = formats.read_model(model_path, device="cpu", dtype=torch.float32)
+    model = TorchTransformer(cfg, device="cpu", dtype=torch.float32)
+    model.load_parameters(params)
+    g = torch.Generator().manual_seed(seed)
+    x = torch.randint(0, cfg.vocab_size, (B, T), generator=g, dtype=torch.int32)
+    y = torch.randint(0, cfg.vocab_size, (B, T), generator=g, dtype=torch.int32)
+    model.zero_grad()
+    model.forward(x, y)
+    model.backward()
+    logits = model.logits_view().reshape(B, T, -1)[..., : cfg.vocab_size].float().numpy()
+    formats.write_debug_state(out_path, x.numpy(), y.numpy(), np.ascontiguousarray(logits), model.mean_loss(), model.grads.float().numpy())
+
+
+def check_debug_state(model_path: str, state_path: str, device: str = "", logit_tol: float = 0.0, loss_tol: float = 0.0) -> list[str]:
+    """Problems found when the framework's model, loaded from ``model_path``, is run on the batch of ``state_path``.
+    Default tolerances: bf16 CUDA path logits 0.25 / loss 0.05 (the reference accepts 25.0 on bf16 logits and 0.05 on
+    the loss, test_gpt2.cu:223-229, 326-347), fp32 path 1e-3 / 1e-4; gradients per tensor ``thr + 0.079 * |ref|`` on at
+    least 99.5 % of the elements, ``thr`` by tensor kind as in test_gpt2.cu:9-50."""
+    import torch
+
+    cfg, params = formats.read_model(model_path, device="cpu", dtype=torch.float32)
+    layout = cfg.layout()
+    state = formats.read_debug_state(state_path, cfg.vocab_size, layout.total)
+    cuda = (device or ("cuda" if torch.cuda.is_available() else "cpu")).startswith("cuda")
+    x, y = torch.from_numpy(state["x"].copy()), torch.from_numpy(state["y"].copy())
+    if cuda:
+        from ..models.moe import MoETransformer
+        from ..models.transformer import Transformer
+
+        cls = MoETransformer if cfg.family == "moe" else Transformer
+        model = cls(cfg, device="cuda", recompute=0)
+        model.params.copy_(params.to(torch.bfloat16))
+        x, y = x.cuda(), y.cuda()
+    else:
+        from ..oracle.torch_model import TorchTransformer
+
+        model = TorchTransformer(cfg, device="cpu", dtype=torch.float32)
+        model.load_parameters(params)
+    logit_tol = logit_tol or (0.25 if cuda else 1e-3)
+    loss_tol = loss_tol or (0.05 if cuda else 1e-4)
+    problems = []
+    model.forward(x, y, compute_dlogits=False)
+    logits = model.logits_view().reshape(state["B"], state["T"], -1)[..., : cfg.vocab_size].float().cpu()
+    err = (logits - torch.from_numpy(state["logits"].copy())).abs().max().item()
+    if not err <= logit_tol:
+        problems.append(f"logits differ by up to {err:.4g} (tolerance {logit_tol})")
+    model.zero_grad()
+    model.forward(x, y)
+    loss = model.mean_loss()
+    if not abs(loss - state["loss"]) <= loss_tol:
+        problems.append(f"loss {loss:.6f} vs stored {state['loss']:.6f} (tolerance {loss_tol})")
+    model.backward()
+    grads = model.grads.float().cpu()
+    ref = torch.from_numpy(state["grads"].copy())
+    for slot in layout.slots:
+        g, r = grads[slot.offset: slot.offset + slot.total], ref[slot.offset: slot.offset + slot.total]
+        thr = (5e-3 if slot.spec.name in ("wte", "lm_head") else 2e-2) if cuda else 1e-5
+        bad = ((g - r).abs() > thr + (0.079 if cuda else 1e-3) * r.abs()).float().mean().item()
+        if not bad <= (5e-3 if cuda else 0.0):
+            problems.append(f"gradient of {slot.spec.name}: {100 * bad:.2f} % of the elements are outside {thr} + 0.079*|ref| "
+                            f"(max abs diff {(g - r).abs().max().item():.4g})")
+    return problems
+
+
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(prog="llm_kittens_b200.cli.check", description=__doc__,
                                  formatter_class=argparse.RawDescriptionHelpFormatter)
@@ -123,6 +201,18 @@ def main(argv=None) -> int:
     p = sub.add_parser("checkpoint")
     p.add_argument("directory")
     p.add_argument("--step", type=int)
+    p = sub.add_parser("write-debug-state")
+    p.add_argument("model")
+    p.add_argument("out")
+    p.add_argument("--batch", type=int, default=4)
+    p.add_argument("--seq", type=int, default=64)
+    p.add_argument("--seed", type=int, default=1337)
+    p = sub.add_parser("debug-state")
+    p.add_argument("model")
+    p.add_argument("state")
+    p.add_argument("--device", default="")
+    p.add_argument("--logit-tol", type=float, default=0.0)
+    p.add_argument("--loss-tol", type=float, default=0.0)
     args = ap.parse_args(argv)
 
     if args.command == "log":
@@ -131,6 +221,11 @@ def main(argv=None) -> int:
         problems = compare_logs(args.a, args.b, args.rel_tol, args.abs_tol)
     elif args.command == "zero-layout":
         problems = check_zero_layout(args.models, args.world)
+    elif args.command == "write-debug-state":
+        write_debug_state(args.model, args.out, args.batch, args.seq, args.seed)
+        problems = []
+    elif args.command == "debug-state":
+        problems = check_debug_state(args.model, args.state, args.device, args.logit_tol, args.loss_tol)
     else:
         problems = check_checkpoint(args.directory, args.step)
     for line in problems:

@@ -30,7 +30,11 @@ def flops_promised(device_name: str, precision: str = "bf16") -> float:
 
 
 def measured_peak_tflops(path: str | None = None) -> float | None:
-    path = path or os.path.join(os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)))), "MEASURED_PEAKS.json")
+    """bf16 TFLOP/s from a JSON file with a ``bf16_tflops`` field (a measurement of this machine): ``path`` or the
+    file named by ``LLMK_MEASURED_PEAKS``; None when neither is given or the file cannot be read."""
+    path = path or os.environ.get("LLMK_MEASURED_PEAKS")
+    if not path:
+        return None
     try:
         return float(json.load(open(path))["bf16_tflops"])
     except Exception:

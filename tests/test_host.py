@@ -529,3 +529,30 @@ def test_grouped_gemm_wrapper_falls_back_to_one_launch_per_group(monkeypatch):
         assert args[2].data_ptr() == dy[g * Kt:].data_ptr() and args[3].data_ptr() == x[g * Kt:].data_ptr()
         assert args[4].data_ptr() == gw[g].data_ptr() and args[7].data_ptr() == gw[g].data_ptr()
         assert args[8:11] == (256, N, Kt)
+
+
+def test_debug_state_commands_round_trip(tmp_path):
+    """`check write-debug-state` + `check debug-state` on a small model file: the PyTorch path reproduces the stored
+    logits, loss and gradients; a perturbed model file is reported tensor by tensor."""
+    import torch
+
+    from llm_kittens_b200.cli import check
+    from llm_kittens_b200.models.config import ModelConfig
+    from llm_kittens_b200.oracle.torch_model import TorchTransformer
+    from llm_kittens_b200.utils import formats
+
+    cfg = ModelConfig(family="gpt2", max_seq_len=64, vocab_size=300, padded_vocab_size=320, num_layers=2, num_heads=2,
+                      num_kv_heads=2, channels=64, hidden_dim=256)
+    model = TorchTransformer(cfg, device="cpu", dtype=torch.float32)
+    model.init_weights(7)
+    mp, sp = str(tmp_path / "model.bin"), str(tmp_path / "debug_state.bin")
+    formats.write_model(mp, cfg, model.params)
+    assert check.main(["write-debug-state", mp, sp, "--batch", "2", "--seq", "32"]) == 0
+    state = formats.read_debug_state(sp, cfg.vocab_size, model.num_parameters)
+    assert state["x"].shape == (2, 32) and state["logits"].shape == (2, 32, 300) and state["grads"].shape == (model.num_parameters,)
+    # the model file stores bf16 unless asked otherwise: compare through the same file
+    assert check.check_debug_state(mp, sp, device="cpu") == []
+    model.params[model.layout["fcw"].offset: model.layout["fcw"].offset + 50].add_(0.5)
+    formats.write_model(str(tmp_path / "other.bin"), cfg, model.params)
+    problems = check.check_debug_state(str(tmp_path / "other.bin"), sp, device="cpu")
+    assert problems and any("logits" in p or "gradient" in p for p in problems)

@@ -328,3 +328,19 @@ def test_non_finite_gradient_skips_the_update_on_the_gpu():
     assert torch.equal(model.params, before) and torch.equal(tr.m, m_before) and torch.equal(tr.master, master_before)
     r = tr.train_step([(x.cuda(), y.cuda())])
     assert not r.skipped and torch.isfinite(model.params.float()).all()
+
+
+def test_debug_state_gate_on_the_cuda_path(tmp_path):
+    """The exported-artefact gate: a model file and the fp32 debug state written from it by the PyTorch model are
+    checked against the CUDA path (logits, loss, every gradient tensor)."""
+    from llm_kittens_b200.cli import check
+    from llm_kittens_b200.oracle.torch_model import TorchTransformer
+    from llm_kittens_b200.utils import formats
+
+    cfg = small_gpt2()
+    ref = TorchTransformer(cfg, device="cpu", dtype=torch.float32)
+    ref.init_weights(11)
+    mp, sp = str(tmp_path / "model.bin"), str(tmp_path / "debug_state.bin")
+    formats.write_model(mp, cfg, ref.params)
+    check.write_debug_state(mp, sp, B=4, T=128)
+    assert check.check_debug_state(mp, sp, device="cuda") == []
