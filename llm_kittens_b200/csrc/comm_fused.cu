@@ -159,8 +159,8 @@ rs_bucket_kernel(Peers grads, const int* my_ctrl, int slot, int epoch, const lon
 // One block. Sums `n` partials, exchanges the sum with the peers, clip coefficient on the device.
 __global__ void __launch_bounds__(1024)
 norm_exchange_kernel(Peers ctrl, const float* __restrict__ partials, int n, int norm_slot, int my_rank, int P, int epoch,
-                     float clip, float* scale_out, float* norm_out, int* flag_out, float* loss_inout, long long limit_ns,
-                     int* status) {
+                     float clip, float* scale_out, float* norm_out, int* flag_out, float* loss_inout, float norm_scale,
+                     long long limit_ns, int* status) {
     __shared__ float sh[32];
     float s = 0.f;
     for (int i = threadIdx.x; i < n; i += blockDim.x) s += partials[i];
@@ -187,7 +187,8 @@ norm_exchange_kernel(Peers ctrl, const float* __restrict__ partials, int n, int 
         } else {
             total = NAN;
         }
-        const float nv = sqrtf(total);
+        // norm_scale = 1/P when every rank holds the complete (replicated) sum and the exchange adds it P times
+        const float nv = sqrtf(total * norm_scale);
         norm_out[0] = nv;
         if (!isfinite(nv)) {
             scale_out[0] = 0.f;
@@ -412,12 +413,13 @@ LLMK_API int llmk_comm_ag_bucket_flags(const long long* shard_ptrs, void* stagin
 
 LLMK_API int llmk_comm_norm_exchange(const long long* ctrl_ptrs, const void* partials, int n, int norm_slot, int my_rank, int P,
                                      int epoch, float clip, void* scale_out, void* norm_out, void* flag_out, void* loss_inout,
-                                     long limit_ns, int* status, void* stream) {
+                                     float norm_scale, long limit_ns, int* status, void* stream) {
     // loss_inout (optional): in = this rank's mean loss of the step, out = the mean over the P ranks
     if (P > MAXP) return LLMK_ERR_SHAPE;
     norm_exchange_kernel<<<1, 1024, 0, (cudaStream_t)stream>>>(make_peers(ctrl_ptrs, P), (const float*)partials, n, norm_slot,
                                                               my_rank, P, epoch, clip, (float*)scale_out, (float*)norm_out,
-                                                              (int*)flag_out, (float*)loss_inout, (long long)limit_ns, status);
+                                                              (int*)flag_out, (float*)loss_inout, norm_scale, (long long)limit_ns,
+                                                              status);
     LLMK_LAUNCH_CHECK();
     return LLMK_OK;
 }

@@ -86,6 +86,9 @@ class MoETransformer(Transformer):
         a["aux_acc"] = torch.zeros(1, dtype=f32, device=dev)
         a["dw"] = torch.empty(N, K, dtype=f32, device=dev)
         a["dlogits"] = torch.empty(N, (E + 7) // 8 * 8, dtype=BF16, device=dev)
+        if E % 8:
+            a["routerw_pad"] = torch.zeros((E + 7) // 8 * 8, C, dtype=BF16, device=dev)
+            a["grouter_pad"] = torch.zeros((E + 7) // 8 * 8, C, dtype=BF16, device=dev)
         Lg = 1 if self.recompute >= 1 else L
         a["hid_pre"] = torch.empty(L, rows, H, dtype=BF16, device=dev)
         a["hid_act"] = torch.empty(Lg, rows, H, dtype=BF16, device=dev)
@@ -225,10 +228,14 @@ class MoETransformer(Transformer):
         if E % 8 == 0:
             gemm.gemm_tn(dlog, ln2, out=g["routerw"][l], accumulate=True)
             gemm.gemm_nn(dlog, p["routerw"][l], out=d_ln2, add=d_ln2)
-        else:  # expert counts that are not a multiple of 8 take the (tiny) library path
-            dl = dlog[:, :E].float()
-            g["routerw"][l].add_((dl.T @ ln2.float()).to(BF16))
-            d_ln2.add_((dl @ p["routerw"][l].float()).to(BF16))
+        else:
+            # expert counts that are not a multiple of 8: the same tcgen05 GEMMs on a router matrix padded with zero
+            # rows up to the next multiple of 8 (dlogits is already that wide, with zero columns)
+            wr_pad, gr_pad = a["routerw_pad"], a["grouter_pad"]
+            wr_pad[:E].copy_(p["routerw"][l])
+            gemm.gemm_tn(dlog, ln2, out=gr_pad)
+            ew.add(g["routerw"][l], gr_pad[:E], out=g["routerw"][l])
+            gemm.gemm_nn(dlog, wr_pad, out=d_ln2, add=d_ln2)
 
     # ------------------------------------------------------------------ forward wrapper: aux-loss bookkeeping
     def forward(self, tokens, targets=None, grad_accum_steps: int = 1, micro_step: int = 0, compute_dlogits: bool = True):

@@ -40,8 +40,12 @@ class FusedComm:
     fused = True
 
     def __init__(self, plan: ZeroPlan, model, device: torch.device, timeout_ms: int | None = None):
-        if not plan.sharded:
-            raise RuntimeError("the fused path implements ZeRO stages >= 1 (use library collectives for stage 0)")
+        if plan.P < 2:
+            raise RuntimeError("the fused path needs at least two ranks")
+        # ZeRO-0 (replicated optimizer state): the same kernels with whole tensors as "shards": every rank peer-loads
+        # and averages all P copies of every gradient (a one-shot all-reduce), holds the complete norm, and updates
+        # all parameters in its own buffer; nothing is pushed.
+        self.replicated = not plan.sharded
         os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
         import torch.distributed._symmetric_memory as symm_mem
 
@@ -106,6 +110,7 @@ class FusedComm:
         self.expert_base = base
         base += len(erows) * self.grid_x
         self.own_grad_ptr = (ctypes.c_longlong * 1)(int(self.grads.data_ptr()))
+        self.own_param_ptr = (ctypes.c_longlong * 1)(int(self.params.data_ptr()))
         self.num_partials = base
         self.partials = torch.zeros(base, dtype=torch.float32, device=device)
         # optimizer table (parameter offset, state offset, length, decay flag)
@@ -150,13 +155,16 @@ class FusedComm:
         """Global gradient norm and clip coefficient; ``loss`` (one float, this rank's mean loss) comes back as the mean
         over the ranks from the same exchange, so a step has no library all-reduce."""
         N.call("llmk_comm_norm_exchange", self.ctrl_ptrs, self.partials, self.num_partials, self.slot_norm, self.rank,
-               self.world_size, self.epoch, float(clip), scale, norm, flag, loss, self.limit_ns, N.status_word())
+               self.world_size, self.epoch, float(clip), scale, norm, flag, loss,
+               1.0 / self.world_size if self.replicated else 1.0, self.limit_ns, N.status_word())
 
     def adamw_push(self, master, m, v, lr, beta1, beta2, step, eps, wd, scale, seed) -> None:
         b1c, b2c = 1.0 - beta1 ** step, 1.0 - beta2 ** step
-        N.call("llmk_comm_adamw_push", self.param_ptrs, master, self.gshard, m, v, self.adam_segs, int(self.adam_segs.shape[0]),
+        # replicated state: every rank updates everything in its own buffer (a one-entry peer table)
+        ptrs, P, me = (self.own_param_ptr, 1, 0) if self.replicated else (self.param_ptrs, self.world_size, self.rank)
+        N.call("llmk_comm_adamw_push", ptrs, master, self.gshard, m, v, self.adam_segs, int(self.adam_segs.shape[0]),
                self.adam_max_len, float(lr), float(beta1), float(beta2), float(b1c), float(b2c), float(eps), float(wd), scale,
-               int(seed) & 0xFFFFFFFF, self.world_size, self.rank)
+               int(seed) & 0xFFFFFFFF, P, me)
         N.call("llmk_comm_signal", self.ctrl_ptrs, self.slot_params, self.rank, self.world_size, self.epoch)
 
     def skip_update(self) -> None:

@@ -365,7 +365,7 @@ class ShardedComm:
             self._gathers_in_flight.clear()
         optim.global_norm2(self.gshard, self.shard_segs, self.shard_max_len, out=self.norm2[:1], partials=self.norm_partials)
         N.call("llmk_comm_norm_exchange", self.ctrl_ptrs, self.norm2, 1, self.slot_norm, self.rank, self.world_size, self.epoch,
-               float(clip), scale, norm, flag, loss, self.limit_ns, N.status_word())
+               float(clip), scale, norm, flag, loss, 1.0, self.limit_ns, N.status_word())
 
     # ------------------------------------------------------------------ optimizer
     def adamw_shard(self, master, m, v, lr, beta1, beta2, step, eps, wd, scale, seed) -> None:

@@ -5,6 +5,7 @@ modes:
   cpu_zero<k>      gloo, PyTorch oracle model in fp32, ZeRO stage k, library collectives
   gpu_library<k>   NCCL, CUDA model, ZeRO stage k, library collectives
   gpu_fused        NCCL bootstrap, CUDA model, ZeRO-1 through the fused peer-memory kernels
+  gpu_fused0       the same kernels with replicated optimizer state (ZeRO-0: one-shot all-reduce by peer loads)
   gpu_sharded<k>   ZeRO stage 2 / 3 with really sharded gradients / parameters (peer-memory kernels); every
                    step is split into two micro-steps so that the shard accumulation is exercised
   gpu_moe_a2a1     the same with the experts' rows exchanged through all_to_all_single (the measured baseline)
@@ -98,7 +99,7 @@ def main():
         model = Transformer(cfg, device=device, recompute=int(os.environ.get("LLMK_TEST_RECOMPUTE", "0")))
     model.init_weights(42)
     plan = ZeroPlan(cfg, world, rank, stage)
-    if mode in ("gpu_fused", "gpu_moe_fused"):
+    if mode in ("gpu_fused", "gpu_fused0", "gpu_moe_fused"):
         from llm_kittens_b200.parallel.fused import FusedComm
 
         comm = FusedComm(plan, model, device, timeout_ms=20000)

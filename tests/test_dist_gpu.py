@@ -41,6 +41,21 @@ def test_fused_comm_matches_library_and_zero0(tmp_path):
     assert f0["losses"][-1] < f0["losses"][0]
 
 
+def test_fused_comm_with_replicated_state_matches_library_zero0(tmp_path):
+    """ZeRO-0 on the framework's own kernels: every rank averages all copies of every gradient by peer loads and
+    updates all parameters itself; same training as the NCCL all-reduce path, replicas bit-identical."""
+    _need_two_gpus()
+    f0, f1 = _run("gpu_fused0", tmp_path)
+    z0, _ = _run("gpu_library0", tmp_path)
+    assert torch.equal(f0["params"], f1["params"])
+    assert f0["losses"] == f1["losses"] and f0["norms"] == f1["norms"]
+    for a, b in zip(f0["losses"], z0["losses"]):
+        assert abs(a - b) < 0.02
+    for a, b in zip(f0["norms"], z0["norms"]):
+        assert abs(a - b) < 0.03 * max(1.0, b)
+    assert (f0["params"] - z0["params"]).abs().max().item() < 0.02
+
+
 def test_fused_comm_micro_step_replayed_from_cuda_graphs(tmp_path):
     """The fused ZeRO-1 micro-step (forward, backward, per-bucket signals and reduce-scatter kernels that read the
     step's epoch from device memory) captured once and replayed: the same losses, norms and parameters as eager
