@@ -122,34 +122,47 @@ rs_bucket_kernel(Peers grads, const int* my_ctrl, int slot, int epoch, const lon
     const size_t g_off = (size_t)seg[0], s_off = (size_t)seg[1], len = (size_t)seg[2];
     float nrm = 0.f;
     if (ok) {
-        for (size_t i = ((size_t)blockIdx.x * TPB + threadIdx.x) * 8; i < len; i += (size_t)gridDim.x * TPB * 8) {
-            float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-            uint4 raw[MAXP];
+        // two 8-element groups per thread and iteration: 2 * P independent 128-bit peer loads are in flight before the
+        // first one is used (with P = 2 a single group leaves the links idle most of the time)
+        const size_t stride = (size_t)gridDim.x * TPB * 8;
+        for (size_t i0 = ((size_t)blockIdx.x * TPB + threadIdx.x) * 8; i0 < len; i0 += 2 * stride) {
+            const size_t i1 = i0 + stride;
+            const bool two = i1 < len;
+            uint4 raw[2][MAXP];
 #pragma unroll
             for (int r = 0; r < MAXP; r++)
-                if (r < P) raw[r] = ld_volatile_v4(static_cast<const bf16*>(grads.p[r]) + g_off + i);
-#pragma unroll
-            for (int r = 0; r < MAXP; r++) {
                 if (r < P) {
-                    float f[8];
-                    unpack8(*reinterpret_cast<const bf16x8*>(&raw[r]), f);
-#pragma unroll
-                    for (int j = 0; j < 8; j++) acc[j] += f[j];
+                    raw[0][r] = ld_volatile_v4(static_cast<const bf16*>(grads.p[r]) + g_off + i0);
+                    if (two) raw[1][r] = ld_volatile_v4(static_cast<const bf16*>(grads.p[r]) + g_off + i1);
                 }
-            }
 #pragma unroll
-            for (int j = 0; j < 8; j++) {
-                acc[j] *= inv_p;
-                nrm += acc[j] * acc[j];
+            for (int h = 0; h < 2; h++) {
+                if (h == 1 && !two) break;
+                const size_t i = h ? i1 : i0;
+                float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+#pragma unroll
+                for (int r = 0; r < MAXP; r++) {
+                    if (r < P) {
+                        float f[8];
+                        unpack8(*reinterpret_cast<const bf16x8*>(&raw[h][r]), f);
+#pragma unroll
+                        for (int j = 0; j < 8; j++) acc[j] += f[j];
+                    }
+                }
+#pragma unroll
+                for (int j = 0; j < 8; j++) {
+                    acc[j] *= inv_p;
+                    nrm += acc[j] * acc[j];
+                }
+                float4* dst = reinterpret_cast<float4*>(gshard + s_off + i);
+                if (accumulate) {   // later micro-steps of a sharded-gradient step add to the running shard
+                    const float4 o0 = dst[0], o1 = dst[1];
+                    acc[0] += o0.x; acc[1] += o0.y; acc[2] += o0.z; acc[3] += o0.w;
+                    acc[4] += o1.x; acc[5] += o1.y; acc[6] += o1.z; acc[7] += o1.w;
+                }
+                dst[0] = make_float4(acc[0], acc[1], acc[2], acc[3]);
+                dst[1] = make_float4(acc[4], acc[5], acc[6], acc[7]);
             }
-            float4* dst = reinterpret_cast<float4*>(gshard + s_off + i);
-            if (accumulate) {   // later micro-steps of a sharded-gradient step add to the running shard
-                const float4 o0 = dst[0], o1 = dst[1];
-                acc[0] += o0.x; acc[1] += o0.y; acc[2] += o0.z; acc[3] += o0.w;
-                acc[4] += o1.x; acc[5] += o1.y; acc[6] += o1.z; acc[7] += o1.w;
-            }
-            dst[0] = make_float4(acc[0], acc[1], acc[2], acc[3]);
-            dst[1] = make_float4(acc[4], acc[5], acc[6], acc[7]);
         }
     }
     nrm = block_sum(nrm, sh);

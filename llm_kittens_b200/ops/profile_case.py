@@ -3,7 +3,9 @@
     python -m llm_kittens_b200.ops.profile_case <case> [launches]
 
 cases: gemm_nt, gemm_nt_gelu, gemm_nn, gemm_tn, attn_fwd, attn_bwd, layernorm_fwd, layernorm_bwd,
-classifier, adamw, comm_rs, comm_adamw_push (the peer-memory kernels with all ranks emulated on one GPU).
+classifier, adamw, comm_rs, comm_adamw_push, comm_ag_flags (the peer-memory kernels with all ranks emulated on one GPU),
+gemm_b_ready (the GEMM that polls the flags of a gathered weight, flags already set), gemm_qkv_rope (QKV projection with
+RoPE in the epilogue), moe_dispatch / moe_grouped_a_ready (the expert exchange with its arrival table, ranks emulated).
 Each case allocates inputs larger than the L2 (but well under a few GB), runs
 the op twice as warm-up and then `launches` (default 2) more times, and checks the status word.
 Used as ``ncu --set full --clock-control none -k regex:<kernel> -s <warm-up launches> -c 1 ...``.
@@ -96,6 +98,78 @@ def build(case: str):
         scale = torch.ones(1, device="cuda")
         return lambda: N.call("llmk_comm_adamw_push", ptrs, master, gshard, m, v, segs, L, shard, 1e-4, 0.9, 0.95, 0.1, 0.05, 1e-8,
                               0.1, scale, 1234, P, 0)
+    if case == "comm_ag_flags":
+        # the tile-granular gather of one Llama-3 8B block's matrices from 8 "ranks" that are 8 local buffers
+        import ctypes
+
+        P = 8
+        tensors = [4096 * 6144, 4096 * 4096, 4096 * 14336, 4096 * 14336, 14336 * 4096]
+        shard_total = sum(t // P for t in tensors)
+        shards = [_rnd(shard_total, scale=0.02) for _ in range(P)]
+        ptrs = (ctypes.c_longlong * P)(*[int(b.data_ptr()) for b in shards])
+        staging = torch.empty(sum(tensors), dtype=BF, device="cuda")
+        rows, off, s_off, nflags = [], 0, 0, 0
+        for size in tensors:
+            ln = size // P
+            cps = max(1, min(8, ln // (1 << 19)))
+            while cps > 1 and ln % (cps * 8):
+                cps -= 1
+            rows.append((s_off, off, ln, nflags, cps))
+            nflags += P * cps
+            off += size
+            s_off += ln
+        table = torch.tensor(rows, dtype=torch.int64, device="cuda")
+        flags, arrivals = torch.zeros(nflags, dtype=torch.int32, device="cuda"), torch.zeros(nflags, dtype=torch.int32, device="cuda")
+        tick = [0]
+
+        def run():
+            tick[0] += 1
+            N.call("llmk_comm_ag_bucket_flags", ptrs, staging, table, len(rows), max(r[4] for r in rows), P, flags, arrivals,
+                   max(1, min(16, 600 // nflags)), tick[0])
+
+        return run
+    if case == "gemm_b_ready":
+        M, Nn, K = 8192, 6144, 4096                      # Llama-3 8B QKV projection on 8192 tokens
+        a, w, out = _rnd(M, K), _rnd(Nn, K, scale=0.02), torch.empty(M, Nn, device="cuda", dtype=BF)
+        chunk = 524288
+        flags = torch.full(((Nn * K) // chunk,), 5, dtype=torch.int32, device="cuda")
+        entry = gemm.register_b_ready(w, flags, 0, chunk, int(1e9))
+        entry[3] = 5
+        return lambda: gemm.gemm_nt(a, w, out=out)
+    if case == "gemm_qkv_rope":
+        from . import elementwise as ew
+
+        B, T, NH, NKVH, HS, Cc = 2, 4096, 32, 8, 128, 4096
+        x, w = _rnd(B * T, Cc), _rnd((NH + 2 * NKVH) * HS, Cc, scale=0.02)
+        out = torch.empty(B * T, (NH + 2 * NKVH) * HS, device="cuda", dtype=BF)
+        table = ew.rope_tables(T, HS, 500000.0, False)
+        return lambda: gemm.gemm_qkv_rope(x, w, table, T, (NH + NKVH) * HS, HS, out=out)
+    if case in ("moe_dispatch", "moe_grouped_a_ready"):
+        # one MoE layer's exchange at the d24 shape (C=1024, H=4096, 8 experts, top-2, 16384 tokens): this GPU plays all
+        # ranks (a one-entry peer table), so dispatch, arrival table and the waiting GEMM are exercised without a peer
+        from . import moe as moe_ops
+
+        Ntok, Cc, H, E, K = 16384, 1024, 4096, 8, 2
+        cap = int(-(-1.25 * K * Ntok // E))
+        cap = (cap + 7) // 8 * 8
+        x, wr = _rnd(Ntok, Cc), _rnd(E, Cc, scale=0.5)
+        probs, idx, tw = moe_ops.router_fwd(x, wr, K)
+        slot, counts = moe_ops.assign_slots(idx, E, cap)
+        recv = torch.zeros(E * cap, Cc, dtype=BF, device="cuda")
+        arrive = torch.zeros(E, dtype=torch.int32, device="cuda")
+        done = torch.zeros(1, dtype=torch.int32, device="cuda")
+        ep = [0]
+        w1, b1 = _rnd(E * H, Cc, scale=0.02), _rnd(E * H)
+        act, pre = torch.empty(E * cap, H, dtype=BF, device="cuda"), torch.empty(E * cap, H, dtype=BF, device="cuda")
+
+        def run():
+            ep[0] += 1
+            moe_ops.dispatch_signal(moe_ops.ptr_table([recv]), x, idx, slot, tw, counts, E, cap, 0, 1, False, moe_ops.ptr_table([arrive]),
+                                    0, done, ep[0])
+            if case == "moe_grouped_a_ready":
+                gemm.gemm_nt(recv, w1, bias=b1, out=act, gelu_pre_out=pre, groups=E, a_ready=(arrive, cap, ep[0], int(1e9)))
+
+        return run
     raise SystemExit(f"unknown case {case}")
 
 

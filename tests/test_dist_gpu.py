@@ -182,3 +182,39 @@ def test_rank_that_leaves_between_steps_is_noticed_on_the_host(tmp_path):
     r0, r1 = torch.load(tmp_path / "rank0.pt"), torch.load(tmp_path / "rank1.pt")
     assert r1["outcome"] == "left" and r0["outcome"] == "peer_left"
     assert len(r0["losses"]) == 2 and r0["losses"] == r1["losses"]
+
+
+def test_two_devices_in_one_process():
+    """Function attributes (opt-in shared memory) and cached device properties are per device: a process that has
+    used the kernels on cuda:0 must be able to use them on cuda:1 as well (GEMM, attention, norm backward, classifier:
+    the launchers that need more than the default shared memory)."""
+    _need_two_gpus()
+    from llm_kittens_b200.ops import _native, attention, classifier, gemm, norm
+
+    results = []
+    for dev in (0, 1, 0):
+        with torch.cuda.device(dev):
+            g = torch.Generator(device=f"cuda:{dev}").manual_seed(3)
+            rnd = lambda *s: (torch.randn(*s, generator=g, device=f"cuda:{dev}") * 0.1).to(torch.bfloat16)
+            a, w, bias = rnd(512, 256), rnd(768, 256), rnd(768)
+            out = gemm.gemm_nt(a, w, bias=bias)
+            pre = torch.empty_like(out)
+            act = gemm.gemm_nt(a, w, bias=bias, gelu_pre_out=pre)
+            dw = gemm.gemm_tn(out, a)
+            qkv = rnd(1, 256, 3 * 4 * 64)
+            o, lse = attention.attention_fwd(qkv, 1, 256, 4, 4, 64)
+            dqkv = attention.attention_bwd(rnd(1, 256, 4 * 64), qkv, o, lse, 1, 256, 4, 4, 64)
+            x, lw, lb = rnd(512, 768), rnd(768) + 1, rnd(768)
+            ln, mean, rstd = norm.layernorm_fwd(x, lw, lb)
+            dinp, dlw, dlb = torch.zeros_like(x), torch.zeros_like(lw), torch.zeros_like(lb)
+            norm.layernorm_bwd(dinp, dlw, dlb, ln, x, lw, mean, rstd)
+            logits = rnd(64, 50304)
+            tg = torch.randint(0, 50257, (64,), generator=g, device=f"cuda:{dev}", dtype=torch.int32)
+            losses = classifier.fused_classifier(logits, tg, 50257, 1.0 / 64)
+            torch.cuda.synchronize()
+            _native.check_status()
+            results.append([t.float().cpu() for t in (out, act, dw, o, dqkv, dinp, losses)])
+    for a, b in zip(results[0], results[1]):
+        assert torch.equal(a, b)      # the same seeded inputs give the same bits on both devices
+    for a, b in zip(results[0], results[2]):
+        assert torch.equal(a, b)
