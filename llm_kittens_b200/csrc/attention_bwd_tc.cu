@@ -139,7 +139,10 @@ __global__ void __launch_bounds__(THREADS, Inner<HS>::CTAS)
 attn_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_constant__ CUtensorMap tmQKVin,
                        const __grid_constant__ CUtensorMap tmDOin, const __grid_constant__ CUtensorMap tmDQKV,
                        const float* __restrict__ lse, const float* __restrict__ dvec, int T, int NH, int NKVH, float scale,
-                       int* status, const float2* __restrict__ rope) {
+                       int* status, const float2* __restrict__ rope, int Tkv, int causal) {
+    // Tkv / causal: in a context-parallel (ring) step the keys and values (tmQKV, and the output tmDQKV) belong to
+    // another chunk of the sequence, Tkv rows per batch entry, possibly in a peer's memory; causal = 0 means every key
+    // precedes every query, so all query sub-tiles are visited and nothing is masked. Usual case: Tkv = T, causal = 1.
     using C = DkvCfg<HS>;
     constexpr int RING = C::RING, BN = C::BN;
     extern __shared__ __align__(1024) uint8_t smem[];
@@ -170,9 +173,10 @@ attn_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_c
     const int kt = blockIdx.x, hk = blockIdx.y, b = blockIdx.z;
     const int hr = NH / NKVH;
     const int kv0 = kt * BM;
-    const int nq = (T - kv0) / BN;   // query sub-tiles starting at kv0
+    const int q_first = causal ? kv0 : 0;
+    const int nq = (T - q_first) / BN;   // query sub-tiles that see these keys
     const int total = nq * hr;
-    const int row_base = b * T;
+    const int row_base = b * T, kv_row_base = b * Tkv;
     const int k_col = (NH + hk) * HS, v_col = (NH + NKVH + hk) * HS;
     const float scale_log2 = scale * LOG2E;
 
@@ -203,14 +207,14 @@ attn_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_c
     if (warp == 0) {
         if (lane == 0) {
             ptx::mbar_arrive_expect_tx(kv_full, 2 * C::TILE);
-            load_tile<HS, BM>(sK, &tmQKV, kv_full, k_col, row_base + kv0);
-            load_tile<HS, BM>(sV, &tmQKV, kv_full, v_col, row_base + kv0);
+            load_tile<HS, BM>(sK, &tmQKV, kv_full, k_col, kv_row_base + kv0);
+            load_tile<HS, BM>(sV, &tmQKV, kv_full, v_col, kv_row_base + kv0);
         }
         __syncwarp();
         for (int it = 0; it < total; it++) {
             const int s = it % RING;
             if (!ptx::mbar_wait(&ring_empty[s], ((it / RING) & 1) ^ 1, abort_flag, status, LLMK_ST_TIMEOUT_TMA_EMPTY, it)) break;
-            const int hq = hk * hr + it / nq, q0 = kv0 + (it % nq) * BN;
+            const int hq = hk * hr + it / nq, q0 = q_first + (it % nq) * BN;
             if (lane == 0) {
                 ptx::mbar_arrive_expect_tx(&ring_full[s], 2 * C::RT);
                 load_tile<HS, BN>(sRing + s * 2 * C::RT, &tmQKVin, &ring_full[s], hq * HS, row_base + q0);
@@ -305,7 +309,7 @@ attn_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_c
                 if (!ok) break;
             }
             ptx::tc_fence_after();
-            const bool diag = dq0 < BM;                      // some (key, query) pairs of this sub-tile are masked
+            const bool diag = causal && dq0 < BM;            // some (key, query) pairs of this sub-tile are masked
             // the two TMEM loads of chunk c4+1 are issued before chunk c4 is processed (two register sets)
             uint32_t vsA[32], vdA[32], vsB[32], vdB[32];
             auto process = [&](int c4, const uint32_t (&vs)[32], const uint32_t (&vd)[32]) {
@@ -383,8 +387,8 @@ attn_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_c
                 if (ptx::mbar_wait(epi, 0, abort_flag, status, LLMK_ST_TIMEOUT_ACC_FULL, 4000)) {
 #pragma unroll
                     for (int c = 0; c < HS / 64; c++) {
-                        ptx::tma_store_2d(&tmDQKV, stage_dk + c * (BM * 128), k_col + 64 * c, row_base + kv0);
-                        ptx::tma_store_2d(&tmDQKV, stage_dv + c * (BM * 128), v_col + 64 * c, row_base + kv0);
+                        ptx::tma_store_2d(&tmDQKV, stage_dk + c * (BM * 128), k_col + 64 * c, kv_row_base + kv0);
+                        ptx::tma_store_2d(&tmDQKV, stage_dv + c * (BM * 128), v_col + 64 * c, kv_row_base + kv0);
                     }
                     ptx::tma_store_commit();
                     ptx::tma_store_wait_read<0>();
@@ -673,7 +677,8 @@ __global__ void __launch_bounds__(THREADS, Inner<HS>::CTAS)
 attn_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_constant__ CUtensorMap tmDO,
                       const __grid_constant__ CUtensorMap tmQKVin, const __grid_constant__ CUtensorMap tmDQKV,
                       const float* __restrict__ lse, const float* __restrict__ dvec, int T, int NH, int NKVH, float scale,
-                      int* status, const float2* __restrict__ rope) {
+                      int* status, const float2* __restrict__ rope, int Tkv, int causal) {
+    // Tkv / causal: as in the dK/dV kernel; here tmQKVin (the key / value sub-tiles) may cover another chunk
     using C = DqCfg<HS>;
     constexpr int BN = C::BN;
     extern __shared__ __align__(1024) uint8_t smem[];
@@ -702,8 +707,8 @@ attn_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_co
     const int h = blockIdx.y, b = blockIdx.z;
     const int hk = h / (NH / NKVH);
     const int q0 = qt * BM;
-    const int nkv = (q0 + BM) / BN;   // key sub-tiles up to and including the diagonal
-    const int row_base = b * T;
+    const int nkv = causal ? (q0 + BM) / BN : Tkv / BN;   // key sub-tiles up to and including the diagonal / all of them
+    const int row_base = b * T, kv_row_base = b * Tkv;
     const int q_col = h * HS, k_col = (NH + hk) * HS, v_col = (NH + NKVH + hk) * HS;
     const float scale_log2 = scale * LOG2E;
 
@@ -742,8 +747,8 @@ attn_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_co
             if (!ptx::mbar_wait(&ring_empty[s], ((j >> 1) & 1) ^ 1, abort_flag, status, LLMK_ST_TIMEOUT_TMA_EMPTY, j)) break;
             if (lane == 0) {
                 ptx::mbar_arrive_expect_tx(&ring_full[s], 2 * C::RT);
-                load_tile<HS, BN>(sRing + s * 2 * C::RT, &tmQKVin, &ring_full[s], k_col, row_base + j * BN);
-                load_tile<HS, BN>(sRing + s * 2 * C::RT + C::RT, &tmQKVin, &ring_full[s], v_col, row_base + j * BN);
+                load_tile<HS, BN>(sRing + s * 2 * C::RT, &tmQKVin, &ring_full[s], k_col, kv_row_base + j * BN);
+                load_tile<HS, BN>(sRing + s * 2 * C::RT + C::RT, &tmQKVin, &ring_full[s], v_col, kv_row_base + j * BN);
             }
             __syncwarp();
         }
@@ -809,7 +814,7 @@ attn_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_co
             }
             ptx::tc_fence_after();
             const int dk0 = j * BN - q0;            // first key of the sub-tile relative to the first query
-            const bool diag = dk0 + BN > 0;         // reaches past the first query: some pairs are masked
+            const bool diag = causal && dk0 + BN > 0;   // reaches past the first query: some pairs are masked
             uint32_t vsA[32], vdA[32], vsB[32], vdB[32];
             auto process = [&](int c4, const uint32_t (&vs)[32], const uint32_t (&vd)[32]) {
 #pragma unroll
@@ -885,9 +890,14 @@ attn_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_co
 }
 
 template <int HS>
+// `kv_qkv` / `dkv_out` / `Tkv` / `causal`: a context-parallel step takes its keys and values from another packed tensor
+// (possibly a peer's) and writes dK / dV into a tensor shaped like it; the usual backward passes qkv, dqkv, T, 1.
 static int launch(const void* qkv, const void* dout, bf16* dqkv, const float* lse, const float* dvec, int B, int T, int NH, int NKVH,
-                  int* status, const float2* rope, cudaStream_t stream) {
+                  int* status, const float2* rope, cudaStream_t stream, const void* kv_qkv = nullptr, bf16* dkv_out = nullptr,
+                  int Tkv = 0, int causal = 1) {
     constexpr int BN = Inner<HS>::BN;
+    const bool ring = kv_qkv != nullptr;
+    if (!ring) { kv_qkv = qkv; dkv_out = dqkv; Tkv = T; causal = 1; }
     static PerDeviceOnce once_configured;
     if (once_configured.first()) {
         LLMK_CUDA_TRY(cudaFuncSetAttribute(attn_bwd_dkv_tc_kernel<HS>, cudaFuncAttributeMaxDynamicSharedMemorySize, DkvCfg<HS>::SMEM_BYTES));
@@ -898,13 +908,18 @@ static int launch(const void* qkv, const void* dout, bf16* dqkv, const float* ls
                                            cudaSharedmemCarveoutMaxShared));
     }
     const uint64_t width = (uint64_t)(NH + 2 * NKVH) * HS, rows = (uint64_t)B * T, cw = (uint64_t)NH * HS;
-    CUtensorMap tq, tq_in, tdo, tdo_in, tdqkv;
+    const uint64_t kv_rows = (uint64_t)B * Tkv;
+    // tq / tq_in: the queries (128-row tiles / sub-tiles); tkv / tkv_in: the keys and values; tdqkv / tdkv: outputs
+    CUtensorMap tq, tq_in, tdo, tdo_in, tdqkv, tkv, tkv_in, tdkv;
     int rc;
     if ((rc = gemm::make_tmap_2d(&tq, qkv, width, rows, width, 64, BM))) return rc;
     if ((rc = gemm::make_tmap_2d(&tq_in, qkv, width, rows, width, 64, BN))) return rc;
     if ((rc = gemm::make_tmap_2d(&tdo, dout, cw, rows, cw, 64, BM))) return rc;
     if ((rc = gemm::make_tmap_2d(&tdo_in, dout, cw, rows, cw, 64, BN))) return rc;
     if ((rc = gemm::make_tmap_2d(&tdqkv, dqkv, width, rows, width, 64, BM))) return rc;
+    if ((rc = gemm::make_tmap_2d(&tkv, kv_qkv, width, kv_rows, width, 64, BM))) return rc;
+    if ((rc = gemm::make_tmap_2d(&tkv_in, kv_qkv, width, kv_rows, width, 64, BN))) return rc;
+    if ((rc = gemm::make_tmap_2d(&tdkv, dkv_out, width, kv_rows, width, 64, BM))) return rc;
     const float scale = 1.0f / sqrtf((float)HS);
     // The pipelined kernel has no second CTA on its SM to hide its prologue and epilogue behind, so it only pays off
     // when a CTA loops over many sub-tiles (long sequences, grouped queries): measured 1.08 vs 1.12 ms at T=2048 with
@@ -912,7 +927,7 @@ static int launch(const void* qkv, const void* dout, bf16* dqkv, const float* ls
     const char* dkv_env = getenv("LLMK_ATTN_BWD_DKV");   // read on every call, so that one process can run both versions
     const bool long_loops = (T / 64) * (NH / NKVH) >= 64;
     const bool use_v2 = dkv_env != nullptr ? dkv_env[0] == '2' : long_loops;
-    if (HS == 64 && use_v2) {
+    if (HS == 64 && use_v2 && !ring) {
         static PerDeviceOnce once_configured2;
         if (once_configured2.first()) {
             LLMK_CUDA_TRY(cudaFuncSetAttribute(dkv2::attn_bwd_dkv2_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, dkv2::SMEM_BYTES));
@@ -924,12 +939,12 @@ static int launch(const void* qkv, const void* dout, bf16* dqkv, const float* ls
         dkv2::attn_bwd_dkv2_kernel<<<dim3(T / BM, NKVH, B), dkv2::THREADS2, dkv2::SMEM_BYTES, stream>>>(tq, tq_in64, tdo_in64, tdqkv, lse, dvec,
                                                                                                     T, NH, NKVH, scale, status, rope);
     } else {
-        attn_bwd_dkv_tc_kernel<HS><<<dim3(T / BM, NKVH, B), THREADS, DkvCfg<HS>::SMEM_BYTES, stream>>>(tq, tq_in, tdo_in, tdqkv, lse, dvec,
-                                                                                                     T, NH, NKVH, scale, status, rope);
+        attn_bwd_dkv_tc_kernel<HS><<<dim3(Tkv / BM, NKVH, B), THREADS, DkvCfg<HS>::SMEM_BYTES, stream>>>(
+            tkv, tq_in, tdo_in, tdkv, lse, dvec, T, NH, NKVH, scale, status, rope, Tkv, causal);
     }
     LLMK_LAUNCH_CHECK();
-    attn_bwd_dq_tc_kernel<HS><<<dim3(T / BM, NH, B), THREADS, DqCfg<HS>::SMEM_BYTES, stream>>>(tq, tdo, tq_in, tdqkv, lse, dvec, T, NH,
-                                                                                             NKVH, scale, status, rope);
+    attn_bwd_dq_tc_kernel<HS><<<dim3(T / BM, NH, B), THREADS, DqCfg<HS>::SMEM_BYTES, stream>>>(tq, tdo, tkv_in, tdqkv, lse, dvec, T, NH,
+                                                                                             NKVH, scale, status, rope, Tkv, causal);
     LLMK_LAUNCH_CHECK();
     return LLMK_OK;
 }
@@ -956,6 +971,23 @@ static int attention_bwd_tc_impl(void* dqkv, const void* dvec, const void* dout,
 LLMK_API int llmk_attention_bwd_tc(void* dqkv, const void* dvec, const void* dout, const void* qkv, const void* lse, int B, int T,
                                    int NH, int NKVH, int HS, int* status, void* stream_) {
     return attention_bwd_tc_impl(dqkv, dvec, dout, qkv, lse, B, T, NH, NKVH, HS, status, nullptr, stream_);
+}
+
+// One step of context-parallel (ring) attention, backward: the queries of `qkv` [B, T, W] with their output gradient
+// `dout`, the FINAL log-sum-exp `lse` and D = rowsum(dO * O) of the merged output, against the keys and values of
+// `kv_qkv` [B, Tkv, W] (possibly another rank's chunk in peer memory, pulled by TMA loads). Writes this step's dQ into
+// the q columns of `dq_step` [B, T, W] and this rank's contribution to the chunk's dK / dV into the k / v columns of
+// `dkv_step` [B, Tkv, W]; the caller sums dQ over the steps and the chunk's owner sums dK / dV over the ranks.
+LLMK_API int llmk_attention_bwd_ring_step(void* dq_step, void* dkv_step, const void* dvec, const void* dout, const void* qkv,
+                                          const void* kv_qkv, const void* lse, int B, int T, int Tkv, int NH, int NKVH, int HS,
+                                          int causal, int* status, void* stream_) {
+    cudaStream_t stream = (cudaStream_t)stream_;
+    if (T % 128 || Tkv % 128 || NH % NKVH || (HS != 64 && HS != 128) || (causal && T != Tkv) || kv_qkv == nullptr) return LLMK_ERR_SHAPE;
+    if (HS == 64)
+        return attn_bwd_tc::launch<64>(qkv, dout, (bf16*)dq_step, (const float*)lse, (const float*)dvec, B, T, NH, NKVH, status, nullptr,
+                                       stream, kv_qkv, (bf16*)dkv_step, Tkv, causal ? 1 : 0);
+    return attn_bwd_tc::launch<128>(qkv, dout, (bf16*)dq_step, (const float*)lse, (const float*)dvec, B, T, NH, NKVH, status, nullptr,
+                                    stream, kv_qkv, (bf16*)dkv_step, Tkv, causal ? 1 : 0);
 }
 
 // The same with the backward of RoPE folded into the dQ and dK output tiles: `qkv` holds ROTATED q and k (as the QKV

@@ -129,8 +129,12 @@ __device__ __forceinline__ float chunk_probs(const uint32_t (&s)[32], uint8_t* a
 
 template <int HS>
 __global__ void __launch_bounds__(THREADS, Cfg<HS>::CTAS_PER_SM)
-attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQKV, bf16* __restrict__ out, float* __restrict__ lse, int T, int NH,
-                   int NKVH, float scale_log2, int* status) {
+attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_constant__ CUtensorMap tmKV, bf16* __restrict__ out,
+                   float* __restrict__ lse, int T, int Tkv, int causal, int NH, int NKVH, float scale_log2, int* status) {
+    // tmKV / Tkv / causal: the keys and values may come from ANOTHER packed QKV tensor of the same layout (a peer's
+    // chunk of the sequence in context-parallel attention; the map may cover that peer's memory, loads only, no
+    // multicast). causal = 1: queries and keys cover the same positions (the usual case, tmKV == tmQKV); causal = 0:
+    // every key precedes every query, all Tkv / 128 key tiles are used unmasked.
     using C = Cfg<HS>;
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     uint8_t* smem = smem_raw;
@@ -163,8 +167,8 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQKV, bf16* __restrict__
     const int qb = gridDim.x - 1 - blockIdx.x;  // late (long) query blocks first
     const int h = blockIdx.y, b = blockIdx.z;
     const int hk = h / (NH / NKVH);
-    const int nkv = qb + 1;
-    const int row_base = b * T;
+    const int nkv = causal ? qb + 1 : Tkv / BKV;
+    const int row_base = b * T, kv_row_base = b * Tkv;
     const int q_col = h * HS, k_col = (NH + hk) * HS, v_col = (NH + NKVH + hk) * HS;
 
     if (threadIdx.x == 0) {
@@ -180,6 +184,7 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQKV, bf16* __restrict__
         *abort_flag = 0;
         ptx::fence_barrier_init();
         ptx::prefetch_tmap(&tmQKV);
+        ptx::prefetch_tmap(&tmKV);
     }
     if (warp == 1) {
         ptx::tmem_alloc(tmem_slot, C::TMEM_COLS);
@@ -206,8 +211,8 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQKV, bf16* __restrict__
                 ptx::mbar_arrive_expect_tx(&kv_full[s], 2 * C::TILE_BYTES);
 #pragma unroll
                 for (int c = 0; c < HS / 64; c++) {
-                    ptx::tma_load_2d(sK + s * C::TILE_BYTES + c * ATOM_BYTES, &tmQKV, &kv_full[s], k_col + 64 * c, row_base + j * BKV);
-                    ptx::tma_load_2d(sV + s * C::TILE_BYTES + c * ATOM_BYTES, &tmQKV, &kv_full[s], v_col + 64 * c, row_base + j * BKV);
+                    ptx::tma_load_2d(sK + s * C::TILE_BYTES + c * ATOM_BYTES, &tmKV, &kv_full[s], k_col + 64 * c, kv_row_base + j * BKV);
+                    ptx::tma_load_2d(sV + s * C::TILE_BYTES + c * ATOM_BYTES, &tmKV, &kv_full[s], v_col + 64 * c, kv_row_base + j * BKV);
                 }
             }
             __syncwarp();
@@ -277,7 +282,7 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQKV, bf16* __restrict__
             ok = ptx::mbar_wait(s_full, j & 1, abort_flag, status, LLMK_ST_TIMEOUT_ACC_FULL, j);
             if (!ok) break;
             ptx::tc_fence_after();
-            const bool diag = (j == nkv - 1);
+            const bool diag = causal && (j == nkv - 1);
             const int nchunks = diag ? lane_group + 1 : 4;   // warp-uniform: later chunks are fully masked
             uint32_t s[4][32];
 #pragma unroll
@@ -369,7 +374,8 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQKV, bf16* __restrict__
 }
 
 template <int HS>
-static int launch(const CUtensorMap& tm, bf16* out, float* lse, int B, int T, int NH, int NKVH, int* status, cudaStream_t stream) {
+static int launch(const CUtensorMap& tm, const CUtensorMap& tm_kv, bf16* out, float* lse, int B, int T, int Tkv, int causal, int NH,
+                  int NKVH, int* status, cudaStream_t stream) {
     static PerDeviceOnce once_configured;
     if (once_configured.first()) {
         LLMK_CUDA_TRY(cudaFuncSetAttribute(attn_fwd_tc_kernel<HS>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<HS>::SMEM_BYTES));
@@ -378,7 +384,8 @@ static int launch(const CUtensorMap& tm, bf16* out, float* lse, int B, int T, in
     }
     const float scale_log2 = 1.4426950408889634f / sqrtf((float)HS);
     dim3 grid(T / BQ, NH, B);
-    attn_fwd_tc_kernel<HS><<<grid, THREADS, Cfg<HS>::SMEM_BYTES, stream>>>(tm, out, lse, T, NH, NKVH, scale_log2, status);
+    attn_fwd_tc_kernel<HS><<<grid, THREADS, Cfg<HS>::SMEM_BYTES, stream>>>(tm, tm_kv, out, lse, T, Tkv, causal, NH, NKVH, scale_log2,
+                                                                            status);
     LLMK_LAUNCH_CHECK();
     return LLMK_OK;
 }
@@ -698,6 +705,144 @@ LLMK_API int llmk_attention_fwd_tc(void* out, void* lse, const void* qkv, int B,
         if (rc2) return rc2;
         return attn_tc::pair::launch(tm, tm_out, (float*)lse, B, T, NH, NKVH, status, stream);
     }
-    if (HS == 64) return attn_tc::launch<64>(tm, (bf16*)out, (float*)lse, B, T, NH, NKVH, status, stream);
-    return attn_tc::launch<128>(tm, (bf16*)out, (float*)lse, B, T, NH, NKVH, status, stream);
+    if (HS == 64) return attn_tc::launch<64>(tm, tm, (bf16*)out, (float*)lse, B, T, T, 1, NH, NKVH, status, stream);
+    return attn_tc::launch<128>(tm, tm, (bf16*)out, (float*)lse, B, T, T, 1, NH, NKVH, status, stream);
+}
+
+// One step of context-parallel (ring) attention, forward: the queries of `qkv` [B, T, W] (this rank's chunk of the
+// sequence, packed q | k | v) against the keys and values of `kv_qkv` [B, Tkv, W], which may be ANOTHER rank's chunk in
+// peer memory (the K/V tiles are pulled straight from there by TMA loads, no copy and no multicast). `causal` = 1 for
+// the rank's own chunk (same positions, T == Tkv), 0 for a chunk that lies entirely before the queries. Writes the
+// normalised output of this step and its log-sum-exp; llmk_attention_ring_merge folds the steps together. Job of the
+// reference's local ring step (llmc/tk/ring_attention_sm120.cuh:55-189).
+LLMK_API int llmk_attention_fwd_ring_step(void* out, void* lse, const void* qkv, const void* kv_qkv, int B, int T, int Tkv, int NH,
+                                          int NKVH, int HS, int causal, int* status, void* stream_) {
+    cudaStream_t stream = (cudaStream_t)stream_;
+    if (T % 128 || Tkv % 128 || NH % NKVH || (HS != 64 && HS != 128) || (causal && T != Tkv)) return LLMK_ERR_SHAPE;
+    const long width = (long)(NH + 2 * NKVH) * HS;
+    CUtensorMap tm, tm_kv;
+    int rc = gemm::make_tmap_2d(&tm, qkv, (uint64_t)width, (uint64_t)B * T, (uint64_t)width, 64, 128);
+    if (rc) return rc;
+    rc = gemm::make_tmap_2d(&tm_kv, kv_qkv, (uint64_t)width, (uint64_t)B * Tkv, (uint64_t)width, 64, 128);
+    if (rc) return rc;
+    if (HS == 64) return attn_tc::launch<64>(tm, tm_kv, (bf16*)out, (float*)lse, B, T, Tkv, causal ? 1 : 0, NH, NKVH, status, stream);
+    return attn_tc::launch<128>(tm, tm_kv, (bf16*)out, (float*)lse, B, T, Tkv, causal ? 1 : 0, NH, NKVH, status, stream);
+}
+
+namespace llmk {
+namespace attn_tc {
+// acc (fp32, [rows, HS] per head row) and lse_acc fold in one more step: new = logaddexp(lse_acc, lse_step),
+// acc = acc * exp(lse_acc - new) + step * exp(lse_step - new). `first` initialises instead. One warp per (token, head).
+__global__ void __launch_bounds__(256)
+ring_merge_kernel(float* __restrict__ acc, float* __restrict__ lse_acc, const bf16* __restrict__ step, const float* __restrict__ lse_step,
+                  int B, int T, int NH, int HS, int first) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const size_t row = (size_t)blockIdx.x * 8 + warp;           // (b * T + t) * NH + h
+    if (row >= (size_t)B * T * NH) return;
+    const int h = row % NH;
+    const size_t bt = row / NH;
+    const size_t li = ((bt / T) * NH + h) * T + (bt % T);         // lse is [B, NH, T]
+    const float ls = lse_step[li];
+    float wa = 0.f, ws = 1.f, ln = ls;
+    if (!first) {
+        const float la = lse_acc[li];
+        ln = fmaxf(la, ls) + log1pf(__expf(-fabsf(la - ls)));
+        wa = __expf(la - ln);
+        ws = __expf(ls - ln);
+    }
+    for (int i = lane; i < HS; i += 32) {
+        const size_t o = row * HS + i;
+        const float sv = __bfloat162float(step[o]);
+        acc[o] = first ? sv : acc[o] * wa + sv * ws;
+    }
+    if (lane == 0) lse_acc[li] = ln;
+}
+// acc[row][c] (+)= step[row][col0 + c] for c < ncols (fp32 accumulator of a column range of a packed bf16 tensor)
+__global__ void __launch_bounds__(256)
+ring_accumulate_kernel(float* __restrict__ acc, const bf16* __restrict__ step, long rows, int W, int col0, int ncols, int first) {
+    const long i = ((long)blockIdx.x * blockDim.x + threadIdx.x) * 8;
+    if (i >= rows * ncols) return;
+    const long row = i / ncols;
+    const int c = (int)(i - row * ncols);
+    float f[8];
+    unpack8(ld128(step + row * W + col0 + c), f);
+    float4* a = reinterpret_cast<float4*>(acc + i);
+    if (!first) {
+        const float4 a0 = a[0], a1 = a[1];
+        f[0] += a0.x; f[1] += a0.y; f[2] += a0.z; f[3] += a0.w;
+        f[4] += a1.x; f[5] += a1.y; f[6] += a1.z; f[7] += a1.w;
+    }
+    a[0] = make_float4(f[0], f[1], f[2], f[3]);
+    a[1] = make_float4(f[4], f[5], f[6], f[7]);
+}
+
+// out[row][col0 + c] = bf16(acc[row][c])
+__global__ void __launch_bounds__(256)
+ring_store_cols_kernel(bf16* __restrict__ out, const float* __restrict__ acc, long rows, int W, int col0, int ncols) {
+    const long i = ((long)blockIdx.x * blockDim.x + threadIdx.x) * 8;
+    if (i >= rows * ncols) return;
+    const long row = i / ncols;
+    const int c = (int)(i - row * ncols);
+    const float4 a0 = *reinterpret_cast<const float4*>(acc + i), a1 = *reinterpret_cast<const float4*>(acc + i + 4);
+    const float f[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
+    st128(out + row * W + col0 + c, pack8(f));
+}
+
+struct RingPeers {
+    const bf16* p[8];
+};
+// out[row][col0 + c] = sum over ranks r_first..P-1, in rank order, of peer_r[row][col0 + c] (fp32 sum, bf16 result):
+// the owner of a sequence chunk collects the dK / dV contributions that the later ranks left in their buffers.
+__global__ void __launch_bounds__(256)
+ring_sum_peers_kernel(bf16* __restrict__ out, RingPeers peers, long rows, int W, int col0, int ncols, int r_first, int P) {
+    const long i = ((long)blockIdx.x * blockDim.x + threadIdx.x) * 8;
+    if (i >= rows * ncols) return;
+    const long row = i / ncols;
+    const int c = (int)(i - row * ncols);
+    const long off = row * W + col0 + c;
+    float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    for (int r = r_first; r < P; r++) {
+        float f[8];
+        unpack8(ld128(peers.p[r] + off), f);
+#pragma unroll
+        for (int j = 0; j < 8; j++) acc[j] += f[j];
+    }
+    st128(out + off, pack8(acc));
+}
+}  // namespace attn_tc
+}  // namespace llmk
+
+LLMK_API int llmk_ring_accumulate(void* acc, const void* step, long rows, int W, int col0, int ncols, int first, void* stream) {
+    if (ncols % 8 || col0 % 8 || W % 8) return LLMK_ERR_SHAPE;
+    attn_tc::ring_accumulate_kernel<<<ceil_div(rows * ncols / 8, 256), 256, 0, (cudaStream_t)stream>>>((float*)acc, (const bf16*)step, rows,
+                                                                                                     W, col0, ncols, first);
+    LLMK_LAUNCH_CHECK();
+    return LLMK_OK;
+}
+LLMK_API int llmk_ring_store_cols(void* out, const void* acc, long rows, int W, int col0, int ncols, void* stream) {
+    if (ncols % 8 || col0 % 8 || W % 8) return LLMK_ERR_SHAPE;
+    attn_tc::ring_store_cols_kernel<<<ceil_div(rows * ncols / 8, 256), 256, 0, (cudaStream_t)stream>>>((bf16*)out, (const float*)acc, rows, W,
+                                                                                                     col0, ncols);
+    LLMK_LAUNCH_CHECK();
+    return LLMK_OK;
+}
+// `peer_ptrs`: host array of P device pointers, each to that rank's contribution buffer FOR THIS RANK'S CHUNK.
+LLMK_API int llmk_ring_sum_peers(void* out, const long long* peer_ptrs, long rows, int W, int col0, int ncols, int r_first, int P,
+                                 void* stream) {
+    if (ncols % 8 || col0 % 8 || W % 8 || P > 8 || r_first < 0 || r_first >= P) return LLMK_ERR_SHAPE;
+    attn_tc::RingPeers q;
+    for (int i = 0; i < 8; i++) q.p[i] = i < P ? reinterpret_cast<const bf16*>(peer_ptrs[i]) : nullptr;
+    attn_tc::ring_sum_peers_kernel<<<ceil_div(rows * ncols / 8, 256), 256, 0, (cudaStream_t)stream>>>((bf16*)out, q, rows, W, col0, ncols,
+                                                                                                    r_first, P);
+    LLMK_LAUNCH_CHECK();
+    return LLMK_OK;
+}
+
+LLMK_API int llmk_attention_ring_merge(void* acc, void* lse_acc, const void* step, const void* lse_step, int B, int T, int NH, int HS,
+                                       int first, void* stream) {
+    const long rows = (long)B * T * NH;
+    attn_tc::ring_merge_kernel<<<ceil_div(rows, 8), 256, 0, (cudaStream_t)stream>>>((float*)acc, (float*)lse_acc, (const bf16*)step,
+                                                                                   (const float*)lse_step, B, T, NH, HS, first);
+    LLMK_LAUNCH_CHECK();
+    return LLMK_OK;
 }

@@ -11,6 +11,7 @@ modes:
   gpu_moe_a2a1     the same with the experts' rows exchanged through all_to_all_single (the measured baseline)
   gpu_moe_library1 / gpu_moe_fused   mixture-of-experts model, experts split over the ranks (peer-memory
                    dispatch / combine), dense parameters ZeRO-1 through library / fused communication
+  gpu_cp64 / gpu_cp128   context-parallel attention (head size 64 / 128) against the single-GPU kernels on the full sequence
   cpu_fail_rank1   gloo; rank 1 raises before its first collective (failure-detection test)
 environment: LLMK_TEST_LAYERS (dense model depth, default 2), LLMK_TEST_RECOMPUTE (default 0),
 LLMK_TEST_GRAPH (replay the micro-step from CUDA graphs), LLMK_TEST_SKIP_STEP (index of a step whose optimizer update is left out, as the z-score guards of the trainer do)
@@ -78,6 +79,36 @@ def main():
             outcome = "error:" + type(e).__name__
         torch.save({"outcome": outcome}, os.path.join(out_dir, f"rank{rank}.pt"))
         os._exit(0)
+    if mode.startswith("gpu_cp"):
+        # context-parallel attention: every rank holds one chunk of a seeded full sequence; rank 0 also runs the plain
+        # single-GPU kernels on the whole sequence as the reference
+        from llm_kittens_b200.ops import _native, attention
+        from llm_kittens_b200.parallel.context import ContextParallelAttention
+
+        HS = 128 if mode.endswith("128") else 64
+        B, T, NH, NKVH = 2, 256, 4, 2
+        W = (NH + 2 * NKVH) * HS
+        g = torch.Generator().manual_seed(77)
+        full = (torch.randn(B, world * T, W, generator=g) * 0.7).to(torch.bfloat16)
+        dfull = (torch.randn(B, world * T, NH * HS, generator=g) * 0.5).to(torch.bfloat16)
+        cp = ContextParallelAttention(B, T, NH, NKVH, HS, device, timeout_ms=20000)
+        out = dqkv = None
+        for _ in range(2):     # twice: the buffers are reused, and the results must be bit-identical
+            prev = (out, dqkv)
+            out = cp.forward(full[:, rank * T:(rank + 1) * T].contiguous().to(device)).clone()
+            dqkv = cp.backward(dfull[:, rank * T:(rank + 1) * T].contiguous().to(device)).clone()
+        torch.cuda.synchronize()
+        _native.check_status()
+        res = {"out": out.float().cpu(), "dqkv": dqkv.float().cpu(), "same": torch.equal(out, prev[0]) and torch.equal(dqkv, prev[1])}
+        if rank == 0:
+            fq = full.to(device)
+            o, lse = attention.attention_fwd(fq, B, world * T, NH, NKVH, HS)
+            d = attention.attention_bwd(dfull.to(device), fq, o, lse, B, world * T, NH, NKVH, HS)
+            res["ref_out"], res["ref_dqkv"] = o.float().cpu(), d.float().cpu()
+        torch.save(res, os.path.join(out_dir, f"rank{rank}.pt"))
+        dist.barrier()
+        dist.destroy_process_group()
+        return
     moe = "moe" in mode
     cfg = tiny_moe_config() if moe else tiny_config()
     B, T, steps = (2, 128, 3) if moe else (2, 64, 4)
