@@ -51,7 +51,7 @@ constexpr int GROUP_M = 8;
 constexpr int TMEM_COLS = 512;
 
 enum { MODE_NT = 0, MODE_NN = 1, MODE_TN = 2 };
-enum { EPI_BIAS = 1, EPI_GELU = 2, EPI_DGELU = 4, EPI_ADD = 8, EPI_PARTIAL = 16, EPI_ROPE = 32 };
+enum { EPI_BIAS = 1, EPI_GELU = 2, EPI_DGELU = 4, EPI_ADD = 8, EPI_PARTIAL = 16, EPI_ROPE = 32, EPI_SCATTER = 64 };
 
 template <int EPI, bool PAIR>
 struct Cfg {
@@ -125,6 +125,16 @@ struct Params {
     // rope[token][i] = (cos, sin); the columns after them (v) pass through.
     const float2* rope;
     int rope_T, rope_cols, rope_hs;
+    // EPI_SCATTER: the rows of C are the outputs of a mixture-of-experts layer's local experts, stacked as
+    // [e_local][source rank][slot]; instead of a local C, row m goes straight into the `back` buffer of the rank that
+    // sent the token: sc_dst[src] + ((my_rank * Eloc + e_local) * cap + slot) * N (peer stores of whole 128-byte
+    // lines). Every stored (32-row x 64-column) piece is counted per block of `cap` rows in sc_count (local memory,
+    // left at zero); the piece that completes a block release-stores sc_epoch into entry sc_off + e of that source
+    // rank's arrival table (sc_arrive[src]), which is what the combine kernel there waits for.
+    void* sc_dst[8];
+    int* sc_arrive[8];
+    int* sc_count;
+    int sc_cap, sc_P, sc_Eloc, sc_rank, sc_off, sc_epoch;
 };
 
 __device__ __forceinline__ int ld_acquire_sys_s32(const int* ptr) {
@@ -567,12 +577,51 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
                     *reinterpret_cast<bf16x8*>(buf + off) = res[cc];
                     if (EPI & EPI_GELU) *reinterpret_cast<bf16x8*>(buf2 + off) = res2[(EPI & EPI_GELU) ? cc : 0];
                 }
-                ptx::fence_proxy_async_smem();
-                __syncwarp();
-                if (lane == 0) {
-                    ptx::tma_store_2d(&tmC, buf, n_base, row0);
-                    if (EPI & EPI_GELU) ptx::tma_store_2d(&tmX, buf2, n_base, row0);
-                    ptx::tma_store_commit();
+                if constexpr ((EPI & EPI_SCATTER) != 0) {
+                    // the staged 32 x 64 piece leaves through the generic proxy: 8 lanes write one row's 128 bytes, so
+                    // a warp store covers four whole lines of the destination rank's memory
+                    __syncwarp();
+                    const int blocks_first = row0 / p.sc_cap;
+#pragma unroll
+                    for (int k = 0; k < 8; k++) {
+                        const int rr = k * 4 + (lane >> 3), seg = lane & 7;
+                        const int m = row0 + rr;
+                        if (m < p.M && n_base + seg * 8 < p.N) {
+                            const int blk = m / p.sc_cap, slot = m - blk * p.sc_cap;
+                            const int src = blk % p.sc_P, el = blk / p.sc_P;
+                            bf16* dst = static_cast<bf16*>(p.sc_dst[src]) +
+                                        ((size_t)(p.sc_rank * p.sc_Eloc + el) * p.sc_cap + slot) * p.N + n_base + seg * 8;
+                            *reinterpret_cast<bf16x8*>(dst) = *reinterpret_cast<const bf16x8*>(buf + rr * 128 + ((seg ^ (rr & 7)) << 4));
+                        }
+                    }
+                    __syncwarp();
+                    if (lane == 0) {
+                        __threadfence_system();
+                        // rows [row0, row0 + 32) lie in at most two blocks (cap >= 32 is checked on the host)
+                        const int row_end = min(row0 + 32, p.M);
+                        const int per_block = p.sc_cap * ((p.N + 63) / 64);   // pieces are counted in rows
+                        for (int blk = blocks_first; blk * p.sc_cap < row_end; blk++) {
+                            const int lo = max(row0, blk * p.sc_cap), hi = min(row_end, (blk + 1) * p.sc_cap);
+                            if (hi <= lo) continue;
+                            if (atomicAdd(p.sc_count + blk, hi - lo) + (hi - lo) == per_block) {
+                                p.sc_count[blk] = 0;
+                                __threadfence_system();
+                                const int src = blk % p.sc_P, el = blk / p.sc_P;
+                                asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(p.sc_arrive[src] + p.sc_off + p.sc_rank * p.sc_Eloc + el),
+                                             "r"(p.sc_epoch)
+                                             : "memory");
+                            }
+                        }
+                    }
+                    __syncwarp();
+                } else {
+                    ptx::fence_proxy_async_smem();
+                    __syncwarp();
+                    if (lane == 0) {
+                        ptx::tma_store_2d(&tmC, buf, n_base, row0);
+                        if (EPI & EPI_GELU) ptx::tma_store_2d(&tmX, buf2, n_base, row0);
+                        ptx::tma_store_commit();
+                    }
                 }
             }
             if (!ok) break;
@@ -785,6 +834,10 @@ struct Ready {
     long long limit_ns = 0;
     const float2* rope = nullptr;
     int rope_T = 1, rope_cols = 0, rope_hs = 64;
+    const long long* sc_dst = nullptr;      // EPI_SCATTER: host arrays of P pointers
+    const long long* sc_arrive = nullptr;
+    int* sc_count = nullptr;
+    int sc_cap = 0, sc_P = 0, sc_Eloc = 0, sc_rank = 0, sc_off = 0, sc_epoch = 0;
 };
 
 static int gemm_impl(int mode, int epi, const void* A, const void* B, void* C, void* C2, const void* bias, const void* aux,
@@ -825,6 +878,19 @@ static int gemm_impl(int mode, int epi, const void* A, const void* B, void* C, v
     p.ready_limit_ns = ready.limit_ns > 0 ? ready.limit_ns : (long long)LLMK_WAIT_LIMIT_NS;
     if ((p.b_ready != nullptr || p.a_ready != nullptr) && mode == MODE_TN) return LLMK_ERR_SHAPE;
     p.rope = ready.rope; p.rope_T = ready.rope_T; p.rope_cols = ready.rope_cols; p.rope_hs = ready.rope_hs;
+    for (int i = 0; i < 8; i++) { p.sc_dst[i] = nullptr; p.sc_arrive[i] = nullptr; }
+    p.sc_count = ready.sc_count;
+    p.sc_cap = ready.sc_cap; p.sc_P = ready.sc_P; p.sc_Eloc = ready.sc_Eloc; p.sc_rank = ready.sc_rank;
+    p.sc_off = ready.sc_off; p.sc_epoch = ready.sc_epoch;
+    if (epi & EPI_SCATTER) {
+        if (ready.sc_dst == nullptr || ready.sc_arrive == nullptr || ready.sc_count == nullptr || mode == MODE_TN || ready.sc_P <= 0 ||
+            ready.sc_P > 8 || ready.sc_cap < 32 || ready.sc_Eloc <= 0 || M != ready.sc_Eloc * ready.sc_P * ready.sc_cap || (N % 8))
+            return LLMK_ERR_SHAPE;
+        for (int i = 0; i < ready.sc_P; i++) {
+            p.sc_dst[i] = reinterpret_cast<void*>(ready.sc_dst[i]);
+            p.sc_arrive[i] = reinterpret_cast<int*>(ready.sc_arrive[i]);
+        }
+    }
     if (epi & EPI_ROPE) {
         if (p.rope == nullptr || mode != MODE_NT || p.rope_T <= 0 || (p.rope_hs != 64 && p.rope_hs != 128) ||
             p.rope_cols % p.rope_hs || p.rope_cols > N || (reinterpret_cast<uintptr_t>(p.rope) & 15))
@@ -877,6 +943,8 @@ static int gemm_impl(int mode, int epi, const void* A, const void* B, void* C, v
     LLMK_GEMM_CASE(MODE_NT, EPI_ADD)
     LLMK_GEMM_CASE(MODE_NT, EPI_BIAS | EPI_ADD)
     LLMK_GEMM_CASE(MODE_NT, EPI_ROPE)
+    LLMK_GEMM_CASE(MODE_NT, EPI_BIAS | EPI_SCATTER)
+    LLMK_GEMM_CASE(MODE_NN, EPI_SCATTER)
     LLMK_GEMM_CASE(MODE_NN, 0)
     LLMK_GEMM_CASE(MODE_NN, EPI_DGELU)
     LLMK_GEMM_CASE(MODE_NN, EPI_ADD)
@@ -934,6 +1002,28 @@ LLMK_API int llmk_gemm_grouped_a_ready(int mode, int epi, const void* A, const v
     r.limit_ns = limit_ns;
     if (a_ready != nullptr && a_rows <= 0) return LLMK_ERR_SHAPE;
     return gemm_impl(mode, epi, A, B, C, C2, bias, aux, M, N, K, groups, workspace, workspace_bytes, status, max_ctas, stream_, r);
+}
+
+// The second GEMM of a mixture-of-experts layer with the all-to-all back fused into its epilogue: mode NT with bias
+// (forward: expert outputs) or NN without (backward: input gradients), `groups` local experts of `P * cap` rows each.
+// Nothing is written locally: the epilogue stores every row into the `back` buffer of the rank that sent the token
+// (dst_ptrs[src]) and publishes each (source rank, local expert) block in that rank's arrival table when its last
+// piece has been stored (see Params::sc_*). `count`: groups * P zeroed ints of local scratch. A local C of the same
+// shape must still be passed for the tensor map (it is not written). Jobs of the reference's unpermute +
+// all-to-all (llmc/moe.cuh:180-237, llmc/distributed_ext.cuh:28-41) inside grouped_gemm (llmc/gemm_ext.cuh:132-158).
+LLMK_API int llmk_gemm_grouped_scatter(int mode, int with_bias, const void* A, const void* B, void* C_shape_only, const void* bias,
+                                       int M, int N, int K, int groups, int* status, int max_ctas, const long long* dst_ptrs,
+                                       const long long* arrive_ptrs, int arrive_off, void* count, int cap, int P, int my_rank,
+                                       int epoch, void* stream_) {
+    Ready r;
+    r.sc_dst = dst_ptrs;
+    r.sc_arrive = arrive_ptrs;
+    r.sc_count = static_cast<int*>(count);
+    r.sc_cap = cap; r.sc_P = P; r.sc_Eloc = groups; r.sc_rank = my_rank; r.sc_off = arrive_off; r.sc_epoch = epoch;
+    if (M != P * cap) return LLMK_ERR_SHAPE;
+    const int epi = EPI_SCATTER | (with_bias ? EPI_BIAS : 0);
+    if ((mode == MODE_NT) != (with_bias != 0)) return LLMK_ERR_SHAPE;
+    return gemm_impl(mode, epi, A, B, C_shape_only, nullptr, bias, nullptr, M, N, K, groups, nullptr, 0, status, max_ctas, stream_, r);
 }
 
 // QKV projection with RoPE in the epilogue: C = A B^T where C is a packed [tokens, (NH + 2 NKVH) * HS] tensor; the

@@ -112,6 +112,8 @@ class MoETransformer(Transformer):
         # 2 = output gradients out, 3 = input gradients back; the values are exchange numbers that only grow
         self.arrive, self.arrive_ptrs = self.exchange.arrival_table(L * 4 * E, dev)
         self.done = torch.zeros(1 + Eloc * P, dtype=i32, device=dev)
+        # the second GEMM stores its rows straight into the source ranks' buffers when the row blocks are whole tiles
+        self.scatter = (P * cap) % gemm.tile_rows() == 0 and cap >= 32 and H % 64 == 0
         self._epoch = 0
         self.library = bool(getattr(self.exchange, "library", False))
         if self.library:
@@ -173,13 +175,19 @@ class MoETransformer(Transformer):
         gemm.gemm_nt(self.recv_x[l][rows], p["fcw"][l][loc], bias=p["fcb"][l][loc], out=act_l[rows],
                      gelu_pre_out=a["hid_pre"][l][rows], groups=G,
                      a_ready=None if lib else (self.arrive[r_out:], cap, ep, lim))
-        gemm.gemm_nt(act_l[rows], p["fcprojw"][l][loc], bias=p["fcprojb"][l][loc], out=a["y_loc"][rows], groups=G)
         if lib:
+            gemm.gemm_nt(act_l[rows], p["fcprojw"][l][loc], bias=p["fcprojb"][l][loc], out=a["y_loc"][rows], groups=G)
             self._library_back(a["y_loc"], self.back_y[l])
             moe_ops.combine(out, res2, self.back_y[l], a["top_idx"][l], a["slot"][l], a["top_w"][l], cap)
             return
-        moe_ops.return_signal(self.back_y_ptrs[l], a["y_loc"], cfg.channels, E, cap, self.ep_rank, P, self.arrive_ptrs, r_back,
-                              self.done[1:], ep)
+        if self.scatter:
+            # the GEMM's epilogue IS the way back: rows go to the senders' buffers, blocks are published as they complete
+            gemm.gemm_grouped_scatter(act_l[rows], p["fcprojw"][l][loc], p["fcprojb"][l][loc], a["y_loc"][rows], G,
+                                      self.back_y_ptrs[l], self.arrive_ptrs, r_back, self.done[1:], cap, P, self.ep_rank, ep)
+        else:
+            gemm.gemm_nt(act_l[rows], p["fcprojw"][l][loc], bias=p["fcprojb"][l][loc], out=a["y_loc"][rows], groups=G)
+            moe_ops.return_signal(self.back_y_ptrs[l], a["y_loc"], cfg.channels, E, cap, self.ep_rank, P, self.arrive_ptrs, r_back,
+                                  self.done[1:], ep)
         moe_ops.combine_wait(out, res2, self.back_y[l], a["top_idx"][l], a["slot"][l], a["top_w"][l], cap,
                              self.arrive[r_back:], E, ep, lim)
 
@@ -209,7 +217,12 @@ class MoETransformer(Transformer):
                      a_ready=None if lib else (self.arrive[r_out:], cap, ep, lim))
         gemm.gemm_tn(dy, act_l[rows], out=g["fcprojw"][l][loc], accumulate=True, groups=G)
         gemm.gemm_tn(d_hid, x, out=g["fcw"][l][loc], accumulate=True, groups=G)
-        gemm.gemm_nn(d_hid, p["fcw"][l][loc], out=a["y_loc"][rows], groups=G)
+        fused_back = self.scatter and not lib
+        if fused_back:
+            gemm.gemm_grouped_scatter(d_hid, p["fcw"][l][loc], None, a["y_loc"][rows], G, self.back_dx_ptrs, self.arrive_ptrs, r_back,
+                                      self.done[1:], cap, P, self.ep_rank, ep, nn=True)
+        else:
+            gemm.gemm_nn(d_hid, p["fcw"][l][loc], out=a["y_loc"][rows], groups=G)
         for el in range(G):
             gb1, gb2 = self._expert_views(l, el)[5], self._expert_views(l, el)[7]
             r = slice(el * per, (el + 1) * per)
@@ -219,8 +232,9 @@ class MoETransformer(Transformer):
             self._library_back(a["y_loc"], self.back_dx)
             moe_ops.combine(d_ln2, None, self.back_dx, idx, slot, None, cap)
         else:
-            moe_ops.return_signal(self.back_dx_ptrs, a["y_loc"], C, E, cap, self.ep_rank, P, self.arrive_ptrs, r_back,
-                                  self.done[1:], ep)
+            if not fused_back:
+                moe_ops.return_signal(self.back_dx_ptrs, a["y_loc"], C, E, cap, self.ep_rank, P, self.arrive_ptrs, r_back,
+                                      self.done[1:], ep)
             moe_ops.combine_wait(d_ln2, None, self.back_dx, idx, slot, None, cap, self.arrive[r_back:], E, ep, lim)
         # router: gradient through the renormalised top-k weights plus the load-balance term
         aux_scale = cfg.aux_loss_coef * E * 2.0 / N * self._loss_scale

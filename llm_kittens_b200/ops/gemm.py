@@ -152,6 +152,25 @@ def gemm_qkv_rope(a, w, rope, T, rope_cols, HS, out=None):
     return out
 
 
+def gemm_grouped_scatter(a, b, bias, shape_like, groups, dst_ptrs, arrive_ptrs, arrive_off, count, cap, P, rank, epoch, nn=False):
+    """Second GEMM of a mixture-of-experts layer with the way back fused into its epilogue: ``a`` [G*P*cap, K] times the
+    local experts' weights (``b`` [G, N, K] with ``bias`` [G, N], or with ``nn`` [G, K, N] and no bias); row
+    (e_local, source rank, slot) of the result is stored into that source rank's buffer (``dst_ptrs``), and every
+    completed (source rank, expert) block is published in the source rank's arrival table (``arrive_ptrs`` at
+    ``arrive_off`` + expert index) with ``epoch``. ``count``: G*P zeroed int32; ``shape_like``: a local [G*P*cap, N]
+    tensor that only lends its shape to a tensor map."""
+    b2 = _flat2(b, groups)
+    K = a.shape[1]
+    M = a.shape[0] // groups
+    Nn = b2.shape[1] if nn else b2.shape[0] // groups
+    if bias is not None and bias.dim() == 2:
+        bias = bias.reshape(-1)
+    if M != P * cap or M % tile_rows() or (nn and K % 64):
+        raise N.NativeError("gemm_grouped_scatter: expert row blocks must be whole tiles")
+    N.call("llmk_gemm_grouped_scatter", MODE_NN if nn else MODE_NT, 0 if nn else 1, a, b2, shape_like, bias, M, Nn, K, groups,
+           N.status_word(), _MAX_CTAS, dst_ptrs, arrive_ptrs, arrive_off, count, cap, P, rank, epoch)
+
+
 def gemm_nn(a, b, out=None, dgelu_of=None, add=None, groups=1, a_ready=None):
     """``out = a @ b`` with ``a``: [M,K], ``b``: [K,N]; optionally ``* gelu'(dgelu_of)`` or ``+ add``.
     ``groups`` > 1: ``a`` [G*M,K], ``b`` [G,K,N] or [G*K,N], ``out`` / aux [G*M,N]."""

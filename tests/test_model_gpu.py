@@ -159,11 +159,11 @@ def test_grad_accumulation_matches_big_batch():
     assert (err > 2e-3 + 0.05 * full.abs()).float().mean().item() < 2e-3
 
 
-def small_moe(L=2, C=256, NH=4, T=128, V=1000, Vp=1024, E=8, K=2):
+def small_moe(L=2, C=256, NH=4, T=128, V=1000, Vp=1024, E=8, K=2, capacity_factor=1.25):
     from llm_kittens_b200.models.config import ModelConfig
 
     return ModelConfig(family="moe", max_seq_len=T, vocab_size=V, padded_vocab_size=Vp, num_layers=L, num_heads=NH,
-                       num_kv_heads=NH, channels=C, hidden_dim=4 * C, num_experts=E, top_k=K, capacity_factor=1.25,
+                       num_kv_heads=NH, channels=C, hidden_dim=4 * C, num_experts=E, top_k=K, capacity_factor=capacity_factor,
                        aux_loss_coef=0.01)
 
 
@@ -202,14 +202,16 @@ def test_moe_ops_against_torch():
         assert pad.numel() == 0 or pad.abs().max().item() == 0
 
 
-@pytest.mark.parametrize("E", [8, 6])
-def test_moe_model_matches_oracle(E):
-    """E = 6 is not a multiple of 8: the router's gradient GEMMs run on a zero-padded router matrix."""
+@pytest.mark.parametrize("E,cf", [(8, 1.25), (6, 1.25), (8, 2.0)])
+def test_moe_model_matches_oracle(E, cf):
+    """E = 6 is not a multiple of 8: the router's gradient GEMMs run on a zero-padded router matrix. Capacity factor 2
+    makes every expert's row block a whole number of GEMM tiles (256 rows), which is when the second GEMM stores its
+    rows straight into the senders' buffers from its epilogue instead of through the return kernel."""
     from llm_kittens_b200.models.moe import MoETransformer
     from llm_kittens_b200.oracle.torch_model import TorchTransformer
     from llm_kittens_b200.ops import _native
 
-    cfg = small_moe(E=E)
+    cfg = small_moe(E=E, capacity_factor=cf)
     model = MoETransformer(cfg, device="cuda", recompute=0)
     model.init_weights(42)
     torch.manual_seed(1)
