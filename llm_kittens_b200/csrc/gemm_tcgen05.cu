@@ -51,12 +51,15 @@ constexpr int GROUP_M = 8;
 constexpr int TMEM_COLS = 512;
 
 enum { MODE_NT = 0, MODE_NN = 1, MODE_TN = 2 };
-enum { EPI_BIAS = 1, EPI_GELU = 2, EPI_DGELU = 4, EPI_ADD = 8, EPI_PARTIAL = 16, EPI_ROPE = 32, EPI_SCATTER = 64 };
+enum { EPI_BIAS = 1, EPI_GELU = 2, EPI_DGELU = 4, EPI_ADD = 8, EPI_PARTIAL = 16, EPI_ROPE = 32, EPI_SCATTER = 64, EPI_SWIGLU = 128 };
 
 template <int EPI, bool PAIR>
 struct Cfg {
     static constexpr bool DUAL = (EPI & (EPI_GELU | EPI_DGELU | EPI_ADD)) != 0;
-    static constexpr int STAGES = PAIR ? (DUAL ? 5 : 6) : (DUAL ? 3 : 4);
+    // SwiGLU epilogue (pair kernel only): three outputs per piece (up, gate, activation), so three staging buffers
+    // per epilogue warp and a 4-stage operand ring
+    static constexpr bool SWI = (EPI & EPI_SWIGLU) != 0;
+    static constexpr int STAGES = PAIR ? (SWI ? 4 : (DUAL ? 5 : 6)) : (DUAL ? 3 : 4);
     // Wide epilogue (pair kernel, dGELU): 16 epilogue warps, four per TMEM lane group, one 64-column chunk each per
     // tile; the result overwrites the aux tile in its staging buffer. With K = 768 this epilogue sets the pace of the
     // kernel and it is bound by latency, not by issue slots or a pipe, so twice the warps per scheduler helps
@@ -67,7 +70,7 @@ struct Cfg {
     static constexpr bool WIDE = PAIR && EPI == EPI_DGELU;
     static constexpr int EPI_WARPS = WIDE ? 16 : NUM_EPI_WARPS;
     static constexpr int NTHREADS = 32 * (2 + EPI_WARPS);
-    static constexpr int NBUF = (DUAL && !WIDE) ? 2 : 1;   // staging buffers per epilogue warp
+    static constexpr int NBUF = SWI ? 3 : ((DUAL && !WIDE) ? 2 : 1);   // staging buffers per epilogue warp
     static constexpr int SMEM_MAIN = STAGES * Geo<PAIR>::STAGE_BYTES + EPI_WARPS * NBUF * STAGING_BYTES;
     static constexpr int SMEM_BYTES = SMEM_MAIN + 1024 /*alignment slack*/ + 512 /*barriers*/;
 };
@@ -131,6 +134,7 @@ struct Params {
     // lines). Every stored (32-row x 64-column) piece is counted per block of `cap` rows in sc_count (local memory,
     // left at zero); the piece that completes a block release-stores sc_epoch into entry sc_off + e of that source
     // rank's arrival table (sc_arrive[src]), which is what the combine kernel there waits for.
+    const int* b_ready2;   // EPI_SWIGLU: readiness flags of the gate matrix (b_ready: the up matrix), same geometry
     void* sc_dst[8];
     int* sc_arrive[8];
     int* sc_count;
@@ -180,6 +184,10 @@ struct Work {
     int m0, n0, kb_begin, kb_end, split, g;
 };
 
+struct ExtraMaps {
+    CUtensorMap b2, y;
+};
+
 __device__ __forceinline__ Work decode_unit(const Params& p, int u) {
     Work w;
     const int tile = u / p.splits;
@@ -200,8 +208,10 @@ __device__ __forceinline__ Work decode_unit(const Params& p, int u) {
 template <int MODE, int EPI, bool PAIR>
 __global__ void __launch_bounds__((Cfg<EPI, PAIR>::NTHREADS), 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-            const __grid_constant__ CUtensorMap tmC, const __grid_constant__ CUtensorMap tmX, const Params p) {
+            const __grid_constant__ CUtensorMap tmC, const __grid_constant__ CUtensorMap tmX,
+            const __grid_constant__ ExtraMaps xm, const Params p) {
     // tmX: second output (GELU pre-activation) or auxiliary [M,N] input (DGELU / ADD); same geometry as tmC
+    // xm (EPI_SWIGLU): b2 = the gate weights (tmB = the up weights), y = the third output (gate; tmX = up, tmC = activation)
     constexpr int STAGES = Cfg<EPI, PAIR>::STAGES;
     constexpr int SMEM_MAIN = Cfg<EPI, PAIR>::SMEM_MAIN;
     constexpr bool DUAL = Cfg<EPI, PAIR>::DUAL;
@@ -289,13 +299,19 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
                                     p.ready_limit_ns, abort_flag, p.status, 7000);
                 if (!__shfl_sync(0xffffffffu, fl, 0)) { ok = false; break; }
             }
-            if (p.b_ready != nullptr && MODE == MODE_NT && n_own < p.N) {
-                // NT: this CTA's rows [n_own, n_own + BN_CTA) of B, all of K
+            // SwiGLU: the pair's 256 accumulator columns are 128 hidden units of `up` (loaded by the leader from tmB)
+            // followed by the same 128 units of `gate` (loaded by the peer from xm.b2); rows [b_row, b_row + 128) of each
+            constexpr bool SWI = (EPI & EPI_SWIGLU) != 0;
+            const int b_row = SWI ? w.n0 / 2 : n_own;
+            const int b_rows_total = SWI ? p.N / 2 : p.N;
+            const int* b_flags = (SWI && rank == 1) ? p.b_ready2 : p.b_ready;
+            if (b_flags != nullptr && MODE == MODE_NT && b_row < b_rows_total) {
+                // NT: this CTA's rows [b_row, b_row + BN_CTA) of B, all of K
                 bool fl = true;
                 if (lane == 0) {
-                    const long long e0 = (long long)(n_own + w.g * p.N) * p.K;
-                    const long long e1 = (long long)(min(n_own + BN_CTA, p.N) + w.g * p.N) * p.K - 1;
-                    fl = ready_wait(p.b_ready, e0 / p.b_chunk, e1 / p.b_chunk, p.b_tick, b_done, p.ready_limit_ns, abort_flag,
+                    const long long e0 = (long long)(b_row + w.g * b_rows_total) * p.K;
+                    const long long e1 = (long long)(min(b_row + BN_CTA, b_rows_total) + w.g * b_rows_total) * p.K - 1;
+                    fl = ready_wait(b_flags, e0 / p.b_chunk, e1 / p.b_chunk, p.b_tick, b_done, p.ready_limit_ns, abort_flag,
                                     p.status, 7100);
                 }
                 if (!__shfl_sync(0xffffffffu, fl, 0)) { ok = false; break; }
@@ -331,7 +347,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
 #pragma unroll
                         for (int j = 0; j < BN_CTA / 64; j++) load(sB + j * CHUNK_BYTES, &tmB, &full_bar[s], n_own + 64 * j, k0 + w.g * p.K);
                     } else {      // NT: the rows of B are the N dimension, stacked per group
-                        load(sB, &tmB, &full_bar[s], k0, n_own + w.g * p.N);
+                        load(sB, (SWI && rank == 1) ? &xm.b2 : &tmB, &full_bar[s], k0, b_row + w.g * b_rows_total);
                     }
                 }
                 __syncwarp();
@@ -430,6 +446,54 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
             for (int chunk = chunk_sel; chunk < BN / 64; chunk += CH_STEP) {
                 const int n_base = w.n0 + chunk * 64;
                 if (n_base >= p.N) break;
+                if constexpr ((EPI & EPI_SWIGLU) != 0) {
+                    // one piece per warp and tile: accumulator chunk `chunk_sel` holds 64 hidden units of `up`, chunk
+                    // `chunk_sel + 2` the same units of `gate`. Both are rounded to bf16 and stored (the backward needs
+                    // them), and the activation gate * sigmoid(gate) * up is computed from the ROUNDED values, so that
+                    // recomputing it later from the stored tensors gives the same bits as the stand-alone kernel.
+                    if (chunk != chunk_sel) break;
+                    const int hcol = w.n0 / 2 + chunk_sel * 64;      // hidden-unit column of this piece in the [M, H] outputs
+                    if (hcol >= p.N / 2) break;
+                    uint8_t* bufU = buf + STAGING_BYTES;
+                    uint8_t* bufG = buf + 2 * STAGING_BYTES;
+                    if (lane == 0) ptx::tma_store_wait_read<0>();      // the previous tile's stores have read the buffers
+                    __syncwarp();
+#pragma unroll
+                    for (int half = 0; half < 2; half++) {
+                        uint32_t vu[32], vg[32];
+                        ptx::tmem_ld_32x32b_x32(t_row + chunk_sel * 64 + half * 32, vu);
+                        ptx::tmem_ld_32x32b_x32(t_row + (chunk_sel + 2) * 64 + half * 32, vg);
+                        ptx::tmem_ld_wait();
+#pragma unroll
+                        for (int q = 0; q < 4; q++) {
+                            float u[8], g[8];
+#pragma unroll
+                            for (int j = 0; j < 8; j++) {
+                                u[j] = __uint_as_float(vu[q * 8 + j]);
+                                g[j] = __uint_as_float(vg[q * 8 + j]);
+                            }
+                            const bf16x8 ub = pack8(u), gb = pack8(g);
+                            unpack8(ub, u);
+                            unpack8(gb, g);
+#pragma unroll
+                            for (int j = 0; j < 8; j++) g[j] = g[j] * (1.0f / (1.0f + __expf(-g[j]))) * u[j];
+                            const int cc = half * 4 + q;
+                            const uint32_t off = lane * 128 + ((cc ^ (lane & 7)) << 4);
+                            *reinterpret_cast<bf16x8*>(bufU + off) = ub;
+                            *reinterpret_cast<bf16x8*>(bufG + off) = gb;
+                            *reinterpret_cast<bf16x8*>(buf + off) = pack8(g);
+                        }
+                    }
+                    ptx::fence_proxy_async_smem();
+                    __syncwarp();
+                    if (lane == 0) {
+                        ptx::tma_store_2d(&tmC, buf, hcol, row0);
+                        ptx::tma_store_2d(&tmX, bufU, hcol, row0);
+                        ptx::tma_store_2d(&xm.y, bufG, hcol, row0);
+                        ptx::tma_store_commit();
+                    }
+                    break;
+                }
                 if constexpr (WIDE) {
                     // dGELU, one chunk per warp and tile, 32 columns at a time: result = acc * GELU'(aux), written over the aux tile
                     ok = ptx::mbar_wait(&aux_bar[e], aux_ph, abort_flag, p.status, LLMK_ST_TIMEOUT_ACC_FULL, -2);
@@ -706,7 +770,7 @@ int make_tmap_2d(CUtensorMap* m, const void* ptr, uint64_t inner, uint64_t outer
 static int query_pair_clusters();
 
 template <int MODE, int EPI>
-static int launch(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmC, const CUtensorMap& tmX,
+static int launch(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmC, const CUtensorMap& tmX, const ExtraMaps& xm,
                   const Params& p, int max_ctas, cudaStream_t stream) {
     const int g_num_sms = sm_count_current_device();
     if (g_num_sms <= 0) return LLMK_ERR_CUDA;
@@ -732,9 +796,10 @@ static int launch(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensor
         attr[0].val.clusterDim.z = 1;
         cfg.attrs = attr;
         cfg.numAttrs = 1;
-        LLMK_CUDA_TRY(cudaLaunchKernelEx(&cfg, gemm_kernel<MODE, EPI, true>, tmA, tmB, tmC, tmX, p));
+        LLMK_CUDA_TRY(cudaLaunchKernelEx(&cfg, gemm_kernel<MODE, EPI, true>, tmA, tmB, tmC, tmX, xm, p));
         return LLMK_OK;
     }
+    if (EPI & EPI_SWIGLU) return LLMK_ERR_SHAPE;   // the SwiGLU epilogue needs the pair kernel's accumulator layout
     constexpr int SMEM_BYTES = Cfg<EPI, false>::SMEM_BYTES;
     static PerDeviceOnce once_configured;
     if (once_configured.first()) {
@@ -742,7 +807,7 @@ static int launch(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensor
     }
     int grid = units < g_num_sms ? units : g_num_sms;
     if (max_ctas > 0 && grid > max_ctas) grid = max_ctas;
-    gemm_kernel<MODE, EPI, false><<<grid, Cfg<EPI, false>::NTHREADS, SMEM_BYTES, stream>>>(tmA, tmB, tmC, tmX, p);
+    gemm_kernel<MODE, EPI, false><<<grid, Cfg<EPI, false>::NTHREADS, SMEM_BYTES, stream>>>(tmA, tmB, tmC, tmX, xm, p);
     LLMK_LAUNCH_CHECK();
     return LLMK_OK;
 }
@@ -834,6 +899,9 @@ struct Ready {
     long long limit_ns = 0;
     const float2* rope = nullptr;
     int rope_T = 1, rope_cols = 0, rope_hs = 64;
+    const void* b2 = nullptr;               // EPI_SWIGLU: the gate weights, the third output, the gate's readiness flags
+    void* c3 = nullptr;
+    const int* b_ready2 = nullptr;
     const long long* sc_dst = nullptr;      // EPI_SCATTER: host arrays of P pointers
     const long long* sc_arrive = nullptr;
     int* sc_count = nullptr;
@@ -878,6 +946,13 @@ static int gemm_impl(int mode, int epi, const void* A, const void* B, void* C, v
     p.ready_limit_ns = ready.limit_ns > 0 ? ready.limit_ns : (long long)LLMK_WAIT_LIMIT_NS;
     if ((p.b_ready != nullptr || p.a_ready != nullptr) && mode == MODE_TN) return LLMK_ERR_SHAPE;
     p.rope = ready.rope; p.rope_T = ready.rope_T; p.rope_cols = ready.rope_cols; p.rope_hs = ready.rope_hs;
+    p.b_ready2 = ready.b_ready2;
+    if (epi & EPI_SWIGLU) {
+        // N is the width of the accumulator tile space: 2 H columns (up | gate per 128 hidden units); outputs are [M, H]
+        if (mode != MODE_NT || groups != 1 || !p.pair || ready.b2 == nullptr || ready.c3 == nullptr || C2 == nullptr || (N % 256) ||
+            ((reinterpret_cast<uintptr_t>(ready.b2) | reinterpret_cast<uintptr_t>(ready.c3) | reinterpret_cast<uintptr_t>(C2)) & 15))
+            return LLMK_ERR_SHAPE;
+    }
     for (int i = 0; i < 8; i++) { p.sc_dst[i] = nullptr; p.sc_arrive[i] = nullptr; }
     p.sc_count = ready.sc_count;
     p.sc_cap = ready.sc_cap; p.sc_P = ready.sc_P; p.sc_Eloc = ready.sc_Eloc; p.sc_rank = ready.sc_rank;
@@ -921,12 +996,22 @@ static int gemm_impl(int mode, int epi, const void* A, const void* B, void* C, v
     if (mode == MODE_TN) rc = make_tmap_2d(&tmA, A, M_group, G * K, M_group, 64, BK);   // A[G*K,M_g], box 64(m) x 64(k)
     else rc = make_tmap_2d(&tmA, A, K, M, K, BK, BM);                    // A[M,K], box 64(k) x 128(m)
     if (rc) return rc;
-    if (mode == MODE_NT) rc = make_tmap_2d(&tmB, B, K, G * N, K, BK, p.pair ? BN / 2 : BN);   // B[G*N,K], box 64(k) x 256(n); pair: 128(n) per CTA
+    const bool swi = (epi & EPI_SWIGLU) != 0;
+    const uint64_t b_rows = swi ? (uint64_t)N / 2 : G * N, c_cols = swi ? (uint64_t)N / 2 : (uint64_t)N;
+    if (mode == MODE_NT) rc = make_tmap_2d(&tmB, B, K, b_rows, K, BK, p.pair ? BN / 2 : BN);   // B[G*N,K], box 64(k) x 256(n); pair: 128(n) per CTA
     else rc = make_tmap_2d(&tmB, B, N, G * K, N, 64, BK);                // B[G*K,N], box 64(n) x 64(k)
     if (rc) return rc;
-    rc = make_tmap_2d(&tmC, C, N, M, N, 64, 32);
+    rc = make_tmap_2d(&tmC, C, c_cols, M, c_cols, 64, 32);
     if (rc) return rc;
     tmX = tmC;
+    ExtraMaps xm;
+    xm.b2 = tmB;
+    xm.y = tmC;
+    if (swi) {
+        if ((rc = make_tmap_2d(&xm.b2, ready.b2, K, b_rows, K, BK, BN / 2))) return rc;
+        if ((rc = make_tmap_2d(&tmX, C2, c_cols, M, c_cols, 64, 32))) return rc;
+        if ((rc = make_tmap_2d(&xm.y, ready.c3, c_cols, M, c_cols, 64, 32))) return rc;
+    }
     if (epi & (EPI_GELU | EPI_DGELU | EPI_ADD)) {
         const void* x = (epi & EPI_GELU) ? C2 : aux;
         if (x == nullptr || (reinterpret_cast<uintptr_t>(x) & 15)) return LLMK_ERR_SHAPE;
@@ -935,7 +1020,7 @@ static int gemm_impl(int mode, int epi, const void* A, const void* B, void* C, v
     }
 
 #define LLMK_GEMM_CASE(MODE_, EPI_) \
-    if (mode == MODE_ && epi == (EPI_)) rc = launch<MODE_, EPI_>(tmA, tmB, tmC, tmX, p, max_ctas, stream); else
+    if (mode == MODE_ && epi == (EPI_)) rc = launch<MODE_, EPI_>(tmA, tmB, tmC, tmX, xm, p, max_ctas, stream); else
     rc = LLMK_ERR_SHAPE;
     LLMK_GEMM_CASE(MODE_NT, 0)
     LLMK_GEMM_CASE(MODE_NT, EPI_BIAS)
@@ -943,6 +1028,7 @@ static int gemm_impl(int mode, int epi, const void* A, const void* B, void* C, v
     LLMK_GEMM_CASE(MODE_NT, EPI_ADD)
     LLMK_GEMM_CASE(MODE_NT, EPI_BIAS | EPI_ADD)
     LLMK_GEMM_CASE(MODE_NT, EPI_ROPE)
+    LLMK_GEMM_CASE(MODE_NT, EPI_SWIGLU)
     LLMK_GEMM_CASE(MODE_NT, EPI_BIAS | EPI_SCATTER)
     LLMK_GEMM_CASE(MODE_NN, EPI_SCATTER)
     LLMK_GEMM_CASE(MODE_NN, 0)
@@ -1024,6 +1110,27 @@ LLMK_API int llmk_gemm_grouped_scatter(int mode, int with_bias, const void* A, c
     const int epi = EPI_SCATTER | (with_bias ? EPI_BIAS : 0);
     if ((mode == MODE_NT) != (with_bias != 0)) return LLMK_ERR_SHAPE;
     return gemm_impl(mode, epi, A, B, C_shape_only, nullptr, bias, nullptr, M, N, K, groups, nullptr, 0, status, max_ctas, stream_, r);
+}
+
+// Llama MLP, first half, in one launch: up = A Wup^T, gate = A Wgate^T and act = gate * sigmoid(gate) * up, with the
+// SwiGLU in the epilogue (a CTA pair's accumulator holds 128 hidden units of `up` beside the same units of `gate`: the
+// leader loads the up rows, its peer the gate rows). All three [M, H] tensors are written (the backward needs up and
+// gate). H must be a multiple of 128 and the CTA-pair kernel available, else LLMK_ERR_SHAPE (the caller then runs
+// two GEMMs and the stand-alone SwiGLU kernel). Optional readiness flags for both weights as in llmk_gemm_b_ready.
+// Same job as matmul + swiglu_forward of the reference (llmc/swiglu.cuh:27-61) without the extra pass over up / gate.
+LLMK_API int llmk_gemm_swiglu(const void* A, const void* Wup, const void* Wgate, void* act, void* up, void* gate, int M, int H, int K,
+                              int* status, int max_ctas, const void* up_ready, const void* gate_ready, long b_chunk, int b_tick,
+                              long limit_ns, void* stream_) {
+    if (H % 128) return LLMK_ERR_SHAPE;
+    Ready r;
+    r.b_ready = static_cast<const int*>(up_ready);
+    r.b_ready2 = static_cast<const int*>(gate_ready);
+    r.b_chunk = b_chunk > 0 ? b_chunk : 1;
+    r.b_tick = b_tick;
+    r.limit_ns = limit_ns;
+    r.b2 = Wgate;
+    r.c3 = gate;
+    return gemm_impl(MODE_NT, EPI_SWIGLU, A, Wup, act, up, nullptr, nullptr, M, 2 * H, K, 1, nullptr, 0, status, max_ctas, stream_, r);
 }
 
 // QKV projection with RoPE in the epilogue: C = A B^T where C is a packed [tokens, (NH + 2 NKVH) * HS] tensor; the

@@ -250,9 +250,12 @@ class Transformer:
         a, p = self.acts, self.p
         act = a["act"][gi]
         if self.is_llama:
-            gemm.gemm_nt(ln2, p["fcw_up"][l], out=a["up"][k])
-            gemm.gemm_nt(ln2, p["fcw_gate"][l], out=a["gate"][k])
-            ew.swiglu_fwd(a["gate"][k], a["up"][k], out=act)
+            # up, gate and silu(gate) * up from one launch when the fused-epilogue kernel takes the shape
+            if os.environ.get("LLMK_FUSED_SWIGLU", "1") == "0" or not gemm.gemm_swiglu(ln2, p["fcw_up"][l], p["fcw_gate"][l], act,
+                                                                                   a["up"][k], a["gate"][k]):
+                gemm.gemm_nt(ln2, p["fcw_up"][l], out=a["up"][k])
+                gemm.gemm_nt(ln2, p["fcw_gate"][l], out=a["gate"][k])
+                ew.swiglu_fwd(a["gate"][k], a["up"][k], out=act)
             gemm.gemm_nt(act, p["fcprojw"][l], out=out, add=res2)
         else:
             gemm.gemm_nt(ln2, p["fcw"][l], bias=p["fcb"][l], out=act, gelu_pre_out=a["fch"][k])

@@ -152,6 +152,30 @@ def gemm_qkv_rope(a, w, rope, T, rope_cols, HS, out=None):
     return out
 
 
+def gemm_swiglu(a, w_up, w_gate, act, up, gate) -> bool:
+    """Llama MLP first half in one launch: ``up = a @ w_up.T``, ``gate = a @ w_gate.T``, ``act = silu(gate) * up`` with
+    the SwiGLU in the GEMM's epilogue (all three [M, H] outputs are written). Returns False, having done nothing, when
+    the shape or the device cannot take the fused kernel (H not a multiple of 128, no CTA pairs): the caller then runs
+    two GEMMs and the stand-alone SwiGLU kernel."""
+    M, K = a.shape
+    H = w_up.shape[0]
+    if H % 128 or K % 8 or tile_rows() != 256 or not hasattr(N.lib(), "llmk_gemm_swiglu"):
+        return False
+    for t, nm in ((a, "A"), (w_up, "W_up"), (w_gate, "W_gate"), (act, "act"), (up, "up"), (gate, "gate")):
+        N.require_cuda_tensor(t, torch.bfloat16, nm)
+    ru = _B_READY.get(w_up.data_ptr()) if _B_READY else None
+    rg = _B_READY.get(w_gate.data_ptr()) if _B_READY else None
+    if ru is not None and rg is not None and ru[3] > 0 and rg[3] > 0 and ru[2] == rg[2] and ru[3] == rg[3]:
+        fu, fg, chunk, tick, limit_ns = ru[0], rg[0], ru[2], ru[3], ru[4]
+    elif (ru is not None and ru[3] > 0) or (rg is not None and rg[3] > 0):
+        return False          # weights still arriving with different flag geometries: take the unfused route
+    else:
+        fu = fg = None
+        chunk, tick, limit_ns = 1, 0, 0
+    N.call("llmk_gemm_swiglu", a, w_up, w_gate, act, up, gate, M, H, K, N.status_word(), _MAX_CTAS, fu, fg, chunk, tick, limit_ns)
+    return True
+
+
 def gemm_grouped_scatter(a, b, bias, shape_like, groups, dst_ptrs, arrive_ptrs, arrive_off, count, cap, P, rank, epoch, nn=False):
     """Second GEMM of a mixture-of-experts layer with the way back fused into its epilogue: ``a`` [G*P*cap, K] times the
     local experts' weights (``b`` [G, N, K] with ``bias`` [G, N], or with ``nn`` [G, K, N] and no bias); row

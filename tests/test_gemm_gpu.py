@@ -162,3 +162,23 @@ def test_gemm_polls_readiness_flags_of_its_weight_operand():
         _native.check_status()
     finally:
         gemm.unregister_b_ready(w)
+
+
+@pytest.mark.parametrize("M,H,K", [(256, 128, 64), (512, 768, 256), (300, 1024, 200), (4096, 8192, 2048)])
+def test_gemm_swiglu_epilogue(M, H, K):
+    """up / gate projections with SwiGLU in the epilogue against fp32 references and, bit for bit, against two plain
+    GEMMs followed by the stand-alone SwiGLU kernel (the activation is computed from the rounded up / gate)."""
+    from llm_kittens_b200.ops import _native, elementwise as ew, gemm
+
+    torch.manual_seed(M + H)
+    a, wu, wg = _rand(M, K), _rand(H, K, scale=0.1), _rand(H, K, scale=0.1)
+    act, up, gate = (torch.empty(M, H, device="cuda", dtype=torch.bfloat16) for _ in range(3))
+    if not gemm.gemm_swiglu(a, wu, wg, act, up, gate):
+        pytest.skip("fused SwiGLU kernel not available for this shape / device")
+    _native.check_status()
+    ref_up, ref_gate = a.float() @ wu.float().T, a.float() @ wg.float().T
+    _close(up, ref_up, 0.02 * max(1.0, ref_up.abs().max().item()))
+    _close(gate, ref_gate, 0.02 * max(1.0, ref_gate.abs().max().item()))
+    up2, gate2 = gemm.gemm_nt(a, wu), gemm.gemm_nt(a, wg)
+    assert torch.equal(up, up2) and torch.equal(gate, gate2)
+    assert torch.equal(act, ew.swiglu_fwd(gate2, up2))
