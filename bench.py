@@ -235,6 +235,9 @@ def main() -> int:
     ap.add_argument("--micro-batch", type=int, default=MICRO_B)
     ap.add_argument("--seq-len", type=int, default=SEQ_T)
     ap.add_argument("--total-batch", type=int, default=TOTAL_BATCH)
+    ap.add_argument("--ledger", type=int, default=0,
+                    help="after the timed regions: one more step with every library call between CUDA events; rank 0 prints the "
+                         "per-call device times to stderr (where the step's time goes, multi-GPU waits included)")
     ap.add_argument("--cuda-graph", type=int, default=1,
                     help="replay captured forward+backward graphs per micro-step where the communication path allows it "
                          "(one process, fused ZeRO-1); 0 = launch every kernel from Python")
@@ -393,6 +396,18 @@ def main() -> int:
         sampler.stop()
     if args.impl == "ours":
         _native.check_status()
+    if args.ledger and args.impl == "ours":
+        trainer.enable_cuda_graph(False)
+        step_no[0] = args.warmup          # reuse a batch that is resident on the device
+        sync_all()
+        _native.ledger_start()
+        device_step(0)
+        rows = _native.ledger_stop()
+        if rank == 0:
+            total = sum(ms for _, ms in rows.values())
+            print(f"# ledger of one step (rank 0, eager, events around every call): {total:.2f} ms in calls", file=sys.stderr)
+            for label, (n, ms) in sorted(rows.items(), key=lambda kv: -kv[1][1])[:40]:
+                print(f"{label:56s} {n:6d} calls {ms:9.3f} ms {1e3 * ms / n:9.1f} us/call", file=sys.stderr)
 
     if rank == 0:
         tokens = args.total_batch * args.steps

@@ -122,6 +122,7 @@ struct Params {
     const int* a_ready;
     long long b_chunk;
     int b_tick, a_rows, a_need;
+    int b_nflags;          // flags that cover B (0 = unknown); once a CTA has seen them all it stops looking
     long long ready_limit_ns;
     // EPI_ROPE: rotate the q and k heads of a packed QKV projection in the epilogue. Row r of C is token r % rope_T;
     // columns [0, rope_cols) are heads of rope_hs columns whose interleaved pairs (2i, 2i+1) turn by the angle in
@@ -305,7 +306,12 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
             const int b_row = SWI ? w.n0 / 2 : n_own;
             const int b_rows_total = SWI ? p.N / 2 : p.N;
             const int* b_flags = (SWI && rank == 1) ? p.b_ready2 : p.b_ready;
-            if (b_flags != nullptr && MODE == MODE_NT && b_row < b_rows_total) {
+            // every flag of B seen by this CTA (at most 64 are remembered): nothing left to poll, and no index arithmetic
+            // (the mask lives in lane 0, which does the polling: its verdict is broadcast so that the warp branches as one)
+            const bool b_all_lane = p.b_nflags > 0 && p.b_nflags <= 64 &&
+                                    b_done == (p.b_nflags == 64 ? ~0ull : ((1ull << p.b_nflags) - 1ull));
+            const bool b_all = __shfl_sync(0xffffffffu, (int)b_all_lane, 0) != 0;
+            if (b_flags != nullptr && !b_all && MODE == MODE_NT && b_row < b_rows_total) {
                 // NT: this CTA's rows [b_row, b_row + BN_CTA) of B, all of K
                 bool fl = true;
                 if (lane == 0) {
@@ -316,15 +322,25 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
                 }
                 if (!__shfl_sync(0xffffffffu, fl, 0)) { ok = false; break; }
             }
+            const bool b_all_nn = b_all;   // decided once per unit
+            const bool small_b = (long long)p.K * p.N * (p.group_m > 0 ? (p.M / p.group_m) : 1) < (1ll << 32) && p.b_chunk < (1ll << 32);
             for (int kb = w.kb_begin; kb < w.kb_end; kb++) {
-                if (p.b_ready != nullptr && MODE == MODE_NN) {
-                    // NN: rows [k0, k0 + 64) of B (the K dimension), whole rows
+                if (p.b_ready != nullptr && MODE == MODE_NN && !b_all_nn) {
+                    // NN: rows [k0, k0 + 64) of B (the K dimension), whole rows. The index arithmetic runs in 32 bits
+                    // when B has fewer than 2^32 elements (64-bit divisions in this loop cost more than the loads)
                     bool fl = true;
                     if (lane == 0) {
                         const long long r0 = (long long)kb * BK + (long long)w.g * p.K;
                         const long long r1 = min((long long)(kb + 1) * BK, (long long)p.K) + (long long)w.g * p.K;
-                        fl = ready_wait(p.b_ready, r0 * p.N / p.b_chunk, (r1 * p.N - 1) / p.b_chunk, p.b_tick, b_done,
-                                        p.ready_limit_ns, abort_flag, p.status, 7200);
+                        long long f0, f1;
+                        if (small_b) {
+                            f0 = (unsigned)((unsigned)r0 * (unsigned)p.N) / (unsigned)p.b_chunk;
+                            f1 = (unsigned)((unsigned)r1 * (unsigned)p.N - 1u) / (unsigned)p.b_chunk;
+                        } else {
+                            f0 = r0 * p.N / p.b_chunk;
+                            f1 = (r1 * p.N - 1) / p.b_chunk;
+                        }
+                        fl = ready_wait(p.b_ready, f0, f1, p.b_tick, b_done, p.ready_limit_ns, abort_flag, p.status, 7200);
                     }
                     if (!__shfl_sync(0xffffffffu, fl, 0)) { ok = false; break; }
                 }
@@ -895,7 +911,7 @@ struct Ready {
     const int* b_ready = nullptr;
     const int* a_ready = nullptr;
     long long b_chunk = 1;
-    int b_tick = 0, a_rows = 1, a_need = 0;
+    int b_tick = 0, a_rows = 1, a_need = 0, b_nflags = 0;
     long long limit_ns = 0;
     const float2* rope = nullptr;
     int rope_T = 1, rope_cols = 0, rope_hs = 64;
@@ -942,6 +958,7 @@ static int gemm_impl(int mode, int epi, const void* A, const void* B, void* C, v
     p.status = status;
     p.b_ready = ready.b_ready; p.a_ready = ready.a_ready;
     p.b_chunk = ready.b_chunk > 0 ? ready.b_chunk : 1;
+    p.b_nflags = ready.b_nflags;
     p.b_tick = ready.b_tick; p.a_rows = ready.a_rows > 0 ? ready.a_rows : 1; p.a_need = ready.a_need;
     p.ready_limit_ns = ready.limit_ns > 0 ? ready.limit_ns : (long long)LLMK_WAIT_LIMIT_NS;
     if ((p.b_ready != nullptr || p.a_ready != nullptr) && mode == MODE_TN) return LLMK_ERR_SHAPE;
@@ -1069,6 +1086,7 @@ LLMK_API int llmk_gemm_b_ready(int mode, int epi, const void* A, const void* B, 
     r.b_tick = b_tick;
     r.limit_ns = limit_ns;
     if (b_ready != nullptr && b_chunk <= 0) return LLMK_ERR_SHAPE;
+    if (b_ready != nullptr) r.b_nflags = (int)(((long long)N * K + b_chunk - 1) / b_chunk);   // B holds N * K elements in NT and NN
     return gemm_impl(mode, epi, A, B, C, C2, bias, aux, M, N, K, 1, workspace, workspace_bytes, status, max_ctas, stream_, r);
 }
 
@@ -1128,6 +1146,7 @@ LLMK_API int llmk_gemm_swiglu(const void* A, const void* Wup, const void* Wgate,
     r.b_chunk = b_chunk > 0 ? b_chunk : 1;
     r.b_tick = b_tick;
     r.limit_ns = limit_ns;
+    if (up_ready != nullptr) r.b_nflags = (int)(((long long)H * K + r.b_chunk - 1) / r.b_chunk);   // per matrix (up and gate alike)
     r.b2 = Wgate;
     r.c3 = gate;
     return gemm_impl(MODE_NT, EPI_SWIGLU, A, Wup, act, up, nullptr, nullptr, M, 2 * H, K, 1, nullptr, 0, status, max_ctas, stream_, r);
@@ -1146,6 +1165,7 @@ LLMK_API int llmk_gemm_qkv_rope(const void* A, const void* B, void* C, int M, in
     r.b_chunk = b_chunk > 0 ? b_chunk : 1;
     r.b_tick = b_tick;
     r.limit_ns = limit_ns;
+    if (b_ready != nullptr) r.b_nflags = (int)(((long long)N * K + r.b_chunk - 1) / r.b_chunk);
     r.rope = static_cast<const float2*>(rope);
     r.rope_T = T; r.rope_cols = rope_cols; r.rope_hs = HS;
     return gemm_impl(MODE_NT, EPI_ROPE, A, B, C, nullptr, nullptr, nullptr, M, N, K, 1, nullptr, 0, status, max_ctas, stream_, r);
