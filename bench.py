@@ -79,8 +79,9 @@ def reference_arm(args) -> int:
 
     script = os.path.join(REF_DIR, "train_gpt2.py")
     if not os.path.exists(script):
-        upstream = os.path.join(os.environ.get("LLMK_REFERENCE_ROOT", "/root/reference"), "train_gpt2.py")
-        if not os.path.exists(upstream):
+        # LLMK_REFERENCE_ROOT: a checkout of the reference project to take the trainer from when the copy is missing
+        upstream = os.path.join(os.environ.get("LLMK_REFERENCE_ROOT", ""), "train_gpt2.py")
+        if not os.environ.get("LLMK_REFERENCE_ROOT") or not os.path.exists(upstream):
             return say({"unavailable": "baseline/_ref/train_gpt2.py (copy of the reference's PyTorch trainer) is missing"})
         os.makedirs(REF_DIR, exist_ok=True)
         tmp = f"{script}.{os.getpid()}.tmp"

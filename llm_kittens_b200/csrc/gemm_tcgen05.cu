@@ -307,7 +307,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
             const int b_rows_total = SWI ? p.N / 2 : p.N;
             const int* b_flags = (SWI && rank == 1) ? p.b_ready2 : p.b_ready;
             // every flag of B seen by this CTA (at most 64 are remembered): nothing left to poll, and no index arithmetic
-            // (the mask lives in lane 0, which does the polling: its verdict is broadcast so that the warp branches as one)
+            // (the mask lives in lane 0, which does the polling: its answer is broadcast so that the warp branches as one)
             const bool b_all_lane = p.b_nflags > 0 && p.b_nflags <= 64 &&
                                     b_done == (p.b_nflags == 64 ? ~0ull : ((1ull << p.b_nflags) - 1ull));
             const bool b_all = __shfl_sync(0xffffffffu, (int)b_all_lane, 0) != 0;
