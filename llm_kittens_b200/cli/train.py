@@ -150,6 +150,10 @@ def train(args: TrainArgs, trainer_name: str) -> int:
     comm = make_comm(plan, model, world, rank, device)
     trainer = Trainer(model, zero_stage=args.zero_stage, use_master_weights=bool(args.use_master_weights),
                       learning_rate=args.learning_rate, weight_decay=args.weight_decay, comm=comm, num_processes=world, rank=rank)
+    # micro-steps replayed from CUDA graphs where the model and the communication path can be captured (dense models,
+    # one process or the fused ZeRO-0/1 path); the first step runs eagerly, the second one is captured
+    if os.environ.get("LLMK_CUDA_GRAPH", "1") != "0":
+        trainer.enable_cuda_graph(True)
 
     # ---- config table
     printf0(rank, "+-----------------------+----------------------------------------------------+")

@@ -180,8 +180,11 @@ __global__ void rope_qk_vec_kernel(bf16* __restrict__ qkv, const float2* __restr
 // stage 1: partial[chunk][c] = sum over the chunk's rows of dout[row][c]; stage 2 sums chunks in order.
 constexpr int DB_ROWS = 256;  // rows per chunk
 __global__ void dbias_partial_kernel(float* __restrict__ partial, const bf16* __restrict__ dout, int rows, int OC) {
-    // block = 32 (column vectors of 8) x 8 (row lanes); grid = (OC/256, chunks)
+    // block = 32 (column vectors of 8) x 8 (row lanes); grid = (OC/256, chunks, groups): group g sums its own `rows`
+    // rows of the stacked dout into its own partials
     __shared__ float sh[8][32][8];
+    dout += (size_t)blockIdx.z * rows * OC;
+    partial += (size_t)blockIdx.z * gridDim.y * OC;
     const int cv = blockIdx.x * 32 + threadIdx.x;  // column vector index
     const int c = cv * 8;
     float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
@@ -222,6 +225,8 @@ __global__ void dbias_partial_kernel(float* __restrict__ partial, const bf16* __
 __global__ void dbias_finish_kernel(bf16* __restrict__ dbias, const float* __restrict__ partial, int chunks, int OC,
                                     int accumulate) {
     __shared__ float sh[32][33];
+    dbias += (size_t)blockIdx.y * OC;                 // grid.y = group
+    partial += (size_t)blockIdx.y * chunks * OC;
     const int c = blockIdx.x * 32 + threadIdx.x;
     float s = 0.f;
     if (c < OC)
@@ -387,6 +392,20 @@ LLMK_API int llmk_dbias(void* dbias, void* scratch, const void* dout, int rows, 
     LLMK_LAUNCH_CHECK();
     dbias_finish_kernel<<<ceil_div(OC, 32), dim3(32, 32), 0, (cudaStream_t)stream>>>((bf16*)dbias, (const float*)scratch, chunks,
                                                                                   OC, accumulate);
+    LLMK_LAUNCH_CHECK();
+    return LLMK_OK;
+}
+// The same for `groups` row blocks stacked in dout [groups * rows, OC] (the local experts of a mixture-of-experts
+// layer): dbias [groups, OC] (+)= per-block column sums, two launches in all. scratch: groups * llmk_dbias_scratch_bytes.
+LLMK_API int llmk_dbias_grouped(void* dbias, void* scratch, const void* dout, int rows, int OC, int groups, int accumulate,
+                                void* stream) {
+    if (OC % 8 || groups <= 0 || groups > 65535) return LLMK_ERR_SHAPE;
+    const int chunks = ceil_div(rows, DB_ROWS);
+    dim3 grid(ceil_div(OC, 256), chunks, groups), block(32, 8);
+    dbias_partial_kernel<<<grid, block, 0, (cudaStream_t)stream>>>((float*)scratch, (const bf16*)dout, rows, OC);
+    LLMK_LAUNCH_CHECK();
+    dbias_finish_kernel<<<dim3(ceil_div(OC, 32), groups), dim3(32, 32), 0, (cudaStream_t)stream>>>((bf16*)dbias, (const float*)scratch,
+                                                                                                 chunks, OC, accumulate);
     LLMK_LAUNCH_CHECK();
     return LLMK_OK;
 }

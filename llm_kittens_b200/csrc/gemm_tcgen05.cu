@@ -109,6 +109,10 @@ struct Params {
     // Grouped (batched) problems: `group_m` rows of C per group (0 = one problem). Group g of a tile is m0 / group_m.
     // NT: B is [G*N, K] and bias [G*N]; NN: B is [G*K, N]; TN: A is [G*K, M_g], B is [G*K, N], C is [G*M_g, N].
     int group_m;
+    // Rotation of the M-tile order (in tiles): every rank of an expert-parallel layer walks its row blocks starting from
+    // a different source rank, so that at any moment the ranks' epilogues store to (and their producers wait for)
+    // different peers instead of all hitting the same GPU's NVLink port.
+    int m_rotate;
     const bf16* bias;  // [N]
     const bf16* aux;   // [M,N] pre-GELU input (DGELU) or addend (ADD; may alias C)
     float* partial;    // [splits, M, N] fp32 (PARTIAL)
@@ -198,7 +202,12 @@ __device__ __forceinline__ Work decode_unit(const Params& p, int u) {
     const int first_m = group * GROUP_M;
     const int gm = min(p.tiles_m - first_m, GROUP_M);
     const int r = tile - group * group_size;
-    w.m0 = (first_m + r % gm) * (p.pair ? 2 * BM : BM);
+    int tm = first_m + r % gm;
+    if (p.m_rotate > 0) {
+        tm += p.m_rotate;
+        if (tm >= p.tiles_m) tm -= p.tiles_m;
+    }
+    w.m0 = tm * (p.pair ? 2 * BM : BM);
     w.n0 = (r / gm) * BN;
     w.kb_begin = w.split * p.kb_per_split;
     w.kb_end = min(p.kb_total, w.kb_begin + p.kb_per_split);
@@ -915,6 +924,7 @@ struct Ready {
     long long limit_ns = 0;
     const float2* rope = nullptr;
     int rope_T = 1, rope_cols = 0, rope_hs = 64;
+    int rotate_rows = 0;                    // start the walk over the rows of C this many rows in (rounded down to tiles)
     const void* b2 = nullptr;               // EPI_SWIGLU: the gate weights, the third output, the gate's readiness flags
     void* c3 = nullptr;
     const int* b_ready2 = nullptr;
@@ -959,6 +969,7 @@ static int gemm_impl(int mode, int epi, const void* A, const void* B, void* C, v
     p.b_ready = ready.b_ready; p.a_ready = ready.a_ready;
     p.b_chunk = ready.b_chunk > 0 ? ready.b_chunk : 1;
     p.b_nflags = ready.b_nflags;
+    p.m_rotate = 0;
     p.b_tick = ready.b_tick; p.a_rows = ready.a_rows > 0 ? ready.a_rows : 1; p.a_need = ready.a_need;
     p.ready_limit_ns = ready.limit_ns > 0 ? ready.limit_ns : (long long)LLMK_WAIT_LIMIT_NS;
     if ((p.b_ready != nullptr || p.a_ready != nullptr) && mode == MODE_TN) return LLMK_ERR_SHAPE;
@@ -1001,6 +1012,7 @@ static int gemm_impl(int mode, int epi, const void* A, const void* B, void* C, v
             epi = EPI_PARTIAL;
         }
     }
+    if (ready.rotate_rows > 0) p.m_rotate = (ready.rotate_rows / (p.pair ? 2 * BM : BM)) % p.tiles_m;
     p.kb_per_split = ceil_div(p.kb_total, p.splits);
     if ((long)p.kb_per_split * (p.splits - 1) >= p.kb_total) {  // avoid empty trailing splits
         p.splits = ceil_div(p.kb_total, p.kb_per_split);
@@ -1098,8 +1110,9 @@ LLMK_API int llmk_gemm_b_ready(int mode, int epi, const void* A, const void* B, 
 LLMK_API int llmk_gemm_grouped_a_ready(int mode, int epi, const void* A, const void* B, void* C, void* C2, const void* bias,
                                        const void* aux, int M, int N, int K, int groups, void* workspace, long workspace_bytes,
                                        int* status, int max_ctas, const void* a_ready, int a_rows, int a_need, long limit_ns,
-                                       void* stream_) {
+                                       int rotate_rows, void* stream_) {
     Ready r;
+    r.rotate_rows = rotate_rows;
     r.a_ready = static_cast<const int*>(a_ready);
     r.a_rows = a_rows;
     r.a_need = a_need;
@@ -1120,6 +1133,7 @@ LLMK_API int llmk_gemm_grouped_scatter(int mode, int with_bias, const void* A, c
                                        const long long* arrive_ptrs, int arrive_off, void* count, int cap, int P, int my_rank,
                                        int epoch, void* stream_) {
     Ready r;
+    r.rotate_rows = ((my_rank + 1) % P) * cap;   // rank r starts with the rows of rank r + 1: no two ranks store to the same peer
     r.sc_dst = dst_ptrs;
     r.sc_arrive = arrive_ptrs;
     r.sc_count = static_cast<int*>(count);

@@ -174,7 +174,7 @@ class MoETransformer(Transformer):
         # every M tile of the first GEMM waits only for the source rank whose rows it loads
         gemm.gemm_nt(self.recv_x[l][rows], p["fcw"][l][loc], bias=p["fcb"][l][loc], out=act_l[rows],
                      gelu_pre_out=a["hid_pre"][l][rows], groups=G,
-                     a_ready=None if lib else (self.arrive[r_out:], cap, ep, lim))
+                     a_ready=None if lib else (self.arrive[r_out:], cap, ep, lim, ((self.ep_rank + 1) % P) * cap))
         if lib:
             gemm.gemm_nt(act_l[rows], p["fcprojw"][l][loc], bias=p["fcprojb"][l][loc], out=a["y_loc"][rows], groups=G)
             self._library_back(a["y_loc"], self.back_y[l])
@@ -214,7 +214,7 @@ class MoETransformer(Transformer):
             ew.gelu_fwd(a["hid_pre"][l][rows], out=act_l[rows])
         # the first consumer of dy waits tile by tile for its source ranks; the products after it find dy complete
         gemm.gemm_nn(dy, p["fcprojw"][l][loc], out=d_hid, dgelu_of=a["hid_pre"][l][rows], groups=G,
-                     a_ready=None if lib else (self.arrive[r_out:], cap, ep, lim))
+                     a_ready=None if lib else (self.arrive[r_out:], cap, ep, lim, ((self.ep_rank + 1) % P) * cap))
         gemm.gemm_tn(dy, act_l[rows], out=g["fcprojw"][l][loc], accumulate=True, groups=G)
         gemm.gemm_tn(d_hid, x, out=g["fcw"][l][loc], accumulate=True, groups=G)
         fused_back = self.scatter and not lib
@@ -223,11 +223,9 @@ class MoETransformer(Transformer):
                                       self.done[1:], cap, P, self.ep_rank, ep, nn=True)
         else:
             gemm.gemm_nn(d_hid, p["fcw"][l][loc], out=a["y_loc"][rows], groups=G)
-        for el in range(G):
-            gb1, gb2 = self._expert_views(l, el)[5], self._expert_views(l, el)[7]
-            r = slice(el * per, (el + 1) * per)
-            ew.dbias(gb2, dy[r], accumulate=True)
-            ew.dbias(gb1, d_hid[r], accumulate=True)
+        # bias gradients of all local experts: one grouped column sum per projection
+        ew.dbias_grouped(g["fcprojb"][l][loc], dy, G, accumulate=True)
+        ew.dbias_grouped(g["fcb"][l][loc], d_hid, G, accumulate=True)
         if lib:
             self._library_back(a["y_loc"], self.back_dx)
             moe_ops.combine(d_ln2, None, self.back_dx, idx, slot, None, cap)

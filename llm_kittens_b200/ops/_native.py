@@ -89,7 +89,8 @@ def _conv(a: Any):
 
 # kernels launched by one call of a library entry point (default 1); used for the launch counter
 _KERNELS_PER_CALL = {"llmk_layernorm_bwd": 2, "llmk_rmsnorm_bwd": 2, "llmk_dbias": 2, "llmk_attention_bwd": 3, "llmk_attention_bwd_tc": 2,
-                     "llmk_encoder_bwd": 2, "llmk_global_norm2": 2, "llmk_bucket_sort": 6, "llmk_moe_dispatch_signal": 2, "llmk_moe_dispatch": 2}
+                     "llmk_encoder_bwd": 2, "llmk_global_norm2": 2, "llmk_bucket_sort": 6, "llmk_moe_dispatch_signal": 2, "llmk_moe_dispatch": 2,
+                     "llmk_dbias_grouped": 2, "llmk_attention_bwd_tc_rope": 2, "llmk_attention_bwd_ring_step": 2}
 _LAUNCHES = 0
 
 

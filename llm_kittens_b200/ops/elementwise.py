@@ -88,6 +88,19 @@ def dbias(dbias_t, dout, accumulate=True):
     return dbias_t
 
 
+def dbias_grouped(dbias_t, dout, groups, accumulate=True):
+    """``dbias_t`` [groups, OC] (+)= column sums of each of the ``groups`` equal row blocks stacked in ``dout``."""
+    rows, OC = dout.shape[0] // groups, dout.shape[1]
+    if groups == 1 or not hasattr(N.lib(), "llmk_dbias_grouped"):
+        for g in range(groups):
+            dbias(dbias_t[g], dout[g * rows:(g + 1) * rows], accumulate)
+        return dbias_t
+    nbytes = groups * int(N.lib().llmk_dbias_scratch_bytes(rows, OC))
+    N.call("llmk_dbias_grouped", dbias_t, N.scratch_buffer(_DBIAS_SCRATCH, nbytes, 1 << 20, "bias-gradient partials"), dout, rows, OC,
+           groups, int(accumulate))
+    return dbias_t
+
+
 def encoder_fwd(tokens, wte, wpe, out=None):
     B, T = tokens.shape
     C = wte.shape[1]

@@ -70,7 +70,7 @@ def _gemm(mode, epi, a, b, c, c2, bias, aux, M, Nn, K, groups=1, a_ready=None):
         a_rows, b_rows = (K, K) if mode == MODE_TN else (M, Nn if mode == MODE_NT else K)
         for g in range(groups):
             cut = lambda t, r: None if t is None else t[g * r:(g + 1) * r]
-            ar = None if a_ready is None else (a_ready[0][g * (M // a_ready[1]):], *a_ready[1:])
+            ar = None if a_ready is None else (a_ready[0][g * (M // a_ready[1]):], *a_ready[1:4])
             _gemm(mode, epi, cut(a, a_rows), cut(b, b_rows), cut(c, M), cut(c2, M), cut(bias, Nn) if bias is not None and bias.dim() == 1 else bias,
                   cut(aux, M), M, Nn, K, a_ready=ar)
         return c
@@ -85,9 +85,10 @@ def _gemm(mode, epi, a, b, c, c2, bias, aux, M, Nn, K, groups=1, a_ready=None):
     if a_ready is not None:
         if mode == MODE_TN or M % a_ready[1]:
             raise N.NativeError("gemm: a_ready needs an NT / NN product whose group rows are whole flag blocks")
-        flags, rows_per, need, limit_ns = a_ready
+        flags, rows_per, need, limit_ns = a_ready[:4]
+        rotate = a_ready[4] if len(a_ready) > 4 else 0     # rows to start the walk at (a different source rank per rank)
         N.call("llmk_gemm_grouped_a_ready", mode, epi, a, b, c, c2, bias, aux, M, Nn, K, groups, ws, ws_bytes, N.status_word(),
-               _MAX_CTAS, flags, rows_per, need, limit_ns)
+               _MAX_CTAS, flags, rows_per, need, limit_ns, rotate)
     elif groups > 1:
         N.call("llmk_gemm_grouped", mode, epi, a, b, c, c2, bias, aux, M, Nn, K, groups, ws, ws_bytes, N.status_word(), _MAX_CTAS)
     elif ready is not None and ready[3] > 0:

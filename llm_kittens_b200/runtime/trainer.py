@@ -49,7 +49,7 @@ class Trainer:
         self.lr, self.wd, self.beta1, self.beta2, self.eps, self.grad_clip = learning_rate, weight_decay, beta1, beta2, eps, grad_clip
         self.step_count = 0
         self.use_cuda_graph = False
-        self._graph, self._graph_key, self._eager_steps = None, None, 0
+        self._graph, self._graph_key, self._steps_begun = None, None, 0
         self.rng = Xorshift(rng_state)
         self.rng_state_last_update = rng_state
         n = self.plan.state_elements
@@ -145,20 +145,23 @@ class Trainer:
     # ------------------------------------------------------------------ the step
     def accumulate(self, micro_batches) -> int:
         """zero grads, run forward/backward over the micro-batches, start bucket reductions."""
-        model = self.model
         self.begin_step()
         batches = list(micro_batches)
         accum = len(batches)
-        if self.use_cuda_graph and self._graph_usable(batches):
-            return self._accumulate_graph(batches)
         for i, (x, y) in enumerate(batches):
             self.micro_step(x, y, i, accum)
-        self._eager_steps += 1
         return accum
 
     def micro_step(self, x, y, index: int, accum: int) -> None:
         """Forward + backward of micro-batch ``index`` of ``accum`` (after :meth:`begin_step`). Loops that drive the
-        micro-steps themselves must go through here: the sharded communication path counts micro-steps."""
+        micro-steps themselves must go through here: the sharded communication path counts micro-steps. With CUDA
+        graphs enabled (and a communication path that can be captured) the first optimizer step runs eagerly, the
+        second one captures its micro-steps and every later one replays them."""
+        if index == 0:
+            self._steps_begun = getattr(self, "_steps_begun", 0) + 1
+        if self.use_cuda_graph and self._steps_begun > 1 and self._graph_usable([(x, y)]):
+            self._micro_step_graph(x, y, index, accum)
+            return
         if self.sharded_state:
             self.comm.start_micro_step(index)
         with nvtx_range("forward"):
@@ -177,15 +180,14 @@ class Trainer:
 
     def _graph_usable(self, batches) -> bool:
         comm_ok = isinstance(self.comm, SingleProcessComm) or getattr(self.comm, "graph_capturable", False)
-        return (self.native and comm_ok and self._eager_steps > 0
-                and type(self.model).__name__ == "Transformer" and len({tuple(x.shape) for x, _ in batches}) == 1)
+        return (self.native and comm_ok and type(self.model).__name__ == "Transformer"
+                and len({tuple(x.shape) for x, _ in batches}) == 1)
 
-    def _accumulate_graph(self, batches) -> int:
-        model = self.model
-        accum = len(batches)
-        key = (tuple(batches[0][0].shape), accum)
+    def _micro_step_graph(self, x, y, index: int, accum: int) -> None:
         from ..ops import _native
 
+        model = self.model
+        key = (tuple(x.shape), accum)
         with_comm = not isinstance(self.comm, SingleProcessComm)
         if self._graph_key != key:
             B, T = key[0]
@@ -213,15 +215,13 @@ class Trainer:
             else:
                 self._graph, self._graph_kernels = self._graph_last, self._graph_last_kernels
             self._graph_key = key
-        for i, (x, y) in enumerate(batches):
-            self._gx.copy_(x, non_blocking=True)
-            self._gy.copy_(y, non_blocking=True)
-            if i == 0:
-                model.acts["loss_acc"].zero_()
-            last = i == accum - 1
-            (self._graph_last if last else self._graph).replay()
-            _native.count_replayed(self._graph_last_kernels if last else self._graph_kernels)
-        return accum
+        self._gx.copy_(x, non_blocking=True)
+        self._gy.copy_(y, non_blocking=True)
+        if index == 0:
+            model.acts["loss_acc"].zero_()
+        last = index == accum - 1
+        (self._graph_last if last else self._graph).replay()
+        _native.count_replayed(self._graph_last_kernels if last else self._graph_kernels)
 
     def begin_step(self) -> None:
         """Start of an optimizer step: wait for the peers (fused communication) and zero the gradients."""
