@@ -300,6 +300,73 @@ combine_kernel(bf16* __restrict__ out, const bf16* __restrict__ base, const bf16
     }
 }
 
+// The way back as a PULL, fused with the combine: out[t] = base[t] + sum_k w[t,k] * y(e(t,k), slot(t,k)), where the
+// row y lives in the memory of the rank that owns expert e: y_ptrs[owner] + ((e_local * P + my_rank) * cap + slot) * C
+// (the owner's local expert-output buffer, laid out [e_local][source rank][slot]). Rows are fetched with 128-bit peer
+// loads by the warp that combines the token; only rows that are really used cross NVLink (no capacity padding), and
+// the owners' expert GEMMs keep their plain local epilogue. `returned` / `epoch`: as in combine_kernel, every block
+// first waits until all E owners have published their outputs. `save` (optional, [E * cap, C] local): the fetched
+// rows are also kept locally at [e][slot], where the backward pass finds them for the routing-weight gradient.
+__global__ void __launch_bounds__(256)
+combine_pull_kernel(bf16* __restrict__ out, const bf16* __restrict__ base, Peers y_ptrs, bf16* __restrict__ save,
+                    const int* __restrict__ top_idx, const int* __restrict__ slot, const float* __restrict__ weights, int N, int K,
+                    int C, int cap, int Eloc, int my_rank, int P, const int* __restrict__ returned, int E, int epoch,
+                    long long limit_ns, int* status) {
+    if (returned != nullptr && !wait_entries_block(returned, E, epoch, limit_ns, status, 310)) return;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const size_t t = (size_t)blockIdx.x * (blockDim.x >> 5) + warp;
+    if (t >= (size_t)N) return;
+    const bf16* rows[MAXK];
+    bf16* keep[MAXK];
+    float wk[MAXK];
+    int nk = 0;
+    for (int k = 0; k < K; k++) {
+        const int s = slot[t * K + k];
+        if (s < 0) continue;
+        const int e = top_idx[t * K + k];
+        const int owner = e / Eloc, el = e % Eloc;
+        rows[nk] = static_cast<const bf16*>(y_ptrs.p[owner]) + (((size_t)el * P + my_rank) * cap + s) * C;
+        keep[nk] = save != nullptr ? save + ((size_t)e * cap + s) * C : nullptr;
+        wk[nk] = weights ? weights[t * K + k] : 1.0f;
+        nk++;
+    }
+    for (int v = lane; v < C / 8; v += 32) {
+        float acc[8];
+        if (base != nullptr) {
+            unpack8(ld128(base + t * C + v * 8), acc);
+        } else {
+#pragma unroll
+            for (int j = 0; j < 8; j++) acc[j] = 0.f;
+        }
+        bf16x8 r[MAXK];
+#pragma unroll
+        for (int k = 0; k < MAXK; k++)
+            if (k < nk) r[k] = ld128_stream(rows[k] + v * 8);      // all of a token's rows in flight before the first is used
+#pragma unroll
+        for (int k = 0; k < MAXK; k++) {
+            if (k < nk) {
+                float f[8];
+                unpack8(r[k], f);
+#pragma unroll
+                for (int j = 0; j < 8; j++) acc[j] += wk[k] * f[j];
+                if (keep[k] != nullptr) st128(keep[k] + v * 8, r[k]);
+            }
+        }
+        st128(out + t * C + v * 8, pack8(acc));
+    }
+}
+
+// Owner side of the pull: once everything queued before this launch has finished (the second expert GEMM wrote its
+// outputs locally), tell every source rank that the outputs of this rank's experts can be fetched: entry
+// [arrive_off + my_rank * Eloc + el] of every rank's arrival table gets `epoch` (release at system scope).
+__global__ void publish_kernel(Peers arrive, int arrive_off, int Eloc, int my_rank, int P, int epoch) {
+    const int r = threadIdx.x / Eloc, el = threadIdx.x % Eloc;
+    if (r < P) {
+        __threadfence_system();
+        st_release_sys(static_cast<int*>(arrive.p[r]) + arrive_off + my_rank * Eloc + el, epoch);
+    }
+}
+
 // dw[t,k] = dot(dout[t], back[e][slot])  (gradient of the combine with respect to the routing weight)
 __global__ void __launch_bounds__(256)
 combine_dweight_kernel(float* __restrict__ dw, const bf16* __restrict__ dout, const bf16* __restrict__ back,
@@ -476,6 +543,23 @@ LLMK_API int llmk_moe_combine_wait(void* out, const void* base, const void* back
                                                                     (const int*)top_idx, (const int*)slot, (const float*)weights,
                                                                     N, K, C, cap, (const int*)returned, E, epoch,
                                                                     (long long)limit_ns, status);
+    LLMK_LAUNCH_CHECK();
+    return LLMK_OK;
+}
+LLMK_API int llmk_moe_combine_pull(void* out, const void* base, const long long* y_ptrs, void* save, const void* top_idx,
+                                   const void* slot, const void* weights, int N, int K, int C, int E, int cap, int my_rank, int P,
+                                   const void* returned, int epoch, long limit_ns, int* status, void* stream) {
+    if (P > MAXP || E % P || E > MAXE || K > MAXK || C % 8) return LLMK_ERR_SHAPE;
+    combine_pull_kernel<<<ceil_div(N, 8), 256, 0, (cudaStream_t)stream>>>((bf16*)out, (const bf16*)base, make_peers(y_ptrs, P), (bf16*)save,
+                                                                         (const int*)top_idx, (const int*)slot, (const float*)weights,
+                                                                         N, K, C, cap, E / P, my_rank, P, (const int*)returned, E, epoch,
+                                                                         (long long)limit_ns, status);
+    LLMK_LAUNCH_CHECK();
+    return LLMK_OK;
+}
+LLMK_API int llmk_moe_publish(const long long* arrive_ptrs, int arrive_off, int E, int my_rank, int P, int epoch, void* stream) {
+    if (P > MAXP || E % P || E > MAXE) return LLMK_ERR_SHAPE;
+    publish_kernel<<<1, 128, 0, (cudaStream_t)stream>>>(make_peers(arrive_ptrs, P), arrive_off, E / P, my_rank, P, epoch);
     LLMK_LAUNCH_CHECK();
     return LLMK_OK;
 }

@@ -23,6 +23,8 @@ models); expert parameters are owned by one rank each and are neither reduced no
 """
 from __future__ import annotations
 
+import os
+
 import torch
 
 from ..ops import elementwise as ew
@@ -92,7 +94,10 @@ class MoETransformer(Transformer):
         Lg = 1 if self.recompute >= 1 else L
         a["hid_pre"] = torch.empty(L, rows, H, dtype=BF16, device=dev)
         a["hid_act"] = torch.empty(Lg, rows, H, dtype=BF16, device=dev)
-        a["y_loc"] = torch.empty(rows, C, dtype=BF16, device=dev)        # expert outputs / input grads before return
+        # expert outputs / input grads of this rank's experts, [e_local][source rank][slot]: peers fetch their rows from
+        # here (pull-style way back), so it lives in the exchange's (symmetric) memory
+        t, self.y_loc_ptrs = self.exchange.alloc(rows * C, dev)
+        a["y_loc"] = t.view(rows, C)
         a["d_hid"] = torch.empty(rows, H, dtype=BF16, device=dev)
         # exchange buffers (symmetric memory when expert-parallel)
         self.recv_x, self.recv_x_ptrs = [], []
@@ -114,6 +119,11 @@ class MoETransformer(Transformer):
         self.done = torch.zeros(1 + Eloc * P, dtype=i32, device=dev)
         # the second GEMM stores its rows straight into the source ranks' buffers when the row blocks are whole tiles
         self.scatter = (P * cap) % gemm.tile_rows() == 0 and cap >= 32 and H % 64 == 0
+        # the way back: "pull" (default: plain local GEMM epilogue, the combine fetches its rows from the owners by peer
+        # loads), "scatter" (the GEMM's epilogue stores into the senders' buffers) or "push" (a return kernel does)
+        self.way_back = os.environ.get("LLMK_MOE_RETURN", "pull")
+        if self.way_back == "scatter" and not self.scatter:
+            self.way_back = "push"
         self._epoch = 0
         self.library = bool(getattr(self.exchange, "library", False))
         if self.library:
@@ -180,7 +190,13 @@ class MoETransformer(Transformer):
             self._library_back(a["y_loc"], self.back_y[l])
             moe_ops.combine(out, res2, self.back_y[l], a["top_idx"][l], a["slot"][l], a["top_w"][l], cap)
             return
-        if self.scatter:
+        if self.way_back == "pull":
+            gemm.gemm_nt(act_l[rows], p["fcprojw"][l][loc], bias=p["fcprojb"][l][loc], out=a["y_loc"][rows], groups=G)
+            moe_ops.publish(self.arrive_ptrs, r_back, E, self.ep_rank, P, ep)
+            moe_ops.combine_pull(out, res2, self.y_loc_ptrs, self.back_y[l], a["top_idx"][l], a["slot"][l], a["top_w"][l], E, cap,
+                                 self.ep_rank, P, self.arrive[r_back:], ep, lim)
+            return
+        if self.way_back == "scatter":
             # the GEMM's epilogue IS the way back: rows go to the senders' buffers, blocks are published as they complete
             gemm.gemm_grouped_scatter(act_l[rows], p["fcprojw"][l][loc], p["fcprojb"][l][loc], a["y_loc"][rows], G,
                                       self.back_y_ptrs[l], self.arrive_ptrs, r_back, self.done[1:], cap, P, self.ep_rank, ep)
@@ -217,7 +233,7 @@ class MoETransformer(Transformer):
                      a_ready=None if lib else (self.arrive[r_out:], cap, ep, lim, ((self.ep_rank + 1) % P) * cap))
         gemm.gemm_tn(dy, act_l[rows], out=g["fcprojw"][l][loc], accumulate=True, groups=G)
         gemm.gemm_tn(d_hid, x, out=g["fcw"][l][loc], accumulate=True, groups=G)
-        fused_back = self.scatter and not lib
+        fused_back = self.way_back == "scatter" and not lib
         if fused_back:
             gemm.gemm_grouped_scatter(d_hid, p["fcw"][l][loc], None, a["y_loc"][rows], G, self.back_dx_ptrs, self.arrive_ptrs, r_back,
                                       self.done[1:], cap, P, self.ep_rank, ep, nn=True)
@@ -229,6 +245,10 @@ class MoETransformer(Transformer):
         if lib:
             self._library_back(a["y_loc"], self.back_dx)
             moe_ops.combine(d_ln2, None, self.back_dx, idx, slot, None, cap)
+        elif self.way_back == "pull":
+            moe_ops.publish(self.arrive_ptrs, r_back, E, self.ep_rank, P, ep)
+            moe_ops.combine_pull(d_ln2, None, self.y_loc_ptrs, None, idx, slot, None, E, cap, self.ep_rank, P, self.arrive[r_back:],
+                                 ep, lim)
         else:
             if not fused_back:
                 moe_ops.return_signal(self.back_dx_ptrs, a["y_loc"], C, E, cap, self.ep_rank, P, self.arrive_ptrs, r_back,

@@ -63,6 +63,22 @@ def combine_wait(out, base, back, top_idx, slot, weights, cap, returned, E, epoc
     return out
 
 
+def publish(arrive_ptrs, arrive_off, E, rank, P, epoch):
+    """Owner side of the pull-style way back: after everything queued so far (the second expert GEMM), entry
+    ``arrive_off + e`` of every rank's arrival table gets ``epoch`` for each expert ``e`` of this rank."""
+    N.call("llmk_moe_publish", arrive_ptrs, arrive_off, E, rank, P, epoch)
+
+
+def combine_pull(out, base, y_ptrs, save, top_idx, slot, weights, E, cap, rank, P, returned, epoch, limit_ns):
+    """:func:`combine` whose rows are fetched from the owners' expert-output buffers (``y_ptrs``: the ranks' buffers laid
+    out [e_local][source rank][slot]) by peer loads, after an in-kernel wait for the owners' ``publish``; ``save``
+    (optional [E*cap, C]) keeps the fetched rows locally."""
+    Nn, K = top_idx.shape
+    N.call("llmk_moe_combine_pull", out, base, y_ptrs, save, top_idx, slot, weights, Nn, K, out.shape[1], E, cap, rank, P, returned,
+           epoch, limit_ns, N.status_word())
+    return out
+
+
 def return_rows(back_ptrs, y, C, E, cap, rank=0, P=1):
     N.call("llmk_moe_return", back_ptrs, y, C, E, cap, rank, P)
 

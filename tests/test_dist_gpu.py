@@ -94,8 +94,9 @@ def test_expert_parallel_moe_matches_single_process(tmp_path):
     ref = []
     for x, y in global_batches(cfg, 3, 2, 2, 128):
         ref.append(tr.train_step([(x[:2].contiguous(), y[:2].contiguous()), (x[2:].contiguous(), y[2:].contiguous())]).loss)
-    for mode in ("gpu_moe_library1", "gpu_moe_fused", "gpu_moe_a2a1"):
-        r0, r1 = _run(mode, tmp_path)
+    for mode, env in (("gpu_moe_library1", {}), ("gpu_moe_fused", {}), ("gpu_moe_a2a1", {}),
+                      ("gpu_moe_fused", {"LLMK_MOE_RETURN": "scatter"}), ("gpu_moe_fused", {"LLMK_MOE_RETURN": "push"})):
+        r0, r1 = _run(mode, tmp_path, **env)
         assert r0["losses"] == r1["losses"]
         for a, b in zip(r0["losses"], ref):
             assert abs(a - b) < 0.03, (mode, r0["losses"], ref)

@@ -202,11 +202,14 @@ def test_moe_ops_against_torch():
         assert pad.numel() == 0 or pad.abs().max().item() == 0
 
 
-@pytest.mark.parametrize("E,cf", [(8, 1.25), (6, 1.25), (8, 2.0)])
-def test_moe_model_matches_oracle(E, cf):
+@pytest.mark.parametrize("E,cf,way_back", [(8, 1.25, "pull"), (6, 1.25, "pull"), (8, 2.0, "pull"), (8, 2.0, "scatter"), (8, 1.25, "push")])
+def test_moe_model_matches_oracle(E, cf, way_back, monkeypatch):
     """E = 6 is not a multiple of 8: the router's gradient GEMMs run on a zero-padded router matrix. Capacity factor 2
     makes every expert's row block a whole number of GEMM tiles (256 rows), which is when the second GEMM stores its
-    rows straight into the senders' buffers from its epilogue instead of through the return kernel."""
+    rows straight into the senders' buffers from its epilogue instead of through the return kernel. The three ways
+    back (the combine pulls its rows from the owners; the GEMM's epilogue scatters them; a return kernel pushes them) must
+    all match."""
+    monkeypatch.setenv("LLMK_MOE_RETURN", way_back)
     from llm_kittens_b200.models.moe import MoETransformer
     from llm_kittens_b200.oracle.torch_model import TorchTransformer
     from llm_kittens_b200.ops import _native
