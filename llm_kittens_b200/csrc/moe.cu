@@ -246,6 +246,91 @@ zero_pad_kernel(Peers recv, const int* __restrict__ counts, int E, int C, int ca
     }
 }
 
+// ------------------------------------------------------------------ dispatch as a PULL
+// Source side: the inverse of the slot assignment, inv_tok[e * cap + s] = token whose assignment got slot s of expert
+// e (-1: the slot is unused) and inv_w = its routing weight; both live in peer-readable memory, as does a copy of the
+// token rows. Owner side (dispatch_pull_kernel): one warp per row of recv[e_local][src][slot] reads the token index
+// from rank src's map and copies that token's row out of rank src's memory with 128-bit peer loads (zeros for unused
+// slots, times the routing weight in the backward pass); loads cross NVLink faster than the stores of the push
+// variant, nothing is packed or padded on the way, and every (source, expert) block is published in the LOCAL arrival
+// table by the block that completes it, which is what the expert GEMM's producer warp polls per M tile.
+__global__ void __launch_bounds__(256)
+inverse_map_kernel(int* __restrict__ inv_tok, float* __restrict__ inv_w, const int* __restrict__ top_idx, const int* __restrict__ slot,
+                   const float* __restrict__ top_w, int NK, int K, int cap) {
+    const int a = blockIdx.x * blockDim.x + threadIdx.x;
+    if (a >= NK) return;
+    const int s = slot[a];
+    if (s < 0) return;
+    const int e = top_idx[a];
+    inv_tok[(size_t)e * cap + s] = a / K;
+    inv_w[(size_t)e * cap + s] = top_w[a];
+}
+
+struct PullSrc {
+    const bf16* x[MAXP];       // the ranks' token rows [N, C]
+    const int* inv_tok[MAXP];  // the ranks' inverse maps [E * cap]
+    const float* inv_w[MAXP];
+};
+
+// grid = (ceil(cap / 8), P, Eloc), 8 warps per block: warp w of block x copies row x * 8 + w of block (el, src).
+// `ready` = this rank's arrival entries: [E + src] is written by rank src when its rows and map are in place (waited
+// for here, bounded), [el * P + src] is written here when the block is complete.
+__global__ void __launch_bounds__(256)
+dispatch_pull_kernel(bf16* __restrict__ recv, PullSrc src_tab, int C, int cap, int E, int Eloc, int my_rank, int P, int scale_by_weight,
+                     int* __restrict__ ready, int* __restrict__ done_counters, int epoch, long long limit_ns, int* status) {
+    const int src = blockIdx.y, el = blockIdx.z;
+    __shared__ int sh_ok;
+    if (threadIdx.x == 0) {
+        sh_ok = (status != nullptr && *reinterpret_cast<volatile int*>(status) != 0) ? 0 : 1;
+        if (sh_ok) {
+            const unsigned long long t0 = now_ns();
+            unsigned int spins = 0;
+            while (ld_acquire_sys(ready + E + src) < epoch) {
+                if ((++spins & 31u) == 0 && (long long)(now_ns() - t0) > limit_ns) {
+                    sh_ok = 0;
+                    if (status != nullptr && atomicCAS(status, 0, LLMK_ST_TIMEOUT_PEER) == 0) {
+                        status[1] = 320;
+                        status[2] = src;
+                        status[3] = el;
+                    }
+                    break;
+                }
+                __nanosleep(64);
+            }
+        }
+    }
+    __syncthreads();
+    if (!sh_ok) return;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int s = blockIdx.x * 8 + warp;
+    if (s < cap) {
+        const int e = my_rank * Eloc + el;
+        const int t = src_tab.inv_tok[src][(size_t)e * cap + s];
+        bf16* dst = recv + (((size_t)el * P + src) * cap + s) * C;
+        if (t < 0) {
+            bf16x8 z;
+#pragma unroll
+            for (int i = 0; i < 4; i++) z.v[i] = __floats2bfloat162_rn(0.f, 0.f);
+            for (int v = lane; v < C / 8; v += 32) st128(dst + v * 8, z);
+        } else {
+            const bf16* from = src_tab.x[src] + (size_t)t * C;
+            const float w = scale_by_weight ? src_tab.inv_w[src][(size_t)e * cap + s] : 1.0f;
+            for (int v = lane; v < C / 8; v += 32) {
+                bf16x8 r = ld128_stream(from + v * 8);
+                if (scale_by_weight) {
+                    float f[8];
+                    unpack8(r, f);
+#pragma unroll
+                    for (int j = 0; j < 8; j++) f[j] *= w;
+                    r = pack8(f);
+                }
+                st128(dst + v * 8, r);
+            }
+        }
+    }
+    if (last_cta_done(done_counters + el * P + src, gridDim.x)) st_release_sys(ready + el * P + src, epoch);
+}
+
 // ------------------------------------------------------------------ return (all-to-all back)
 // Owner side: copy the block of rows that rank `src` sent to local expert `el` back into that rank's
 // `back[e][cap][C]` buffer. grid = (chunks, P, Eloc).
@@ -505,6 +590,48 @@ LLMK_API int llmk_moe_dispatch_signal(const long long* recv_ptrs, const void* x,
     LLMK_LAUNCH_CHECK();
     zero_pad_kernel<<<dim3(32, E), 256, 0, st>>>(recv, (const int*)counts, E, C, cap, Eloc, my_rank, P, make_peers(arrive_ptrs, P),
                                                  arrive_off, (int*)done_counter, epoch);
+    LLMK_LAUNCH_CHECK();
+    return LLMK_OK;
+}
+// Source side of the pull-style dispatch (forward only: the backward pass reuses the maps): inverse slot maps of this
+// rank's assignments. inv_tok / inv_w: [E * cap] in peer-readable memory.
+LLMK_API int llmk_moe_inverse_map(void* inv_tok, void* inv_w, const void* top_idx, const void* slot, const void* top_w, int N, int K,
+                                  int E, int cap, void* stream) {
+    cudaStream_t st = (cudaStream_t)stream;
+    LLMK_CUDA_TRY(cudaMemsetAsync(inv_tok, 0xff, (size_t)E * cap * 4, st));
+    inverse_map_kernel<<<ceil_div((long)N * K, 256), 256, 0, st>>>((int*)inv_tok, (float*)inv_w, (const int*)top_idx, (const int*)slot,
+                                                                   (const float*)top_w, N * K, K, cap);
+    LLMK_LAUNCH_CHECK();
+    return LLMK_OK;
+}
+// This rank's rows and maps are in place: entry [arrive_off + E + my_rank] of every rank's arrival table gets `epoch`.
+__global__ void source_ready_kernel(Peers arrive, int idx, int P, int epoch) {
+    if ((int)threadIdx.x < P) {
+        __threadfence_system();
+        st_release_sys(static_cast<int*>(arrive.p[threadIdx.x]) + idx, epoch);
+    }
+}
+LLMK_API int llmk_moe_source_ready(const long long* arrive_ptrs, int arrive_off, int E, int my_rank, int P, int epoch, void* stream) {
+    if (P > MAXP) return LLMK_ERR_SHAPE;
+    source_ready_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(make_peers(arrive_ptrs, P), arrive_off + E + my_rank, P, epoch);
+    LLMK_LAUNCH_CHECK();
+    return LLMK_OK;
+}
+// Owner side: fill recv[e_local][src][slot][C] from the sources' memory. x_ptrs / tok_ptrs / w_ptrs: host arrays of the P
+// ranks' token rows, inverse token maps and inverse weight maps; `ready`: this rank's arrival entries of the exchange
+// (2 * E ints: [0, E) block flags written here, [E, E + P) source flags waited for); done_counters: Eloc * P zeroed ints.
+LLMK_API int llmk_moe_dispatch_pull(void* recv, const long long* x_ptrs, const long long* tok_ptrs, const long long* w_ptrs, int C, int E,
+                                    int cap, int my_rank, int P, int scale_by_weight, void* ready, void* done_counters, int epoch,
+                                    long limit_ns, int* status, void* stream) {
+    if (P > MAXP || E % P || C % 8) return LLMK_ERR_SHAPE;
+    PullSrc t;
+    for (int i = 0; i < MAXP; i++) {
+        t.x[i] = i < P ? reinterpret_cast<const bf16*>(x_ptrs[i]) : nullptr;
+        t.inv_tok[i] = i < P ? reinterpret_cast<const int*>(tok_ptrs[i]) : nullptr;
+        t.inv_w[i] = i < P ? reinterpret_cast<const float*>(w_ptrs[i]) : nullptr;
+    }
+    dispatch_pull_kernel<<<dim3(ceil_div(cap, 8), P, E / P), 256, 0, (cudaStream_t)stream>>>(
+        (bf16*)recv, t, C, cap, E, E / P, my_rank, P, scale_by_weight, (int*)ready, (int*)done_counters, epoch, (long long)limit_ns, status);
     LLMK_LAUNCH_CHECK();
     return LLMK_OK;
 }

@@ -115,7 +115,19 @@ class MoETransformer(Transformer):
         self.back_dx = t.view(E * cap, C)
         # arrival tables: E entries per (layer, exchange), exchange 0 = tokens out, 1 = expert outputs back,
         # 2 = output gradients out, 3 = input gradients back; the values are exchange numbers that only grow
-        self.arrive, self.arrive_ptrs = self.exchange.arrival_table(L * 4 * E, dev)
+        # (2 * E entries per exchange: [0, E) block / expert flags, [E, E + P) "source rank is ready" flags of the pull-style dispatch)
+        self.arrive, self.arrive_ptrs = self.exchange.arrival_table(L * 4 * 2 * E, dev)
+        # pull-style dispatch: a peer-readable copy of the token rows and, per layer, the inverse slot maps
+        self.dispatch_mode = os.environ.get("LLMK_MOE_DISPATCH", "pull")
+        t, x_ptrs = self.exchange.alloc(N * C, dev)
+        self.x_sym, self.x_sym_ptrs = t.view(N, C), x_ptrs
+        t, tok_ptrs = self.exchange.alloc(2 * L * E * cap, dev)       # int32 viewed through a bf16 allocation
+        self.inv_tok = t.view(torch.int32).view(L, E * cap)
+        t, w_ptrs = self.exchange.alloc(2 * L * E * cap, dev)
+        self.inv_w = t.view(torch.float32).view(L, E * cap)
+        per_layer = E * cap * 4
+        self.inv_tok_ptrs = [moe_ops.ptr_table([int(q) + l * per_layer for q in tok_ptrs]) for l in range(L)]
+        self.inv_w_ptrs = [moe_ops.ptr_table([int(q) + l * per_layer for q in w_ptrs]) for l in range(L)]
         self.done = torch.zeros(1 + Eloc * P, dtype=i32, device=dev)
         # the second GEMM stores its rows straight into the source ranks' buffers when the row blocks are whole tiles
         self.scatter = (P * cap) % gemm.tile_rows() == 0 and cap >= 32 and H % 64 == 0
@@ -169,10 +181,17 @@ class MoETransformer(Transformer):
         moe_ops.assign_slots(a["top_idx"][l], E, cap, a["slot"][l], a["counts"][l])
         moe_ops.density(a["probs"][l], cfg.aux_loss_coef * self._loss_scale, a["density"][l], a["aux_acc"], accumulate=True)
         ep, lim = self._epoch, self.exchange.limit_ns
-        r_out, r_back = (4 * l + 0) * E, (4 * l + 1) * E
+        r_out, r_back = (4 * l + 0) * 2 * E, (4 * l + 1) * 2 * E
         lib = self.library
         if lib:
             self._library_out(ln2, a["top_idx"][l], a["slot"][l], a["top_w"][l], a["counts"][l], self.recv_x[l], False)
+        elif self.dispatch_mode == "pull":
+            # the owners fetch the rows: this rank only exposes its tokens and the inverse of its slot assignment
+            self.x_sym.copy_(ln2)
+            moe_ops.inverse_map(self.inv_tok[l], self.inv_w[l], a["top_idx"][l], a["slot"][l], a["top_w"][l], E, cap)
+            moe_ops.source_ready(self.arrive_ptrs, r_out, E, self.ep_rank, P, ep)
+            moe_ops.dispatch_pull(self.recv_x[l], self.x_sym_ptrs, self.inv_tok_ptrs[l], self.inv_w_ptrs[l], cfg.channels, E, cap,
+                                  self.ep_rank, P, False, self.arrive[r_out:], self.done[1:], ep, lim)
         else:
             moe_ops.dispatch_signal(self.recv_x_ptrs[l], ln2, a["top_idx"][l], a["slot"][l], a["top_w"][l], a["counts"][l], E, cap,
                                     self.ep_rank, P, False, self.arrive_ptrs, r_out, self.done[0:1], ep)
@@ -214,10 +233,15 @@ class MoETransformer(Transformer):
         idx, slot, w = a["top_idx"][l], a["slot"][l], a["top_w"][l]
         moe_ops.combine_dweight(dres, self.back_y[l], idx, slot, cap, dw=a["dw"])
         ep, lim = self._epoch, self.exchange.limit_ns
-        r_out, r_back = (4 * l + 2) * E, (4 * l + 3) * E
+        r_out, r_back = (4 * l + 2) * 2 * E, (4 * l + 3) * 2 * E
         lib = self.library
         if lib:
             self._library_out(dres, idx, slot, w, a["counts"][l], self.recv_dy, True)
+        elif self.dispatch_mode == "pull":
+            self.x_sym.copy_(dres)
+            moe_ops.source_ready(self.arrive_ptrs, r_out, E, self.ep_rank, P, ep)
+            moe_ops.dispatch_pull(self.recv_dy, self.x_sym_ptrs, self.inv_tok_ptrs[l], self.inv_w_ptrs[l], C, E, cap, self.ep_rank, P,
+                                  True, self.arrive[r_out:], self.done[1:], ep, lim)
         else:
             moe_ops.dispatch_signal(self.recv_dy_ptrs, dres, idx, slot, w, a["counts"][l], E, cap, self.ep_rank, P, True,
                                     self.arrive_ptrs, r_out, self.done[0:1], ep)

@@ -63,6 +63,25 @@ def combine_wait(out, base, back, top_idx, slot, weights, cap, returned, E, epoc
     return out
 
 
+def inverse_map(inv_tok, inv_w, top_idx, slot, top_w, E, cap):
+    """Source side of the pull-style dispatch: ``inv_tok[e*cap + s]`` = token that holds slot ``s`` of expert ``e`` (-1:
+    unused), ``inv_w`` its routing weight; both in peer-readable memory."""
+    Nn, K = top_idx.shape
+    N.call("llmk_moe_inverse_map", inv_tok, inv_w, top_idx, slot, top_w, Nn, K, E, cap)
+
+
+def source_ready(arrive_ptrs, arrive_off, E, rank, P, epoch):
+    """This rank's token rows and maps are in place: entry ``arrive_off + E + rank`` of every rank's table gets ``epoch``."""
+    N.call("llmk_moe_source_ready", arrive_ptrs, arrive_off, E, rank, P, epoch)
+
+
+def dispatch_pull(recv, x_ptrs, tok_ptrs, w_ptrs, C, E, cap, rank, P, scale_by_weight, ready, done, epoch, limit_ns):
+    """Owner side: fill ``recv`` [e_local][source][slot][C] by peer loads from the sources' rows and maps; waits per source
+    for its ``source_ready``, publishes every finished (source, expert) block in ``ready[e_local*P + source]``."""
+    N.call("llmk_moe_dispatch_pull", recv, x_ptrs, tok_ptrs, w_ptrs, C, E, cap, rank, P, int(scale_by_weight), ready, done, epoch,
+           limit_ns, N.status_word())
+
+
 def publish(arrive_ptrs, arrive_off, E, rank, P, epoch):
     """Owner side of the pull-style way back: after everything queued so far (the second expert GEMM), entry
     ``arrive_off + e`` of every rank's arrival table gets ``epoch`` for each expert ``e`` of this rank."""

@@ -95,7 +95,8 @@ def test_expert_parallel_moe_matches_single_process(tmp_path):
     for x, y in global_batches(cfg, 3, 2, 2, 128):
         ref.append(tr.train_step([(x[:2].contiguous(), y[:2].contiguous()), (x[2:].contiguous(), y[2:].contiguous())]).loss)
     for mode, env in (("gpu_moe_library1", {}), ("gpu_moe_fused", {}), ("gpu_moe_a2a1", {}),
-                      ("gpu_moe_fused", {"LLMK_MOE_RETURN": "scatter"}), ("gpu_moe_fused", {"LLMK_MOE_RETURN": "push"})):
+                      ("gpu_moe_fused", {"LLMK_MOE_RETURN": "scatter", "LLMK_MOE_DISPATCH": "push"}),
+                      ("gpu_moe_fused", {"LLMK_MOE_RETURN": "push", "LLMK_MOE_DISPATCH": "push"})):
         r0, r1 = _run(mode, tmp_path, **env)
         assert r0["losses"] == r1["losses"]
         for a, b in zip(r0["losses"], ref):

@@ -210,6 +210,7 @@ def test_moe_model_matches_oracle(E, cf, way_back, monkeypatch):
     back (the combine pulls its rows from the owners; the GEMM's epilogue scatters them; a return kernel pushes them) must
     all match."""
     monkeypatch.setenv("LLMK_MOE_RETURN", way_back)
+    monkeypatch.setenv("LLMK_MOE_DISPATCH", "pull" if way_back == "pull" else "push")   # all-pull, and the two push designs
     from llm_kittens_b200.models.moe import MoETransformer
     from llm_kittens_b200.oracle.torch_model import TorchTransformer
     from llm_kittens_b200.ops import _native
