@@ -91,7 +91,7 @@ def main():
         g = torch.Generator().manual_seed(77)
         full = (torch.randn(B, world * T, W, generator=g) * 0.7).to(torch.bfloat16)
         dfull = (torch.randn(B, world * T, NH * HS, generator=g) * 0.5).to(torch.bfloat16)
-        cp = ContextParallelAttention(B, T, NH, NKVH, HS, device, timeout_ms=20000)
+        cp = ContextParallelAttention(B, T, NH, NKVH, HS, device, timeout_ms=60000)
         out = dqkv = None
         for _ in range(2):     # twice: the buffers are reused, and the results must be bit-identical
             prev = (out, dqkv)
@@ -118,7 +118,7 @@ def main():
         from llm_kittens_b200.parallel.expert import LibraryExchange, PeerExchange
 
         # gpu_moe_a2a1: the baseline exchange through all_to_all_single
-        exchange = LibraryExchange(device) if "a2a" in mode else PeerExchange(device, timeout_ms=20000)
+        exchange = LibraryExchange(device) if "a2a" in mode else PeerExchange(device, timeout_ms=60000)
         model = MoETransformer(cfg, device=device, recompute=0, exchange=exchange)
     elif cpu:
         from llm_kittens_b200.oracle.torch_model import TorchTransformer
@@ -133,11 +133,11 @@ def main():
     if mode in ("gpu_fused", "gpu_fused0", "gpu_moe_fused"):
         from llm_kittens_b200.parallel.fused import FusedComm
 
-        comm = FusedComm(plan, model, device, timeout_ms=20000)
+        comm = FusedComm(plan, model, device, timeout_ms=60000)
     elif mode.startswith("gpu_sharded"):
         from llm_kittens_b200.parallel.sharded import ShardedComm
 
-        comm = ShardedComm(plan, model, device, timeout_ms=20000)
+        comm = ShardedComm(plan, model, device, timeout_ms=60000)
     else:
         comm = LibraryComm(plan, None, device)
     trainer = Trainer(model, zero_stage=stage, use_master_weights=True, learning_rate=1e-3, weight_decay=0.1, comm=comm,

@@ -20,7 +20,7 @@ def free_port():
     return p
 
 
-def launch(mode, out_dir, world=2, extra_env=None, timeout=300):
+def launch(mode, out_dir, world=2, extra_env=None, timeout=420):
     port = free_port()
     procs = []
     for r in range(world):
