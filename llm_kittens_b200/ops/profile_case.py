@@ -5,7 +5,8 @@
 cases: gemm_nt, gemm_nt_gelu, gemm_nn, gemm_tn, attn_fwd, attn_bwd, layernorm_fwd, layernorm_bwd,
 classifier, adamw, comm_rs, comm_adamw_push, comm_ag_flags (the peer-memory kernels with all ranks emulated on one GPU),
 gemm_b_ready (the GEMM that polls the flags of a gathered weight, flags already set), gemm_qkv_rope (QKV projection with
-RoPE in the epilogue), moe_dispatch / moe_grouped_a_ready (the expert exchange with its arrival table, ranks emulated).
+RoPE in the epilogue), moe_dispatch / moe_grouped_a_ready / moe_dispatch_pull / moe_combine_pull (the expert exchange with
+its arrival table, ranks emulated).
 Each case allocates inputs larger than the L2 (but well under a few GB), runs
 the op twice as warm-up and then `launches` (default 2) more times, and checks the status word.
 Used as ``ncu --set full --clock-control none -k regex:<kernel> -s <warm-up launches> -c 1 ...``.
@@ -144,6 +145,28 @@ def build(case: str):
         out = torch.empty(B * T, (NH + 2 * NKVH) * HS, device="cuda", dtype=BF)
         table = ew.rope_tables(T, HS, 500000.0, False)
         return lambda: gemm.gemm_qkv_rope(x, w, table, T, (NH + NKVH) * HS, HS, out=out)
+    if case in ("moe_dispatch_pull", "moe_combine_pull"):
+        # the pull-style expert exchange at the d24 shape with this GPU as every rank: the owner-side dispatch that fetches
+        # routed rows through the inverse slot map, and the combine that fetches expert outputs; flags pre-set
+        from . import moe as moe_ops
+
+        Ntok, Cc, E, K = 16384, 1024, 8, 2
+        cap = (int(-(-1.25 * K * Ntok // E)) + 7) // 8 * 8
+        x, wr = _rnd(Ntok, Cc), _rnd(E, Cc, scale=0.5)
+        probs, idx, tw = moe_ops.router_fwd(x, wr, K)
+        slot, counts = moe_ops.assign_slots(idx, E, cap)
+        inv_tok = torch.empty(E * cap, dtype=torch.int32, device="cuda")
+        inv_w = torch.empty(E * cap, dtype=torch.float32, device="cuda")
+        moe_ops.inverse_map(inv_tok, inv_w, idx, slot, tw, E, cap)
+        recv = torch.zeros(E * cap, Cc, dtype=BF, device="cuda")
+        ready = torch.full((2 * E,), 1 << 20, dtype=torch.int32, device="cuda")
+        done = torch.zeros(E, dtype=torch.int32, device="cuda")
+        out = torch.empty(Ntok, Cc, dtype=BF, device="cuda")
+        save = torch.empty(E * cap, Cc, dtype=BF, device="cuda")
+        tab = lambda t: moe_ops.ptr_table([t])
+        if case == "moe_dispatch_pull":
+            return lambda: moe_ops.dispatch_pull(recv, tab(x), tab(inv_tok), tab(inv_w), Cc, E, cap, 0, 1, False, ready, done, 1, int(1e9))
+        return lambda: moe_ops.combine_pull(out, x, tab(recv), save, idx, slot, tw, E, cap, 0, 1, ready, 1, int(1e9))
     if case in ("moe_dispatch", "moe_grouped_a_ready"):
         # one MoE layer's exchange at the d24 shape (C=1024, H=4096, 8 experts, top-2, 16384 tokens): this GPU plays all
         # ranks (a one-entry peer table), so dispatch, arrival table and the waiting GEMM are exercised without a peer
