@@ -51,7 +51,9 @@ constexpr int GROUP_M = 8;
 constexpr int TMEM_COLS = 512;
 
 enum { MODE_NT = 0, MODE_NN = 1, MODE_TN = 2 };
-enum { EPI_BIAS = 1, EPI_GELU = 2, EPI_DGELU = 4, EPI_ADD = 8, EPI_PARTIAL = 16, EPI_ROPE = 32, EPI_SCATTER = 64, EPI_SWIGLU = 128 };
+enum { EPI_BIAS = 1, EPI_GELU = 2, EPI_DGELU = 4, EPI_ADD = 8, EPI_PARTIAL = 16, EPI_ROPE = 32, EPI_SCATTER = 64, EPI_SWIGLU = 128,
+       EPI_DBIAS = 256 };
+constexpr int DB_WARPS = 4;   // EPI_DBIAS: column-sum warps per CTA, one per 32 columns of the A stage
 
 template <int EPI, bool PAIR>
 struct Cfg {
@@ -69,7 +71,12 @@ struct Cfg {
     // lm-head 3.85 -> 4.02 ms with 16 warps and 5 stages).
     static constexpr bool WIDE = PAIR && EPI == EPI_DGELU;
     static constexpr int EPI_WARPS = WIDE ? 16 : NUM_EPI_WARPS;
-    static constexpr int NTHREADS = 32 * (2 + EPI_WARPS);
+    // Bias gradient inside the weight-gradient GEMM (mode TN, A = dout [tokens, OC]): four more warps per CTA read every
+    // A stage of the tiles in the first tile column out of shared memory, beside the tensor core, and sum it over the
+    // tokens; the bias gradient costs no pass over dout of its own. (Two warps, one per 64-column box, could not keep
+    // up with the tensor core: the tiles they summed ran at half speed.)
+    static constexpr bool DB = (EPI & EPI_DBIAS) != 0;
+    static constexpr int NTHREADS = 32 * (2 + EPI_WARPS + (DB ? DB_WARPS : 0));
     static constexpr int NBUF = SWI ? 3 : ((DUAL && !WIDE) ? 2 : 1);   // staging buffers per epilogue warp
     static constexpr int SMEM_MAIN = STAGES * Geo<PAIR>::STAGE_BYTES + EPI_WARPS * NBUF * STAGING_BYTES;
     static constexpr int SMEM_BYTES = SMEM_MAIN + 1024 /*alignment slack*/ + 512 /*barriers*/;
@@ -114,6 +121,11 @@ struct Params {
     // different peers instead of all hitting the same GPU's NVLink port.
     int m_rotate;
     const bf16* bias;  // [N]
+    // EPI_DBIAS (mode TN): dbias[m] (+)= sum over the K rows of A[k][m]. One split: written as bf16 by the kernel
+    // (added to the old value with EPI_ADD). Split K: every split writes its fp32 sums to db_partial[split][M] and the
+    // split-K reduction kernel finishes them.
+    bf16* dbias;
+    float* db_partial;
     const bf16* aux;   // [M,N] pre-GELU input (DGELU) or addend (ADD; may alias C)
     float* partial;    // [splits, M, N] fp32 (PARTIAL)
     int* status;
@@ -240,7 +252,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
     uint64_t* acc_full = bars + 2 * MAX_STAGES;        // [2]
     uint64_t* acc_empty = bars + 2 * MAX_STAGES + 2;   // [2]
     uint64_t* aux_bar = bars + 2 * MAX_STAGES + 4;     // [MAX_EPI_WARPS]
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(aux_bar + MAX_EPI_WARPS);
+    uint32_t* relay = reinterpret_cast<uint32_t*>(aux_bar + MAX_EPI_WARPS);   // [MAX_STAGES + 2] EPI_DBIAS, pair: see below
+    uint32_t* tmem_slot = relay + MAX_STAGES + 2;
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -256,7 +269,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
         skip_word = (p.status != nullptr && *reinterpret_cast<volatile int*>(p.status) != 0) ? 1 : 0;
         for (int i = 0; i < STAGES; i++) {
             ptx::mbar_init(&full_bar[i], 1);
-            ptx::mbar_init(&empty_bar[i], 1);
+            // a stage is free again when the MMAs that read it have finished and, with EPI_DBIAS, when this CTA's
+            // column-sum warps have read it too
+            ptx::mbar_init(&empty_bar[i], Cfg<EPI, PAIR>::DB ? 1 + DB_WARPS : 1);
+            relay[i] = 0;
         }
         for (int i = 0; i < 2; i++) {
             ptx::mbar_init(&acc_full[i], 1);
@@ -433,6 +449,108 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
                 else ptx::mma_commit(&acc_full[a]);
             }
             __syncwarp();
+        }
+    } else if (warp >= 2 + EPI_WARPS) {
+        // ------------------------------------------------------------ column sums of A (EPI_DBIAS, mode TN)
+        // An A stage is BM / 64 boxes of 64 (k) rows x 64 (m) columns, 128 bytes per row, 16-byte pieces swizzled by
+        // the row number. A warp takes 32 columns (four pieces) of one box: lane (c, r) adds piece c of rows r, r + 8, ...
+        // where a quarter warp reads its four pieces of rows q and q + 4, whose swizzles put them into different halves
+        // of the 128-byte bank window (no bank conflicts). Only the tiles of the first tile column are summed (every
+        // (row tile, split) is there exactly once); for the others the warps just keep step with the ring.
+        // The stage's bytes are credited to the LEADER's barrier, which the peer CTA cannot wait on: a lane of the
+        // leader's first warp passes each completion on by storing the stage's use count into relay[stage] of the peer,
+        // which the peer's warps poll. (A remote mbarrier arrive with release semantics instead of the plain store held
+        // the leader's warp for about a microsecond per stage: 0.21 -> 0.45 ms at 3072 x 768 x 65536.) The copy into the
+        // peer's shared memory is complete before its bytes are credited to the leader's barrier, so it is in place
+        // when the count arrives.
+        if constexpr (Cfg<EPI, PAIR>::DB) {
+            const int dw = warp - (2 + EPI_WARPS);          // 0..3
+            const int box = dw >> 1;
+            const int c = (dw & 1) * 4 + (lane & 3);        // 16-byte piece of the box's 128-byte rows
+            const int kr = ((lane >> 3) & 3) + 4 * ((lane >> 2) & 1);   // first row: q or q + 4 for quarter warp q
+            int s = 0;
+            uint32_t ph = 0, pass = 1;                      // pass = use count of the stages in this turn of the ring
+            bool ok = true;
+            for (int u = unit0; u < total_units && ok; u += unit_step) {
+                const Work w = decode_unit(p, u);
+                const bool mine = w.n0 == 0;
+                ptx::f32x2 acc[4];
+#pragma unroll
+                for (int j = 0; j < 4; j++) acc[j] = ptx::pack2(0.f, 0.f);
+                for (int kb = w.kb_begin; kb < w.kb_end; kb++) {
+                    if (PAIR && rank == 1) {
+                        // bounded poll of the leader's count for this stage
+                        uint32_t spins = 0;
+                        uint64_t t0 = 0;
+                        while (ptx::ld_shared_acquire_cluster_u32(&relay[s]) != pass) {
+                            if ((++spins & 0xfffu) == 0) {
+                                if (t0 == 0) t0 = ptx::globaltimer_ns();
+                                if (*abort_flag) { ok = false; break; }
+                                if (ptx::globaltimer_ns() - t0 > LLMK_WAIT_LIMIT_NS) {
+                                    *abort_flag = 1;
+                                    if (p.status != nullptr && atomicCAS(p.status, 0, LLMK_ST_TIMEOUT_TMA_FULL) == 0) {
+                                        p.status[1] = -3;
+                                        p.status[2] = (int)blockIdx.x;
+                                        p.status[3] = (int)threadIdx.x;
+                                    }
+                                    ok = false;
+                                    break;
+                                }
+                            }
+                        }
+                        ok = __all_sync(0xffffffffu, ok);
+                        ptx::fence_proxy_async_smem();   // the tile was written through the async proxy
+                    } else {
+                        ok = ptx::mbar_wait(&full_bar[s], ph, abort_flag, p.status, LLMK_ST_TIMEOUT_TMA_FULL, -3);
+                    }
+                    if (!ok) break;
+                    if (PAIR && rank == 0 && dw == 0 && lane == 0) ptx::st_shared_cluster_u32(&relay[s], 1, pass);
+                    if (mine) {
+                        const uint8_t* sBox = smem + s * STAGE_BYTES + box * CHUNK_BYTES;
+#pragma unroll
+                        for (int i = 0; i < BK / 8; i++) {
+                            const int k = kr + 8 * i;
+                            const uint4 v = *reinterpret_cast<const uint4*>(sBox + k * 128 + ((c ^ (k & 7)) << 4));
+                            const uint32_t wd[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+                            for (int j = 0; j < 4; j++)   // a bf16 pair -> two fp32 values (low half first)
+                                acc[j] = ptx::add2(acc[j], ptx::pack2(__uint_as_float(wd[j] << 16), __uint_as_float(wd[j] & 0xffff0000u)));
+                        }
+                    }
+                    __syncwarp();
+                    if (lane == 0) ptx::mbar_arrive(&empty_bar[s]);
+                    if (++s == STAGES) { s = 0; ph ^= 1; pass++; }
+                }
+                if (!ok) break;
+                if (mine) {
+                    // the eight lanes with the same c hold the same 8 columns: fixed-order tree, result in lanes 0..3
+                    float f[8];
+#pragma unroll
+                    for (int j = 0; j < 4; j++) ptx::unpack2(acc[j], f[2 * j], f[2 * j + 1]);
+#pragma unroll
+                    for (int j = 0; j < 8; j++) {
+                        f[j] += __shfl_xor_sync(0xffffffffu, f[j], 4);
+                        f[j] += __shfl_xor_sync(0xffffffffu, f[j], 8);
+                        f[j] += __shfl_xor_sync(0xffffffffu, f[j], 16);
+                    }
+                    const int col = w.m0 + rank * BM + box * 64 + c * 8;
+                    if (lane < 4 && col < p.M) {
+                        if (EPI & EPI_PARTIAL) {
+                            float4* dst = reinterpret_cast<float4*>(p.db_partial + (size_t)w.split * p.M + col);
+                            dst[0] = make_float4(f[0], f[1], f[2], f[3]);
+                            dst[1] = make_float4(f[4], f[5], f[6], f[7]);
+                        } else {
+                            if (EPI & EPI_ADD) {
+                                float old[8];
+                                unpack8(ld128(p.dbias + col), old);
+#pragma unroll
+                                for (int j = 0; j < 8; j++) f[j] += old[j];
+                            }
+                            st128(p.dbias + col, pack8(f));
+                        }
+                    }
+                }
+            }
         }
     } else if (warp >= 2) {
         // ------------------------------------------------------------ epilogue warps
@@ -738,10 +856,27 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
 }
 
 // fp32 split-K partials -> bf16 output (optionally += existing contents).
+// With `dbias`: the first M / 8 threads also finish the bias gradient from db_partial [splits, M] (EPI_DBIAS).
 __global__ void splitk_reduce_kernel(bf16* __restrict__ out, const float* __restrict__ partial, size_t n, int splits,
-                                     int accumulate) {
+                                     int accumulate, bf16* __restrict__ dbias, const float* __restrict__ db_partial, int M) {
     size_t i = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) * 8;
     if (i >= n) return;
+    if (dbias != nullptr && i < (size_t)M) {
+        float d[8];
+        if (accumulate) {
+            unpack8(ld128(dbias + i), d);
+        } else {
+#pragma unroll
+            for (int j = 0; j < 8; j++) d[j] = 0.f;
+        }
+        for (int s = 0; s < splits; s++) {
+            const float4* src = reinterpret_cast<const float4*>(db_partial + (size_t)s * M + i);
+            const float4 a = src[0], b = src[1];
+            d[0] += a.x; d[1] += a.y; d[2] += a.z; d[3] += a.w;
+            d[4] += b.x; d[5] += b.y; d[6] += b.z; d[7] += b.w;
+        }
+        st128(dbias + i, pack8(d));
+    }
     float acc[8];
     if (accumulate) {
         unpack8(ld128(out + i), acc);
@@ -824,7 +959,7 @@ static int launch(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensor
         LLMK_CUDA_TRY(cudaLaunchKernelEx(&cfg, gemm_kernel<MODE, EPI, true>, tmA, tmB, tmC, tmX, xm, p));
         return LLMK_OK;
     }
-    if (EPI & EPI_SWIGLU) return LLMK_ERR_SHAPE;   // the SwiGLU epilogue needs the pair kernel's accumulator layout
+    if (EPI & (EPI_SWIGLU | EPI_DBIAS)) return LLMK_ERR_SHAPE;   // these epilogues exist for the pair kernel only
     constexpr int SMEM_BYTES = Cfg<EPI, false>::SMEM_BYTES;
     static PerDeviceOnce once_configured;
     if (once_configured.first()) {
@@ -909,7 +1044,7 @@ long llmk_gemm_workspace_bytes(int mode, int M, int N, int K, int num_sms) {
     int s = pick_splits(mode, M, N, K, num_sms > 0 ? num_sms : 148);
     const int s2 = pick_splits(mode, M, N, K, (num_sms > 0 ? num_sms : 148) / 2, 2 * BM);
     if (s2 > s) s = s2;
-    return s > 1 ? (long)s * M * N * 4 : 0;
+    return s > 1 ? (long)s * M * N * 4 + (long)s * M * 4 /* bias-gradient partials */ : 0;
 }
 
 // C = op(A) op(B) with the epilogue selected by `epi` (bit-or of: 1 bias, 2 GELU with pre-activation
@@ -932,6 +1067,7 @@ struct Ready {
     const long long* sc_arrive = nullptr;
     int* sc_count = nullptr;
     int sc_cap = 0, sc_P = 0, sc_Eloc = 0, sc_rank = 0, sc_off = 0, sc_epoch = 0;
+    void* dbias = nullptr;                  // EPI_DBIAS: [M] bf16
 };
 
 static int gemm_impl(int mode, int epi, const void* A, const void* B, void* C, void* C2, const void* bias, const void* aux,
@@ -975,6 +1111,13 @@ static int gemm_impl(int mode, int epi, const void* A, const void* B, void* C, v
     if ((p.b_ready != nullptr || p.a_ready != nullptr) && mode == MODE_TN) return LLMK_ERR_SHAPE;
     p.rope = ready.rope; p.rope_T = ready.rope_T; p.rope_cols = ready.rope_cols; p.rope_hs = ready.rope_hs;
     p.b_ready2 = ready.b_ready2;
+    p.dbias = static_cast<bf16*>(ready.dbias);
+    p.db_partial = nullptr;
+    if (epi & EPI_DBIAS) {
+        if (mode != MODE_TN || groups != 1 || !p.pair || ready.dbias == nullptr || (epi & ~(EPI_DBIAS | EPI_ADD)) ||
+            (reinterpret_cast<uintptr_t>(ready.dbias) & 15))
+            return LLMK_ERR_SHAPE;
+    }
     if (epi & EPI_SWIGLU) {
         // N is the width of the accumulator tile space: 2 H columns (up | gate per 128 hidden units); outputs are [M, H]
         if (mode != MODE_NT || groups != 1 || !p.pair || ready.b2 == nullptr || ready.c3 == nullptr || C2 == nullptr || (N % 256) ||
@@ -1000,16 +1143,18 @@ static int gemm_impl(int mode, int epi, const void* A, const void* B, void* C, v
             return LLMK_ERR_SHAPE;
     }
     bool split_accumulate = false;
-    if (mode == MODE_TN && (epi == 0 || epi == EPI_ADD)) {
+    const int with_dbias = epi & EPI_DBIAS;
+    if (mode == MODE_TN && ((epi & ~EPI_DBIAS) == 0 || (epi & ~EPI_DBIAS) == EPI_ADD)) {
         const int workers = p.pair ? pair_clusters : g_num_sms;
         const int cap = max_ctas > 0 ? (p.pair ? (max_ctas / 2 > 0 ? max_ctas / 2 : 1) : max_ctas) : workers;
         int s = pick_splits(mode, M, N, K, cap < workers ? cap : workers, p.pair ? 2 * BM : BM);
         if (s > 1) {
-            if (workspace == nullptr || workspace_bytes < (long)s * M * N * 4) return LLMK_ERR_WORKSPACE;
+            if (workspace == nullptr || workspace_bytes < (long)s * M * N * 4 + (with_dbias ? (long)s * M * 4 : 0)) return LLMK_ERR_WORKSPACE;
             p.splits = s;
             p.partial = static_cast<float*>(workspace);
-            split_accumulate = (epi == EPI_ADD);
-            epi = EPI_PARTIAL;
+            p.db_partial = p.partial + (size_t)s * M * N;   // behind the partials of C (s = the largest split count in use)
+            split_accumulate = (epi & EPI_ADD) != 0;
+            epi = EPI_PARTIAL | with_dbias;
         }
     }
     if (ready.rotate_rows > 0) p.m_rotate = (ready.rotate_rows / (p.pair ? 2 * BM : BM)) % p.tiles_m;
@@ -1066,13 +1211,17 @@ static int gemm_impl(int mode, int epi, const void* A, const void* B, void* C, v
     LLMK_GEMM_CASE(MODE_TN, 0)
     LLMK_GEMM_CASE(MODE_TN, EPI_ADD)
     LLMK_GEMM_CASE(MODE_TN, EPI_PARTIAL)
+    LLMK_GEMM_CASE(MODE_TN, EPI_DBIAS)
+    LLMK_GEMM_CASE(MODE_TN, EPI_ADD | EPI_DBIAS)
+    LLMK_GEMM_CASE(MODE_TN, EPI_PARTIAL | EPI_DBIAS)
     { rc = LLMK_ERR_SHAPE; }
 #undef LLMK_GEMM_CASE
     if (rc) return rc;
-    if (epi == EPI_PARTIAL) {
+    if (epi & EPI_PARTIAL) {
         const size_t n = (size_t)M * N;
         splitk_reduce_kernel<<<ceil_div((long)(n / 8), 256), 256, 0, stream>>>(static_cast<bf16*>(C), p.partial, n, p.splits,
-                                                                            split_accumulate ? 1 : 0);
+                                                                            split_accumulate ? 1 : 0, with_dbias ? p.dbias : nullptr,
+                                                                            p.db_partial, M);
         LLMK_LAUNCH_CHECK();
     }
     return LLMK_OK;
@@ -1082,6 +1231,20 @@ LLMK_API int llmk_gemm(int mode, int epi, const void* A, const void* B, void* C,
                        const void* aux, int M, int N, int K, void* workspace, long workspace_bytes, int* status,
                        int max_ctas, void* stream_) {
     return gemm_impl(mode, epi, A, B, C, C2, bias, aux, M, N, K, 1, workspace, workspace_bytes, status, max_ctas, stream_);
+}
+
+// Weight gradient and bias gradient of a linear layer in one launch: C[M, N] (+)= A^T B and dbias[M] (+)= the column
+// sums of A, where A = dout [K tokens, M output channels] and B = the layer's input [K, N]; `accumulate` adds to the
+// old contents of both. The sums are taken from the A tiles in shared memory while the tensor core works on them
+// (see Cfg::DB), in a fixed order. CTA-pair kernel only: LLMK_ERR_SHAPE otherwise (the caller then runs llmk_gemm and
+// the stand-alone column-sum kernel). Same job as matmul_backward's dbias kernel plus its dweight GEMM
+// (llmc/matmul.cuh:465-539, 1238-1338) without the extra pass over dout.
+LLMK_API int llmk_gemm_tn_dbias(const void* A, const void* B, void* C, void* dbias, int accumulate, int M, int N, int K, void* workspace,
+                                long workspace_bytes, int* status, int max_ctas, void* stream_) {
+    Ready r;
+    r.dbias = dbias;
+    return gemm_impl(MODE_TN, EPI_DBIAS | (accumulate ? EPI_ADD : 0), A, B, C, nullptr, nullptr, accumulate ? C : nullptr, M, N, K, 1,
+                     workspace, workspace_bytes, status, max_ctas, stream_, r);
 }
 
 // llmk_gemm whose B operand (a weight matrix, NT or NN) is still being filled by another kernel: `b_ready` holds one

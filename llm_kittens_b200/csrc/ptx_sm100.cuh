@@ -328,6 +328,23 @@ __device__ __forceinline__ void mbar_arrive_cluster(uint64_t* bar, uint32_t cta)
         : "memory");
 }
 
+// Plain (relaxed) 32-bit store into the word at this shared-memory offset in CTA `cta` of the cluster: fire and
+// forget, unlike a remote mbarrier arrive with release semantics, which held its issuer for about a microsecond.
+__device__ __forceinline__ void st_shared_cluster_u32(const void* local_ptr, uint32_t cta, uint32_t v) {
+    asm volatile(
+        "{\n\t.reg .b32 remAddr32;\n\t"
+        "mapa.shared::cluster.u32 remAddr32, %0, %1;\n\t"
+        "st.relaxed.cluster.shared::cluster.u32 [remAddr32], %2;\n\t}" ::"r"(smem_u32(local_ptr)),
+        "r"(cta), "r"(v)
+        : "memory");
+}
+// Acquire load (cluster scope) of a word of this CTA's shared memory that a thread of another CTA stores to.
+__device__ __forceinline__ uint32_t ld_shared_acquire_cluster_u32(const void* local_ptr) {
+    uint32_t v;
+    asm volatile("ld.acquire.cluster.shared::cta.u32 %0, [%1];" : "=r"(v) : "r"(smem_u32(local_ptr)) : "memory");
+    return v;
+}
+
 // ------------------------------------------------------------------ descriptors
 // Shared-memory matrix descriptor for a 128-byte-swizzled operand tile (bf16).
 //   K-major tile  : rows of 64 elements (128 B) stacked every 128 B, 8-row groups every 1024 B

@@ -200,6 +200,17 @@ class Transformer:
             torch.cuda.current_stream().wait_stream(self.side)
             self._side_busy = False
 
+    def _dweight(self, dout: torch.Tensor, inp: torch.Tensor, gw: torch.Tensor, gb: torch.Tensor | None) -> None:
+        """``gw += dout^T inp`` and, for a layer with a bias, ``gb += column sums of dout``: one launch when the
+        weight-gradient GEMM can sum its A tiles on the way, else the column sums run on the side stream."""
+        if gb is None:
+            gemm.gemm_tn(dout, inp, out=gw, accumulate=True)
+        elif gemm.fused_dbias_available():
+            gemm.gemm_tn(dout, inp, out=gw, accumulate=True, dbias=gb)
+        else:
+            self._fork(lambda: ew.dbias(gb, dout, accumulate=True))
+            gemm.gemm_tn(dout, inp, out=gw, accumulate=True)
+
     def _fused_rope(self) -> bool:
         """Llama with interleaved pairs on the tcgen05 attention path: RoPE lives in the QKV projection's epilogue and
         its backward in the output tiles of the attention backward kernels; no separate pass over QKV or dQKV. The
@@ -283,12 +294,10 @@ class Transformer:
             if 1 <= self.recompute < 3:
                 ew.gelu_fwd(a["fch"][k], out=act)
             d_fch = a["d_wide"].view(-1)[: BT * H].view(BT, H)
-            self._fork(lambda: ew.dbias(g["fcprojb"][l], dres, accumulate=True))
-            gemm.gemm_tn(dres, act, out=g["fcprojw"][l], accumulate=True)
+            self._dweight(dres, act, g["fcprojw"][l], g["fcprojb"][l])
             gemm.gemm_nn(dres, p["fcprojw"][l], out=d_fch, dgelu_of=a["fch"][k])
-            self._fork(lambda: ew.dbias(g["fcb"][l], d_fch, accumulate=True))
             gemm.gemm_nn(d_fch, p["fcw"][l], out=d_ln2)
-            gemm.gemm_tn(d_fch, ln2, out=g["fcw"][l], accumulate=True)
+            self._dweight(d_fch, ln2, g["fcw"][l], g["fcb"][l])
 
     # ------------------------------------------------------------------ forward
     def forward(self, tokens: torch.Tensor, targets: torch.Tensor | None = None, grad_accum_steps: int = 1,
@@ -375,11 +384,9 @@ class Transformer:
 
             def attention_side_work():
                 prep[0] = attn_ops.attention_bwd_prep(d_btc, a["atty"][k], a["dvec"], B, T, cfg.num_heads, cfg.head_size)
-                if not self.is_llama:
-                    ew.dbias(g["attprojb"][l], dres, accumulate=True)
 
             self._fork(attention_side_work)
-            gemm.gemm_tn(dres, a["atty"][k], out=g["attprojw"][l], accumulate=True)
+            self._dweight(dres, a["atty"][k], g["attprojw"][l], None if self.is_llama else g["attprojb"][l])
             self._join()   # D is needed now, and the next kernel overwrites the buffer that the MLP's column sum read
             dqkv = a["d_wide"].view(-1)[: BT * QW].view(BT, QW)
             fused_rope = self._fused_rope()
@@ -391,10 +398,8 @@ class Transformer:
                             inverse=True)
             if self.recompute == 2:
                 self._norm_fwd(x_in, p["ln1w"][l], None if self.is_llama else p["ln1b"][l], ln1, mean1, a["ln1_rstd"][k])
-            if not self.is_llama:
-                self._fork(lambda: ew.dbias(g["qkvb"][l], dqkv, accumulate=True))
             gemm.gemm_nn(dqkv, p["qkvw"][l], out=d_btc)
-            gemm.gemm_tn(dqkv, ln1, out=g["qkvw"][l], accumulate=True)
+            self._dweight(dqkv, ln1, g["qkvw"][l], None if self.is_llama else g["qkvb"][l])
             self._join()   # bias gradients of this block are complete before its bucket is handed over
             self._norm_bwd(dres, g["ln1w"][l], None if self.is_llama else g["ln1b"][l], d_btc, x_in, p["ln1w"][l], mean1,
                            a["ln1_rstd"][k], accumulate=True)

@@ -134,6 +134,8 @@ def _ledger_label(name: str, args) -> str:
         mode, epi = args[0], args[1]
         M, Nn, K = args[8], args[9], args[10]
         return f"{name[5:]} {('NT', 'NN', 'TN')[mode]} epi={epi} {M}x{Nn}x{K}"
+    if name == "llmk_gemm_tn_dbias":
+        return f"gemm TN +dbias {args[5]}x{args[6]}x{args[7]}"
     return name[5:]
 
 

@@ -9,6 +9,8 @@ They replace matmul_forward / matmul_forward_gelu / matmul_backward of the refer
 """
 from __future__ import annotations
 
+import os
+
 import torch
 
 from . import _native as N
@@ -215,9 +217,17 @@ def gemm_nn(a, b, out=None, dgelu_of=None, add=None, groups=1, a_ready=None):
     return _gemm(MODE_NN, epi, a, b, out, None, None, aux, M, Nn, K, groups, a_ready=a_ready)
 
 
-def gemm_tn(a, b, out=None, accumulate=False, groups=1):
+def fused_dbias_available() -> bool:
+    """The weight-gradient GEMM can also produce the bias gradient (CTA-pair kernel; ``LLMK_FUSED_DBIAS=0`` turns it off)."""
+    return tile_rows() == 256 and hasattr(N.lib(), "llmk_gemm_tn_dbias") and os.environ.get("LLMK_FUSED_DBIAS", "1") != "0"
+
+
+def gemm_tn(a, b, out=None, accumulate=False, groups=1, dbias=None):
     """``out (+)= a.T @ b`` with ``a``: [K,M], ``b``: [K,N] (K = token dimension).
-    ``groups`` > 1: ``a`` [G*K,M], ``b`` [G*K,N], ``out`` [G,M,N] or [G*M,N]: group g uses rows [g*K,(g+1)*K)."""
+    ``groups`` > 1: ``a`` [G*K,M], ``b`` [G*K,N], ``out`` [G,M,N] or [G*M,N]: group g uses rows [g*K,(g+1)*K).
+
+    ``dbias`` [M]: also ``dbias (+)= a.sum(0)`` (the bias gradient of the linear layer whose output gradient is ``a``),
+    from the same launch when the fused kernel takes the call, else from the stand-alone column-sum kernel."""
     M = a.shape[1]
     K = a.shape[0] // groups
     Nn = b.shape[1]
@@ -226,5 +236,20 @@ def gemm_tn(a, b, out=None, accumulate=False, groups=1):
         assert not accumulate
         out = torch.empty(M * groups, Nn, dtype=torch.bfloat16, device=a.device)
     out2 = _flat2(out, groups)
+    if dbias is not None and groups == 1 and fused_dbias_available() and dbias.data_ptr() % 16 == 0 and dbias.is_contiguous():
+        for t, nm in ((a, "A"), (b, "B"), (out2, "C"), (dbias, "dbias")):
+            N.require_cuda_tensor(t, torch.bfloat16, nm)
+        ws_bytes = int(N.lib().llmk_gemm_workspace_bytes(MODE_TN, M, Nn, K, 0))
+        ws = workspace(ws_bytes) if ws_bytes else None
+        N.call("llmk_gemm_tn_dbias", a, b, out2, dbias, int(accumulate), M, Nn, K, ws, ws.numel() if ws is not None else 0,
+               N.status_word(), _MAX_CTAS)
+        return out
     _gemm(MODE_TN, EPI_ADD if accumulate else 0, a, b, out2, None, None, out2 if accumulate else None, M, Nn, K, groups)
+    if dbias is not None:
+        from . import elementwise as ew
+
+        if groups == 1:
+            ew.dbias(dbias, a, accumulate=accumulate)
+        else:
+            ew.dbias_grouped(dbias, a, groups, accumulate=accumulate)
     return out

@@ -82,6 +82,42 @@ def test_gemm_tn(M, N, K):
     _native.check_status()
 
 
+@pytest.mark.parametrize("M,N,K", [(768, 768, 4096), (3072, 768, 8192), (3072, 3072, 2048), (200, 136, 1000), (2304, 768, 640)])
+def test_gemm_tn_with_bias_gradient_from_the_same_launch(M, N, K):
+    """dW and dbias of a linear layer from one kernel: the column sums of dout are taken from the A tiles in shared
+    memory. The shapes cover split K (partials finished by the reduction kernel), one split with two tiles per CTA
+    pair (sums written by the GEMM kernel itself), a ragged tile and a K that is no multiple of the k-block."""
+    from llm_kittens_b200.ops import gemm, _native
+
+    if not gemm.fused_dbias_available():
+        pytest.skip("needs the CTA-pair GEMM kernel")
+    launches = _native.launch_count()
+    a, b = _rand(K, M, scale=0.1), _rand(K, N, scale=0.1)
+    ref, ref_db = a.float().T @ b.float(), a.float().sum(0)
+
+    def close_db(got, want):                          # one bf16 rounding of a sum of K values: relative
+        err = (got.float() - want).abs()
+        bad = err > 0.005 * want.abs() + 0.02
+        assert not bad.any(), f"{int(bad.sum())} columns off, worst {err.max().item()}"
+
+    db = torch.full((M,), 7.0, device="cuda", dtype=torch.bfloat16)
+    out = gemm.gemm_tn(a, b, dbias=db)
+    assert _native.launch_count() == launches + 1     # no stand-alone column-sum kernel ran
+    _close(out, ref, 0.1)
+    close_db(db, ref_db)
+    acc, db2 = _rand(M, N), _rand(M)
+    acc0, db0 = acc.clone(), db2.clone()
+    gemm.gemm_tn(a, b, out=acc, accumulate=True, dbias=db2)
+    _close(acc, ref + acc0.float(), 0.15)
+    close_db(db2, ref_db + db0.float())
+    # run-to-run bit equality (fixed summation order), and the same bits as the GEMM without the column sums
+    db3 = torch.empty_like(db)
+    out3 = gemm.gemm_tn(a, b, dbias=db3)
+    assert torch.equal(db3, db) and torch.equal(out3, out)
+    assert torch.equal(gemm.gemm_tn(a, b), out)
+    _native.check_status()
+
+
 def test_gemm_deterministic():
     from llm_kittens_b200.ops import gemm
 
