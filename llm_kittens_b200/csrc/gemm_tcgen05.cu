@@ -122,8 +122,8 @@ struct Params {
     int m_rotate;
     const bf16* bias;  // [N]
     // EPI_DBIAS (mode TN): dbias[m] (+)= sum over the K rows of A[k][m]. One split: written as bf16 by the kernel
-    // (added to the old value with EPI_ADD). Split K: every split writes its fp32 sums to db_partial[split][M] and the
-    // split-K reduction kernel finishes them.
+    // (added to the old value with EPI_ADD). Split K: every work unit writes its fp32 sums to
+    // db_partial[split * tiles_n + tile column][M] and the split-K reduction kernel finishes them.
     bf16* dbias;
     float* db_partial;
     const bf16* aux;   // [M,N] pre-GELU input (DGELU) or addend (ADD; may alias C)
@@ -455,8 +455,12 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
         // An A stage is BM / 64 boxes of 64 (k) rows x 64 (m) columns, 128 bytes per row, 16-byte pieces swizzled by
         // the row number. A warp takes 32 columns (four pieces) of one box: lane (c, r) adds piece c of rows r, r + 8, ...
         // where a quarter warp reads its four pieces of rows q and q + 4, whose swizzles put them into different halves
-        // of the 128-byte bank window (no bank conflicts). Only the tiles of the first tile column are summed (every
-        // (row tile, split) is there exactly once); for the others the warps just keep step with the ring.
+        // of the 128-byte bank window (no bank conflicts). The reads share the shared-memory bandwidth with the tensor
+        // core's operand reads (which keep it about 80 % busy), so a tile whose every stage is summed runs about 12 %
+        // longer. With split K the work is therefore dealt out: the unit of tile column j sums the k-blocks kb with
+        // kb % tiles_n == j, every unit writes a partial row, and all units slow down a little instead of a few a lot.
+        // Without a split the units of the first tile column sum everything and write the result themselves; the
+        // other units' warps just keep step with the ring.
         // The stage's bytes are credited to the LEADER's barrier, which the peer CTA cannot wait on: a lane of the
         // leader's first warp passes each completion on by storing the stage's use count into relay[stage] of the peer,
         // which the peer's warps poll. (A remote mbarrier arrive with release semantics instead of the plain store held
@@ -473,7 +477,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
             bool ok = true;
             for (int u = unit0; u < total_units && ok; u += unit_step) {
                 const Work w = decode_unit(p, u);
-                const bool mine = w.n0 == 0;
+                constexpr bool DEAL = (EPI & EPI_PARTIAL) != 0;
+                const int tn = w.n0 / BN;
+                const bool unit_mine = DEAL || tn == 0;
+                int r = DEAL ? w.kb_begin % p.tiles_n : 0;
                 ptx::f32x2 acc[4];
 #pragma unroll
                 for (int j = 0; j < 4; j++) acc[j] = ptx::pack2(0.f, 0.f);
@@ -505,6 +512,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
                     }
                     if (!ok) break;
                     if (PAIR && rank == 0 && dw == 0 && lane == 0) ptx::st_shared_cluster_u32(&relay[s], 1, pass);
+                    const bool mine = DEAL ? r == tn : unit_mine;
+                    if (DEAL && ++r == p.tiles_n) r = 0;
                     if (mine) {
                         const uint8_t* sBox = smem + s * STAGE_BYTES + box * CHUNK_BYTES;
 #pragma unroll
@@ -522,7 +531,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
                     if (++s == STAGES) { s = 0; ph ^= 1; pass++; }
                 }
                 if (!ok) break;
-                if (mine) {
+                if (unit_mine) {
                     // the eight lanes with the same c hold the same 8 columns: fixed-order tree, result in lanes 0..3
                     float f[8];
 #pragma unroll
@@ -536,7 +545,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
                     const int col = w.m0 + rank * BM + box * 64 + c * 8;
                     if (lane < 4 && col < p.M) {
                         if (EPI & EPI_PARTIAL) {
-                            float4* dst = reinterpret_cast<float4*>(p.db_partial + (size_t)w.split * p.M + col);
+                            float4* dst = reinterpret_cast<float4*>(p.db_partial + (size_t)(w.split * p.tiles_n + tn) * p.M + col);
                             dst[0] = make_float4(f[0], f[1], f[2], f[3]);
                             dst[1] = make_float4(f[4], f[5], f[6], f[7]);
                         } else {
@@ -856,9 +865,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
 }
 
 // fp32 split-K partials -> bf16 output (optionally += existing contents).
-// With `dbias`: the first M / 8 threads also finish the bias gradient from db_partial [splits, M] (EPI_DBIAS).
+// With `dbias`: the first M / 8 threads also finish the bias gradient from db_partial [db_rows, M] (EPI_DBIAS).
 __global__ void splitk_reduce_kernel(bf16* __restrict__ out, const float* __restrict__ partial, size_t n, int splits,
-                                     int accumulate, bf16* __restrict__ dbias, const float* __restrict__ db_partial, int M) {
+                                     int accumulate, bf16* __restrict__ dbias, const float* __restrict__ db_partial, int M,
+                                     int db_rows) {
     size_t i = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) * 8;
     if (i >= n) return;
     if (dbias != nullptr && i < (size_t)M) {
@@ -869,7 +879,7 @@ __global__ void splitk_reduce_kernel(bf16* __restrict__ out, const float* __rest
 #pragma unroll
             for (int j = 0; j < 8; j++) d[j] = 0.f;
         }
-        for (int s = 0; s < splits; s++) {
+        for (int s = 0; s < db_rows; s++) {
             const float4* src = reinterpret_cast<const float4*>(db_partial + (size_t)s * M + i);
             const float4 a = src[0], b = src[1];
             d[0] += a.x; d[1] += a.y; d[2] += a.z; d[3] += a.w;
@@ -1044,7 +1054,7 @@ long llmk_gemm_workspace_bytes(int mode, int M, int N, int K, int num_sms) {
     int s = pick_splits(mode, M, N, K, num_sms > 0 ? num_sms : 148);
     const int s2 = pick_splits(mode, M, N, K, (num_sms > 0 ? num_sms : 148) / 2, 2 * BM);
     if (s2 > s) s = s2;
-    return s > 1 ? (long)s * M * N * 4 + (long)s * M * 4 /* bias-gradient partials */ : 0;
+    return s > 1 ? (long)s * M * N * 4 + (long)s * ceil_div(N, BN) * M * 4 /* bias-gradient partials */ : 0;
 }
 
 // C = op(A) op(B) with the epilogue selected by `epi` (bit-or of: 1 bias, 2 GELU with pre-activation
@@ -1149,7 +1159,7 @@ static int gemm_impl(int mode, int epi, const void* A, const void* B, void* C, v
         const int cap = max_ctas > 0 ? (p.pair ? (max_ctas / 2 > 0 ? max_ctas / 2 : 1) : max_ctas) : workers;
         int s = pick_splits(mode, M, N, K, cap < workers ? cap : workers, p.pair ? 2 * BM : BM);
         if (s > 1) {
-            if (workspace == nullptr || workspace_bytes < (long)s * M * N * 4 + (with_dbias ? (long)s * M * 4 : 0)) return LLMK_ERR_WORKSPACE;
+            if (workspace == nullptr || workspace_bytes < (long)s * M * N * 4 + (with_dbias ? (long)s * p.tiles_n * M * 4 : 0)) return LLMK_ERR_WORKSPACE;
             p.splits = s;
             p.partial = static_cast<float*>(workspace);
             p.db_partial = p.partial + (size_t)s * M * N;   // behind the partials of C (s = the largest split count in use)
@@ -1221,7 +1231,7 @@ static int gemm_impl(int mode, int epi, const void* A, const void* B, void* C, v
         const size_t n = (size_t)M * N;
         splitk_reduce_kernel<<<ceil_div((long)(n / 8), 256), 256, 0, stream>>>(static_cast<bf16*>(C), p.partial, n, p.splits,
                                                                             split_accumulate ? 1 : 0, with_dbias ? p.dbias : nullptr,
-                                                                            p.db_partial, M);
+                                                                            p.db_partial, M, p.splits * p.tiles_n);
         LLMK_LAUNCH_CHECK();
     }
     return LLMK_OK;
