@@ -2,7 +2,8 @@
 
 * :func:`gemm_nt`  ``C[M,N] = A[M,K] @ B[N,K]^T``  (+bias, +GELU with pre-activation, +addend)
 * :func:`gemm_nn`  ``C[M,N] = A[M,K] @ B[K,N]``    (optionally times GELU'(aux), or + addend)
-* :func:`gemm_tn`  ``C[M,N] (+)= A[K,M]^T @ B[K,N]`` (split-K through an fp32 workspace)
+* :func:`gemm_tn`  ``C[M,N] (+)= A[K,M]^T @ B[K,N]`` (split-K through an fp32 workspace; optionally the bias gradient
+  ``dbias[M] (+)= A.sum(0)`` from the same launch, job of llmc/matmul.cuh:465-539)
 
 They replace matmul_forward / matmul_forward_gelu / matmul_backward of the reference
 (llmc/matmul.cuh:678-785, 1138-1201, 1238-1338).
