@@ -17,6 +17,12 @@
   runs forward + backward of the framework's model (the CUDA path on a GPU, else the PyTorch model) on the stored
   batch and compares logits, loss and every gradient tensor with the stored values, tensor by tensor.
 
+* ``device [--peers]`` — preflight of the machine (job of ``dev/cuda/cuda_runtime_check.cu:53-133`` for this
+  framework's one target): driver / runtime versions, every visible GPU with its compute capability, SM count and
+  memory; fails unless all of them are sm_100 (B200 / GB200: the kernels are built for ``sm_100a`` only), the CUDA
+  library loads and reports resident CTA pairs, and a 1-byte allocate / memset / synchronise works; ``--peers`` also
+  requires peer access between every pair of GPUs (the fused communication kernels need it).
+
 Every command prints its findings and exits 1 if there are any.
 """
 from __future__ import annotations
@@ -180,6 +186,88 @@ def check_debug_state(model_path: str, state_path: str, device: str = "", logit_
     return problems
 
 
+class _TorchProbe:
+    """What ``check_device`` asks of the machine; tests pass a stand-in."""
+
+    def versions(self) -> tuple[str, str]:
+        import torch
+
+        drv = "?"
+        try:
+            import pynvml
+
+            pynvml.nvmlInit()
+            drv = pynvml.nvmlSystemGetDriverVersion()
+            drv = drv.decode() if isinstance(drv, bytes) else str(drv)
+        except Exception:      # NVML is optional here: the runtime version is enough to go on
+            pass
+        return drv, str(torch.version.cuda)
+
+    def devices(self) -> list[dict]:
+        import torch
+
+        out = []
+        for i in range(torch.cuda.device_count() if torch.cuda.is_available() else 0):
+            p = torch.cuda.get_device_properties(i)
+            out.append({"name": p.name, "major": p.major, "minor": p.minor, "sms": p.multi_processor_count, "memory": p.total_memory})
+        return out
+
+    def can_access_peer(self, a: int, b: int) -> bool:
+        import torch
+
+        return bool(torch.cuda.can_device_access_peer(a, b))
+
+    def touch(self, dev: int) -> None:
+        import torch
+
+        t = torch.zeros(1, dtype=torch.uint8, device=f"cuda:{dev}")
+        torch.cuda.synchronize(dev)
+        del t
+
+    def pair_clusters(self, dev: int) -> int:
+        import torch
+
+        from ..ops import _native
+
+        with torch.cuda.device(dev):
+            return int(_native.lib().llmk_gemm_pair_clusters())
+
+
+def check_device(peers: bool = False, probe=None, out=print) -> list[str]:
+    probe = probe or _TorchProbe()
+    problems: list[str] = []
+    drv, rt = probe.versions()
+    out(f"CUDA driver version: {drv}")
+    out(f"CUDA runtime version: {rt}")
+    devs = probe.devices()
+    out(f"CUDA visible devices: {len(devs)}")
+    if not devs:
+        return ["no CUDA devices visible to the runtime"]
+    for i, d in enumerate(devs):
+        out(f"CUDA device {i}: {d['name']} (sm_{d['major']}{d['minor']}), {d['sms']} SMs, {d['memory'] / 2**30:.0f} GiB")
+        if (d["major"], d["minor"]) != (10, 0):
+            problems.append(f"device {i} is {d['name']} (sm_{d['major']}{d['minor']}): the kernels are built for sm_100a (B200 / GB200) only")
+    if problems:
+        return problems
+    for i in range(len(devs)):
+        try:
+            probe.touch(i)
+            pairs = probe.pair_clusters(i)
+        except Exception as e:      # report, do not crash: this command exists to explain a broken machine
+            problems.append(f"device {i}: {type(e).__name__}: {e}")
+            continue
+        out(f"CUDA device {i}: library loaded, {pairs} resident CTA pairs for the tcgen05 GEMM")
+        if pairs <= 0:
+            problems.append(f"device {i}: the CTA-pair GEMM kernel cannot be resident (LLMK_GEMM_PAIR=0 set, or shared memory opt-in refused)")
+    if peers:
+        for a in range(len(devs)):
+            for b in range(len(devs)):
+                if a != b and not probe.can_access_peer(a, b):
+                    problems.append(f"no peer access from device {a} to device {b}: the fused communication kernels need it "
+                                    f"(the trainers then fall back to library collectives)")
+    return problems
+
+
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(prog="llm_kittens_b200.cli.check", description=__doc__,
                                  formatter_class=argparse.RawDescriptionHelpFormatter)
@@ -213,9 +301,13 @@ def main(argv=None) -> int:
     p.add_argument("--device", default="")
     p.add_argument("--logit-tol", type=float, default=0.0)
     p.add_argument("--loss-tol", type=float, default=0.0)
+    p = sub.add_parser("device")
+    p.add_argument("--peers", action="store_true")
     args = ap.parse_args(argv)
 
-    if args.command == "log":
+    if args.command == "device":
+        problems = check_device(args.peers)
+    elif args.command == "log":
         problems = validate_log(args.path, args.final_step, args.max_train_loss, args.max_val_loss, not args.no_decrease)
     elif args.command == "compare":
         problems = compare_logs(args.a, args.b, args.rel_tol, args.abs_tol)

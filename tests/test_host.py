@@ -556,3 +556,43 @@ def test_debug_state_commands_round_trip(tmp_path):
     formats.write_model(str(tmp_path / "other.bin"), cfg, model.params)
     problems = check.check_debug_state(str(tmp_path / "other.bin"), sp, device="cpu")
     assert problems and any("logits" in p or "gradient" in p for p in problems)
+
+
+def test_device_preflight_against_a_stand_in_machine(capsys):
+    """`check device` on pretended machines: eight B200s pass, a Hopper card or a missing peer link is named, a machine
+    without GPUs fails (the job of the reference's dev/cuda/cuda_runtime_check.cu:53-133 for this framework's target)."""
+    from llm_kittens_b200.cli import check
+
+    class Probe:
+        def __init__(self, devs, no_peer=(), pairs=74):
+            self.devs, self.no_peer, self.pairs, self.touched = devs, set(no_peer), pairs, []
+
+        def versions(self):
+            return "580.159", "12.8"
+
+        def devices(self):
+            return self.devs
+
+        def can_access_peer(self, a, b):
+            return (a, b) not in self.no_peer
+
+        def touch(self, dev):
+            self.touched.append(dev)
+
+        def pair_clusters(self, dev):
+            return self.pairs
+
+    b200 = {"name": "NVIDIA B200", "major": 10, "minor": 0, "sms": 148, "memory": 183359 << 20}
+    h100 = {"name": "NVIDIA H100", "major": 9, "minor": 0, "sms": 132, "memory": 80 << 30}
+    lines = []
+    p = Probe([b200] * 8)
+    assert check.check_device(peers=True, probe=p, out=lines.append) == [] and p.touched == list(range(8))
+    assert any("sm_100" in l and "148 SMs" in l for l in lines) and any("74 resident CTA pairs" in l for l in lines)
+    bad = check.check_device(probe=Probe([b200, h100]), out=lines.append)
+    assert len(bad) == 1 and "device 1" in bad[0] and "sm_90" in bad[0]
+    bad = check.check_device(peers=True, probe=Probe([b200] * 2, no_peer=[(0, 1)]), out=lines.append)
+    assert len(bad) == 1 and "from device 0 to device 1" in bad[0]
+    assert check.check_device(probe=Probe([b200], pairs=0), out=lines.append)
+    assert check.check_device(probe=Probe([]), out=lines.append) == ["no CUDA devices visible to the runtime"]
+    if not torch.cuda.is_available():
+        assert check.main(["device"]) == 1 and "no CUDA devices" in capsys.readouterr().out
