@@ -43,3 +43,11 @@ def test_train_checkpoint_resume_is_bit_exact(tmp_path):
     assert later and all(s in resumed["train"] for s in later)
     for s in later:                        # loss, learning rate and gradient norm as logged: identical digits
         assert resumed["train"][s] == full["train"][s], (s, resumed["train"][s], full["train"][s])
+
+
+def test_device_preflight_passes_on_this_machine(capsys):
+    from llm_kittens_b200.cli import check
+
+    assert check.main(["device"]) == 0
+    out = capsys.readouterr().out
+    assert "sm_100" in out and "resident CTA pairs" in out and out.rstrip().endswith("ok")
