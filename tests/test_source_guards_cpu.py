@@ -1,0 +1,90 @@
+"""Source guards: properties of the sources themselves that no run on a CPU box can show, checked by reading them
+(the idea of the reference's dev/validate_*_source.py scripts, e.g. dev/validate_nccl_source.py:1-349, applied to this
+framework's own rules)."""
+import os
+import re
+
+REPO = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+PKG = os.path.join(REPO, "llm_kittens_b200")
+CSRC = os.path.join(PKG, "csrc")
+
+
+def _read(path):
+    with open(path, encoding="utf-8") as f:
+        return f.read()
+
+
+def _files(root, exts):
+    for d, _, names in os.walk(root):
+        if "_lib" in d or "__pycache__" in d:
+            continue
+        for n in sorted(names):
+            if n.endswith(exts):
+                yield os.path.join(d, n)
+
+
+def _strip_comments(src):
+    src = re.sub(r"/\*.*?\*/", " ", src, flags=re.S)
+    return re.sub(r"//[^\n]*", " ", src)
+
+
+def test_every_entry_point_called_from_python_is_exported_by_the_cuda_sources():
+    exported = set()
+    for path in _files(CSRC, (".cu", ".cpp", ".cuh", ".h")):
+        exported |= set(re.findall(r"\b(llmk_[a-z0-9_]+)\s*\(", _read(path)))
+    called = {}
+    for path in list(_files(PKG, (".py",))) + [os.path.join(REPO, "bench.py"), os.path.join(REPO, "__graft_entry__.py")]:
+        src = _read(path)
+        for name in re.findall(r"""(?:N|_native|native)\.call\(\s*["'](llmk_[a-z0-9_]+)["']""", src):
+            called.setdefault(name, path)
+        for name in re.findall(r"""lib\(\)\.(llmk_[a-z0-9_]+)\b""", src):
+            called.setdefault(name, path)
+    assert len(called) > 60, "the scan found suspiciously few call sites"
+    missing = {n: p for n, p in called.items() if n not in exported}
+    assert not missing, f"called from Python but defined nowhere in csrc: {missing}"
+
+
+def test_no_bulk_or_tensor_load_multicasts_across_a_cluster():
+    """The only cluster multicast in the kernels is the tcgen05.commit arrival (an mbarrier signal, no data)."""
+    for path in _files(CSRC, (".cu", ".cuh")):
+        code = _strip_comments(_read(path))
+        for m in re.finditer(r"multicast::cluster", code):
+            line = code[code.rfind("\n", 0, m.start()) + 1: code.find("\n", m.end())]
+            assert "tcgen05.commit" in line, f"{path}: {line.strip()}"
+
+
+def test_device_code_has_no_trap_and_every_polling_loop_has_a_time_limit():
+    for path in _files(CSRC, (".cu", ".cuh")):
+        code = _strip_comments(_read(path))
+        assert "__trap" not in code and "asm(\"trap" not in code and not re.search(r"(?<![\w])assert\(", code), path
+        # every loop that polls memory written by another kernel, CTA or GPU sits next to a timer read and an abort path
+        for m in re.finditer(r"while\s*\([^)]*(ld_acquire|ld_shared_acquire|ld_volatile|mbar_test|mbar_poll)", code):
+            window = code[m.start(): m.start() + 1500]
+            assert re.search(r"globaltimer_ns|now_ns\(\)|clock64", window), f"{path}: polling loop without a time limit near: {window[:80]!r}"
+        for m in re.finditer(r"while\s*\(\s*true\s*\)", code):
+            window = code[m.start(): m.start() + 1200]
+            assert re.search(r"globaltimer_ns|now_ns\(\)|clock64|break|return", window), f"{path}: endless loop near {window[:80]!r}"
+
+
+def test_every_profiler_command_line_leaves_the_clocks_alone():
+    hits = 0
+    for path in list(_files(PKG, (".py",))) + list(_files(os.path.join(REPO, "profiles"), (".md",))) + [os.path.join(REPO, "README.md")]:
+        src = _read(path)
+        for m in re.finditer(r"""(?<![\w`.])ncu(?:["',\s]+)--""", src):
+            window = src[m.start(): m.start() + 700]
+            assert "--clock-control" in window and "none" in window, f"{path}: ncu without --clock-control none near {window[:80]!r}"
+            hits += 1
+    assert hits >= 5
+
+
+def test_build_targets_sm_100a_only_and_keeps_line_info():
+    src = _read(os.path.join(PKG, "build.py"))
+    assert "arch=compute_100a,code=sm_100a" in src and "-lineinfo" in src
+    assert not re.search(r"sm_(80|86|89|90a?|120)\b", src)
+
+
+def test_nothing_committed_depends_on_the_scratch_folder():
+    for path in list(_files(PKG, (".py",))) + list(_files(os.path.join(REPO, "tests"), (".py",))) + [os.path.join(REPO, "bench.py")]:
+        if path.endswith("test_source_guards_cpu.py"):
+            continue
+        assert "_work/" not in _read(path) and "_work\\" not in _read(path), path
