@@ -35,3 +35,36 @@ def test_synthetic_and_eval_files(tmp_path):
     assert prepare.main(["hellaswag", "--input", str(jl), "--out", str(out), "--tokenizer", "bytes"]) == 0
     ev = EvalLoader(str(out), 8, 32)
     assert ev.num_examples == 8
+
+
+def test_documents_from_parquet_jsonl_and_json_stream_into_shards(tmp_path):
+    """The corpus command (job of the reference's dev/data/fineweb.py and tinystories.py on local files): documents from
+    parquet / JSON-lines / JSON files, tokenized by a process pool in document order, first shard = validation."""
+    import pyarrow as pa
+    import pyarrow.parquet as pq
+
+    docs = [f"document number {i} " * (3 + i % 5) for i in range(60)]
+    pq.write_table(pa.table({"text": docs[:25], "id": list(range(25))}), str(tmp_path / "a_000.parquet"), row_group_size=10)
+    (tmp_path / "a_001.jsonl").write_text("\n".join(json.dumps({"text": d}) for d in docs[25:45]) + "\n")
+    (tmp_path / "a_002.json").write_text(json.dumps([{"text": d} for d in docs[45:]]))
+    tok = prepare.get_tokenizer("bytes")
+    want = np.concatenate([[tok.eot] + tok.encode(d.strip()) for d in docs])
+
+    out1 = prepare.prepare_documents(str(tmp_path / "a_*"), str(tmp_path / "o1"), "bytes", name="mini", shard_size=2048, workers=0)
+    assert out1[0].endswith("mini_val_000000.bin") and out1[1].endswith("mini_train_000000.bin") and len(out1) >= 3
+    got = np.concatenate([formats.read_tokens(p) for p in out1])
+    assert len(formats.read_tokens(out1[0])) == 2048 and (got == want).all()
+
+    # a pool of two worker processes writes byte-identical shards, through the command line
+    assert prepare.main(["docs", "--input", str(tmp_path / "a_*"), "--out-dir", str(tmp_path / "o2"), "--name", "mini", "--tokenizer", "bytes",
+                         "--shard-size", "2048", "--workers", "2"]) == 0
+    for p in out1:
+        q = tmp_path / "o2" / p.split("/")[-1]
+        assert q.read_bytes() == open(p, "rb").read()
+
+    # another field name (the TinyStories files hold {"story": ...}); the loader reads what was written
+    (tmp_path / "t.json").write_text(json.dumps([{"story": d} for d in docs[:10]]))
+    out3 = prepare.prepare_documents(str(tmp_path / "t.json"), str(tmp_path / "o3"), "bytes", name="ts", field="story", shard_size=512)
+    loader = DataLoader(str(tmp_path / "o3" / "ts_train_*.bin"), 2, 16)
+    x, _ = loader.next_batch()
+    assert (x.flatten()[:8].numpy() == formats.read_tokens(out3[1])[:8]).all()
