@@ -1124,7 +1124,7 @@ static int gemm_impl(int mode, int epi, const void* A, const void* B, void* C, v
     p.dbias = static_cast<bf16*>(ready.dbias);
     p.db_partial = nullptr;
     if (epi & EPI_DBIAS) {
-        if (mode != MODE_TN || groups != 1 || !p.pair || ready.dbias == nullptr || (epi & ~(EPI_DBIAS | EPI_ADD)) ||
+        if (mode != MODE_TN || !p.pair || ready.dbias == nullptr || (epi & ~(EPI_DBIAS | EPI_ADD)) ||
             (reinterpret_cast<uintptr_t>(ready.dbias) & 15))
             return LLMK_ERR_SHAPE;
     }
@@ -1255,6 +1255,16 @@ LLMK_API int llmk_gemm_tn_dbias(const void* A, const void* B, void* C, void* dbi
     r.dbias = dbias;
     return gemm_impl(MODE_TN, EPI_DBIAS | (accumulate ? EPI_ADD : 0), A, B, C, nullptr, nullptr, accumulate ? C : nullptr, M, N, K, 1,
                      workspace, workspace_bytes, status, max_ctas, stream_, r);
+}
+
+// The same for `groups` stacked problems (the experts of a mixture-of-experts layer): A [G*K, M], B [G*K, N],
+// C [G*M, N], dbias [G*M]; M a multiple of 256 and K of 64 as for llmk_gemm_grouped, else LLMK_ERR_SHAPE.
+LLMK_API int llmk_gemm_grouped_tn_dbias(const void* A, const void* B, void* C, void* dbias, int accumulate, int M, int N, int K,
+                                        int groups, void* workspace, long workspace_bytes, int* status, int max_ctas, void* stream_) {
+    Ready r;
+    r.dbias = dbias;
+    return gemm_impl(MODE_TN, EPI_DBIAS | (accumulate ? EPI_ADD : 0), A, B, C, nullptr, nullptr, accumulate ? C : nullptr, M, N, K,
+                     groups, workspace, workspace_bytes, status, max_ctas, stream_, r);
 }
 
 // llmk_gemm whose B operand (a weight matrix, NT or NN) is still being filled by another kernel: `b_ready` holds one

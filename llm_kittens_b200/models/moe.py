@@ -255,17 +255,15 @@ class MoETransformer(Transformer):
         # the first consumer of dy waits tile by tile for its source ranks; the products after it find dy complete
         gemm.gemm_nn(dy, p["fcprojw"][l][loc], out=d_hid, dgelu_of=a["hid_pre"][l][rows], groups=G,
                      a_ready=None if lib else (self.arrive[r_out:], cap, ep, lim, ((self.ep_rank + 1) % P) * cap))
-        gemm.gemm_tn(dy, act_l[rows], out=g["fcprojw"][l][loc], accumulate=True, groups=G)
-        gemm.gemm_tn(d_hid, x, out=g["fcw"][l][loc], accumulate=True, groups=G)
+        # weight and bias gradients of all local experts: one grouped launch per projection
+        gemm.gemm_tn(dy, act_l[rows], out=g["fcprojw"][l][loc], accumulate=True, groups=G, dbias=g["fcprojb"][l][loc])
+        gemm.gemm_tn(d_hid, x, out=g["fcw"][l][loc], accumulate=True, groups=G, dbias=g["fcb"][l][loc])
         fused_back = self.way_back == "scatter" and not lib
         if fused_back:
             gemm.gemm_grouped_scatter(d_hid, p["fcw"][l][loc], None, a["y_loc"][rows], G, self.back_dx_ptrs, self.arrive_ptrs, r_back,
                                       self.done[1:], cap, P, self.ep_rank, ep, nn=True)
         else:
             gemm.gemm_nn(d_hid, p["fcw"][l][loc], out=a["y_loc"][rows], groups=G)
-        # bias gradients of all local experts: one grouped column sum per projection
-        ew.dbias_grouped(g["fcprojb"][l][loc], dy, G, accumulate=True)
-        ew.dbias_grouped(g["fcb"][l][loc], d_hid, G, accumulate=True)
         if lib:
             self._library_back(a["y_loc"], self.back_dx)
             moe_ops.combine(d_ln2, None, self.back_dx, idx, slot, None, cap)

@@ -227,8 +227,9 @@ def gemm_tn(a, b, out=None, accumulate=False, groups=1, dbias=None):
     """``out (+)= a.T @ b`` with ``a``: [K,M], ``b``: [K,N] (K = token dimension).
     ``groups`` > 1: ``a`` [G*K,M], ``b`` [G*K,N], ``out`` [G,M,N] or [G*M,N]: group g uses rows [g*K,(g+1)*K).
 
-    ``dbias`` [M]: also ``dbias (+)= a.sum(0)`` (the bias gradient of the linear layer whose output gradient is ``a``),
-    from the same launch when the fused kernel takes the call, else from the stand-alone column-sum kernel."""
+    ``dbias`` [M] ([G, M] with groups): also ``dbias (+)= a.sum(0)`` per group (the bias gradient of the linear layer
+    whose output gradient is ``a``), from the same launch when the fused kernel takes the call, else from the
+    stand-alone column-sum kernel."""
     M = a.shape[1]
     K = a.shape[0] // groups
     Nn = b.shape[1]
@@ -237,13 +238,20 @@ def gemm_tn(a, b, out=None, accumulate=False, groups=1, dbias=None):
         assert not accumulate
         out = torch.empty(M * groups, Nn, dtype=torch.bfloat16, device=a.device)
     out2 = _flat2(out, groups)
-    if dbias is not None and groups == 1 and fused_dbias_available() and dbias.data_ptr() % 16 == 0 and dbias.is_contiguous():
+    fused = dbias is not None and fused_dbias_available() and dbias.data_ptr() % 16 == 0 and dbias.is_contiguous()
+    if fused and groups > 1:      # stacked problems: whole tiles per group, as for every grouped launch
+        fused = M % tile_rows() == 0 and K % 64 == 0 and hasattr(N.lib(), "llmk_gemm_grouped_tn_dbias")
+    if fused:
         for t, nm in ((a, "A"), (b, "B"), (out2, "C"), (dbias, "dbias")):
             N.require_cuda_tensor(t, torch.bfloat16, nm)
-        ws_bytes = int(N.lib().llmk_gemm_workspace_bytes(MODE_TN, M, Nn, K, 0))
+        ws_bytes = int(N.lib().llmk_gemm_workspace_bytes(MODE_TN, M * groups, Nn, K, 0))
         ws = workspace(ws_bytes) if ws_bytes else None
-        N.call("llmk_gemm_tn_dbias", a, b, out2, dbias, int(accumulate), M, Nn, K, ws, ws.numel() if ws is not None else 0,
-               N.status_word(), _MAX_CTAS)
+        ws_n = ws.numel() if ws is not None else 0
+        if groups == 1:
+            N.call("llmk_gemm_tn_dbias", a, b, out2, dbias, int(accumulate), M, Nn, K, ws, ws_n, N.status_word(), _MAX_CTAS)
+        else:
+            N.call("llmk_gemm_grouped_tn_dbias", a, b, out2, dbias, int(accumulate), M, Nn, K, groups, ws, ws_n, N.status_word(),
+                   _MAX_CTAS)
         return out
     _gemm(MODE_TN, EPI_ADD if accumulate else 0, a, b, out2, None, None, out2 if accumulate else None, M, Nn, K, groups)
     if dbias is not None:

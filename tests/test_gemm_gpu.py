@@ -118,6 +118,34 @@ def test_gemm_tn_with_bias_gradient_from_the_same_launch(M, N, K):
     _native.check_status()
 
 
+@pytest.mark.parametrize("G,M,N,K", [(4, 512, 512, 256), (2, 256, 1000, 192), (4, 768, 3072, 4096), (2, 200, 264, 128)])
+def test_grouped_gemm_tn_with_bias_gradients_per_group(G, M, N, K):
+    """The experts of a mixture-of-experts layer: dW [G, M, N] and dbias [G, M] from one grouped launch (the last shape
+    has ragged tiles and takes the route of one GEMM per group plus the grouped column-sum kernel)."""
+    from llm_kittens_b200.ops import gemm, _native
+
+    if not gemm.fused_dbias_available():
+        pytest.skip("needs the CTA-pair GEMM kernel")
+    a, b = _rand(G * K, M, scale=0.1), _rand(G * K, N, scale=0.1)
+    ref = torch.stack([a[g * K:(g + 1) * K].float().T @ b[g * K:(g + 1) * K].float() for g in range(G)])
+    ref_db = torch.stack([a[g * K:(g + 1) * K].float().sum(0) for g in range(G)])
+    acc, db = _rand(G, M, N), _rand(G, M)
+    acc0, db0 = acc.clone(), db.clone()
+    launches = _native.launch_count()
+    gemm.gemm_tn(a, b, out=acc, accumulate=True, groups=G, dbias=db)
+    if M % 256 == 0 and K % 64 == 0:
+        assert _native.launch_count() == launches + 1
+    _close(acc, ref + acc0.float(), 0.15)
+    err = (db.float() - (ref_db + db0.float())).abs()
+    assert not (err > 0.005 * ref_db.abs() + 0.03).any(), err.max().item()
+    out, db2 = torch.empty(G, M, N, device="cuda", dtype=torch.bfloat16), torch.empty(G, M, device="cuda", dtype=torch.bfloat16)
+    gemm.gemm_tn(a, b, out=out, groups=G, dbias=db2)
+    _close(out, ref, 0.1)
+    assert not ((db2.float() - ref_db).abs() > 0.005 * ref_db.abs() + 0.02).any()
+    assert torch.equal(gemm.gemm_tn(a, b, groups=G).view(G, M, N), out)
+    _native.check_status()
+
+
 def test_gemm_deterministic():
     from llm_kittens_b200.ops import gemm
 
