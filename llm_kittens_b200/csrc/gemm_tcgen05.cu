@@ -52,12 +52,12 @@ constexpr int TMEM_COLS = 512;
 
 enum { MODE_NT = 0, MODE_NN = 1, MODE_TN = 2 };
 enum { EPI_BIAS = 1, EPI_GELU = 2, EPI_DGELU = 4, EPI_ADD = 8, EPI_PARTIAL = 16, EPI_ROPE = 32, EPI_SCATTER = 64, EPI_SWIGLU = 128,
-       EPI_DBIAS = 256 };
+       EPI_DBIAS = 256, EPI_DROW = 512 };
 constexpr int DB_WARPS = 4;   // EPI_DBIAS: column-sum warps per CTA, one per 32 columns of the A stage
 
 template <int EPI, bool PAIR>
 struct Cfg {
-    static constexpr bool DUAL = (EPI & (EPI_GELU | EPI_DGELU | EPI_ADD)) != 0;
+    static constexpr bool DUAL = (EPI & (EPI_GELU | EPI_DGELU | EPI_ADD | EPI_DROW)) != 0;
     // SwiGLU epilogue (pair kernel only): three outputs per piece (up, gate, activation), so three staging buffers
     // per epilogue warp and a 4-stage operand ring
     static constexpr bool SWI = (EPI & EPI_SWIGLU) != 0;
@@ -126,6 +126,11 @@ struct Params {
     // db_partial[split * tiles_n + tile column][M] and the split-K reduction kernel finishes them.
     bf16* dbias;
     float* db_partial;
+    // EPI_DROW (attention projection's input gradient, head size 64): C = dO and, per row and 64-column chunk (= head),
+    // drow[(b * NH + h) * T + t] = sum over the chunk of round_bf16(C) * aux, with aux = O (row = b * T + t): the D
+    // term of the attention backward, taken while dO is still in registers instead of in a pass of its own
+    float* drow;
+    int drow_T, drow_NH;
     const bf16* aux;   // [M,N] pre-GELU input (DGELU) or addend (ADD; may alias C)
     float* partial;    // [splits, M, N] fp32 (PARTIAL)
     int* status;
@@ -570,7 +575,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
         constexpr int NBUF = Cfg<EPI, PAIR>::NBUF;
         uint8_t* buf = staging + e * NBUF * STAGING_BYTES;            // output tile
         uint8_t* buf2 = NBUF == 2 ? buf + STAGING_BYTES : buf;        // second output / aux input (DUAL); wide dGELU: the same buffer
-        constexpr bool AUX_IN = (EPI & (EPI_DGELU | EPI_ADD)) != 0;
+        constexpr bool AUX_IN = (EPI & (EPI_DGELU | EPI_ADD | EPI_DROW)) != 0;
         uint32_t aux_ph = 0;
         int it = 0;
         bool ok = true;
@@ -701,6 +706,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
                 }
                 bf16x8 res[8];
                 bf16x8 res2[(EPI & EPI_GELU) ? 8 : 1];
+                float drow_acc = 0.f;
                 // both TMEM loads of the chunk and its bias are in flight before anything waits: a warp has only one other
                 // epilogue warp on its scheduler to hide latency behind, so the loads overlap each other instead
                 uint32_t vv[2][32];
@@ -755,7 +761,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
                                 xp[j] = ptx::fma2(xp[j], cs[j], ptx::pack2(-x1 * sn[j], x0 * sn[j]));
                             }
                         }
-                        if (AUX_IN) {
+                        if (AUX_IN && !(EPI & EPI_DROW)) {
                             float g[8];
                             unpack8(*reinterpret_cast<const bf16x8*>(buf2 + off), g);
 #pragma unroll
@@ -776,7 +782,19 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
                             for (int j = 0; j < 4; j++) ptx::unpack2(gelu_fwd2(ptx::pack2(x[2 * j], x[2 * j + 1])), x[2 * j], x[2 * j + 1]);
                         }
                         res[cc] = pack8(x);
+                        if (EPI & EPI_DROW) {
+                            // the products use the ROUNDED output, as a pass over the stored tensor would
+                            float r[8], o[8];
+                            unpack8(res[cc], r);
+                            unpack8(*reinterpret_cast<const bf16x8*>(buf2 + off), o);
+#pragma unroll
+                            for (int j = 0; j < 8; j++) drow_acc = fmaf(o[j], r[j], drow_acc);
+                        }
                     }
+                }
+                if ((EPI & EPI_DROW) && row_ok) {
+                    const int bi = row / p.drow_T;
+                    p.drow[((size_t)bi * p.drow_NH + (n_base >> 6)) * p.drow_T + (row - bi * p.drow_T)] = drow_acc;
                 }
                 if (lane == 0) ptx::tma_store_wait_read<0>();  // earlier stores have finished reading the buffers
                 __syncwarp();
@@ -1078,6 +1096,8 @@ struct Ready {
     int* sc_count = nullptr;
     int sc_cap = 0, sc_P = 0, sc_Eloc = 0, sc_rank = 0, sc_off = 0, sc_epoch = 0;
     void* dbias = nullptr;                  // EPI_DBIAS: [M] bf16
+    float* drow = nullptr;                  // EPI_DROW: [M / T, N / 64, T] fp32
+    int drow_T = 1, drow_NH = 1;
 };
 
 static int gemm_impl(int mode, int epi, const void* A, const void* B, void* C, void* C2, const void* bias, const void* aux,
@@ -1126,6 +1146,12 @@ static int gemm_impl(int mode, int epi, const void* A, const void* B, void* C, v
     if (epi & EPI_DBIAS) {
         if (mode != MODE_TN || !p.pair || ready.dbias == nullptr || (epi & ~(EPI_DBIAS | EPI_ADD)) ||
             (reinterpret_cast<uintptr_t>(ready.dbias) & 15))
+            return LLMK_ERR_SHAPE;
+    }
+    p.drow = ready.drow; p.drow_T = ready.drow_T; p.drow_NH = ready.drow_NH;
+    if (epi & EPI_DROW) {
+        if (epi != EPI_DROW || mode != MODE_NN || groups != 1 || ready.drow == nullptr || aux == nullptr || ready.drow_T <= 0 ||
+            M % ready.drow_T || N != ready.drow_NH * 64)
             return LLMK_ERR_SHAPE;
     }
     if (epi & EPI_SWIGLU) {
@@ -1196,7 +1222,7 @@ static int gemm_impl(int mode, int epi, const void* A, const void* B, void* C, v
         if ((rc = make_tmap_2d(&tmX, C2, c_cols, M, c_cols, 64, 32))) return rc;
         if ((rc = make_tmap_2d(&xm.y, ready.c3, c_cols, M, c_cols, 64, 32))) return rc;
     }
-    if (epi & (EPI_GELU | EPI_DGELU | EPI_ADD)) {
+    if (epi & (EPI_GELU | EPI_DGELU | EPI_ADD | EPI_DROW)) {
         const void* x = (epi & EPI_GELU) ? C2 : aux;
         if (x == nullptr || (reinterpret_cast<uintptr_t>(x) & 15)) return LLMK_ERR_SHAPE;
         rc = make_tmap_2d(&tmX, x, N, M, N, 64, 32);
@@ -1218,6 +1244,7 @@ static int gemm_impl(int mode, int epi, const void* A, const void* B, void* C, v
     LLMK_GEMM_CASE(MODE_NN, 0)
     LLMK_GEMM_CASE(MODE_NN, EPI_DGELU)
     LLMK_GEMM_CASE(MODE_NN, EPI_ADD)
+    LLMK_GEMM_CASE(MODE_NN, EPI_DROW)
     LLMK_GEMM_CASE(MODE_TN, 0)
     LLMK_GEMM_CASE(MODE_TN, EPI_ADD)
     LLMK_GEMM_CASE(MODE_TN, EPI_PARTIAL)
@@ -1257,7 +1284,7 @@ LLMK_API int llmk_gemm_tn_dbias(const void* A, const void* B, void* C, void* dbi
                      workspace, workspace_bytes, status, max_ctas, stream_, r);
 }
 
-// The same for `groups` stacked problems (the experts of a mixture-of-experts layer): A [G*K, M], B [G*K, N],
+// llmk_gemm_tn_dbias for `groups` stacked problems (the experts of a mixture-of-experts layer): A [G*K, M], B [G*K, N],
 // C [G*M, N], dbias [G*M]; M a multiple of 256 and K of 64 as for llmk_gemm_grouped, else LLMK_ERR_SHAPE.
 LLMK_API int llmk_gemm_grouped_tn_dbias(const void* A, const void* B, void* C, void* dbias, int accumulate, int M, int N, int K,
                                         int groups, void* workspace, long workspace_bytes, int* status, int max_ctas, void* stream_) {
@@ -1265,6 +1292,20 @@ LLMK_API int llmk_gemm_grouped_tn_dbias(const void* A, const void* B, void* C, v
     r.dbias = dbias;
     return gemm_impl(MODE_TN, EPI_DBIAS | (accumulate ? EPI_ADD : 0), A, B, C, nullptr, nullptr, accumulate ? C : nullptr, M, N, K,
                      groups, workspace, workspace_bytes, status, max_ctas, stream_, r);
+}
+
+// Input gradient of the attention output projection with the D term of the attention backward in its epilogue:
+// C [M, N] = A B (A = d(residual) [M, K], B = the projection weight [K, N]) is dO, and dvec[b][h][t] = sum over head h's
+// 64 columns of dO * O for row b * T + t (O [M, N] = the attention output). Head size 64 only (one epilogue chunk is one
+// head). Same job as the D pre-pass of the reference's attention backward (bwd_attend_prep_ker, llmc/tk/attention_h100.cuh:342-395)
+// without reading dO back.
+LLMK_API int llmk_gemm_nn_drow(const void* A, const void* B, void* C, const void* O, void* dvec, int M, int N, int K, int T, int NH,
+                               int* status, int max_ctas, void* stream_) {
+    Ready r;
+    r.drow = static_cast<float*>(dvec);
+    r.drow_T = T;
+    r.drow_NH = NH;
+    return gemm_impl(MODE_NN, EPI_DROW, A, B, C, nullptr, nullptr, O, M, N, K, 1, nullptr, 0, status, max_ctas, stream_, r);
 }
 
 // llmk_gemm whose B operand (a weight matrix, NT or NN) is still being filled by another kernel: `b_ready` holds one

@@ -379,13 +379,18 @@ class Transformer:
             self._norm_bwd(dres, g["ln2w"][l], None if self.is_llama else g["ln2b"][l], d_btc, res2, p["ln2w"][l], mean2,
                            a["ln2_rstd"][k], accumulate=True)
             # ---- attention
-            gemm.gemm_nn(dres, p["attprojw"][l], out=d_btc)
+            # dO, and with 64-wide heads D = rowsum(dO * O) from the same epilogue; else D is a pass of its own on the side stream
             prep = [False]
+            if (gemm.fused_drow_available(cfg.head_size) and attn_ops.fused_rope_available(T)
+                    and gemm.gemm_nn(dres, p["attprojw"][l], out=d_btc, drow_of=(a["atty"][k], a["dvec"], T)) is not False):
+                prep[0] = True
+            else:
+                gemm.gemm_nn(dres, p["attprojw"][l], out=d_btc)
 
-            def attention_side_work():
-                prep[0] = attn_ops.attention_bwd_prep(d_btc, a["atty"][k], a["dvec"], B, T, cfg.num_heads, cfg.head_size)
+                def attention_side_work():
+                    prep[0] = attn_ops.attention_bwd_prep(d_btc, a["atty"][k], a["dvec"], B, T, cfg.num_heads, cfg.head_size)
 
-            self._fork(attention_side_work)
+                self._fork(attention_side_work)
             self._dweight(dres, a["atty"][k], g["attprojw"][l], None if self.is_llama else g["attprojb"][l])
             self._join()   # D is needed now, and the next kernel overwrites the buffer that the MLP's column sum read
             dqkv = a["d_wide"].view(-1)[: BT * QW].view(BT, QW)

@@ -199,9 +199,19 @@ def gemm_grouped_scatter(a, b, bias, shape_like, groups, dst_ptrs, arrive_ptrs, 
            N.status_word(), _MAX_CTAS, dst_ptrs, arrive_ptrs, arrive_off, count, cap, P, rank, epoch)
 
 
-def gemm_nn(a, b, out=None, dgelu_of=None, add=None, groups=1, a_ready=None):
+def fused_drow_available(head_size: int) -> bool:
+    """The input-gradient GEMM of the attention projection can also produce D = rowsum(dO * O) per head (head size 64:
+    one epilogue chunk is one head; ``LLMK_FUSED_DROW=0`` turns it off)."""
+    return head_size == 64 and hasattr(N.lib(), "llmk_gemm_nn_drow") and os.environ.get("LLMK_FUSED_DROW", "1") != "0"
+
+
+def gemm_nn(a, b, out=None, dgelu_of=None, add=None, groups=1, a_ready=None, drow_of=None):
     """``out = a @ b`` with ``a``: [M,K], ``b``: [K,N]; optionally ``* gelu'(dgelu_of)`` or ``+ add``.
-    ``groups`` > 1: ``a`` [G*M,K], ``b`` [G,K,N] or [G*K,N], ``out`` / aux [G*M,N]."""
+    ``groups`` > 1: ``a`` [G*M,K], ``b`` [G,K,N] or [G*K,N], ``out`` / aux [G*M,N].
+
+    ``drow_of`` = (O [M,N], dvec [M/T, N/64, T] fp32, T): also ``dvec[b, h, t] = sum(out[b*T+t, 64h:64h+64] * O[...])``
+    from the epilogue (the D term of the attention backward, with ``out`` = dO); returns False instead of the output,
+    having done nothing, when the fused kernel cannot take the call (a weight that is still being gathered)."""
     b = _flat2(b, groups)
     K = a.shape[1]
     M = a.shape[0] // groups
@@ -209,6 +219,17 @@ def gemm_nn(a, b, out=None, dgelu_of=None, add=None, groups=1, a_ready=None):
     assert b.shape[0] == K * groups and a.shape[0] == M * groups
     if out is None:
         out = torch.empty(M * groups, Nn, dtype=torch.bfloat16, device=a.device)
+    if drow_of is not None:
+        o, dvec, T = drow_of
+        ready = _B_READY.get(b.data_ptr()) if _B_READY else None
+        if groups != 1 or dgelu_of is not None or add is not None or Nn % 64 or M % T or (ready is not None and ready[3] > 0):
+            return False
+        for t, nm in ((a, "A"), (b, "B"), (out, "C"), (o, "O")):
+            N.require_cuda_tensor(t, torch.bfloat16, nm)
+        N.require_cuda_tensor(dvec, torch.float32, "dvec")
+        assert o.numel() == M * Nn and dvec.numel() == M * (Nn // 64)
+        N.call("llmk_gemm_nn_drow", a, b, out, o, dvec, M, Nn, K, T, Nn // 64, N.status_word(), _MAX_CTAS)
+        return out
     epi = 0
     aux = None
     if dgelu_of is not None:

@@ -146,6 +146,32 @@ def test_grouped_gemm_tn_with_bias_gradients_per_group(G, M, N, K):
     _native.check_status()
 
 
+@pytest.mark.parametrize("B,T,NH,K", [(2, 256, 4, 256), (4, 1024, 12, 768), (1, 2048, 32, 2048), (3, 128, 3, 192)])
+def test_gemm_nn_with_the_attention_backward_row_sums_in_its_epilogue(B, T, NH, K):
+    """dO = dres @ W from the GEMM and D[b, h, t] = sum over head h of dO * O from its epilogue, against the stand-alone
+    pre-pass of the attention backward and an fp32 formula; the GEMM's own output must not change by a bit."""
+    from llm_kittens_b200.ops import attention, gemm, _native
+
+    if not gemm.fused_drow_available(64):
+        pytest.skip("entry point not built")
+    M, N = B * T, NH * 64
+    a, w, o = _rand(M, K), _rand(K, N, scale=0.05), _rand(M, N)
+    plain = gemm.gemm_nn(a, w)
+    dvec = torch.full((B, NH, T), 7.0, device="cuda", dtype=torch.float32)
+    out = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+    assert gemm.gemm_nn(a, w, out=out, drow_of=(o, dvec, T)) is out
+    assert torch.equal(out, plain)
+    ref = (plain.float() * o.float()).view(B, T, NH, 64).sum(-1).permute(0, 2, 1)
+    assert (dvec - ref).abs().max().item() <= 1e-3 * ref.abs().max().item() + 1e-4
+    prep = torch.empty_like(dvec)
+    assert attention.attention_bwd_prep(plain, o, prep, B, T, NH, 64)
+    assert (dvec - prep).abs().max().item() <= 1e-3 * ref.abs().max().item() + 1e-4
+    dvec2 = torch.empty_like(dvec)
+    gemm.gemm_nn(a, w, out=out, drow_of=(o, dvec2, T))
+    assert torch.equal(dvec2, dvec)
+    _native.check_status()
+
+
 def test_gemm_deterministic():
     from llm_kittens_b200.ops import gemm
 
