@@ -2,7 +2,7 @@
 
     python -m llm_kittens_b200.ops.profile_case <case> [launches]
 
-cases: gemm_nt, gemm_nt_gelu, gemm_nn, gemm_tn, gemm_tn_dbias (weight and bias gradient from one launch), attn_fwd, attn_bwd, layernorm_fwd, layernorm_bwd,
+cases: gemm_nt, gemm_nt_gelu, gemm_nn, gemm_tn, gemm_tn_dbias (weight and bias gradient from one launch), gemm_nn_drow (dO and the attention backward's row sums), attn_fwd, attn_bwd, layernorm_fwd, layernorm_bwd,
 classifier, adamw, comm_rs, comm_adamw_push, comm_ag_flags (the peer-memory kernels with all ranks emulated on one GPU),
 gemm_b_ready (the GEMM that polls the flags of a gathered weight, flags already set), gemm_qkv_rope (QKV projection with
 RoPE in the epilogue), moe_dispatch / moe_grouped_a_ready / moe_dispatch_pull / moe_combine_pull (the expert exchange with
@@ -43,6 +43,11 @@ def build(case: str):
     if case == "gemm_tn":
         a, b, out = _rnd(BT, 4 * C, scale=0.1), _rnd(BT, C, scale=0.1), torch.zeros(4 * C, C, device="cuda", dtype=BF)
         return lambda: gemm.gemm_tn(a, b, out=out, accumulate=True)
+    if case == "gemm_nn_drow":
+        B, T, NH = 64, 1024, 12
+        a, b, o = _rnd(BT, C), _rnd(C, C, scale=0.05), _rnd(BT, C)
+        out, dvec = torch.empty(BT, C, device="cuda", dtype=BF), torch.empty(B, NH, T, device="cuda")
+        return lambda: gemm.gemm_nn(a, b, out=out, drow_of=(o, dvec, T))
     if case == "gemm_tn_dbias":
         a, b, out = _rnd(BT, 4 * C, scale=0.1), _rnd(BT, C, scale=0.1), torch.zeros(4 * C, C, device="cuda", dtype=BF)
         db = torch.zeros(4 * C, device="cuda", dtype=BF)
