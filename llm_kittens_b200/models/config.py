@@ -16,7 +16,7 @@ stacked over layers ``(L, ...)``; that order is also the order in the ``.bin`` c
 """
 from __future__ import annotations
 
-from dataclasses import dataclass, field, replace
+from dataclasses import dataclass, replace
 
 
 @dataclass(frozen=True)

@@ -25,7 +25,6 @@ import os
 import math
 from typing import Callable
 
-import numpy as np
 import torch
 
 from ..ops import attention as attn_ops

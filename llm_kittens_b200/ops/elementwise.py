@@ -5,7 +5,6 @@ from __future__ import annotations
 import torch
 
 from . import _native as N
-from .norm import _scratch
 
 _DBIAS_SCRATCH: dict[int, torch.Tensor] = {}
 

@@ -12,8 +12,6 @@ from __future__ import annotations
 
 import os
 
-import torch
-
 from ..utils import formats
 
 

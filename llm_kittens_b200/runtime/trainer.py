@@ -14,7 +14,6 @@ the CPU (oracle / gloo tests).
 """
 from __future__ import annotations
 
-import math
 from dataclasses import dataclass
 
 import torch
