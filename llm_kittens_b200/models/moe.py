@@ -148,12 +148,6 @@ class MoETransformer(Transformer):
         return False
 
     # ------------------------------------------------------------------ MLP = mixture of experts
-    def _expert_views(self, l: int, el: int):
-        e = self.ep_rank * self.Eloc + el
-        p, g = self.p, self.g
-        return (p["fcw"][l][e], p["fcb"][l][e], p["fcprojw"][l][e], p["fcprojb"][l][e],
-                g["fcw"][l][e], g["fcb"][l][e], g["fcprojw"][l][e], g["fcprojb"][l][e])
-
     # ---- baseline route through all_to_all_single (LibraryExchange) -------------------------------------------------
     def _library_out(self, x, idx, slot, w, counts, recv_rows, scale_by_weight):
         """rows of ``x`` -> this rank's packed [E][cap][C] send buffer -> all-to-all -> ``recv_rows`` [el][src][cap][C]."""
