@@ -18,7 +18,9 @@ def generate(model, prompt: list[int], num_tokens: int, rng_state: int = 1337) -
     cfg = model.config
     rng = Xorshift(rng_state)
     toks = list(prompt)
-    saved = (model.B, model.T, model.acts)
+    # the training-shape buffers come back untouched afterwards, token / target buffers included: a captured CUDA graph
+    # of the training micro-step keeps their addresses
+    saved = (model.B, model.T, model.acts, getattr(model, "tokens", None), getattr(model, "targets", None))
     pad_to = 64
     limit = min(num_tokens, cfg.max_seq_len)
     eot = prompt[0] if prompt else 0
@@ -34,9 +36,7 @@ def generate(model, prompt: list[int], num_tokens: int, rng_state: int = 1337) -
             logits = model.logits_view()[0, t - 1, : cfg.vocab_size].float().cpu().numpy()
             toks.append(sample_softmax(np.ascontiguousarray(logits), rng.f32()))
     finally:
-        model.B, model.T, model.acts = saved
-        if model.acts is not None and hasattr(model, "tokens"):
-            B, T = saved[0], saved[1]
-            model.tokens = torch.zeros(B, T, dtype=torch.int32, device=model.device)
-            model.targets = torch.zeros(B, T, dtype=torch.int32, device=model.device)
+        model.B, model.T, model.acts = saved[:3]
+        if saved[3] is not None:
+            model.tokens, model.targets = saved[3], saved[4]
     return toks

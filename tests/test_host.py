@@ -596,3 +596,44 @@ def test_device_preflight_against_a_stand_in_machine(capsys):
     assert check.check_device(probe=Probe([]), out=lines.append) == ["no CUDA devices visible to the runtime"]
     if not torch.cuda.is_available():
         assert check.main(["device"]) == 1 and "no CUDA devices" in capsys.readouterr().out
+
+
+def test_sampling_hands_the_training_buffers_back_untouched():
+    """``generate`` re-runs the model on (1, T) windows; afterwards the training-shape activations AND the token /
+    target buffers must be the very tensors they were (a captured CUDA graph of the micro-step keeps their addresses)."""
+    from types import SimpleNamespace
+
+    from llm_kittens_b200.runtime.sampling import generate
+
+    class Stub:
+        def __init__(self):
+            self.config = SimpleNamespace(max_seq_len=128, vocab_size=50)
+            self.device = "cpu"
+            self.B, self.T = 4, 128
+            self.acts = {"marker": torch.zeros(1)}
+            self.tokens = torch.zeros(4, 128, dtype=torch.int32)
+            self.targets = torch.zeros(4, 128, dtype=torch.int32)
+            self.calls = []
+
+        def forward(self, x, y):
+            B, T = x.shape
+            if self.acts is None or (self.B, self.T) != (B, T):    # what Transformer.allocate does for a new shape
+                self.B, self.T, self.acts = B, T, {"marker": torch.ones(1)}
+                self.tokens = torch.zeros(B, T, dtype=torch.int32)
+                self.targets = torch.zeros(B, T, dtype=torch.int32)
+            self.tokens.copy_(x)
+            self.calls.append((B, T))
+
+        def logits_view(self):
+            g = torch.Generator().manual_seed(len(self.calls))
+            return torch.randn(self.B, self.T, 64, generator=g)
+
+    m = Stub()
+    acts, tokens, targets = m.acts, m.tokens, m.targets
+    out = generate(m, [7], 70)
+    assert len(out) == 70 and out[0] == 7 and all(0 <= t < 50 for t in out)
+    assert m.calls[0] == (1, 64) and m.calls[-1] == (1, 128)            # windows padded to multiples of 64
+    assert (m.B, m.T) == (4, 128) and m.acts is acts and m.tokens is tokens and m.targets is targets
+    assert int(tokens.abs().sum()) == 0                                  # the training buffers were not written
+    m.calls.clear()
+    assert generate(m, [7], 70) == out                                   # same logits, same coin stream, same sample
