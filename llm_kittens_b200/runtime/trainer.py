@@ -48,7 +48,7 @@ class Trainer:
         self.lr, self.wd, self.beta1, self.beta2, self.eps, self.grad_clip = learning_rate, weight_decay, beta1, beta2, eps, grad_clip
         self.step_count = 0
         self.use_cuda_graph = False
-        self._graph, self._graph_key, self._steps_begun = None, None, 0
+        self._graph, self._graph_key, self._graph_acts, self._steps_begun = None, None, None, 0
         self.rng = Xorshift(rng_state)
         self.rng_state_last_update = rng_state
         n = self.plan.state_elements
@@ -188,8 +188,11 @@ class Trainer:
         model = self.model
         key = (tuple(x.shape), accum)
         with_comm = not isinstance(self.comm, SingleProcessComm)
-        if self._graph_key != key:
+        if self._graph_key != key or self._graph_acts is not model.acts:
+            # (re)capture: first use, another shape, or the model's activation buffers were reallocated since (a
+            # forward of another shape ran in between): the old graphs point at the old buffers
             B, T = key[0]
+            model.allocate(B, T)          # outside the capture: these buffers outlive the graph's own pool
             self._gx = torch.zeros(B, T, dtype=torch.int32, device=self.device)
             self._gy = torch.zeros(B, T, dtype=torch.int32, device=self.device)
             torch.cuda.synchronize(self.device)
@@ -213,7 +216,7 @@ class Trainer:
                 self._graph, self._graph_kernels = capture(False)
             else:
                 self._graph, self._graph_kernels = self._graph_last, self._graph_last_kernels
-            self._graph_key = key
+            self._graph_key, self._graph_acts = key, model.acts
         self._gx.copy_(x, non_blocking=True)
         self._gy.copy_(y, non_blocking=True)
         if index == 0:
