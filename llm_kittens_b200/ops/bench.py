@@ -91,9 +91,31 @@ def bench_gemm(BT=65536):
         t = time_fn(lambda: gemm.gemm_tn(a, b, out=out, accumulate=True))
         t_ref = time_fn(lambda: torch.matmul(a.T, b, out=out))
         rows.append(("TN " + name, M, Nn, K, t, t_ref))
+        if name != "dW lmhead" and gemm.fused_dbias_available():
+            # the same product with the bias gradient from the same launch, beside dW + the stand-alone column sums
+            from . import elementwise as ew
+
+            db = torch.zeros(M, dtype=torch.bfloat16, device="cuda")
+            t_f = time_fn(lambda: gemm.gemm_tn(a, b, out=out, accumulate=True, dbias=db))
+            t_s = time_fn(lambda: ew.dbias(db, a, accumulate=True))
+            rows.append(("TN " + name + " +dbias", M, Nn, K, t_f, t + t_s))
         del a, b, out
+    if gemm.fused_drow_available(64):
+        # dO = dres W with the attention backward's D = rowsum(dO * O) in the epilogue, beside the GEMM + the pre-pass
+        from . import attention
+
+        B_, T_, NH_ = BT // 1024, 1024, C // 64
+        a, b, o = rnd(BT, C), rnd(C, C), rnd(BT, C)
+        out = torch.empty(BT, C, dtype=torch.bfloat16, device="cuda")
+        dvec = torch.empty(B_, NH_, T_, dtype=torch.float32, device="cuda")
+        t_f = time_fn(lambda: gemm.gemm_nn(a, b, out=out, drow_of=(o, dvec, T_)))
+        t_g = time_fn(lambda: gemm.gemm_nn(a, b, out=out))
+        t_p = time_fn(lambda: attention.attention_bwd_prep(out, o, dvec, B_, T_, NH_, 64))
+        rows.append(("NN d attproj +D", BT, C, C, t_f, t_g + t_p))
+        del a, b, o, out
     N.check_status()
-    print(f"# GEMM (tcgen05) vs cuBLAS; peak {tf_peak} TFLOP/s bf16 ({how})")
+    print(f"# GEMM (tcgen05) vs cuBLAS; peak {tf_peak} TFLOP/s bf16 ({how}); for the '+dbias' and '+D' rows the last two")
+    print("# columns compare with this library's own unfused pair of kernels instead of cuBLAS")
     print(f"{'shape':28s} {'M':>6s} {'N':>6s} {'K':>6s} {'ms':>8s} {'TFLOP/s':>8s} {'frac':>6s} {'cublas ms':>9s} {'ratio':>6s}")
     for name, M, Nn, K, t, t_ref in rows:
         tf = 2.0 * M * Nn * K / (t * 1e-3) / 1e12
