@@ -637,3 +637,65 @@ def test_sampling_hands_the_training_buffers_back_untouched():
     assert int(tokens.abs().sum()) == 0                                  # the training buffers were not written
     m.calls.clear()
     assert generate(m, [7], 70) == out                                   # same logits, same coin stream, same sample
+
+
+def test_dataloader_properties_over_random_geometries(tmp_path_factory):
+    """Random shard counts and sizes (unequal shards), batch shapes and rank counts: in sequential mode every rank reads
+    exactly the windows that the reference's loader formula gives (llmc/dataloader.h:174-218: per shard
+    (tokens - 1) // (B*T*P) samples, rank r at offset sample*B*T*P + r*B*T, next shard afterwards, wrapping around); in
+    shuffle mode one epoch hands out every (shard, sample) window of a rank exactly once and targets are inputs
+    shifted by one token."""
+    from hypothesis import HealthCheck, given, settings
+    from hypothesis import strategies as st
+
+    @settings(max_examples=25, deadline=None, suppress_health_check=[HealthCheck.function_scoped_fixture])
+    @given(sizes=st.lists(st.integers(40, 400), min_size=1, max_size=4), B=st.integers(1, 3), T=st.integers(2, 9),
+           P=st.integers(1, 3), seed=st.integers(0, 1000))
+    def run(sizes, B, T, P, seed):
+        chunk = B * T * P
+        if min(sizes) - 1 < chunk:
+            return
+        d = tmp_path_factory.mktemp("geo")
+        rng = np.random.default_rng(seed)
+        shards = []
+        for i, n in enumerate(sizes):
+            toks = rng.integers(0, 60000, size=n)
+            formats.write_tokens(str(d / f"s_{i:03d}.bin"), toks, "gpt-2")
+            shards.append(toks)
+        per_shard = [(n - 1) // chunk for n in sizes]
+        for r in range(P):
+            ld = DataLoader(str(d / "s_*.bin"), B, T, r, P, False)
+            assert ld.num_tokens == sum(sizes) and ld.num_shards == len(sizes)
+            for shard in list(range(len(sizes))) + [0]:                       # one epoch and the wrap-around
+                for s in range(per_shard[shard]):
+                    x, y = ld.next_batch()
+                    off = s * chunk + r * B * T
+                    assert np.array_equal(x.numpy().ravel(), shards[shard][off: off + B * T]), (sizes, B, T, P, r, shard, s)
+                    assert np.array_equal(y.numpy().ravel(), shards[shard][off + 1: off + B * T + 1])
+            ld.close()
+        # shuffle: an epoch is a permutation of the rank's windows
+        r = P - 1
+        ld = DataLoader(str(d / "s_*.bin"), B, T, r, P, True)
+        want = {(shard, s) for shard in range(len(sizes)) for s in range(per_shard[shard])}
+        index = {}
+        for shard in range(len(sizes)):
+            for s in range(per_shard[shard]):
+                off = s * chunk + r * B * T
+                index.setdefault(tuple(shards[shard][off: off + B * T + 1]), set()).add((shard, s))
+        seen = []
+        for _ in range(len(want)):
+            x, y = ld.next_batch()
+            xs, ys = x.numpy().ravel(), y.numpy().ravel()
+            assert np.array_equal(xs[1:], ys[:-1])
+            key = tuple(list(xs) + [ys[-1]])
+            assert key in index
+            seen.append(key)
+        # every window handed out belongs to the rank; windows with unique contents appear exactly once
+        from collections import Counter
+        counts = Counter(seen)
+        for key, c in counts.items():
+            assert c <= len(index[key])
+        assert sum(counts.values()) == len(want)
+        ld.close()
+
+    run()
