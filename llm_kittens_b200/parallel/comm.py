@@ -107,5 +107,24 @@ class LibraryComm:
                 else:
                     dist.all_gather([full[r * shard:(r + 1) * shard] for r in range(P)], mine.clone(), group=self.group)
 
+    def gather_expert_params(self, params: torch.Tensor) -> None:
+        """Expert-parallel tensors are updated by their owner only and are not part of ``gather_params``; training never
+        reads another rank's experts, but a checkpoint's model file (written by rank 0) must hold all of them: every
+        expert is broadcast from its owner. A collective; called when a checkpoint is written."""
+        plan = self.plan
+        if plan.P <= 1:
+            return
+        for slot in plan.layout.slots:
+            if not slot.spec.expert:
+                continue
+            E = slot.spec.shape[0]
+            per = slot.size // E
+            for l in range(slot.layers):
+                base = slot.offset + l * slot.size
+                for e in range(E):
+                    owner = plan._expert_owner(e, E)
+                    src = owner if self.group is None else dist.get_global_rank(self.group, owner)
+                    dist.broadcast(params[base + e * per: base + (e + 1) * per], src=src, group=self.group)
+
     def barrier(self) -> None:
         dist.barrier(group=self.group)

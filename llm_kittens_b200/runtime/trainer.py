@@ -321,6 +321,9 @@ class Trainer:
         """The complete bf16 parameter vector in checkpoint order (a collective when parameters are sharded)."""
         if self.model.params is None:
             return self.comm.materialize_params()
+        gather_experts = getattr(self.comm, "gather_expert_params", None)
+        if gather_experts is not None and self.plan._has_experts():
+            gather_experts(self.model.params)      # back-ends that keep another rank's experts stale between steps
         return self.model.params
 
     def restore_params_from_master(self) -> None:

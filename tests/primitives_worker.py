@@ -70,6 +70,34 @@ def main():
         ref.backward(dout)
         res = dict(out=out.detach(), ref=ref.detach()[:, :, sl], dq=ql.grad, dk=kl.grad, dv=vl.grad, rdq=qf.grad[:, :, sl],
                    rdk=kf.grad[:, :, sl], rdv=vf.grad[:, :, sl])
+    elif mode == "experts":
+        # expert-parallel parameters before a checkpoint: every rank holds its own experts' values (rank + 1) and stale
+        # values (-1) for the others; after the gather every rank holds every owner's values, dense tensors untouched
+        from llm_kittens_b200.models.config import ModelConfig
+        from llm_kittens_b200.parallel.comm import LibraryComm
+        from llm_kittens_b200.parallel.zero import ZeroPlan
+
+        cfg = ModelConfig(family="moe", max_seq_len=128, vocab_size=512, padded_vocab_size=512, num_layers=2, num_heads=2,
+                          num_kv_heads=2, channels=64, hidden_dim=128, num_experts=4, top_k=2)
+        plan = ZeroPlan(cfg, world, rank, 1)
+        params = torch.full((plan.layout.total,), -1.0, dtype=torch.bfloat16)
+        owner_of = torch.full((plan.layout.total,), -1.0)
+        for slot in plan.layout.slots:
+            if slot.spec.expert:
+                E = slot.spec.shape[0]
+                per = slot.size // E
+                for l in range(slot.layers):
+                    for e in range(E):
+                        lo = slot.offset + l * slot.size + e * per
+                        o = plan._expert_owner(e, E)
+                        owner_of[lo:lo + per] = o + 1
+                        if o == rank:
+                            params[lo:lo + per] = rank + 1
+            else:
+                params[slot.offset: slot.offset + slot.total] = 7.0
+                owner_of[slot.offset: slot.offset + slot.total] = 7.0
+        LibraryComm(plan).gather_expert_params(params)
+        res = dict(params=params.float(), want=owner_of, experts=sum(s.total for s in plan.layout.slots if s.spec.expert))
     torch.save(res, os.path.join(out_dir, f"rank{rank}.pt"))
     dist.barrier()
     dist.destroy_process_group()

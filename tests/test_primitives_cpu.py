@@ -94,3 +94,14 @@ def test_ring_attention_matches_full_causal_attention(tmp_path, world):
         assert torch.allclose(d["out"], d["ref"], atol=1e-5)
         for a, b in (("dq", "rdq"), ("dk", "rdk"), ("dv", "rdv")):
             assert torch.allclose(d[a], d[b], atol=1e-4), (r, a)
+
+
+def test_expert_parameters_are_gathered_from_their_owners_for_a_checkpoint(tmp_path):
+    """Library back-end with expert parallelism: a rank never updates (or reads) another rank's experts, so before the
+    model file is written every expert is broadcast from its owner (``LibraryComm.gather_expert_params``, called by
+    ``Trainer.full_params``)."""
+    res = launch("experts", tmp_path, 2)
+    for r in res:
+        assert r["experts"] > 0
+        assert torch.equal(r["params"], r["want"])
+    assert torch.equal(res[0]["params"], res[1]["params"])
