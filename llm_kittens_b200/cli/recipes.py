@@ -129,7 +129,10 @@ def rendezvous_flags(launcher: str, rendezvous: str, server_ip: str = "", fs_pat
         if not fs_path:
             raise ValueError("--rendezvous fs needs --fs-path (a directory that every node sees)")
         out += ["-pf", fs_path]
-    elif rendezvous != "mpi":
+    elif rendezvous == "mpi":
+        if server_ip:      # more than one node: where rank 0 listens (else MASTER_ADDR, else this host)
+            out += ["-ps", server_ip]
+    else:
         raise ValueError(f"unknown rendezvous {rendezvous}")
     return out
 

@@ -63,6 +63,7 @@ def test_scheduler_launchers_build_the_rendezvous_flags():
     assert recipes.rendezvous_flags("slurm", "tcp", server_ip="10.0.1.220", env=env)[-4:] == ["-pi", "tcp", "-ps", "10.0.1.220"]
     mpi = {"OMPI_COMM_WORLD_SIZE": "16", "OMPI_COMM_WORLD_RANK": "3", "OMPI_COMM_WORLD_LOCAL_SIZE": "8"}
     assert recipes.rendezvous_flags("mpi", "mpi", env=mpi) == ["-pn", "16", "-pr", "3", "-pg", "8", "-pi", "mpi"]
+    assert recipes.rendezvous_flags("mpi", "mpi", server_ip="10.0.0.5", env=mpi)[-2:] == ["-ps", "10.0.0.5"]
     with pytest.raises(ValueError):
         recipes.rendezvous_flags("slurm", "tcp", env=env)            # no server address
     with pytest.raises(ValueError):
