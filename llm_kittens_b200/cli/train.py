@@ -138,7 +138,21 @@ def train(args: TrainArgs, trainer_name: str) -> int:
     if T > cfg.max_seq_len:
         printf0(rank, f"sequence length T={T} exceeds model max_seq_len={cfg.max_seq_len}")
         return 1
-    model = ModelCls(cfg, device=device, recompute=args.recompute)
+    model_kw = {}
+    if cfg.family == "moe" and world > 1:
+        # the experts are split over the ranks (the ZeRO plan gives every expert one owner): rows travel through the
+        # peer-memory exchange inside one NVLink domain, through all_to_all_single otherwise
+        from ..parallel.expert import LibraryExchange, PeerExchange
+
+        if cfg.num_experts % world != 0:
+            printf0(rank, f"{cfg.num_experts} experts cannot be split over {world} processes")
+            return 1
+        try:
+            model_kw["exchange"] = PeerExchange(device)
+        except Exception as e:      # no peer memory between the ranks (several nodes, more than 8 ranks)
+            printf0(rank, f"[llm_kittens_b200] peer-memory expert exchange unavailable ({e}); using all_to_all_single")
+            model_kw["exchange"] = LibraryExchange(device)
+    model = ModelCls(cfg, device=device, recompute=args.recompute, **model_kw)
     if is_ckpt:
         _, flat = formats.read_model(source, device="cpu")
         model.load_parameters(flat.to(device))
@@ -167,7 +181,8 @@ def train(args: TrainArgs, trainer_name: str) -> int:
                  ("vocab_size V", cfg.vocab_size), ("padded_vocab_size Vp", cfg.padded_vocab_size),
                  ("num_layers L", cfg.num_layers), ("num_heads NH", cfg.num_heads), ("channels C", cfg.channels),
                  ("num_parameters", cfg.num_parameters()), ("num_processes", world), ("zero_stage", args.zero_stage),
-                 ("communication", type(comm).__name__), ("grad_accum_steps", grad_accum)):
+                 ("communication", type(comm).__name__ + (f" + {type(model_kw['exchange']).__name__}" if model_kw else "")),
+                 ("grad_accum_steps", grad_accum)):
         printf0(rank, f"| {k:<21} | {str(v):<50} |")
     printf0(rank, "+-----------------------+----------------------------------------------------+")
 
