@@ -213,6 +213,9 @@ def train(args: TrainArgs, trainer_name: str) -> int:
         watchdog = Watchdog(rank, world, deadline, store=store_from_env(rank, world) if world > 1 else None)
         watchdog.start()
 
+    can_sample = not model_kw
+    if not can_sample and args.sample_every > 0:
+        printf0(rank, "sampling (-s) is switched off: with the experts split over the ranks a forward pass needs all of them")
     step = 0
     if resuming:
         step = load_checkpoint(args.output_log_dir, resume_step, trainer, train_loader, world, rank)
@@ -264,8 +267,8 @@ def train(args: TrainArgs, trainer_name: str) -> int:
             accy = float(correct.item()) / eval_loader.num_examples
             printf0(rank, f"HellaSwag: {int(correct.item())}/{eval_loader.num_examples} = {accy:f}")
             logger.log_eval(step, accy)
-        # sampling
-        if rank == 0 and args.sample_every > 0 and step > 0 and (step % args.sample_every == 0 or last_step):
+        # sampling (one process; an expert-parallel forward needs every rank, so those runs do not sample)
+        if rank == 0 and can_sample and args.sample_every > 0 and step > 0 and (step % args.sample_every == 0 or last_step):
             eot = tokenizer.eot_token if tokenizer else 50256 if cfg.family != "llama3" else 128001
             toks = generate(model, [eot], args.genT, rng_state=1337)
             if tokenizer is not None:

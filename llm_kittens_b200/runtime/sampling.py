@@ -18,9 +18,11 @@ def generate(model, prompt: list[int], num_tokens: int, rng_state: int = 1337) -
     cfg = model.config
     rng = Xorshift(rng_state)
     toks = list(prompt)
-    # the training-shape buffers come back untouched afterwards, token / target buffers included: a captured CUDA graph
-    # of the training micro-step keeps their addresses
-    saved = (model.B, model.T, model.acts, getattr(model, "tokens", None), getattr(model, "targets", None))
+    # The model is re-run on (1, T) windows, which makes it reallocate everything that depends on the shape: the
+    # activations, the token / target buffers and, in a mixture-of-experts model, the routing and exchange buffers with
+    # their capacities. All of it is put back afterwards by restoring the model's attribute table, so the training-shape
+    # tensors are the very same objects as before (a captured CUDA graph of the micro-step keeps their addresses).
+    saved = dict(model.__dict__)
     pad_to = 64
     limit = min(num_tokens, cfg.max_seq_len)
     eot = prompt[0] if prompt else 0
@@ -36,7 +38,6 @@ def generate(model, prompt: list[int], num_tokens: int, rng_state: int = 1337) -
             logits = model.logits_view()[0, t - 1, : cfg.vocab_size].float().cpu().numpy()
             toks.append(sample_softmax(np.ascontiguousarray(logits), rng.f32()))
     finally:
-        model.B, model.T, model.acts = saved[:3]
-        if saved[3] is not None:
-            model.tokens, model.targets = saved[3], saved[4]
+        model.__dict__.clear()
+        model.__dict__.update(saved)
     return toks
