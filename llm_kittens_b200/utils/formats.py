@@ -61,6 +61,11 @@ def read_header(path: str) -> np.ndarray:
 # ------------------------------------------------------------------------------------- model files
 def model_header(config: ModelConfig, fp32: bool = False) -> np.ndarray:
     h = _new_header()
+    # what the headers cannot express must not be written: a reader would rebuild another geometry from the file
+    if config.family == "llama3" and config.padded_vocab_size != config.vocab_size:
+        raise FormatError("Llama model files have no padded vocabulary: padded_vocab_size must equal vocab_size")
+    if config.family != "llama3" and config.hidden_dim != 4 * config.channels:
+        raise FormatError("GPT-2 / MoE model files imply hidden_dim = 4 * channels")
     if config.family == "llama3":
         h[0], h[1] = LLAMA_MODEL_MAGIC, 5
         h[2:10] = [config.max_seq_len, config.vocab_size, config.num_layers, config.num_heads, config.num_kv_heads,

@@ -756,3 +756,14 @@ def test_file_formats_round_trip_over_random_models_and_states(tmp_path_factory)
             formats.read_state(spath, family, world, (rank + 1) % world if world > 1 else 1, m2, v2, ma2)
 
     run()
+
+
+def test_model_header_refuses_geometries_the_file_cannot_express():
+    odd = ModelConfig(family="gpt2", max_seq_len=64, vocab_size=100, padded_vocab_size=128, num_layers=1, num_heads=1, num_kv_heads=1,
+                      channels=64, hidden_dim=128)
+    with pytest.raises(formats.FormatError):
+        formats.model_header(odd)
+    odd = ModelConfig(family="llama3", max_seq_len=64, vocab_size=100, padded_vocab_size=128, num_layers=1, num_heads=1, num_kv_heads=1,
+                      channels=64, hidden_dim=128)
+    with pytest.raises(formats.FormatError):
+        formats.model_header(odd)
