@@ -210,7 +210,15 @@ def train(args: TrainArgs, trainer_name: str) -> int:
     deadline = float(os.environ.get("LLMK_WATCHDOG_SECONDS", "0") or 0)
     if deadline > 0:
         from ..runtime.watchdog import Watchdog, store_from_env
-        watchdog = Watchdog(rank, world, deadline, store=store_from_env(rank, world) if world > 1 else None)
+        store = None
+        if world > 1:
+            if args.server_ip:      # -pi tcp / mpi over several nodes: the heartbeat store lives beside rank 0 as well
+                os.environ.setdefault("MASTER_ADDR", args.server_ip)
+            try:
+                store = store_from_env(rank, world)
+            except Exception as e:  # e.g. -pi fs without an address of rank 0: the step deadline still works
+                printf0(rank, f"[llm_kittens_b200] no heartbeat store ({type(e).__name__}: {e}); watchdog runs with the step deadline only")
+        watchdog = Watchdog(rank, world, deadline, store=store)
         watchdog.start()
 
     can_sample = not model_kw
