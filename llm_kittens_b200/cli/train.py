@@ -214,10 +214,12 @@ def train(args: TrainArgs, trainer_name: str) -> int:
         if world > 1:
             if args.server_ip:      # -pi tcp / mpi over several nodes: the heartbeat store lives beside rank 0 as well
                 os.environ.setdefault("MASTER_ADDR", args.server_ip)
-            try:
+            # every rank must come to the same decision, or rank 0 would wait for heartbeats that nobody can send
+            if "MASTER_ADDR" in os.environ or world <= args.gpus_per_node:
                 store = store_from_env(rank, world)
-            except Exception as e:  # e.g. -pi fs without an address of rank 0: the step deadline still works
-                printf0(rank, f"[llm_kittens_b200] no heartbeat store ({type(e).__name__}: {e}); watchdog runs with the step deadline only")
+            else:                   # e.g. -pi fs over several nodes: no address of rank 0 is known
+                printf0(rank, "[llm_kittens_b200] no address for the heartbeat store (set MASTER_ADDR or -ps): the watchdog "
+                              "watches the step deadline only")
         watchdog = Watchdog(rank, world, deadline, store=store)
         watchdog.start()
 
