@@ -91,6 +91,25 @@ def run(argv: list[str], trainer_name: str) -> int:
     return train(args, trainer_name)
 
 
+def resolve_processes(args: TrainArgs, env) -> tuple[int, int, str, int]:
+    """(job size, this process's rank, rendezvous method, local device index) from the launcher's environment and the
+    ``-p*`` flags: ``torch.distributed.run`` sets WORLD_SIZE / RANK / LOCAL_RANK; ``mpirun`` (how the reference's binaries
+    are started, scripts/run_gpt2_124M.sh:45) sets OMPI_COMM_WORLD_*; otherwise ``-pn`` / ``-pr`` / ``-pg`` say it
+    (one task per GPU under ``srun`` with ``-pi tcp`` or ``-pi fs``)."""
+    env_world = int(env.get("WORLD_SIZE", "0"))
+    local_default = None
+    if env_world > 0 and args.nccl_init_method in ("mpi", "env"):
+        world, rank, init = env_world, int(env.get("RANK", "0")), "env"
+    elif args.nccl_init_method == "mpi" and "OMPI_COMM_WORLD_SIZE" in env:
+        world, rank, init = int(env["OMPI_COMM_WORLD_SIZE"]), int(env["OMPI_COMM_WORLD_RANK"]), "mpi"
+        local_default = env.get("OMPI_COMM_WORLD_LOCAL_RANK")
+    else:
+        world, rank, init = args.num_processes, args.process_rank, args.nccl_init_method
+    if local_default is None:
+        local_default = rank % max(1, args.gpus_per_node)
+    return world, rank, init, int(env.get("LOCAL_RANK", local_default))
+
+
 def train(args: TrainArgs, trainer_name: str) -> int:
     import torch.distributed as dist
 
@@ -105,12 +124,7 @@ def train(args: TrainArgs, trainer_name: str) -> int:
 
     zero_mod.validate_zero_stage(args.zero_stage)
     # ---- processes
-    env_world = int(os.environ.get("WORLD_SIZE", "0"))
-    if env_world > 0 and args.nccl_init_method in ("mpi", "env"):
-        world, rank, init = env_world, int(os.environ.get("RANK", "0")), "env"
-    else:
-        world, rank, init = args.num_processes, args.process_rank, args.nccl_init_method
-    local = int(os.environ.get("LOCAL_RANK", rank % max(1, args.gpus_per_node)))
+    world, rank, init, local = resolve_processes(args, os.environ)
     torch.cuda.set_device(local)
     device = torch.device("cuda", local)
     if world > 1:

@@ -767,3 +767,20 @@ def test_model_header_refuses_geometries_the_file_cannot_express():
                       channels=64, hidden_dim=128)
     with pytest.raises(formats.FormatError):
         formats.model_header(odd)
+
+
+def test_process_layout_from_torchrun_mpirun_and_flags():
+    """Job size, rank and device index: from torch.distributed.run's environment, from Open MPI's (the reference's
+    binaries are started by mpirun and ask MPI), or from the -pn / -pr / -pg flags (one task per GPU under srun)."""
+    a = flags_mod.parse_flags([], "gpt2")                           # defaults: -pi mpi, -pn 1
+    assert train_mod.resolve_processes(a, {}) == (1, 0, "mpi", 0)
+    assert train_mod.resolve_processes(a, {"WORLD_SIZE": "8", "RANK": "5", "LOCAL_RANK": "5"}) == (8, 5, "env", 5)
+    ompi = {"OMPI_COMM_WORLD_SIZE": "16", "OMPI_COMM_WORLD_RANK": "11", "OMPI_COMM_WORLD_LOCAL_RANK": "3"}
+    assert train_mod.resolve_processes(a, ompi) == (16, 11, "mpi", 3)
+    del ompi["OMPI_COMM_WORLD_LOCAL_RANK"]
+    assert train_mod.resolve_processes(a, ompi) == (16, 11, "mpi", 3)       # 11 % 8 GPUs per node
+    b = flags_mod.parse_flags(["-pn", "16", "-pr", "9", "-pg", "4", "-pi", "tcp", "-ps", "10.0.0.1"], "gpt2")
+    assert train_mod.resolve_processes(b, {}) == (16, 9, "tcp", 1)
+    assert train_mod.resolve_processes(b, ompi) == (16, 9, "tcp", 1)         # explicit flags win over MPI's environment with -pi tcp
+    # torchrun's environment is not used for an explicit tcp / fs rendezvous either
+    assert train_mod.resolve_processes(b, {"WORLD_SIZE": "2", "RANK": "1"}) == (16, 9, "tcp", 1)
