@@ -7,7 +7,10 @@
 //
 // Epilogue flags (compile-time): +bias[N]; tanh-GELU with the pre-activation stored to a second
 // output; multiply by GELU'(aux); add a bf16 [M,N] addend (residual add / gradient accumulation);
-// or raw fp32 partials for split-K. Same job as matmul_forward / matmul_forward_gelu /
+// or raw fp32 partials for split-K; RoPE on the q / k heads of a packed QKV projection; SwiGLU over an up | gate tile
+// pair; rows scattered to peer GPUs (mixture of experts); the bias gradient summed from the A tiles in shared memory
+// (mode TN); the attention backward's D = rowsum(dO * O) beside dO (mode NN). Operands that another kernel is still
+// filling are polled for, tile by tile (Params::b_ready / a_ready). Same job as matmul_forward / matmul_forward_gelu /
 // matmul_backward in the reference (llmc/matmul.cuh:678-785, 1138-1201, 1238-1338), which has no
 // sm_100 path; this is a new design:
 //
@@ -15,6 +18,7 @@
 //   warp 1      : MMA issuer    (one elected lane; tcgen05.mma; commit -> stage release)
 //   warps 2..   : epilogue      (tcgen05.ld 32 lanes x 32 columns -> math -> swizzled smem -> TMA store);
 //                 8 warps, 16 for the dGELU epilogue
+//   4 more warps: column sums of the A stages (EPI_DBIAS only)
 //   TMEM        : 2 x 256 fp32 columns, so the epilogue of tile i overlaps the main loop of tile i+1.
 //
 // Default: clusters of two CTAs (tcgen05.mma.cta_group::2, one 256x256 tile per pair, 256x256x16 MMAs issued by
