@@ -125,6 +125,10 @@ def train(args: TrainArgs, trainer_name: str) -> int:
     zero_mod.validate_zero_stage(args.zero_stage)
     # ---- processes
     world, rank, init, local = resolve_processes(args, os.environ)
+    if world == 1 and int(os.environ.get("SLURM_NTASKS", "1") or 1) > 1 and int(os.environ.get("SLURM_PROCID", "0") or 0) == 0:
+        print("warning: one of several slurm tasks, but no job size was given (-pn / -pr / -pi tcp|fs, or start the tasks "
+              "through `python -m llm_kittens_b200.cli.recipes <name> --launcher slurm`): every task trains on its own",
+              file=sys.stderr)
     torch.cuda.set_device(local)
     device = torch.device("cuda", local)
     if world > 1:
