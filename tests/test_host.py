@@ -784,3 +784,53 @@ def test_process_layout_from_torchrun_mpirun_and_flags():
     assert train_mod.resolve_processes(b, ompi) == (16, 9, "tcp", 1)         # explicit flags win over MPI's environment with -pi tcp
     # torchrun's environment is not used for an explicit tcp / fs rendezvous either
     assert train_mod.resolve_processes(b, {"WORLD_SIZE": "2", "RANK": "1"}) == (16, 9, "tcp", 1)
+
+
+def test_zero_plans_over_random_geometries_including_experts():
+    """Random model geometries (all three families) and rank counts: whenever ``validate_sharding`` accepts a pair, the
+    ranks' segments tile the parameter buffer exactly once (dense tensors in P equal parts per layer, every expert with
+    one owner), state offsets stay inside the rank's state buffer without overlap, and every shard is a whole number
+    of 16-byte units (what the vectorised optimizer kernels assume)."""
+    from hypothesis import given, settings
+    from hypothesis import strategies as st
+
+    @settings(max_examples=60, deadline=None)
+    @given(family=st.sampled_from(["gpt2", "llama3", "moe"]), layers=st.integers(1, 4), heads=st.sampled_from([1, 2, 3, 4, 6, 8]),
+           head_size=st.sampled_from([64, 128]), vocab_blocks=st.integers(1, 6), P=st.sampled_from([1, 2, 3, 4, 6, 8]),
+           experts=st.sampled_from([2, 4, 8]), stage=st.sampled_from([1, 2, 3]))
+    def run(family, layers, heads, head_size, vocab_blocks, P, experts, stage):
+        C = heads * head_size
+        V = vocab_blocks * 128
+        extra = dict(num_experts=experts, top_k=2) if family == "moe" else {}
+        cfg = ModelConfig(family=family, max_seq_len=64, vocab_size=V, padded_vocab_size=V, num_layers=layers, num_heads=heads,
+                          num_kv_heads=heads, channels=C, hidden_dim=4 * C, **extra)
+        if family == "moe" and P > 1 and experts % P and P % experts:
+            return                                   # experts neither split over the ranks nor ranks over the experts
+        if zero.validate_sharding(cfg, P, stage):
+            with pytest.raises(zero.ZeroError):
+                zero.ZeroPlan(cfg, P, 0, stage)
+            return
+        lay = cfg.layout()
+        owned = np.zeros(lay.total, dtype=np.int16)
+        for r in range(P):
+            plan = zero.ZeroPlan(cfg, P, r, stage)
+            used = np.zeros(plan.state_elements, dtype=np.int8)
+            for s in plan.segments:
+                assert s.length > 0 and s.length % 8 == 0 and s.param_off % 8 == 0 and s.state_off % 8 == 0, (s, P)
+                owned[s.param_off: s.param_off + s.length] += 1
+                used[s.state_off: s.state_off + s.length] += 1
+            assert used.max() <= 1, "two segments of one rank share optimizer state"
+            rows = plan.segment_rows()
+            assert sum(n for _, _, _, n, _ in rows) == sum(s.length for s in plan.segments)
+        if family == "moe" and P > experts:
+            # more ranks than experts: an expert has one owner, the other ranks of its group hold no state for it
+            assert owned.max() == 1
+            dense = np.ones(lay.total, dtype=bool)
+            for slot in lay.slots:
+                if slot.spec.expert:
+                    dense[slot.offset: slot.offset + slot.total] = False
+            assert (owned[dense] == 1).all()
+        else:
+            assert (owned == 1).all(), (family, P, int((owned != 1).sum()))
+
+    run()
