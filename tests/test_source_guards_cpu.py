@@ -90,3 +90,40 @@ def test_nothing_committed_depends_on_the_scratch_folder():
         if path.endswith("test_source_guards_cpu.py"):
             continue
         assert "_work/" not in _read(path) and "_work\\" not in _read(path), path
+
+
+def test_no_function_refers_to_a_name_that_does_not_exist():
+    """Most of the package only runs on a GPU; a misspelt or forgotten name in such a function would not show in the
+    CPU tier. The symbol tables say which names every function takes from the module's globals: each must exist there
+    (after import) or be a builtin."""
+    import builtins
+    import importlib
+    import importlib.util
+    import pkgutil
+    import symtable
+
+    import llm_kittens_b200
+
+    def walk(table, module_names, path, problems):
+        for child in table.get_children():
+            if child.get_type() == "function":
+                for sym in child.get_symbols():
+                    if sym.is_global() and sym.is_referenced() and not sym.is_assigned():
+                        name = sym.get_name()
+                        if name not in module_names and not hasattr(builtins, name):
+                            problems.append(f"{path}: {child.get_name()}() uses undefined name {name!r}")
+            walk(child, module_names, path, problems)
+
+    problems = []
+    mods = [m.name for m in pkgutil.walk_packages(llm_kittens_b200.__path__, "llm_kittens_b200.")]
+    assert len(mods) > 40
+    for name in mods:
+        mod = importlib.import_module(name)
+        path = mod.__file__
+        walk(symtable.symtable(_read(path), path, "exec"), set(vars(mod)), os.path.relpath(path, REPO), problems)
+    for path in (os.path.join(REPO, "bench.py"), os.path.join(REPO, "__graft_entry__.py")):
+        spec = importlib.util.spec_from_file_location("_guard_" + os.path.basename(path)[:-3], path)
+        mod = importlib.util.module_from_spec(spec)
+        spec.loader.exec_module(mod)
+        walk(symtable.symtable(_read(path), path, "exec"), set(vars(mod)), os.path.relpath(path, REPO), problems)
+    assert not problems, "\n".join(problems)
