@@ -127,3 +127,53 @@ def test_no_function_refers_to_a_name_that_does_not_exist():
         spec.loader.exec_module(mod)
         walk(symtable.symtable(_read(path), path, "exec"), set(vars(mod)), os.path.relpath(path, REPO), problems)
     assert not problems, "\n".join(problems)
+
+
+def test_every_attribute_taken_from_a_module_of_the_package_exists():
+    """``gemm.gemm_tn``, ``N.status_word``, ``moe_ops.combine_pull`` ...: where a name is bound by an import to a module
+    (of this package or of the standard library) and an attribute is read from it, the attribute must exist. Catches a
+    misspelt or renamed function in code that only runs on a GPU."""
+    import ast
+    import importlib
+    import pkgutil
+    import types
+
+    import llm_kittens_b200
+
+    problems = []
+    files = []
+    for info in pkgutil.walk_packages(llm_kittens_b200.__path__, "llm_kittens_b200."):
+        files.append((importlib.import_module(info.name).__file__, info.name if info.ispkg else info.name.rsplit(".", 1)[0]))
+    # the GPU tests and the benchmark use the package too, and do not run here either
+    files += [(p, None) for p in _files(os.path.join(REPO, "tests"), (".py",))] + [(os.path.join(REPO, "bench.py"), None)]
+    for file_path, package in files:
+        tree = ast.parse(_read(file_path))
+        bound = {}        # local name -> module object, from every import statement in the file (any scope)
+        for node in ast.walk(tree):
+            if isinstance(node, ast.ImportFrom):
+                base = "." * node.level + (node.module or "")
+                for al in node.names:
+                    for target in (f"{base}.{al.name}" if node.module else f"{base}{al.name}",):
+                        try:
+                            m = importlib.import_module(target, package) if node.level else importlib.import_module(f"{node.module}.{al.name}")
+                        except Exception:
+                            continue
+                        if isinstance(m, types.ModuleType):
+                            bound[al.asname or al.name] = m
+            elif isinstance(node, ast.Import):
+                for al in node.names:
+                    if "." not in al.name or al.asname:
+                        try:
+                            bound[al.asname or al.name] = importlib.import_module(al.name)
+                        except Exception:
+                            pass
+        rebound = {n.id for n in ast.walk(tree) if isinstance(n, ast.Name) and isinstance(n.ctx, ast.Store)}
+        rebound |= {a.arg for n in ast.walk(tree) if isinstance(n, ast.arguments) for a in n.args + n.kwonlyargs}
+        for node in ast.walk(tree):
+            if isinstance(node, ast.Attribute) and isinstance(node.value, ast.Name) and isinstance(node.ctx, ast.Load):
+                name = node.value.id
+                if name in bound and name not in rebound and not hasattr(bound[name], node.attr):
+                    owner = bound[name].__name__
+                    if owner.startswith("llm_kittens_b200") or owner in ("os", "sys", "math", "ctypes", "json", "time", "struct"):
+                        problems.append(f"{os.path.relpath(file_path, REPO)}:{node.lineno}: {name}.{node.attr} does not exist in {owner}")
+    assert not problems, "\n".join(problems)
