@@ -177,3 +177,90 @@ def test_every_attribute_taken_from_a_module_of_the_package_exists():
                     if owner.startswith("llm_kittens_b200") or owner in ("os", "sys", "math", "ctypes", "json", "time", "struct"):
                         problems.append(f"{os.path.relpath(file_path, REPO)}:{node.lineno}: {name}.{node.attr} does not exist in {owner}")
     assert not problems, "\n".join(problems)
+
+
+def test_calls_of_package_functions_fit_their_signatures():
+    """``module.function(a, b, key=c)`` where the module is one of this package: the positional count and the keyword
+    names must bind to the function's signature (calls with ``*args`` / ``**kwargs`` are skipped). A wrong keyword in
+    code that only runs on a GPU would otherwise wait for a GPU to be found."""
+    import ast
+    import importlib
+    import inspect
+    import pkgutil
+    import types
+
+    import llm_kittens_b200
+
+    files = []
+    for info in pkgutil.walk_packages(llm_kittens_b200.__path__, "llm_kittens_b200."):
+        files.append((importlib.import_module(info.name).__file__, info.name if info.ispkg else info.name.rsplit(".", 1)[0]))
+    files += [(p, None) for p in _files(os.path.join(REPO, "tests"), (".py",))] + [(os.path.join(REPO, "bench.py"), None)]
+    problems, checked = [], 0
+    for file_path, package in files:
+        tree = ast.parse(_read(file_path))
+        bound = {}
+        for node in ast.walk(tree):
+            if isinstance(node, ast.ImportFrom):
+                base = "." * node.level + (node.module or "")
+                for al in node.names:
+                    target = f"{base}.{al.name}" if node.module else f"{base}{al.name}"
+                    try:
+                        m = importlib.import_module(target, package) if node.level else importlib.import_module(f"{node.module}.{al.name}")
+                    except Exception:
+                        continue
+                    if isinstance(m, types.ModuleType) and m.__name__.startswith("llm_kittens_b200"):
+                        bound[al.asname or al.name] = m
+        rebound = {n.id for n in ast.walk(tree) if isinstance(n, ast.Name) and isinstance(n.ctx, ast.Store)}
+        rebound |= {a.arg for n in ast.walk(tree) if isinstance(n, ast.arguments) for a in n.args + n.kwonlyargs}
+        for node in ast.walk(tree):
+            if not (isinstance(node, ast.Call) and isinstance(node.func, ast.Attribute) and isinstance(node.func.value, ast.Name)):
+                continue
+            name = node.func.value.id
+            if name not in bound or name in rebound:
+                continue
+            fn = getattr(bound[name], node.func.attr, None)
+            if not inspect.isfunction(fn):
+                continue
+            if any(isinstance(a, ast.Starred) for a in node.args) or any(k.arg is None for k in node.keywords):
+                continue
+            try:
+                inspect.signature(fn).bind(*[None] * len(node.args), **{k.arg: None for k in node.keywords})
+                checked += 1
+            except TypeError as e:
+                problems.append(f"{os.path.relpath(file_path, REPO)}:{node.lineno}: {name}.{node.func.attr}(...): {e}")
+    assert checked > 300, checked
+    assert not problems, "\n".join(problems)
+
+
+def test_native_calls_pass_as_many_arguments_as_the_c_entry_points_take():
+    """``N.call("llmk_x", a, b, ...)`` appends the stream and calls through ctypes without prototypes: a missing or extra
+    argument would not raise, it would shift every later parameter. The C signatures are read from the sources and
+    compared with every call site."""
+    import ast
+
+    sigs = {}
+    for path in _files(CSRC, (".cu", ".cpp")):
+        code = _strip_comments(_read(path))
+        for m in re.finditer(r"LLMK_API\s+[\w\s\*]+?\b(llmk_[a-z0-9_]+)\s*\(([^)]*)\)\s*\{", code):
+            params = [p for p in m.group(2).split(",") if p.strip() and p.strip() != "void"]
+            sigs[m.group(1)] = len(params)
+    assert len(sigs) > 80, len(sigs)
+    problems, checked = [], 0
+    files = list(_files(PKG, (".py",))) + list(_files(os.path.join(REPO, "tests"), (".py",))) + [os.path.join(REPO, "bench.py")]
+    for path in files:
+        for node in ast.walk(ast.parse(_read(path))):
+            if not (isinstance(node, ast.Call) and isinstance(node.func, ast.Attribute) and node.func.attr == "call" and node.args):
+                continue
+            first = node.args[0]
+            if not (isinstance(first, ast.Constant) and isinstance(first.value, str) and first.value.startswith("llmk_")):
+                continue
+            if any(isinstance(a, ast.Starred) for a in node.args) or node.keywords:
+                continue
+            name = first.value
+            assert name in sigs, f"{path}:{node.lineno}: {name} has no definition with a body in csrc"
+            passed = len(node.args) - 1 + 1          # the arguments after the name, plus the stream that call() appends
+            checked += 1
+            if passed != sigs[name]:
+                problems.append(f"{os.path.relpath(path, REPO)}:{node.lineno}: {name} takes {sigs[name]} parameters, the call passes {passed}")
+    assert checked > 80, checked
+    assert not problems, "\n".join(problems)
