@@ -262,5 +262,15 @@ def test_native_calls_pass_as_many_arguments_as_the_c_entry_points_take():
             checked += 1
             if passed != sigs[name]:
                 problems.append(f"{os.path.relpath(path, REPO)}:{node.lineno}: {name} takes {sigs[name]} parameters, the call passes {passed}")
-    assert checked > 80, checked
+            # direct calls through the library handle (size queries and the like) pass exactly what they list
+    direct = 0
+    for path in files:
+        for node in ast.walk(ast.parse(_read(path))):
+            if isinstance(node, ast.Call) and isinstance(node.func, ast.Attribute) and node.func.attr.startswith("llmk_") \
+                    and node.func.attr in sigs and not node.keywords and not any(isinstance(a, ast.Starred) for a in node.args):
+                direct += 1
+                if len(node.args) != sigs[node.func.attr]:
+                    problems.append(f"{os.path.relpath(path, REPO)}:{node.lineno}: {node.func.attr} takes {sigs[node.func.attr]} "
+                                    f"parameters, the call passes {len(node.args)}")
+    assert checked > 80 and direct > 10, (checked, direct)
     assert not problems, "\n".join(problems)
