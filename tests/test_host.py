@@ -834,3 +834,39 @@ def test_zero_plans_over_random_geometries_including_experts():
             assert (owned == 1).all(), (family, P, int((owned != 1).sum()))
 
     run()
+
+
+@pytest.mark.parametrize("family", ["gpt2", "llama3", "moe"])
+def test_sampling_on_the_pytorch_models_leaves_a_training_step_unchanged(family):
+    """``generate`` between two training steps of the PyTorch reference models (the surface the CUDA models share): the
+    step after sampling gives the same loss as without sampling, and the sample is reproducible."""
+    from llm_kittens_b200.oracle.torch_model import TorchTransformer
+    from llm_kittens_b200.runtime.sampling import generate
+    from llm_kittens_b200.runtime.trainer import Trainer
+
+    extra = dict(num_experts=4, top_k=2) if family == "moe" else {}
+    V = 256
+    cfg = ModelConfig(family=family, max_seq_len=128, vocab_size=V, padded_vocab_size=V, num_layers=2, num_heads=2, num_kv_heads=2,
+                      channels=64, hidden_dim=256, **extra)
+    g = torch.Generator().manual_seed(5)
+    batches = [(torch.randint(0, V, (2, 64), generator=g, dtype=torch.int32), torch.randint(0, V, (2, 64), generator=g, dtype=torch.int32))
+               for _ in range(3)]
+
+    def run(sample: bool):
+        model = TorchTransformer(cfg, device="cpu", dtype=torch.float32)
+        model.init_weights(42)
+        tr = Trainer(model, learning_rate=1e-3)
+        losses, text = [], None
+        for i, b in enumerate(batches):
+            losses.append(tr.train_step([b]).loss)
+            if sample and i == 0:
+                acts = model.acts
+                text = generate(model, [0], 70)
+                assert model.acts is acts and (model.B, model.T) == (2, 64)
+                assert generate(model, [0], 70) == text
+        return losses, text
+
+    plain, _ = run(False)
+    sampled, text = run(True)
+    assert sampled == plain
+    assert len(text) == 70 and all(0 <= t < V for t in text)
