@@ -274,3 +274,52 @@ def test_native_calls_pass_as_many_arguments_as_the_c_entry_points_take():
                                     f"parameters, the call passes {len(node.args)}")
     assert checked > 80 and direct > 10, (checked, direct)
     assert not problems, "\n".join(problems)
+
+
+def test_calls_of_imported_functions_and_classes_fit_their_signatures():
+    """The same for names imported directly (``from ..runtime.trainer import Trainer`` ... ``Trainer(model, zero_stage=1)``,
+    ``generate(model, prompt, n, rng_state=s)``): constructor and function calls must bind."""
+    import ast
+    import importlib
+    import inspect
+    import pkgutil
+
+    import llm_kittens_b200
+
+    files = []
+    for info in pkgutil.walk_packages(llm_kittens_b200.__path__, "llm_kittens_b200."):
+        files.append((importlib.import_module(info.name).__file__, info.name if info.ispkg else info.name.rsplit(".", 1)[0]))
+    files += [(p, None) for p in _files(os.path.join(REPO, "tests"), (".py",))] + [(os.path.join(REPO, "bench.py"), None)]
+    problems, checked = [], 0
+    for file_path, package in files:
+        tree = ast.parse(_read(file_path))
+        bound = {}
+        for node in ast.walk(tree):
+            if isinstance(node, ast.ImportFrom) and (node.level or (node.module or "").startswith("llm_kittens_b200")):
+                try:
+                    m = importlib.import_module("." * node.level + (node.module or ""), package) if node.level else importlib.import_module(node.module)
+                except Exception:
+                    continue
+                for al in node.names:
+                    obj = getattr(m, al.name, None)
+                    if inspect.isfunction(obj) or inspect.isclass(obj):
+                        bound[al.asname or al.name] = obj
+        stores = [n.id for n in ast.walk(tree) if isinstance(n, ast.Name) and isinstance(n.ctx, ast.Store)]
+        stores += [n.name for n in ast.walk(tree) if isinstance(n, (ast.FunctionDef, ast.ClassDef))]
+        for node in ast.walk(tree):
+            if not (isinstance(node, ast.Call) and isinstance(node.func, ast.Name) and node.func.id in bound) or node.func.id in stores:
+                continue
+            if any(isinstance(a, ast.Starred) for a in node.args) or any(k.arg is None for k in node.keywords):
+                continue
+            obj = bound[node.func.id]
+            try:
+                sig = inspect.signature(obj)
+            except (TypeError, ValueError):
+                continue
+            try:
+                sig.bind(*[None] * len(node.args), **{k.arg: None for k in node.keywords})
+                checked += 1
+            except TypeError as e:
+                problems.append(f"{os.path.relpath(file_path, REPO)}:{node.lineno}: {node.func.id}(...): {e}")
+    assert checked > 150, checked
+    assert not problems, "\n".join(problems)
